@@ -1,0 +1,118 @@
+/*
+ * gguf_b200 -- C-ABI of the B200 (sm_100a) GGUF quantized-matmul kernels.
+ *
+ * This is the drop-in boundary: the entry points below are what the reference plugin's
+ * native layer (vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu, bound to Python by
+ * csrc/torch_bindings.cpp:22-53) does for this path, minus tensor objects.  Plain pointers
+ * and sizes only; every function returns 0 or a negative GGUF_B200_E_* code, never throws,
+ * never allocates, never synchronises.  Work is enqueued on `stream` (a cudaStream_t passed
+ * as void*).  Scratch memory is provided by the caller (gguf_b200_workspace_bytes).
+ *
+ * Types: GGML ids 2 (Q4_0), 8 (Q8_0), 12 (Q4_K), 14 (Q6_K), 16 (IQ2_XXS), 23 (IQ4_XS).
+ * Weights W are raw GGUF blocks, row-major `uint8 [N][K/QK*type_size]`, base 16-byte aligned.
+ * Activations X are `[M][K]` contiguous in `dtype`; outputs Y are `[M][N]` in the same dtype.
+ */
+#ifndef GGUF_B200_H
+#define GGUF_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { GGUF_B200_F32 = 0, GGUF_B200_F16 = 1, GGUF_B200_BF16 = 2 };
+
+enum {
+  GGUF_B200_OK = 0,
+  GGUF_B200_E_TYPE = -1,      /* block type not supported */
+  GGUF_B200_E_DTYPE = -2,     /* dtype not f32/f16/bf16 */
+  GGUF_B200_E_SHAPE = -3,     /* K not a multiple of the block size, negative size, ... */
+  GGUF_B200_E_POINTER = -4,   /* null or misaligned pointer */
+  GGUF_B200_E_WORKSPACE = -5, /* workspace smaller than gguf_b200_workspace_bytes() */
+  GGUF_B200_E_CUDA = -6,      /* CUDA runtime error at launch */
+  GGUF_B200_E_TOO_LARGE = -7, /* beyond a documented size limit */
+  GGUF_B200_E_TIMEOUT = -8    /* a bounded device-side wait expired (reported by gguf_b200_last_status) */
+};
+
+enum { GGUF_B200_OP_GEMV = 0, GGUF_B200_OP_MMQ = 1, GGUF_B200_OP_MOE = 2, GGUF_B200_OP_MOE_VEC = 3,
+       GGUF_B200_OP_DEQUANT_MATMUL = 4 };
+
+const char* gguf_b200_error_string(int code);
+const char* gguf_b200_version(void);
+
+/* bytes per block / values per block of a type, 0 if unsupported
+ * (gguf.GGML_QUANT_SIZES; ggml-common.h:17-191) */
+int gguf_b200_type_size(int type);
+int gguf_b200_block_size(int type);
+
+/* Bytes of one q8_1-quantized activation row: ceil(K/512)*512/32 blocks of 36 bytes
+ * (gguf_kernel.cu:114-115: int32 [M][Kpad/32*9]). */
+int64_t gguf_b200_q8_1_row_bytes(int64_t K);
+
+/* q8_1 activation quantization, bit-exact with the reference kernel.
+ * Replaces: quantize_q8_1 + quantize_row_q8_1_cuda, gguf_kernel.cu:32-85.
+ * out: M rows of gguf_b200_q8_1_row_bytes(K) bytes: {half d; half sum; int8 qs[32]} blocks. */
+int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int64_t K, void* stream);
+
+/* Standalone dequantize, bit-exact with the reference.
+ * Replaces: ggml_dequantize, gguf_kernel.cu:87-102 (+ dequantize.cuh:527-571 dispatch).
+ * Writes n_elems = m*n values (a multiple of the block size); every output element is
+ * written, so the caller need not zero-fill. */
+int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream);
+
+/* Scratch bytes needed by an op for the given sizes (rows = M, or tokens for the MoE ops). */
+int64_t gguf_b200_workspace_bytes(int op, int type, int64_t M, int64_t N, int64_t K);
+
+/* Decode GEMV: Y[M][N] = q8_1(X) . dequant(W)^T, weights read once for up to 8 vectors.
+ * Replaces: ggml_mul_mat_vec_a8, gguf_kernel.cu:104-218 (+ mmvq.cuh). */
+int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
+                             int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Prefill GEMM on tensor cores (same q8_1-quantized activations).
+ * Replaces: ggml_mul_mat_a8, gguf_kernel.cu:220-290 (+ mmq.cuh).  Types 2, 8, 12, 14. */
+int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
+                         int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Fused dequantize + dense GEMM with unquantized activations: Y = X . dequant(W)^T.
+ * Replaces the two-step route the reference takes for IQ types at larger batches
+ * (quantization/linear.py:50-54: ggml_dequantize then x @ W.T).  dtype f16 or bf16. */
+int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
+                             int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* MoE expert GEMM over expert-sorted token blocks.
+ * Replaces: ggml_moe_a8, gguf_kernel.cu:292-393 (+ moe.cuh:5-129).
+ *   X [tokens][K]; W [E][N][K/QK*type_size] with expert_stride_bytes between experts;
+ *   sorted_token_ids[n_sorted], expert_ids[n_sorted/block], num_tokens_post_padded[1] on device,
+ *   as produced by moe_align_block_size with block = gguf_b200_moe_block_size(type);
+ *   Y [tokens*top_k][N]: row t = sorted id; rows that receive no token are set to zero. */
+int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* workspace, int64_t workspace_bytes,
+                     const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                     const int32_t* num_tokens_post_padded, int64_t n_sorted, int64_t expert_stride_bytes,
+                     int type, int dtype, int64_t tokens, int64_t top_k, int64_t N, int64_t K, void* stream);
+
+/* Small-batch MoE: one GEMV per (token, expert) pair.
+ * Replaces: ggml_moe_a8_vec, gguf_kernel.cu:395-530 (+ moe_vec.cuh:3-53).
+ *   topk_ids [tokens*top_k] on device; Y [tokens*top_k][N]. */
+int gguf_b200_moe_a8_vec(const void* X, const void* W, void* Y, void* workspace, int64_t workspace_bytes,
+                         const int32_t* topk_ids, int64_t n_experts, int type, int dtype, int64_t tokens,
+                         int64_t top_k, int64_t N, int64_t K, void* stream);
+
+/* Token-block size the caller must pass to moe_align_block_size.
+ * Replaces: ggml_moe_get_block_size, gguf_kernel.cu:532-566 (4 for every type there). */
+int gguf_b200_moe_block_size(int type);
+
+/* Device-side status word of the calling thread's current device: 0, or GGUF_B200_E_TIMEOUT if
+ * a kernel gave up on a bounded wait since the last call.  Synchronises the device. */
+int gguf_b200_last_status(void);
+
+/* Numerics pin (tests only): how Q4_K dequantize combines d*q - m in half precision.
+ * 0 = multiply and subtract rounded separately, 1 = one fused multiply-subtract (default:
+ * that is what the reference binary does on sm_100a, where the assembler contracts the
+ * unqualified mul.f16/sub.f16 pair of dequantize.cuh:193-194). */
+void gguf_b200_set_q4k_contract(int fused);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

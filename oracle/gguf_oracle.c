@@ -1,0 +1,580 @@
+/*
+ * CPU oracle for the GGUF quantized-matmul hot path.  TEST INFRASTRUCTURE ONLY:
+ * nothing in the product library links, loads or calls this file; it exists so that
+ * tests (and the CPU-baseline leg of the benchmark) can check the CUDA kernels.
+ *
+ * It restates, in plain C, the arithmetic of the reference plugin's CUDA kernels
+ * (vllm_gguf_plugin/csrc/gguf/ of akmorley/vllm-gguf-plugin-prism) for six block types:
+ *   Q4_0 (2), Q8_0 (8), Q4_K (12), Q6_K (14), IQ2_XXS (16), IQ4_XS (23).
+ * Each function names the reference lines it follows.  Half-precision steps are
+ * emulated exactly (one IEEE rounding per __hmul/__hsub/__int2half_rn), so the
+ * dequantize outputs are bit patterns, not approximations.  Matmul entry points are
+ * evaluated in double precision: they give the value the reference formulas define,
+ * free of the fp32 summation-order noise of any particular GPU schedule.
+ *
+ * Pinning: the reference holds no self-contained golden vectors for this path (its
+ * kernel tests need fixture files from a model hub).  The oracle is pinned instead
+ *  (1) against gguf-py's dequantize (the third-party format definition the reference's
+ *      own tests compare with, tests/test_kernels.py:77-99) on committed fixtures, and
+ *  (2) on a GPU, against the reference's own kernels built by oracle/build_ref.py.
+ *
+ * Known, documented gap: the reference is compiled with --use_fast_math, so the two
+ * fp32 divisions of its q8_1 quantizer are approximate on the GPU; this file uses
+ * IEEE division.  Differences are confined to near-ties and are classified by the
+ * tests (the GPU-vs-reference-GPU comparison is bit-exact).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../include/gguf_b200_iq_tables.h"
+
+#define QK 32
+#define QK_K 256
+
+enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_XS = 23 };
+enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
+
+/* ------------------------------------------------------------------ */
+/* exact half / bfloat16 helpers                                       */
+/* ------------------------------------------------------------------ */
+
+typedef __int128 i128;
+typedef unsigned __int128 u128;
+
+static float h2f(uint16_t h) {
+  uint32_t s = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 31, m = h & 1023, u;
+  if (e == 0) {
+    if (m == 0) {
+      u = s;
+    } else { /* subnormal: value = m * 2^-24 */
+      float f = (float)m * 5.9604644775390625e-08f;
+      memcpy(&u, &f, 4);
+      u |= s;
+    }
+  } else if (e == 31) {
+    u = s | 0x7f800000u | (m << 13);
+  } else {
+    u = s | ((e + 112) << 23) | (m << 13);
+  }
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+/* A finite half as an integer in units of 2^-48 (so that products of two halves,
+ * whose smallest bit is 2^-48, are integers too). */
+static i128 h2s(uint16_t h) {
+  int e = (h >> 10) & 31, m = h & 1023;
+  i128 v = (e == 0) ? ((i128)m << 24) : ((i128)(m | 1024) << (e - 1 + 24));
+  return (h & 0x8000) ? -v : v;
+}
+
+/* Round an exact value (units of 2^-48) to half, round-to-nearest-even. */
+static uint16_t s2h(i128 v) {
+  uint16_t sign = 0;
+  if (v < 0) {
+    sign = 0x8000;
+    v = -v;
+  }
+  u128 m = (u128)v;
+  if (m == 0) return sign;
+  int p = 127;
+  while (!((m >> p) & 1)) --p; /* msb position */
+  int e = p - 48;             /* value in [2^e, 2^(e+1)) */
+  int shift = (e < -14) ? 24 : (p - 10);
+  u128 q = m >> shift, rem = m & (((u128)1 << shift) - 1), half = (u128)1 << (shift - 1);
+  if (shift == 0) {
+    rem = 0;
+    half = 1;
+  }
+  if (rem > half || (rem == half && (q & 1))) ++q;
+  if (e < -14) return sign | (uint16_t)q; /* subnormal (q==1024 carries into the first normal) */
+  if (q == 2048) {
+    q = 1024;
+    ++e;
+  }
+  if (e > 15) return sign | 0x7c00;
+  return sign | (uint16_t)(((e + 15) << 10) | ((int)q & 1023));
+}
+
+static uint16_t hmul(uint16_t a, uint16_t b) { /* one rounding, like mul.f16 */
+  i128 pa = h2s(a) >> 24, pb = h2s(b) >> 24;   /* back to units of 2^-24 each */
+  return s2h(pa * pb);
+}
+static uint16_t hsub(uint16_t a, uint16_t b) { return s2h(h2s(a) - h2s(b)); }
+static uint16_t hfms(uint16_t a, uint16_t b, uint16_t c) { /* a*b - c with a single rounding */
+  i128 pa = h2s(a) >> 24, pb = h2s(b) >> 24;
+  return s2h(pa * pb - h2s(c));
+}
+static uint16_t i2h(int v) { return s2h((i128)v << 48); } /* __int2half_rn */
+
+static uint16_t f2h(float f) { /* __float2half_rn */
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  uint16_t sign = (uint16_t)((u >> 16) & 0x8000);
+  uint32_t e = (u >> 23) & 255, m = u & 0x7fffff;
+  if (e == 255) return sign | 0x7c00 | (m ? 0x200 : 0);
+  if (e == 0) return sign; /* fp32 subnormals are below half the smallest half subnormal */
+  int E = (int)e - 127;
+  if (E > 15) return sign | 0x7c00;
+  if (E < -25) return sign;
+  /* finite, within reach: 24-bit significand M * 2^(E-23); bring to units of 2^-48 */
+  u128 M = (u128)(m | 0x800000);
+  int sh = E - 23 + 48; /* >= 0 because E >= -25 */
+  uint16_t r = s2h((i128)(M << sh));
+  return sign | r;
+}
+
+static uint16_t f2bf(float f) { /* __float2bfloat16_rn */
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffff) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fff + ((u >> 16) & 1);
+  return (uint16_t)(u >> 16);
+}
+static float bf2f(uint16_t b) {
+  uint32_t u = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+static float load_act(const void* x, int dt, int64_t i) {
+  if (dt == DT_F32) return ((const float*)x)[i];
+  if (dt == DT_F16) return h2f(((const uint16_t*)x)[i]);
+  return bf2f(((const uint16_t*)x)[i]);
+}
+
+/* store a value that is already a half (half-arithmetic decoders):
+ * convert_from_half<dst_t>, ggml-common.h:1079-1096 */
+static void store_h(void* out, int dt, int64_t i, uint16_t h) {
+  if (dt == DT_F16)
+    ((uint16_t*)out)[i] = h;
+  else if (dt == DT_F32)
+    ((float*)out)[i] = h2f(h);
+  else
+    ((uint16_t*)out)[i] = f2bf(h2f(h));
+}
+/* store an fp32 value by implicit conversion to dst_t (fp32-arithmetic decoders and all
+ * matmul outputs, e.g. mmvq.cuh:38-40) */
+static void store_f(void* out, int dt, int64_t i, float f) {
+  if (dt == DT_F32)
+    ((float*)out)[i] = f;
+  else if (dt == DT_F16)
+    ((uint16_t*)out)[i] = f2h(f);
+  else
+    ((uint16_t*)out)[i] = f2bf(f);
+}
+
+static uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+
+int oracle_type_size(int type) {
+  switch (type) {
+    case T_Q4_0: return 18;
+    case T_Q8_0: return 34;
+    case T_Q4_K: return 144;
+    case T_Q6_K: return 210;
+    case T_IQ2_XXS: return 66;
+    case T_IQ4_XS: return 136;
+  }
+  return 0;
+}
+int oracle_block_size(int type) { return (type == T_Q4_0 || type == T_Q8_0) ? QK : (oracle_type_size(type) ? QK_K : 0); }
+
+/* 6-bit (scale, min) pair j of a Q4_K super-block: get_scale_min_k4, dequantize.cuh:156-163 */
+static void scale_min_k4(int j, const uint8_t* q, int* sc, int* m) {
+  if (j < 4) {
+    *sc = q[j] & 63;
+    *m = q[j + 4] & 63;
+  } else {
+    *sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+    *m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+  }
+}
+
+/* 6-bit sub-block scale of IQ4_XS minus 32: dequantize.cuh:429, vecdotq.cuh:1801 */
+static int iq4xs_ls(const uint8_t* blk, int ib) {
+  uint16_t sh = rd16(blk + 2);
+  const uint8_t* sl = blk + 4;
+  return (((sl[ib / 2] >> (4 * (ib % 2))) & 0xf) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+}
+
+/* ------------------------------------------------------------------ */
+/* standalone dequantize (ggml_dequantize, gguf_kernel.cu:87-102)      */
+/* ------------------------------------------------------------------ */
+
+/* q4k_contract: 0 = __hmul then __hsub with two roundings (dequantize.cuh:193-194 as
+ * written); 1 = the same pair contracted into one fused multiply-subtract, which the PTX
+ * rules allow the assembler to do for mul.f16/sub.f16 without an explicit .rn.  Which of
+ * the two the reference binary does is decided on the GPU by comparing with it: on sm_100a
+ * (nvcc 12.9, reference flags) it is 1, the fused form. */
+int oracle_dequantize(const uint8_t* w, int type, void* out, int out_dt, int64_t n_elems,
+                      int q4k_contract) {
+  const int ts = oracle_type_size(type), bs = oracle_block_size(type);
+  if (!ts) return -1;
+  const int64_t nb = n_elems / bs;
+  for (int64_t b = 0; b < nb; ++b) {
+    const uint8_t* blk = w + b * ts;
+    const int64_t o = b * bs;
+    switch (type) {
+      case T_Q4_0: { /* dequantize_q4_0, dequantize.cuh:3-15; placement :88-98 */
+        uint16_t d = rd16(blk);
+        for (int j = 0; j < 16; ++j) {
+          int q = blk[2 + j];
+          store_h(out, out_dt, o + j, hmul(hsub(i2h(q & 0xF), i2h(8)), d));
+          store_h(out, out_dt, o + j + 16, hmul(hsub(i2h(q >> 4), i2h(8)), d));
+        }
+      } break;
+      case T_Q8_0: { /* dequantize_q8_0, dequantize.cuh:69-78 */
+        uint16_t d = rd16(blk);
+        for (int j = 0; j < 32; ++j) store_h(out, out_dt, o + j, hmul(i2h((int8_t)blk[2 + j]), d));
+      } break;
+      case T_Q4_K: { /* dequantize_block_q4_K, dequantize.cuh:165-196 */
+        uint16_t dall = rd16(blk), dmin = rd16(blk + 2);
+        const uint8_t *scales = blk + 4, *qs = blk + 16;
+        for (int il = 0; il < 4; ++il) {
+          int sc, m;
+          scale_min_k4(2 * il, scales, &sc, &m);
+          uint16_t d1 = hmul(dall, i2h(sc)), m1 = hmul(dmin, i2h(m));
+          scale_min_k4(2 * il + 1, scales, &sc, &m);
+          uint16_t d2 = hmul(dall, i2h(sc)), m2 = hmul(dmin, i2h(m));
+          for (int l = 0; l < 32; ++l) {
+            int q = qs[32 * il + l];
+            uint16_t lo, hi;
+            if (q4k_contract) {
+              lo = hfms(d1, i2h(q & 0xF), m1);
+              hi = hfms(d2, i2h(q >> 4), m2);
+            } else {
+              lo = hsub(hmul(d1, i2h(q & 0xF)), m1);
+              hi = hsub(hmul(d2, i2h(q >> 4)), m2);
+            }
+            store_h(out, out_dt, o + 64 * il + l, lo);
+            store_h(out, out_dt, o + 64 * il + 32 + l, hi);
+          }
+        }
+      } break;
+      case T_Q6_K: { /* dequantize_block_q6_K, dequantize.cuh:232-256 */
+        const uint8_t *ql = blk, *qh = blk + 128;
+        const int8_t* sc = (const int8_t*)(blk + 192);
+        uint16_t d = rd16(blk + 208);
+        for (int ip = 0; ip < 2; ++ip)
+          for (int il = 0; il < 32; ++il) {
+            int is = 8 * ip + il / 16;
+            int l0 = ql[64 * ip + il], l1 = ql[64 * ip + il + 32], h = qh[32 * ip + il];
+            int q0 = (int8_t)((l0 & 0xF) | (((h >> 0) & 3) << 4)) - 32;
+            int q1 = (int8_t)((l1 & 0xF) | (((h >> 2) & 3) << 4)) - 32;
+            int q2 = (int8_t)((l0 >> 4) | (((h >> 4) & 3) << 4)) - 32;
+            int q3 = (int8_t)((l1 >> 4) | (((h >> 6) & 3) << 4)) - 32;
+            int64_t y = o + 128 * ip + il;
+            store_h(out, out_dt, y + 0, hmul(d, i2h(sc[is + 0] * q0)));
+            store_h(out, out_dt, y + 32, hmul(d, i2h(sc[is + 2] * q1)));
+            store_h(out, out_dt, y + 64, hmul(d, i2h(sc[is + 4] * q2)));
+            store_h(out, out_dt, y + 96, hmul(d, i2h(sc[is + 6] * q3)));
+          }
+      } break;
+      case T_IQ2_XXS: { /* dequantize_block_iq2_xxs, dequantize.cuh:258-275 (fp32 math) */
+        float df = h2f(rd16(blk));
+        for (int ib = 0; ib < 8; ++ib) {
+          const uint8_t* q2 = blk + 2 + 8 * ib;
+          uint32_t aux32 = (uint32_t)q2[4] | ((uint32_t)q2[5] << 8) | ((uint32_t)q2[6] << 16) | ((uint32_t)q2[7] << 24);
+          volatile float d = df * (0.5f + (float)(aux32 >> 28));
+          d = d * 0.25f;
+          for (int il = 0; il < 4; ++il) {
+            uint64_t grid = gguf_b200_iq2xxs_grid[q2[il]];
+            uint8_t signs = gguf_b200_ksigns_iq2xs[(aux32 >> (7 * il)) & 127];
+            for (int j = 0; j < 8; ++j) {
+              volatile float v = d * (float)((grid >> (8 * j)) & 0xff);
+              v = v * ((signs >> j) & 1 ? -1.f : 1.f);
+              store_f(out, out_dt, o + 32 * ib + 8 * il + j, v);
+            }
+          }
+        }
+      } break;
+      case T_IQ4_XS: { /* dequantize_block_iq4_xs, dequantize.cuh:420-435 (fp32 math) */
+        float df = h2f(rd16(blk));
+        const uint8_t* qs = blk + 8;
+        for (int ib = 0; ib < 8; ++ib) {
+          volatile float d = df * (float)iq4xs_ls(blk, ib);
+          for (int j = 0; j < 16; ++j) {
+            int q = qs[16 * ib + j];
+            volatile float lo = d * (float)gguf_b200_kvalues_iq4nl[q & 0xf];
+            volatile float hi = d * (float)gguf_b200_kvalues_iq4nl[q >> 4];
+            store_f(out, out_dt, o + 32 * ib + j, lo);
+            store_f(out, out_dt, o + 32 * ib + j + 16, hi);
+          }
+        }
+      } break;
+    }
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* q8_1 activation quantizer (quantize_q8_1, gguf_kernel.cu:32-69)     */
+/* ------------------------------------------------------------------ */
+
+int64_t oracle_q8_1_row_bytes(int64_t K) { return (K + 511) / 512 * 512 / 32 * 36; }
+
+/* out: M rows of Kpad/32 blocks {half d; half sum; int8 qs[32]}, Kpad = K rounded up to
+ * 512 (gguf_kernel.cu:74); elements beyond K are zeros (:48).  amax and sum use the
+ * xor-butterfly of :53-56 (the order matters for the fp32 sum). */
+int oracle_quantize_q8_1(const void* x, int dt, uint8_t* out, int64_t M, int64_t K) {
+  const int64_t kpad = (K + 511) / 512 * 512, nb = kpad / 32;
+  for (int64_t r = 0; r < M; ++r)
+    for (int64_t b = 0; b < nb; ++b) {
+      float xi[32], s[32], a[32];
+      for (int j = 0; j < 32; ++j) {
+        int64_t k = b * 32 + j;
+        xi[j] = k < K ? load_act(x, dt, r * K + k) : 0.0f;
+        s[j] = xi[j];
+        a[j] = fabsf(xi[j]);
+      }
+      for (int mask = 16; mask > 0; mask >>= 1) {
+        float s2[32], a2[32];
+        for (int j = 0; j < 32; ++j) {
+          volatile float t = s[j] + s[j ^ mask];
+          s2[j] = t;
+          a2[j] = fmaxf(a[j], a[j ^ mask]);
+        }
+        memcpy(s, s2, sizeof s);
+        memcpy(a, a2, sizeof a);
+      }
+      const float amax = a[0];
+      volatile float d = amax / 127;
+      uint8_t* blk = out + (r * nb + b) * 36;
+      uint16_t hd = f2h(d), hs = f2h(s[0]);
+      blk[0] = hd & 255;
+      blk[1] = hd >> 8;
+      blk[2] = hs & 255;
+      blk[3] = hs >> 8;
+      for (int j = 0; j < 32; ++j) {
+        volatile float t = xi[j] / d;
+        blk[4 + j] = (uint8_t)(int8_t)(amax == 0.0f ? 0 : roundf(t));
+      }
+    }
+  return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* block dot products                                                  */
+/* ------------------------------------------------------------------ */
+
+static int idot(const int8_t* a, const int8_t* b, int n) {
+  int s = 0;
+  for (int i = 0; i < n; ++i) s += a[i] * b[i];
+  return s;
+}
+
+/* Unpack one weight block of `type` to its integer codes w[0..bs) in dequantized order. */
+static void unpack_codes(const uint8_t* blk, int type, int8_t* w) {
+  switch (type) {
+    case T_Q4_0:
+      for (int j = 0; j < 16; ++j) {
+        w[j] = blk[2 + j] & 0xF;
+        w[j + 16] = blk[2 + j] >> 4;
+      }
+      break;
+    case T_Q8_0:
+      for (int j = 0; j < 32; ++j) w[j] = (int8_t)blk[2 + j];
+      break;
+    case T_Q4_K:
+      for (int il = 0; il < 4; ++il)
+        for (int l = 0; l < 32; ++l) {
+          w[64 * il + l] = blk[16 + 32 * il + l] & 0xF;
+          w[64 * il + 32 + l] = blk[16 + 32 * il + l] >> 4;
+        }
+      break;
+    case T_Q6_K:
+      for (int ip = 0; ip < 2; ++ip)
+        for (int il = 0; il < 32; ++il) {
+          int l0 = blk[64 * ip + il], l1 = blk[64 * ip + il + 32], h = blk[128 + 32 * ip + il];
+          w[128 * ip + il + 0] = (int8_t)(((l0 & 0xF) | (((h >> 0) & 3) << 4)) - 32);
+          w[128 * ip + il + 32] = (int8_t)(((l1 & 0xF) | (((h >> 2) & 3) << 4)) - 32);
+          w[128 * ip + il + 64] = (int8_t)(((l0 >> 4) | (((h >> 4) & 3) << 4)) - 32);
+          w[128 * ip + il + 96] = (int8_t)(((l1 >> 4) | (((h >> 6) & 3) << 4)) - 32);
+        }
+      break;
+    case T_IQ2_XXS:
+      for (int ib = 0; ib < 8; ++ib) {
+        const uint8_t* q2 = blk + 2 + 8 * ib;
+        uint32_t aux32 = (uint32_t)q2[4] | ((uint32_t)q2[5] << 8) | ((uint32_t)q2[6] << 16) | ((uint32_t)q2[7] << 24);
+        for (int il = 0; il < 4; ++il) {
+          uint64_t grid = gguf_b200_iq2xxs_grid[q2[il]];
+          uint8_t signs = gguf_b200_ksigns_iq2xs[(aux32 >> (7 * il)) & 127];
+          for (int j = 0; j < 8; ++j) {
+            int g = (int)((grid >> (8 * j)) & 0xff);
+            w[32 * ib + 8 * il + j] = (int8_t)(((signs >> j) & 1) ? -g : g);
+          }
+        }
+      }
+      break;
+    case T_IQ4_XS:
+      for (int ib = 0; ib < 8; ++ib)
+        for (int j = 0; j < 16; ++j) {
+          int q = blk[8 + 16 * ib + j];
+          w[32 * ib + j] = gguf_b200_kvalues_iq4nl[q & 0xf];
+          w[32 * ib + j + 16] = gguf_b200_kvalues_iq4nl[q >> 4];
+        }
+      break;
+  }
+}
+
+/* Dot product of one weight block with the aligned q8_1 block(s) y (36-byte blocks).
+ * mmq = 0: the GEMV formulas (vec_dot_*_q8_1, vecdotq.cuh:493-509, 852-867, 1159-1202,
+ *          1417-1441, 1531-1552, 1791-1812);
+ * mmq = 1: the tiled-kernel formulas (vec_dot_*_q8_1_mul_mat, vecdotq.cuh:552-571, 912-921,
+ *          1267-1277 with impl :353-379, 1518-1529), which differ for Q4_K: the min term
+ *          uses the stored fp16 sum of the unquantized activations instead of d8*sum(q8). */
+static double block_dot(const uint8_t* blk, int type, const uint8_t* y, int mmq) {
+  int8_t w[QK_K];
+  unpack_codes(blk, type, w);
+  const int nsub = oracle_block_size(type) / 32;
+  double acc = 0.0;
+  switch (type) {
+    case T_Q4_0: { /* d4 * (sumi*d8 - 8*s8), vec_dot_q4_0_q8_1_impl vecdotq.cuh:46-66 */
+      double d4 = h2f(rd16(blk)), d8 = h2f(rd16(y)), s8 = h2f(rd16(y + 2));
+      acc = d4 * (idot(w, (const int8_t*)y + 4, 32) * d8 - 8.0 * s8);
+    } break;
+    case T_Q8_0: { /* d8_0*d8_1*sumi, vecdotq.cuh:165-177 */
+      acc = (double)h2f(rd16(blk)) * h2f(rd16(y)) * idot(w, (const int8_t*)y + 4, 32);
+    } break;
+    case T_Q4_K: { /* vecdotq.cuh:328-351 (GEMV) / :353-379 (tiled) */
+      double d = h2f(rd16(blk)), dmin = h2f(rd16(blk + 2)), sd = 0, sm = 0;
+      for (int g = 0; g < nsub; ++g) {
+        int sc, m;
+        scale_min_k4(g, blk + 4, &sc, &m);
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        double d8 = h2f(rd16(yb)), s8 = h2f(rd16(yb + 2));
+        sd += d8 * (double)(idot(w + 32 * g, q8, 32) * sc);
+        if (mmq) {
+          sm += s8 * m;
+        } else {
+          int sq = 0;
+          for (int j = 0; j < 32; ++j) sq += q8[j];
+          sm += d8 * (double)(sq * m);
+        }
+      }
+      acc = d * sd - dmin * sm;
+    } break;
+    case T_Q6_K: { /* d * sum d8*(dot16*sc), vecdotq.cuh:447-491 */
+      double d = h2f(rd16(blk + 208)), sf = 0;
+      const int8_t* sc = (const int8_t*)(blk + 192);
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        double d8 = h2f(rd16(yb));
+        sf += d8 * (double)(idot(w + 32 * g, q8, 16) * sc[2 * g] + idot(w + 32 * g + 16, q8 + 16, 16) * sc[2 * g + 1]);
+      }
+      acc = d * sf;
+    } break;
+    case T_IQ2_XXS: { /* d*(0.5+s)*d8*0.25*sumi, vecdotq.cuh:1531-1552 */
+      double d = h2f(rd16(blk));
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        uint32_t s = blk[2 + 8 * g + 7] >> 4;
+        acc += d * (0.5 + s) * h2f(rd16(yb)) * 0.25 * idot(w + 32 * g, (const int8_t*)yb + 4, 32);
+      }
+    } break;
+    case T_IQ4_XS: { /* d*(ls-32)*d8*(sumi1+sumi2), vecdotq.cuh:1791-1812 */
+      double d = h2f(rd16(blk));
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        acc += d * iq4xs_ls(blk, g) * h2f(rd16(yb)) * idot(w + 32 * g, (const int8_t*)yb + 4, 32);
+      }
+    } break;
+  }
+  return acc;
+}
+
+/* ------------------------------------------------------------------ */
+/* matmul entry points                                                 */
+/* ------------------------------------------------------------------ */
+
+/* Y[m, n] = sum over blocks of row n of block_dot(W block, q8_1 blocks of vector m).
+ * Covers ggml_mul_mat_vec_a8 (mmq=0; gguf_kernel.cu:104-218 + mmvq.cuh:2-41) and
+ * ggml_mul_mat_a8 (mmq=1; gguf_kernel.cu:220-290 + mmq.cuh:2-104): both quantize X to q8_1
+ * first.  xq = output of oracle_quantize_q8_1 (row stride Kpad/32 blocks).
+ * y64 receives the unrounded value; out (may be NULL) the value stored as out_dt. */
+int oracle_matmul_a8(const uint8_t* w, int type, const uint8_t* xq, double* y64, void* out, int out_dt,
+                     int64_t M, int64_t N, int64_t K, int mmq) {
+  const int ts = oracle_type_size(type), bs = oracle_block_size(type);
+  if (!ts || K % bs) return -1;
+  const int64_t bpr = K / bs, qrow = oracle_q8_1_row_bytes(K);
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      double acc = 0;
+      for (int64_t b = 0; b < bpr; ++b)
+        acc += block_dot(w + (n * bpr + b) * ts, type, xq + m * qrow + b * (bs / 32) * 36, mmq);
+      if (y64) y64[m * N + n] = acc;
+      if (out) store_f(out, out_dt, m * N + n, (float)acc);
+    }
+  return 0;
+}
+
+/* ggml_moe_a8 (gguf_kernel.cu:292-393 + moe_q, moe.cuh:5-129).  For every position p of
+ * sorted_token_ids below num_tokens_post_padded whose id t = sorted[p] is a real slot
+ * (t < tokens*top_k): activation row t/top_k (moe.cuh:64), expert expert_ids[p/block]
+ * (moe.cuh:32), output row t (moe.cuh:115-126).  Rows never written stay zero
+ * (new_zeros, gguf_kernel.cu:301-302).  Experts outside [0,255] are skipped (moe.cuh:33).
+ * Arithmetic = the tiled-kernel formulas (mmq=1). */
+int oracle_moe_a8(const uint8_t* w, int type, const uint8_t* xq, double* y64, void* out, int out_dt,
+                  const int32_t* sorted_ids, int64_t n_sorted, const int32_t* expert_ids, int32_t n_post_pad,
+                  int block, int64_t expert_stride_bytes, int64_t tokens, int64_t top_k, int64_t N, int64_t K) {
+  const int ts = oracle_type_size(type), bs = oracle_block_size(type);
+  if (!ts || K % bs) return -1;
+  const int64_t bpr = K / bs, qrow = oracle_q8_1_row_bytes(K), rows = tokens * top_k;
+  for (int64_t i = 0; i < rows * N; ++i) {
+    if (y64) y64[i] = 0;
+    if (out) store_f(out, out_dt, i, 0.0f);
+  }
+  for (int64_t p = 0; p < n_sorted && p < n_post_pad; ++p) {
+    const int64_t t = sorted_ids[p];
+    const int e = expert_ids[p / block];
+    if (t < 0 || t >= rows || e < 0 || e > 255) continue;
+    const uint8_t* we = w + e * expert_stride_bytes;
+    const uint8_t* xr = xq + (t / top_k) * qrow;
+    for (int64_t n = 0; n < N; ++n) {
+      double acc = 0;
+      for (int64_t b = 0; b < bpr; ++b) acc += block_dot(we + (n * bpr + b) * ts, type, xr + b * (bs / 32) * 36, 1);
+      if (y64) y64[t * N + n] = acc;
+      if (out) store_f(out, out_dt, t * N + n, (float)acc);
+    }
+  }
+  return 0;
+}
+
+/* ggml_moe_a8_vec (gguf_kernel.cu:395-530 + moe_vec_q, moe_vec.cuh:3-53): output row
+ * s = token*top_k + k uses expert topk_ids[s] and activation row s/top_k, GEMV formulas. */
+int oracle_moe_a8_vec(const uint8_t* w, int type, const uint8_t* xq, double* y64, void* out, int out_dt,
+                      const int32_t* topk_ids, int64_t tokens, int64_t top_k, int64_t N, int64_t K) {
+  const int ts = oracle_type_size(type), bs = oracle_block_size(type);
+  if (!ts || K % bs) return -1;
+  const int64_t bpr = K / bs, qrow = oracle_q8_1_row_bytes(K);
+  for (int64_t s = 0; s < tokens * top_k; ++s) {
+    const uint8_t* we = w + (int64_t)topk_ids[s] * N * bpr * ts;
+    const uint8_t* xr = xq + (s / top_k) * qrow;
+    for (int64_t n = 0; n < N; ++n) {
+      double acc = 0;
+      for (int64_t b = 0; b < bpr; ++b) acc += block_dot(we + (n * bpr + b) * ts, type, xr + b * (bs / 32) * 36, 0);
+      if (y64) y64[s * N + n] = acc;
+      if (out) store_f(out, out_dt, s * N + n, (float)acc);
+    }
+  }
+  return 0;
+}
+
+/* Dense fp32 dot of dequantized weights with raw activations: the arithmetic of the
+ * reference's dequantize-then-matmul route for IQ types at larger batches
+ * (quantization/linear.py:50-54).  wd = fp32 view of the dequantized weights [N,K]. */
+int oracle_dense_matmul(const float* wd, const void* x, int x_dt, double* y64, int64_t M, int64_t N, int64_t K) {
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      double acc = 0;
+      for (int64_t k = 0; k < K; ++k) acc += (double)wd[n * K + k] * load_act(x, x_dt, m * K + k);
+      y64[m * N + n] = acc;
+    }
+  return 0;
+}

@@ -1,0 +1,236 @@
+// extern "C" entry points of libgguf_b200 (declared in include/gguf_b200.h): argument
+// validation, workspace carving and dispatch to the kernel launchers.  No allocation, no
+// synchronisation (except gguf_b200_last_status), no exceptions.
+#include "../../include/gguf_b200.h"
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace gguf_b200;
+
+namespace gguf_b200 {
+
+// Device-side status word written by kernels whose bounded waits expire.
+static __device__ int g_status_word;
+static int g_q4k_contract = 1;  // the reference binary fuses the pair (established on B200 against it)
+
+static int* status_ptr() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  int*& p = ptrs[dev & 63];
+  if (!p) {
+    void* a = nullptr;
+    if (cudaGetSymbolAddress(&a, g_status_word) != cudaSuccess) return nullptr;
+    p = static_cast<int*>(a);
+  }
+  return p;
+}
+
+int mmq_corr_mode(int type) { return type == T_Q4_0 ? CORR_Q4_0 : (type == T_Q4_K ? CORR_MIN : CORR_NONE); }
+int64_t mmq_ldb(int type, int64_t K) {
+  const int64_t kpad = round_up(K, 512);
+  return mmq_corr_mode(type) == CORR_NONE ? kpad : kpad + round_up(kpad / 32, 64);
+}
+
+static bool is_mmq_type(int t) { return t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K; }
+static bool dtype_ok(int d) { return d == DT_F32 || d == DT_F16 || d == DT_BF16; }
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_common(const void* W, const void* X, const void* Y, int type, int dtype, int64_t M, int64_t N, int64_t K) {
+  if (!type_size(type)) return E_BAD_TYPE;
+  if (!dtype_ok(dtype)) return E_BAD_DTYPE;
+  if (M < 0 || N < 0 || K <= 0 || K % block_size(type) != 0) return E_BAD_SHAPE;
+  if (K > (int64_t)1 << 24 || N > (int64_t)1 << 31 || M > (int64_t)1 << 31) return E_TOO_LARGE;
+  if (M == 0 || N == 0) return E_OK;
+  if (!W || !X || !Y || !aligned16(W) || !aligned16(X) || !aligned16(Y)) return E_BAD_POINTER;
+  return E_OK;
+}
+
+}  // namespace gguf_b200
+
+extern "C" {
+
+const char* gguf_b200_version(void) { return "gguf_b200 0.1 (sm_100a)"; }
+
+const char* gguf_b200_error_string(int code) {
+  switch (code) {
+    case E_OK: return "ok";
+    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q8_0=8, Q4_K=12, Q6_K=14, IQ2_XXS=16, IQ4_XS=23)";
+    case E_BAD_DTYPE: return "unsupported dtype (expected f32=0, f16=1, bf16=2)";
+    case E_BAD_SHAPE: return "bad shape (negative size, or K not a multiple of the block size)";
+    case E_BAD_POINTER: return "null or misaligned pointer (16-byte alignment required)";
+    case E_WORKSPACE: return "workspace too small (see gguf_b200_workspace_bytes)";
+    case E_CUDA: return "CUDA runtime error at launch";
+    case E_TOO_LARGE: return "size beyond the supported limit";
+    case E_TIMEOUT: return "a bounded device-side wait expired";
+  }
+  return "unknown error";
+}
+
+int gguf_b200_type_size(int type) { return type_size(type); }
+int gguf_b200_block_size(int type) { return block_size(type); }
+int64_t gguf_b200_q8_1_row_bytes(int64_t K) { return round_up(K, 512) / 32 * 36; }
+void gguf_b200_set_q4k_contract(int fused) { g_q4k_contract = fused ? 1 : 0; }
+int gguf_b200_moe_block_size(int type) { return is_mmq_type(type) ? mmq_moe_block_size() : 0; }
+
+int gguf_b200_last_status(void) {
+  int* p = status_ptr();
+  if (!p) return E_CUDA;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return E_CUDA;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}
+
+int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int64_t K, void* stream) {
+  if (!dtype_ok(dtype)) return E_BAD_DTYPE;
+  if (M < 0 || K <= 0) return E_BAD_SHAPE;
+  if (M == 0) return E_OK;
+  if (!x || !out || (reinterpret_cast<uintptr_t>(out) & 3)) return E_BAD_POINTER;
+  return launch_quantize_q8_1(x, dtype, out, M, K, Q8_MODE_REF, 0, 0, CORR_NONE, nullptr, 1, 0, static_cast<cudaStream_t>(stream));
+}
+
+int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream) {
+  if (!type_size(type)) return E_BAD_TYPE;
+  if (!dtype_ok(out_dtype)) return E_BAD_DTYPE;
+  if (n_elems < 0 || n_elems % block_size(type) != 0) return E_BAD_SHAPE;
+  if (n_elems == 0) return E_OK;
+  if (!W || !out || !aligned16(out) || (reinterpret_cast<uintptr_t>(W) & 15)) return E_BAD_POINTER;
+  return launch_dequantize(W, type, out, out_dtype, n_elems, g_q4k_contract, static_cast<cudaStream_t>(stream));
+}
+
+int64_t gguf_b200_workspace_bytes(int op, int type, int64_t M, int64_t N, int64_t K) {
+  (void)N;
+  if (!type_size(type) || M < 0 || K <= 0) return 0;
+  switch (op) {
+    case GGUF_B200_OP_GEMV:
+    case GGUF_B200_OP_MOE_VEC: return q8_soa_bytes(M, K);
+    case GGUF_B200_OP_MMQ:
+    case GGUF_B200_OP_MOE: return M * mmq_ldb(type, K) * 2;  /* MOE: M = length of sorted_token_ids */
+    case GGUF_B200_OP_DEQUANT_MATMUL: return 0;
+  }
+  return 0;
+}
+
+int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
+                             int64_t M, int64_t N, int64_t K, void* stream) {
+  int rc = check_common(W, X, Y, type, dtype, M, N, K);
+  if (rc || M == 0 || N == 0) return rc;
+  if (!ws || !aligned16(ws)) return E_BAD_POINTER;
+  if (ws_bytes < q8_soa_bytes(M, K)) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the Q4_K GEMV takes its min term from the quantized codes (sum_mode 1), all others from the fp16 sum
+  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s);
+  if (rc) return rc;
+  return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
+}
+
+int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
+                         int64_t M, int64_t N, int64_t K, void* stream) {
+  int rc = check_common(W, X, Y, type, dtype, M, N, K);
+  if (rc || M == 0 || N == 0) return rc;
+  if (!is_mmq_type(type)) return E_BAD_TYPE;
+  if (!ws || !aligned16(ws)) return E_BAD_POINTER;
+  const int64_t ldb = mmq_ldb(type, K);
+  if (ws_bytes < M * ldb * 2) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), nullptr, 1, 0, s);
+  if (rc) return rc;
+  MmqArgs a{};
+  a.w = W; a.b = ws; a.y = Y;
+  a.type = type; a.out_dtype = dtype; a.b_dtype = DT_F16;
+  a.M = M; a.N = N; a.K = K; a.ldb = ldb;
+  a.corr_mode = mmq_corr_mode(type);
+  a.rows_out = M;
+  a.status = st;
+  return launch_mmq(a, s);
+}
+
+int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
+                             int64_t M, int64_t N, int64_t K, void* stream) {
+  (void)ws;
+  (void)ws_bytes;
+  int rc = check_common(W, X, Y, type, dtype, M, N, K);
+  if (rc || M == 0 || N == 0) return rc;
+  if (type != T_IQ2_XXS && type != T_IQ4_XS) return E_BAD_TYPE;
+  if (dtype != DT_F16 && dtype != DT_BF16) return E_BAD_DTYPE;
+  if (K % 64 != 0) return E_BAD_SHAPE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  MmqArgs a{};
+  a.w = W; a.b = X; a.y = Y;
+  a.type = type; a.out_dtype = dtype; a.b_dtype = dtype;
+  a.M = M; a.N = N; a.K = K; a.ldb = K;
+  a.corr_mode = CORR_NONE;
+  a.rows_out = M;
+  a.status = st;
+  return launch_mmq(a, static_cast<cudaStream_t>(stream));
+}
+
+int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* ws, int64_t ws_bytes, const int32_t* sorted_token_ids,
+                     const int32_t* expert_ids, const int32_t* num_tokens_post_padded, int64_t n_sorted,
+                     int64_t expert_stride_bytes, int type, int dtype, int64_t tokens, int64_t top_k, int64_t N,
+                     int64_t K, void* stream) {
+  int rc = check_common(W, X, Y, type, dtype, tokens, N, K);
+  if (rc) return rc;
+  if (!is_mmq_type(type)) return E_BAD_TYPE;
+  if (top_k <= 0 || n_sorted < 0 || n_sorted % mmq_moe_block_size() != 0 || expert_stride_bytes % 16 != 0) return E_BAD_SHAPE;
+  if (tokens == 0 || N == 0) return E_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t rows_out = tokens * top_k;
+  const int64_t esz = dtype == DT_F32 ? 4 : 2;
+  // rows that no routed token writes must read as zero (the reference allocates with new_zeros)
+  if (cudaMemsetAsync(Y, 0, (size_t)(rows_out * N * esz), s) != cudaSuccess) return E_CUDA;
+  if (n_sorted == 0) return E_OK;
+  if (!sorted_token_ids || !expert_ids || !num_tokens_post_padded) return E_BAD_POINTER;
+  if (!ws || !aligned16(ws)) return E_BAD_POINTER;
+  const int64_t ldb = mmq_ldb(type, K);
+  if (ws_bytes < n_sorted * ldb * 2) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  // quantize + gather: row p of the fp16 matrix = activations of token sorted_token_ids[p] / top_k
+  rc = launch_quantize_q8_1(X, dtype, ws, n_sorted, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), sorted_token_ids, top_k,
+                            rows_out, s);
+  if (rc) return rc;
+  MmqArgs a{};
+  a.w = W; a.b = ws; a.y = Y;
+  a.type = type; a.out_dtype = dtype; a.b_dtype = DT_F16;
+  a.M = n_sorted; a.N = N; a.K = K; a.ldb = ldb;
+  a.corr_mode = mmq_corr_mode(type);
+  a.sorted_ids = sorted_token_ids;
+  a.expert_ids = expert_ids;
+  a.n_post_pad = num_tokens_post_padded;
+  a.n_sorted = n_sorted;
+  a.expert_stride_bytes = expert_stride_bytes;
+  a.top_k = top_k;
+  a.rows_out = rows_out;
+  a.moe_block = mmq_moe_block_size();
+  a.status = st;
+  return launch_mmq(a, s);
+}
+
+int gguf_b200_moe_a8_vec(const void* X, const void* W, void* Y, void* ws, int64_t ws_bytes, const int32_t* topk_ids,
+                         int64_t n_experts, int type, int dtype, int64_t tokens, int64_t top_k, int64_t N, int64_t K,
+                         void* stream) {
+  int rc = check_common(W, X, Y, type, dtype, tokens, N, K);
+  if (rc || tokens == 0 || N == 0) return rc;
+  if (top_k <= 0 || n_experts <= 0) return E_BAD_SHAPE;
+  if (!topk_ids || !ws || !aligned16(ws)) return E_BAD_POINTER;
+  if (ws_bytes < q8_soa_bytes(tokens, K)) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = launch_quantize_q8_1(X, dtype, ws, tokens, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s);
+  if (rc) return rc;
+  return launch_moe_gemv(W, ws, Y, topk_ids, type, dtype, tokens, top_k, N, K, n_experts, st, s);
+}
+
+}  // extern "C"

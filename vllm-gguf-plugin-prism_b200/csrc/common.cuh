@@ -1,0 +1,133 @@
+// Shared device helpers of the B200 GGUF kernels: block geometry of the six supported
+// formats, typed stores, bounded mbarrier waits and the 1-D bulk (TMA) copy used to
+// stream packed weight bytes into shared memory.
+//
+// Block layouts (bytes), as defined by the GGUF format and used by the reference at
+// vllm_gguf_plugin/csrc/gguf/ggml-common.h:17-23 (Q4_0), :51-57 (Q8_0), :84-90 (Q4_K),
+// :101-108 (Q6_K), :110-115 (IQ2_XXS), :184-191 (IQ4_XS), :59-65 (q8_1 activations):
+//   Q4_0    18 : half d | u8 qs[16]            value j = qs[j]&15, value j+16 = qs[j]>>4, minus 8
+//   Q8_0    34 : half d | i8 qs[32]
+//   Q4_K   144 : half d | half dmin | u8 scales[12] | u8 qs[128]
+//   Q6_K   210 : u8 ql[128] | u8 qh[64] | i8 scales[16] | half d
+//   IQ2_XXS 66 : half d | u16 qs[32]           per 32 values: 4 grid indices + 28 sign bits + 4-bit scale
+//   IQ4_XS 136 : half d | u16 scales_h | u8 scales_l[4] | u8 qs[128]
+//   q8_1    36 : half d | half sum | i8 qs[32]
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gguf_b200 {
+
+enum : int { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_XS = 23 };
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
+
+// error codes returned through the C-ABI (0 = success)
+enum : int {
+  E_OK = 0,
+  E_BAD_TYPE = -1,      // block type not one of the six supported
+  E_BAD_DTYPE = -2,     // activation/output dtype not f32/f16/bf16
+  E_BAD_SHAPE = -3,     // K not a multiple of the block size, negative sizes, ...
+  E_BAD_POINTER = -4,   // null or insufficiently aligned pointer
+  E_WORKSPACE = -5,     // scratch buffer smaller than gguf_b200_workspace_bytes()
+  E_CUDA = -6,          // a CUDA runtime call failed (see cudaGetLastError)
+  E_TOO_LARGE = -7,     // size beyond what the entry point supports
+  E_TIMEOUT = -8,       // a bounded device-side wait ran out (status word set by the kernel)
+};
+
+template <int TYPE> struct BlockTraits;
+template <> struct BlockTraits<T_Q4_0>    { static constexpr int QK = 32,  TS = 18;  };
+template <> struct BlockTraits<T_Q8_0>    { static constexpr int QK = 32,  TS = 34;  };
+template <> struct BlockTraits<T_Q4_K>    { static constexpr int QK = 256, TS = 144; };
+template <> struct BlockTraits<T_Q6_K>    { static constexpr int QK = 256, TS = 210; };
+template <> struct BlockTraits<T_IQ2_XXS> { static constexpr int QK = 256, TS = 66;  };
+template <> struct BlockTraits<T_IQ4_XS>  { static constexpr int QK = 256, TS = 136; };
+
+__host__ __device__ inline int type_size(int t) {
+  switch (t) {
+    case T_Q4_0: return 18;
+    case T_Q8_0: return 34;
+    case T_Q4_K: return 144;
+    case T_Q6_K: return 210;
+    case T_IQ2_XXS: return 66;
+    case T_IQ4_XS: return 136;
+  }
+  return 0;
+}
+__host__ __device__ inline int block_size(int t) {
+  return (t == T_Q4_0 || t == T_Q8_0) ? 32 : (type_size(t) ? 256 : 0);
+}
+__host__ __device__ inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+// ---- typed stores -----------------------------------------------------------------
+template <typename T> __device__ __forceinline__ T from_float(float f);
+template <> __device__ __forceinline__ float from_float<float>(float f) { return f; }
+template <> __device__ __forceinline__ __half from_float<__half>(float f) { return __float2half_rn(f); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// ---- shared-memory addressing, mbarrier, bulk copy --------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Every wait in this library is bounded: after `limit` polls the caller records a status
+// word and leaves, so a lost completion can never wedge the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 20000000u) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 1-D bulk copy global -> shared (no multicast); src, dst and bytes multiples of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+      "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// 32-bit word from shared memory at an address that is only 2-byte aligned.
+__device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t* p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
+  return __funnelshift_r(w[0], w[1], (uint32_t)(a & 3) * 8u);
+}
+__device__ __forceinline__ float lds_half_as_float(const uint8_t* p) {
+  return __half2float(*reinterpret_cast<const __half*>(p));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+
+}  // namespace gguf_b200

@@ -1,0 +1,230 @@
+// Standalone dequantize: packed GGUF blocks -> dense fp16/bf16/fp32, bit-identical to the
+// reference's ggml_dequantize (vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:87-102 and the
+// per-type kernels of dequantize.cuh:3-15, 69-99, 165-196, 232-256, 258-275, 420-435).
+//
+// The reference spends one 32/64-thread CTA per super-block with 1-2 byte loads and strided
+// 2-byte stores, and zero-fills the output first.  Here the op is treated as what it is -- an
+// output-write-bound stream (2-4 bytes written per 0.26-1.06 bytes read): a persistent grid
+// (multiple of the SM count), every lane produces eight consecutive outputs and writes them
+// with one 16-byte store (two for fp32), so a warp emits 512 contiguous bytes per step.
+//
+// Arithmetic is kept step-for-step equal to the reference so that every rounding happens in
+// the same place: Q4_0/Q8_0/Q4_K/Q6_K decode in IEEE half (one rounding per multiply or
+// subtract; bf16/fp32 outputs are the *half* result converted afterwards), IQ2_XXS/IQ4_XS
+// decode in fp32 and round once on the store.
+#include "common.cuh"
+#include "kernels.h"
+#include "tables.cuh"
+
+namespace gguf_b200 {
+
+template <typename out_t> struct Store8;
+template <> struct Store8<__half> {
+  static __device__ __forceinline__ void st(__half* p, const __half (&h)[8], const float (&)[8], bool from_half) {
+    (void)from_half;
+    uint4 v;
+    v.x = (uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
+    v.y = (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+    v.z = (uint32_t)__half_as_ushort(h[4]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
+    v.w = (uint32_t)__half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+};
+template <> struct Store8<__nv_bfloat16> {
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, const __half (&)[8], const float (&f)[8], bool) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[i] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f[2 * i])) |
+             ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f[2 * i + 1])) << 16);
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Store8<float> {
+  static __device__ __forceinline__ void st(float* p, const __half (&)[8], const float (&f)[8], bool) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+// Eight outputs produced in half arithmetic: 16-bit-float destinations other than half and
+// fp32 destinations receive the half value converted (convert_from_half, ggml-common.h:1079-1096).
+template <typename out_t>
+__device__ __forceinline__ void store_from_half(out_t* p, const __half (&h)[8]) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = __half2float(h[i]);
+  Store8<out_t>::st(p, h, f, true);
+}
+// Eight outputs produced in fp32: rounded once by the store.
+template <typename out_t>
+__device__ __forceinline__ void store_from_float(out_t* p, const float (&f)[8]) {
+  __half h[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(f[i]);
+  Store8<out_t>::st(p, h, f, false);
+}
+
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
+// eight bytes from a 2-byte-aligned global address
+__device__ __forceinline__ uint2 ldg_8_a2(const uint8_t* p) {
+  uint2 r;
+  r.x = ldg_u16(p) | (ldg_u16(p + 2) << 16);
+  r.y = ldg_u16(p + 4) | (ldg_u16(p + 6) << 16);
+  return r;
+}
+__device__ __forceinline__ uint32_t byte_of(uint2 v, int j) { return ((j < 4 ? v.x : v.y) >> (8 * (j & 3))) & 0xffu; }
+
+__device__ __forceinline__ __half hmul_rn(__half a, __half b) { return __hmul_rn(a, b); }
+
+// d1*q - m1 in half.  The reference writes __hsub(__hmul(d1,q), m1) (dequantize.cuh:193-194)
+// with intrinsics that carry no rounding qualifier, which lets the assembler contract the
+// pair into one fused multiply-subtract.  CONTRACT selects the fused form explicitly; the
+// other form pins two roundings.  The GPU parity test against the reference binary shows it
+// uses the fused form on sm_100a; that is the default (gguf_b200_set_q4k_contract).
+template <bool CONTRACT> __device__ __forceinline__ __half q4k_value(__half d1, __half q, __half m1) {
+  if (CONTRACT) return __hfma(d1, q, __hneg(m1));
+  return __hsub_rn(__hmul_rn(d1, q), m1);
+}
+
+template <int TYPE, typename out_t, bool Q4K_CONTRACT>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ w, out_t* __restrict__ y,
+                                                         int64_t n_elems) {
+  __shared__ uint64_t s_grid[TYPE == T_IQ2_XXS ? 256 : 1];
+  __shared__ uint8_t s_signs[TYPE == T_IQ2_XXS ? 128 : 1];
+  __shared__ int8_t s_kv[16];
+  if (TYPE == T_IQ4_XS) {
+    if (threadIdx.x < 16) s_kv[threadIdx.x] = d_kvalues_iq4nl[threadIdx.x];
+    __syncthreads();
+  }
+  if (TYPE == T_IQ2_XXS) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_grid[i] = d_iq2xxs_grid[i];
+    for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = d_ksigns_iq2xs[i];
+    __syncthreads();
+  }
+  constexpr int TS = BlockTraits<TYPE>::TS;
+  const int lane = threadIdx.x & 31;
+  const int64_t chunks = (n_elems + 255) / 256;  // 256 outputs per warp step
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t c = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += warps) {
+    const int64_t o = c * 256 + lane * 8;
+    if (o >= n_elems) continue;
+    __half h[8];
+    float f[8];
+    if (TYPE == T_Q4_0) {  // dequantize_q4_0: (q - 8) exactly, then one half multiply by d
+      const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
+      const __half d = __ushort_as_half((unsigned short)ldg_u16(blk));
+      const uint2 q = ldg_8_a2(blk + 2 + 8 * (lane & 1));
+      const int sh = (lane & 2) ? 4 : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        h[j] = hmul_rn(__hsub_rn(__int2half_rn((int)((byte_of(q, j) >> sh) & 0xF)), __int2half_rn(8)), d);
+      store_from_half(y + o, h);
+    } else if (TYPE == T_Q8_0) {  // dequantize_q8_0
+      const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
+      const __half d = __ushort_as_half((unsigned short)ldg_u16(blk));
+      const uint2 q = ldg_8_a2(blk + 2 + 8 * (lane & 3));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = hmul_rn(__int2half_rn((int)(int8_t)byte_of(q, j)), d);
+      store_from_half(y + o, h);
+    } else if (TYPE == T_Q4_K) {  // dequantize_block_q4_K
+      const uint8_t* blk = w + c * TS;
+      const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(blk));
+      const __half dall = __ushort_as_half((unsigned short)(dm & 0xffff)), dmin = __ushort_as_half((unsigned short)(dm >> 16));
+      const int il = lane >> 3, off = (lane & 7) * 8;       // 64-value group, offset inside it
+      const int hi = off >= 32;                               // upper nibbles belong to sub-block 2*il+1
+      const int is = 2 * il + hi;
+      const uint8_t* sc8 = blk + 4;
+      int sc, m;
+      if (is < 4) {
+        sc = __ldg(sc8 + is) & 63;
+        m = __ldg(sc8 + is + 4) & 63;
+      } else {
+        sc = (__ldg(sc8 + is + 4) & 0xF) | ((__ldg(sc8 + is - 4) >> 6) << 4);
+        m = (__ldg(sc8 + is + 4) >> 4) | ((__ldg(sc8 + is) >> 6) << 4);
+      }
+      const __half d1 = hmul_rn(dall, __int2half_rn(sc)), m1 = hmul_rn(dmin, __int2half_rn(m));
+      const uint2 q = __ldg(reinterpret_cast<const uint2*>(blk + 16 + 32 * il + (off & 31)));
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        h[j] = q4k_value<Q4K_CONTRACT>(d1, __int2half_rn((int)((byte_of(q, j) >> (4 * hi)) & 0xF)), m1);
+      store_from_half(y + o, h);
+    } else if (TYPE == T_Q6_K) {  // dequantize_block_q6_K
+      const uint8_t* blk = w + c * TS;
+      const int ip = lane >> 4, off = (lane & 15) * 8, qd = off >> 5, l0 = off & 31;
+      const uint2 ql = ldg_8_a2(blk + 64 * ip + 32 * (qd & 1) + l0);
+      const uint2 qh = ldg_8_a2(blk + 128 + 32 * ip + l0);
+      const int sc = (int)(int8_t)__ldg(blk + 192 + 8 * ip + 2 * qd + (l0 >> 4));
+      const __half d = __ushort_as_half((unsigned short)ldg_u16(blk + 208));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int lo = (byte_of(ql, j) >> (4 * (qd >> 1))) & 0xF;
+        const int hb = (byte_of(qh, j) >> (2 * qd)) & 3;
+        h[j] = hmul_rn(d, __int2half_rn(sc * ((lo | (hb << 4)) - 32)));
+      }
+      store_from_half(y + o, h);
+    } else if (TYPE == T_IQ2_XXS) {  // dequantize_block_iq2_xxs (fp32)
+      const uint8_t* blk = w + c * TS;
+      const int ib = lane >> 2, il = lane & 3;
+      const uint8_t* q2 = blk + 2 + 8 * ib;
+      const uint32_t aux32 = ldg_u16(q2 + 4) | (ldg_u16(q2 + 6) << 16);
+      const float d = __half2float(__ushort_as_half((unsigned short)ldg_u16(blk))) * (0.5f + (float)(aux32 >> 28)) * 0.25f;
+      const uint64_t grid = s_grid[__ldg(q2 + il)];
+      const uint32_t signs = s_signs[(aux32 >> (7 * il)) & 127];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        f[j] = d * (float)((uint32_t)(grid >> (8 * j)) & 0xffu) * ((signs >> j) & 1 ? -1.f : 1.f);
+      store_from_float(y + o, f);
+    } else {  // T_IQ4_XS: dequantize_block_iq4_xs (fp32)
+      const uint8_t* blk = w + c * TS;
+      const int ib = lane >> 2, off = (lane & 3) * 8, hi = off >= 16;
+      const uint32_t sh = ldg_u16(blk + 2);
+      const int ls = ((__ldg(blk + 4 + ib / 2) >> (4 * (ib & 1))) & 0xf) | (((sh >> (2 * ib)) & 3) << 4);
+      const float d = __half2float(__ushort_as_half((unsigned short)ldg_u16(blk))) * (float)(ls - 32);
+      const uint2 q = __ldg(reinterpret_cast<const uint2*>(blk + 8 + 16 * ib + (off & 15)));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = d * (float)s_kv[(byte_of(q, j) >> (4 * hi)) & 0xF];
+      store_from_float(y + o, f);
+    }
+  }
+}
+
+template <int TYPE, typename out_t>
+static int launch_t(const void* w, void* out, int64_t n, int q4k_contract, cudaStream_t s) {
+  const int64_t chunks = (n + 255) / 256;
+  int64_t ctas = (chunks + 7) / 8;
+  const int64_t cap = 148 * 8;  // 8 resident CTAs of 256 threads per SM
+  if (ctas > cap) ctas = cap;
+  if (ctas < 1) ctas = 1;
+  if (TYPE == T_Q4_K && q4k_contract)
+    dequantize_kernel<TYPE, out_t, true><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n);
+  else
+    dequantize_kernel<TYPE, out_t, false><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n);
+  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+}
+
+template <int TYPE>
+static int launch_d(const void* w, void* out, int dt, int64_t n, int c, cudaStream_t s) {
+  switch (dt) {
+    case DT_F32: return launch_t<TYPE, float>(w, out, n, c, s);
+    case DT_F16: return launch_t<TYPE, __half>(w, out, n, c, s);
+    case DT_BF16: return launch_t<TYPE, __nv_bfloat16>(w, out, n, c, s);
+  }
+  return E_BAD_DTYPE;
+}
+
+int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t n_elems, int q4k_contract,
+                      cudaStream_t stream) {
+  if (n_elems == 0) return E_OK;
+  switch (type) {
+    case T_Q4_0: return launch_d<T_Q4_0>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q8_0: return launch_d<T_Q8_0>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q4_K: return launch_d<T_Q4_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q6_K: return launch_d<T_Q6_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_IQ2_XXS: return launch_d<T_IQ2_XXS>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_IQ4_XS: return launch_d<T_IQ4_XS>(w, out, out_dtype, n_elems, q4k_contract, stream);
+  }
+  return E_BAD_TYPE;
+}
+
+}  // namespace gguf_b200

@@ -1,0 +1,165 @@
+// q8_1 activation quantization: every matmul entry point of the path first turns the
+// fp32/fp16/bf16 activations into blocks of 32 int8 values with an fp16 scale d = amax/127
+// and the fp16 sum of the unquantized inputs (reference: quantize_q8_1,
+// vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:32-69; launcher :71-85, K padded with zeros to a
+// multiple of 512).
+//
+// The values must equal the reference's bit for bit.  Two things make that so:
+//  * lane j of a warp holds element j of a block and the amax/sum reductions use the same
+//    xor-butterfly (masks 16,8,4,2,1), so the fp32 sum is accumulated in the same order;
+//  * this translation unit is compiled with --use_fast_math like the reference
+//    (setup.py:34-42), and d and q use the same expression forms (amax / 127, roundf(x / d)),
+//    so the approximate fp32 divisions are the same instructions.
+//
+// Three output layouts share one device routine:
+//   REF  : the 36-byte block_q8_1 records (what gguf_b200_quantize_q8_1 returns)
+//   SOA  : int8 qs[M][Kpad] followed by float2 ds[M][Kpad/32] -- the layout the GEMV kernels
+//          stage into shared memory with 16-byte copies.  ds.x = d (fp16 value as float);
+//          ds.y = the fp16 sum as float, or, for the Q4_K GEMV, d * sum(q) because that
+//          kernel's min term uses the quantized sum (vecdotq.cuh:342-345).
+//   F16  : x^[m][k] = half(d * q) in a K-major matrix [Mpad][ldb] for the tensor-core kernels,
+//          plus per-block correction columns appended after K (see mmq.cu).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gguf_b200 {
+
+struct Q8Lane {
+  float d;     // fp32 scale before fp16 rounding (the quantity q was divided by)
+  float sum;   // fp32 butterfly sum of the 32 inputs
+  int q;       // this lane's int8 code
+};
+
+__device__ __forceinline__ Q8Lane quantize_lane(float xi) {
+  float amax = fabsf(xi);
+  float sum = xi;
+#pragma unroll
+  for (int mask = 16; mask > 0; mask >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask, 32));
+    sum += __shfl_xor_sync(0xffffffffu, sum, mask, 32);
+  }
+  Q8Lane r;
+  r.d = amax / 127;
+  const int8_t q = amax == 0.0f ? 0 : roundf(xi / r.d);
+  r.q = q;
+  r.sum = sum;
+  return r;
+}
+
+// gather the four int8 codes of lanes 4i..4i+3 into one word held by lane 4i
+__device__ __forceinline__ uint32_t pack4(int q, int lane) {
+  uint32_t b = (uint32_t)q & 0xffu;
+  uint32_t b1 = __shfl_down_sync(0xffffffffu, b, 1);
+  uint32_t b2 = __shfl_down_sync(0xffffffffu, b, 2);
+  uint32_t b3 = __shfl_down_sync(0xffffffffu, b, 3);
+  (void)lane;
+  return b | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+
+template <typename in_t, int MODE>
+__global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restrict__ x, uint8_t* __restrict__ out,
+                                                            int64_t M, int64_t K, int64_t kpad, int sum_mode,
+                                                            int64_t ldb, int corr_mode, const int32_t* __restrict__ gather_ids,
+                                                            int64_t gather_div, int64_t gather_limit) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nbr = kpad / 32;                                   // blocks per row
+  const int64_t total = M * nbr;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); b < total; b += warps) {
+    const int64_t row = b / nbr, kb = b - row * nbr;
+    const int64_t k = kb * 32 + lane;
+    // F16 mode may gather: output row `row` takes input row gather_ids[row] / gather_div
+    // (MoE: sorted slot -> token); ids at or beyond gather_limit are padding and give a zero row.
+    int64_t src = row;
+    bool have = true;
+    if (MODE == Q8_MODE_F16 && gather_ids) {
+      const int64_t id = gather_ids[row];
+      have = id >= 0 && id < gather_limit;
+      src = have ? id / gather_div : 0;
+    }
+    const float xi = (have && k < K) ? to_float<in_t>(x[src * K + k]) : 0.0f;
+    const Q8Lane r = quantize_lane(xi);
+    const __half hd = __float2half(r.d), hs = __float2half(r.sum);
+    if (MODE == Q8_MODE_REF) {
+      uint8_t* blk = out + b * 36;
+      blk[4 + lane] = (uint8_t)r.q;
+      if (lane == 0) {
+        *reinterpret_cast<__half*>(blk) = hd;
+        *reinterpret_cast<__half*>(blk + 2) = hs;
+      }
+    } else if (MODE == Q8_MODE_SOA) {
+      const uint32_t w = pack4(r.q, lane);
+      if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(out + row * kpad + kb * 32 + lane) = w;
+      int qs = r.q;
+#pragma unroll
+      for (int mask = 16; mask > 0; mask >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, mask);
+      if (lane == 0) {
+        const float d8 = __half2float(hd);
+        float2 ds;
+        ds.x = d8;
+        ds.y = sum_mode ? d8 * (float)qs : __half2float(hs);
+        reinterpret_cast<float2*>(out + M * kpad)[b] = ds;
+      }
+    } else {  // Q8_MODE_F16: B operand of the tensor-core kernels
+      __half* xb = reinterpret_cast<__half*>(out);
+      const float d8 = __half2float(hd);
+      xb[row * ldb + k] = __float2half_rn(d8 * (float)r.q);
+      if (corr_mode != CORR_NONE) {
+        int qs = r.q;
+#pragma unroll
+        for (int mask = 16; mask > 0; mask >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, mask);
+        if (lane == 0) {
+          // the reference's tiled kernels subtract (weight offset) * s8, with s8 the fp16 sum of
+          // the unquantized inputs (vecdotq.cuh:61-64, :369-372).  The tensor-core product already
+          // contains (offset-free part) . x^; the appended column carries what is left.
+          const float s8 = __half2float(hs);
+          float c;
+          if (corr_mode == CORR_Q4_0) c = 8.0f * (d8 * (float)qs - s8);  // weights stored as (q-8): add back 8*d*(d8*sum(q) - s8)
+          else c = -s8;                                                  // CORR_MIN: minus min * s8
+          xb[row * ldb + kpad + kb] = __float2half_rn(c);
+        }
+        // zero the tail of the correction area so that padded contraction columns contribute nothing
+        if (kb == 0)
+          for (int64_t c = kpad + nbr + lane; c < ldb; c += 32) xb[row * ldb + c] = __float2half_rn(0.f);
+      }
+    }
+  }
+}
+
+template <int MODE>
+static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int sum_mode, int64_t ldb,
+                       int corr_mode, const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream) {
+  if (M <= 0 || K <= 0) return M < 0 || K < 0 ? E_BAD_SHAPE : E_OK;
+  const int64_t kpad = round_up(K, 512);
+  const int64_t total = M * (kpad / 32);
+  const int blocks = (int)((total + 7) / 8 > 148 * 16 ? 148 * 16 : (total + 7) / 8);
+  uint8_t* o = static_cast<uint8_t*>(out);
+  switch (x_dtype) {
+    case DT_F32:
+      quantize_q8_1_kernel<float, MODE><<<blocks, 256, 0, stream>>>((const float*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      break;
+    case DT_F16:
+      quantize_q8_1_kernel<__half, MODE><<<blocks, 256, 0, stream>>>((const __half*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      break;
+    case DT_BF16:
+      quantize_q8_1_kernel<__nv_bfloat16, MODE><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      break;
+    default:
+      return E_BAD_DTYPE;
+  }
+  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+}
+
+int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
+                         int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
+                         cudaStream_t stream) {
+  switch (mode) {
+    case Q8_MODE_REF: return launch_mode<Q8_MODE_REF>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
+    case Q8_MODE_SOA: return launch_mode<Q8_MODE_SOA>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
+    case Q8_MODE_F16:
+      return launch_mode<Q8_MODE_F16>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, gather_ids, gather_div, gather_limit, stream);
+  }
+  return E_BAD_SHAPE;
+}
+
+}  // namespace gguf_b200

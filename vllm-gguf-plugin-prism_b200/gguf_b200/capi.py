@@ -1,0 +1,140 @@
+"""ctypes binding of the C-ABI (include/gguf_b200.h) for callers that hold torch tensors.
+
+This is the thinnest possible host layer: torch provides device memory and the current
+stream, every computation is one call into ``libgguf_b200.so``.  The parity tests call the
+kernels through this module so that what they exercise is the exported C interface itself.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "vllm_gguf_plugin" / "libgguf_b200.so"
+_lib = None
+
+F32, F16, BF16 = 0, 1, 2
+OP_GEMV, OP_MMQ, OP_MOE, OP_MOE_VEC, OP_DEQUANT_MATMUL = range(5)
+_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+# name -> (restype, argtypes); mirrors include/gguf_b200.h one to one
+_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+SIGNATURES = {
+    "gguf_b200_error_string": (ctypes.c_char_p, [_I]),
+    "gguf_b200_version": (ctypes.c_char_p, []),
+    "gguf_b200_type_size": (_I, [_I]),
+    "gguf_b200_block_size": (_I, [_I]),
+    "gguf_b200_q8_1_row_bytes": (_L, [_L]),
+    "gguf_b200_quantize_q8_1": (_I, [_P, _I, _P, _L, _L, _P]),
+    "gguf_b200_dequantize": (_I, [_P, _I, _P, _I, _L, _P]),
+    "gguf_b200_workspace_bytes": (_L, [_I, _I, _L, _L, _L]),
+    "gguf_b200_mul_mat_vec_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
+    "gguf_b200_mul_mat_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
+    "gguf_b200_dequant_matmul": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
+    "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
+    "gguf_b200_moe_a8_vec": (_I, [_P, _P, _P, _P, _L, _P, _L, _I, _I, _L, _L, _L, _L, _P]),
+    "gguf_b200_moe_block_size": (_I, [_I]),
+    "gguf_b200_last_status": (_I, []),
+    "gguf_b200_set_q4k_contract": (None, [_I]),
+}
+
+
+class GgufB200Error(RuntimeError):
+    def __init__(self, code: int, op: str):
+        self.code = code
+        super().__init__(f"{op} failed ({code}): {lib().gguf_b200_error_string(code).decode()}")
+
+
+def lib():
+    """Load libgguf_b200.so (raises if it has not been built: there is no fallback)."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(f"{_LIB_PATH} is not built; run gguf_b200/build.py")
+        l = ctypes.CDLL(str(_LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            if hasattr(l, name):
+                fn = getattr(l, name)
+                fn.restype, fn.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+def _check(rc: int, op: str):
+    if rc != 0:
+        raise GgufB200Error(rc, op)
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ws(like: torch.Tensor, nbytes: int) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=like.device)
+
+
+def k_of(W: torch.Tensor, qtype: int) -> int:
+    return W.shape[-1] // lib().gguf_b200_type_size(qtype) * lib().gguf_b200_block_size(qtype)
+
+
+def quantize_q8_1(X: torch.Tensor) -> torch.Tensor:
+    M, K = X.shape
+    out = torch.empty((M, lib().gguf_b200_q8_1_row_bytes(K)), dtype=torch.uint8, device=X.device)
+    _check(lib().gguf_b200_quantize_q8_1(X.data_ptr(), _DT[X.dtype], out.data_ptr(), M, K, _stream(X)), "quantize_q8_1")
+    return out
+
+
+def dequantize(W: torch.Tensor, qtype: int, m: int, n: int, dtype=torch.float16) -> torch.Tensor:
+    out = torch.empty((m, n), dtype=dtype, device=W.device)
+    _check(lib().gguf_b200_dequantize(W.data_ptr(), qtype, out.data_ptr(), _DT[dtype], m * n, _stream(W)), "dequantize")
+    return out
+
+
+def _matmul(fn_name: str, op: int, W: torch.Tensor, X: torch.Tensor, qtype: int, N: int) -> torch.Tensor:
+    M, K = X.shape
+    Y = torch.empty((M, N), dtype=X.dtype, device=X.device)
+    nbytes = lib().gguf_b200_workspace_bytes(op, qtype, M, N, K)
+    ws = _ws(X, nbytes)
+    fn = getattr(lib(), fn_name)
+    _check(fn(W.data_ptr(), X.data_ptr(), Y.data_ptr(), ws.data_ptr(), nbytes, qtype, _DT[X.dtype], M, N, K, _stream(X)), fn_name)
+    return Y
+
+
+def mul_mat_vec_a8(W, X, qtype, N):
+    return _matmul("gguf_b200_mul_mat_vec_a8", OP_GEMV, W, X, qtype, N)
+
+
+def mul_mat_a8(W, X, qtype, N):
+    return _matmul("gguf_b200_mul_mat_a8", OP_MMQ, W, X, qtype, N)
+
+
+def dequant_matmul(W, X, qtype, N):
+    return _matmul("gguf_b200_dequant_matmul", OP_DEQUANT_MATMUL, W, X, qtype, N)
+
+
+def moe_a8(X, W, sorted_ids, expert_ids, n_post_pad, qtype, N, top_k, tokens):
+    K = X.shape[1]
+    Y = torch.empty((tokens * top_k, N), dtype=X.dtype, device=X.device)
+    n_sorted = sorted_ids.numel()
+    nbytes = lib().gguf_b200_workspace_bytes(OP_MOE, qtype, n_sorted, N, K)
+    ws = _ws(X, nbytes)
+    _check(lib().gguf_b200_moe_a8(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), nbytes, sorted_ids.data_ptr(),
+                                  expert_ids.data_ptr(), n_post_pad.data_ptr(), n_sorted, W.stride(0), qtype,
+                                  _DT[X.dtype], tokens, top_k, N, K, _stream(X)), "moe_a8")
+    return Y
+
+
+def moe_a8_vec(X, W, topk_ids, top_k, qtype, N, tokens):
+    K = X.shape[1]
+    Y = torch.empty((tokens * top_k, N), dtype=X.dtype, device=X.device)
+    nbytes = lib().gguf_b200_workspace_bytes(OP_MOE_VEC, qtype, tokens, N, K)
+    ws = _ws(X, nbytes)
+    _check(lib().gguf_b200_moe_a8_vec(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), nbytes,
+                                      topk_ids.data_ptr(), W.shape[0], qtype, _DT[X.dtype], tokens, top_k, N, K,
+                                      _stream(X)), "moe_a8_vec")
+    return Y
+
+
+def last_status() -> int:
+    return lib().gguf_b200_last_status()
