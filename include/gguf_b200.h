@@ -69,6 +69,17 @@ int64_t gguf_b200_workspace_bytes(int op, int type, int64_t M, int64_t N, int64_
 int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
                              int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* The two halves of gguf_b200_mul_mat_vec_a8, for callers that multiply the same activations
+ * by several weight matrices (q/k/v, gate/up): quantize once into `workspace`, then run any
+ * number of GEMVs on it.
+ * Replace: the quantize_row_q8_1_cuda call (gguf_kernel.cu:116-118) and the per-type kernel
+ * switch (gguf_kernel.cu:119-215) of ggml_mul_mat_vec_a8 respectively.  `type` matters to the
+ * first half only in that Q4_K needs a different sum term than the other types. */
+int gguf_b200_gemv_prepare(const void* X, int dtype, void* workspace, int64_t workspace_bytes, int type,
+                           int64_t M, int64_t K, void* stream);
+int gguf_b200_gemv_prepared(const void* W, const void* workspace, void* Y, int type, int dtype,
+                            int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Prefill GEMM on tensor cores (same q8_1-quantized activations).
  * Replaces: ggml_mul_mat_a8, gguf_kernel.cu:220-290 (+ mmq.cuh).  Types 2, 8, 12, 14. */
 int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
@@ -83,7 +94,7 @@ int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* worksp
 /* MoE expert GEMM over expert-sorted token blocks.
  * Replaces: ggml_moe_a8, gguf_kernel.cu:292-393 (+ moe.cuh:5-129).
  *   X [tokens][K]; W [E][N][K/QK*type_size] with expert_stride_bytes between experts;
- *   sorted_token_ids[n_sorted], expert_ids[n_sorted/block], num_tokens_post_padded[1] on device,
+ *   sorted_token_ids[n_sorted], expert_ids[ceil(n_sorted/block)], num_tokens_post_padded[1] on device,
  *   as produced by moe_align_block_size with block = gguf_b200_moe_block_size(type);
  *   Y [tokens*top_k][N]: row t = sorted id; rows that receive no token are set to zero. */
 int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* workspace, int64_t workspace_bytes,

@@ -99,14 +99,28 @@ static uint16_t s2h(i128 v) {
   return sign | (uint16_t)(((e + 15) << 10) | ((int)q & 1023));
 }
 
+/* IEEE sign of an exact zero: a product keeps the xor of the signs; a sum of two zeros of
+ * equal sign keeps it, any other exact cancellation gives +0 (round-to-nearest). */
 static uint16_t hmul(uint16_t a, uint16_t b) { /* one rounding, like mul.f16 */
   i128 pa = h2s(a) >> 24, pb = h2s(b) >> 24;   /* back to units of 2^-24 each */
-  return s2h(pa * pb);
+  i128 p = pa * pb;
+  if (p == 0) return (uint16_t)((a ^ b) & 0x8000);
+  return s2h(p);
 }
-static uint16_t hsub(uint16_t a, uint16_t b) { return s2h(h2s(a) - h2s(b)); }
+static uint16_t hsub(uint16_t a, uint16_t b) {
+  i128 v = h2s(a) - h2s(b);
+  if (v == 0) return (uint16_t)(((a & 0x8000) && !(b & 0x8000)) ? 0x8000 : 0); /* (-0) - (+0) = -0 */
+  return s2h(v);
+}
 static uint16_t hfms(uint16_t a, uint16_t b, uint16_t c) { /* a*b - c with a single rounding */
   i128 pa = h2s(a) >> 24, pb = h2s(b) >> 24;
-  return s2h(pa * pb - h2s(c));
+  i128 v = pa * pb - h2s(c);
+  if (v == 0) {
+    const int sp = ((a ^ b) & 0x8000) != 0, sc = !(c & 0x8000); /* signs of the product and of -c */
+    const int both_zero = (pa * pb == 0);
+    return (uint16_t)((both_zero && sp && sc) ? 0x8000 : 0);
+  }
+  return s2h(v);
 }
 static uint16_t i2h(int v) { return s2h((i128)v << 48); } /* __int2half_rn */
 

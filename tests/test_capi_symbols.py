@@ -1,0 +1,83 @@
+"""CPU: the C-ABI library builds, loads, exports every declared symbol and validates arguments
+(no kernel is launched here)."""
+import ctypes
+import re
+
+from helpers import ROOT
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "gguf_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gguf_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(native_libs):
+    lib = ctypes.CDLL(str(native_libs[0]))
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/gguf_b200.h but not exported"
+
+
+def test_binding_table_covers_the_header(native_libs):
+    from gguf_b200 import capi
+
+    assert set(declared_symbols()) == set(capi.SIGNATURES)
+
+
+def test_geometry_and_error_codes(native_libs):
+    from gguf_b200 import capi
+
+    lib = capi.lib()
+    sizes = {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210), 16: (256, 66), 23: (256, 136)}
+    for t, (bs, ts) in sizes.items():
+        assert lib.gguf_b200_block_size(t) == bs and lib.gguf_b200_type_size(t) == ts
+    assert lib.gguf_b200_type_size(3) == 0
+    assert lib.gguf_b200_q8_1_row_bytes(1024) == 1024 // 32 * 36
+    assert lib.gguf_b200_q8_1_row_bytes(800) == 1024 // 32 * 36
+    assert lib.gguf_b200_moe_block_size(2) == 64 and lib.gguf_b200_moe_block_size(16) == 0
+    assert lib.gguf_b200_workspace_bytes(capi.OP_GEMV, 12, 2, 0, 4096) == 2 * 4096 + 2 * 128 * 8
+    assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 8, 4, 0, 1024) == 4 * 1024 * 2
+    assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 12, 4, 0, 1024) == 4 * (1024 + 64) * 2
+    # argument validation happens before any CUDA call
+    null = ctypes.c_void_p(0)
+    p = ctypes.c_void_p(4096)
+    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 3, 1, 1, 8, 256, null) == -1   # type
+    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 12, 7, 1, 8, 256, null) == -2  # dtype
+    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 12, 1, 1, 8, 100, null) == -3  # K % 256
+    assert lib.gguf_b200_mul_mat_vec_a8(null, p, p, p, 1 << 20, 12, 1, 1, 8, 256, null) == -4
+    assert lib.gguf_b200_mul_mat_vec_a8(ctypes.c_void_p(4100), p, p, p, 1 << 20, 12, 1, 1, 8, 256, null) == -4  # alignment
+    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 16, 12, 1, 1, 8, 256, null) == -5       # workspace
+    assert lib.gguf_b200_mul_mat_a8(p, p, p, p, 1 << 20, 16, 1, 1, 8, 256, null) == -1      # IQ has no q8_1 GEMM
+    assert lib.gguf_b200_dequant_matmul(p, p, p, p, 0, 12, 1, 1, 8, 256, null) == -1
+    assert lib.gguf_b200_dequant_matmul(p, p, p, p, 0, 16, 0, 1, 8, 256, null) == -2        # fp32 not fused
+    assert lib.gguf_b200_dequantize(p, 12, p, 1, 100, null) == -3
+    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 0, 12, 1, 0, 8, 256, null) == 0          # empty batch
+    assert b"workspace" in lib.gguf_b200_error_string(-5)
+
+
+def test_ops_module_fails_loudly_without_extension(tmp_path, monkeypatch):
+    """The product path has no fallback: importing ops next to a missing extension raises."""
+    import importlib
+    import shutil
+    import sys
+
+    pkg = tmp_path / "vllm_gguf_plugin"
+    pkg.mkdir()
+    src = ROOT / "vllm-gguf-plugin-prism_b200" / "vllm_gguf_plugin"
+    shutil.copy(src / "ops.py", pkg / "ops.py")
+    (pkg / "__init__.py").write_text("")
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k.split(".")[0] == "vllm_gguf_plugin"}
+    monkeypatch.syspath_prepend(str(tmp_path))
+    try:
+        try:
+            importlib.import_module("vllm_gguf_plugin.ops")
+            raised = False
+        except ImportError as e:
+            raised = "not built" in str(e)
+        assert raised
+    finally:
+        for k in [k for k in sys.modules if k.split(".")[0] == "vllm_gguf_plugin"]:
+            del sys.modules[k]
+        sys.modules.update(saved)

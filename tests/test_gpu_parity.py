@@ -1,0 +1,348 @@
+"""GPU parity tests: every kernel through the C-ABI (gguf_b200.capi -> libgguf_b200.so)
+against the CPU oracle, and -- when oracle/_ref/_C_gguf_ref.so was built -- against the
+reference plugin's own CUDA kernels on the same inputs.
+
+Bars: dequantize and q8_1 quantization bit-exact; matmul outputs within relative L2 2e-3
+(REL_L2_TOL) of the reference kernel of the same entry point."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import MMQ_TYPES, REL_L2_TOL, TYPES, RefCuda, bits, np_act, rel_l2
+
+from gguf_b200 import capi, synth
+from oracle import cpu
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ref(native_libs):
+    return RefCuda()
+
+
+def dev_w(t, n, k, seed):
+    w = synth.make_weight(t, n, k, seed=seed)
+    return w, torch.from_numpy(w).to(DEV)
+
+
+def dev_x(m, k, seed, dtype=torch.float16):
+    x = torch.from_numpy(synth.make_activation(m, k, seed=seed, dtype=np.float32)).to(DEV).to(dtype)
+    return x
+
+
+# ---------------------------------------------------------------- q8_1 quantization ----------
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(1, 1024), (3, 4096), (7, 800), (64, 14336)])
+def test_quantize_q8_1_bit_exact(ref, dtype, shape):
+    M, K = shape
+    x = dev_x(M, K, seed=M, dtype=dtype)
+    if M >= 3:
+        x[1] = 0                    # all-zero blocks
+        x[2, :64] = 1.5             # all-equal blocks
+    got = capi.quantize_q8_1(x)
+    torch.cuda.synchronize()
+    if ref.available:
+        assert torch.equal(got, ref.quantize_q8_1(x)), "differs from the reference kernel"
+    # CPU oracle: IEEE division where the GPU build uses the fast-math approximation, so codes may
+    # differ by one step at exact ties and d by one fp16 ulp; anything else is a bug.
+    xa, dn = np_act(x)
+    want = cpu.quantize_q8_1(xa, dn).reshape(M, -1, 36)
+    g = got.cpu().numpy().reshape(M, -1, 36)
+    dq = g[..., 4:].view(np.int8).astype(np.int32) - want[..., 4:].view(np.int8).astype(np.int32)
+    assert np.abs(dq).max() <= 1
+    assert (dq != 0).mean() < 2e-3
+    dd = g[..., 0:2].copy().view(np.int16).astype(np.int32) - want[..., 0:2].copy().view(np.int16).astype(np.int32)
+    assert np.abs(dd).max() <= 1
+    assert np.array_equal(g[..., 2:4], want[..., 2:4]), "block sums must match exactly (same butterfly order)"
+
+
+# ---------------------------------------------------------------- dequantize -----------------
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("name", TYPES)
+def test_dequantize_bit_exact(ref, name, dtype):
+    t = TYPES[name]
+    N, K = 96, 2048
+    wn, w = dev_w(t, N, K, seed=t)
+    got = capi.dequantize(w, t, N, K, dtype)
+    torch.cuda.synchronize()
+    dn = str(dtype).split(".")[1]
+    want = cpu.dequantize(wn, t, N * K, dn)
+    want_t = torch.from_numpy(want.view(np.int32) if dn == "float32" else want.view(np.int16)).reshape(N, K)
+    assert torch.equal(bits(got).cpu(), want_t), "differs from the CPU oracle"
+    if ref.available:
+        r = ref.ops.ggml_dequantize(w, t, N, K, dtype)
+        assert torch.equal(bits(got), bits(r)), "differs from the reference kernel"
+
+
+def test_dequantize_ragged_counts(ref):
+    """Element counts that are not a multiple of the 256-value warp step (32-value blocks)."""
+    for name in ("Q4_0", "Q8_0"):
+        t = TYPES[name]
+        wn, w = dev_w(t, 1, 32 * 11, seed=3)
+        got = capi.dequantize(w, t, 1, 32 * 11, torch.float16)
+        want = cpu.dequantize(wn, t, 32 * 11, "float16")
+        assert np.array_equal(got.cpu().numpy().view(np.uint16).reshape(-1), want)
+    with pytest.raises(capi.GgufB200Error):
+        capi.dequantize(w, 12, 1, 100, torch.float16)
+
+
+def test_q4k_contraction_knob_selects_oracle_mode():
+    wn, w = dev_w(12, 16, 1024, seed=9)
+    try:
+        for mode in (0, 1):
+            capi.lib().gguf_b200_set_q4k_contract(mode)
+            got = capi.dequantize(w, 12, 16, 1024, torch.float16).cpu().numpy().view(np.uint16).reshape(-1)
+            assert np.array_equal(got, cpu.dequantize(wn, 12, 16 * 1024, "float16", q4k_contract=mode))
+    finally:
+        capi.lib().gguf_b200_set_q4k_contract(1)
+
+
+# ---------------------------------------------------------------- GEMV -----------------------
+
+GEMV_SHAPES = [(3072, 1024, 1), (520, 4096, 1), (257, 2048, 3), (128, 14336, 2), (96, 28672, 1), (64, 3584, 8), (40, 4096, 11)]
+
+
+@pytest.mark.parametrize("shape", GEMV_SHAPES)
+@pytest.mark.parametrize("name", TYPES)
+def test_gemv_parity(ref, name, shape):
+    t = TYPES[name]
+    N, K, M = shape
+    if K % synth.QUANT_SIZES[t][0]:
+        pytest.skip("K not a multiple of the block size")
+    wn, w = dev_w(t, N, K, seed=t + N)
+    x = dev_x(M, K, seed=M)
+    y = capi.mul_mat_vec_a8(w, x, t, N)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    if ref.available:
+        r = ref.ops.ggml_mul_mat_vec_a8(w, x, t, N)
+        assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+        assert rel_l2(y.float().cpu(), r.float().cpu()) <= 1e-4   # in practice: same formulas, fp32 noise
+    if N * K * M <= 16e6:
+        y64, _ = cpu.matmul_a8(wn, t, x.cpu().numpy(), "float16", mmq=False)
+        assert rel_l2(y.float().cpu().numpy(), y64) <= 1e-3       # fp16 output rounding + rare q8_1 tie flips
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemv_other_dtypes(ref, dtype):
+    for name in ("Q4_K", "IQ2_XXS", "Q6_K"):
+        t = TYPES[name]
+        wn, w = dev_w(t, 300, 2048, seed=1)
+        x = dev_x(2, 2048, seed=2, dtype=dtype)
+        y = capi.mul_mat_vec_a8(w, x, t, 300)
+        assert y.dtype == dtype
+        xa, dn = np_act(x)
+        y64, _ = cpu.matmul_a8(wn, t, xa, dn, mmq=False)
+        tol = 1e-5 if dtype == torch.float32 else 5e-3
+        # a q8_1 tie flip (fast-math division) moves one product term: allow it in the fp32 case
+        assert rel_l2(y.float().cpu().numpy(), y64) <= max(tol, 2e-4)
+        if ref.available:
+            r = ref.ops.ggml_mul_mat_vec_a8(w, x, t, 300)
+            assert rel_l2(y.float().cpu(), r.float().cpu()) <= (1e-5 if dtype == torch.float32 else REL_L2_TOL)
+
+
+def test_gemv_empty_and_prepared_split():
+    t = 12
+    wn, w = dev_w(t, 64, 1024, seed=4)
+    assert capi.mul_mat_vec_a8(w, torch.empty((0, 1024), dtype=torch.float16, device=DEV), t, 64).shape == (0, 64)
+    x = dev_x(2, 1024, seed=4)
+    ws = capi.gemv_prepare(x, t)
+    a = capi.gemv_prepared(w, ws, t, 2, 64, 1024)
+    b = capi.mul_mat_vec_a8(w, x, t, 64)
+    assert torch.equal(a, b)
+
+
+def test_gemv_is_deterministic_and_linear_at_full_size():
+    """Full benchmark size (Q4_K 14336x4096): run twice -> identical bits; scaling the weight
+    scales d by 2 (exact in fp16) must scale the output by exactly 2."""
+    t, N, K = 12, 14336, 4096
+    wn = synth.make_weight(t, N, K, seed=0)
+    w = torch.from_numpy(wn).to(DEV)
+    x = dev_x(1, K, seed=0, dtype=torch.float32)
+    y1 = capi.mul_mat_vec_a8(w, x, t, N)
+    y2 = capi.mul_mat_vec_a8(w, x, t, N)
+    assert torch.equal(y1, y2)
+    blocks = wn.reshape(-1, 144).copy()
+    d = blocks[:, 0:4].copy().view(np.float16) * np.float16(2)
+    blocks[:, 0:4] = d.view(np.uint8)
+    y3 = capi.mul_mat_vec_a8(torch.from_numpy(blocks.reshape(N, -1)).to(DEV), x, t, N)
+    assert torch.equal(y3, 2 * y1)
+
+
+# ---------------------------------------------------------------- tensor-core GEMM -----------
+
+MMQ_SHAPES = [(256, 1024, 16), (1000, 2048, 7), (384, 4096, 83), (512, 2048, 130), (300, 1024, 512), (128, 14336, 33)]
+
+
+@pytest.mark.parametrize("shape", MMQ_SHAPES)
+@pytest.mark.parametrize("name", MMQ_TYPES)
+def test_mmq_parity(ref, name, shape):
+    t = TYPES[name]
+    N, K, M = shape
+    wn, w = dev_w(t, N, K, seed=t + M)
+    x = dev_x(M, K, seed=M)
+    y = capi.mul_mat_a8(w, x, t, N)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert not torch.isnan(y).any()
+    if ref.available:
+        r = ref.ops.ggml_mul_mat_a8(w, x, t, N)
+        assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+    if N * K * M <= 2.2e8:
+        y64, _ = cpu.matmul_a8(wn, t, x.cpu().numpy(), "float16", mmq=True)
+        assert rel_l2(y.float().cpu().numpy(), y64) <= REL_L2_TOL
+
+
+def test_mmq_block_multiple_of_32_but_not_64():
+    """K = 32 * odd: the last 64-wide contraction slab is half padding."""
+    for name in ("Q4_0", "Q8_0"):
+        t = TYPES[name]
+        wn, w = dev_w(t, 130, 32 * 37, seed=2)
+        x = dev_x(20, 32 * 37, seed=2)
+        y = capi.mul_mat_a8(w, x, t, 130)
+        y64, _ = cpu.matmul_a8(wn, t, x.cpu().numpy(), "float16", mmq=True)
+        assert rel_l2(y.float().cpu().numpy(), y64) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mmq_other_dtypes(dtype):
+    t = 12
+    wn, w = dev_w(t, 200, 1024, seed=8)
+    x = dev_x(40, 1024, seed=8, dtype=dtype)
+    y = capi.mul_mat_a8(w, x, t, 200)
+    assert y.dtype == dtype
+    xa, dn = np_act(x)
+    y64, _ = cpu.matmul_a8(wn, t, xa, dn, mmq=True)
+    assert rel_l2(y.float().cpu().numpy(), y64) <= (REL_L2_TOL if dtype == torch.float32 else 6e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ4_XS"])
+def test_dequant_matmul_parity(ref, name, dtype):
+    """IQ types above the GEMV threshold: the reference dequantizes and calls a dense matmul."""
+    t = TYPES[name]
+    for (N, K, M) in [(256, 1024, 16), (1000, 2048, 40), (384, 4096, 128)]:
+        wn, w = dev_w(t, N, K, seed=N)
+        x = dev_x(M, K, seed=M, dtype=dtype)
+        y = capi.dequant_matmul(w, x, t, N)
+        torch.cuda.synchronize()
+        assert capi.last_status() == 0
+        wd = capi.dequantize(w, t, N, K, dtype)
+        want = x @ wd.T                                    # the reference's second step
+        assert rel_l2(y.float().cpu(), want.float().cpu()) <= REL_L2_TOL
+        if ref.available:
+            r = x @ ref.ops.ggml_dequantize(w, t, N, K, dtype).T
+            assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+        dq = cpu.as_float(cpu.dequantize(wn, t, N * K, "float32"), "float32").reshape(N, K)
+        xa, dn = np_act(x)
+        y64 = cpu.dense_matmul(dq, xa, dn)
+        assert rel_l2(y.float().cpu().numpy(), y64) <= (REL_L2_TOL if dtype == torch.float16 else 6e-3)
+
+
+# ---------------------------------------------------------------- MoE ------------------------
+
+def moe_case(t, E, N, K, T, top_k, seed):
+    w = np.stack([synth.make_weight(t, N, K, seed=seed + e) for e in range(E)])
+    x = synth.make_activation(T, K, seed=seed)
+    tw, ids = synth.make_routing(T, E, top_k, seed)
+    return w, x, tw, ids
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_K", "Q8_0"])
+def test_moe_a8_parity(ref, name):
+    t = TYPES[name]
+    E, N, K, T, top_k = 8, 192, 1024, 70, 2
+    wn, xn, _, ids = moe_case(t, E, N, K, T, top_k, seed=11)
+    w, x = torch.from_numpy(wn).to(DEV), torch.from_numpy(xn).to(DEV)
+    blk = capi.lib().gguf_b200_moe_block_size(t)
+    s, e, n = synth.moe_align_block_size(ids, blk, E)
+    y = capi.moe_a8(x, w, torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV), t, N, top_k, T)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    y64, _ = cpu.moe_a8(wn, t, xn, s, e, int(n[0]), blk, top_k, T)
+    assert rel_l2(y.float().cpu().numpy(), y64) <= REL_L2_TOL
+    if ref.available:
+        s4, e4, n4 = synth.moe_align_block_size(ids, 4, E)   # the reference's own block size
+        r = ref.ops.ggml_moe_a8(x, w, torch.from_numpy(s4).to(DEV), torch.from_numpy(e4).to(DEV),
+                                torch.from_numpy(n4).to(DEV), t, N, top_k, T)
+        assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+
+
+def test_moe_a8_padding_rows_are_zero_and_bad_experts_skipped():
+    t, E, N, K, T, top_k = 2, 4, 128, 512, 20, 2
+    wn, xn, _, ids = moe_case(t, E, N, K, T, top_k, seed=5)
+    w, x = torch.from_numpy(wn).to(DEV), torch.from_numpy(xn).to(DEV)
+    blk = capi.lib().gguf_b200_moe_block_size(t)
+    s, e, n = synth.moe_align_block_size(ids, blk, E)
+    e_bad = e.copy()
+    e_bad[0] = 300                                           # expert id outside [0, 255]: block skipped
+    y = capi.moe_a8(x, w, torch.from_numpy(s).to(DEV), torch.from_numpy(e_bad).to(DEV), torch.from_numpy(n).to(DEV), t, N, top_k, T)
+    y64, _ = cpu.moe_a8(wn, t, xn, s, e_bad, int(n[0]), blk, top_k, T)
+    assert rel_l2(y.float().cpu().numpy(), y64) <= REL_L2_TOL
+    skipped = s[:blk][s[:blk] < T * top_k]
+    assert float(y[torch.from_numpy(skipped).long().to(DEV)].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q6_K", "IQ4_XS"])
+def test_moe_a8_vec_parity(ref, name):
+    t = TYPES[name]
+    E, N, K, T, top_k = 8, 160, 1024, 6, 3
+    wn, xn, _, ids = moe_case(t, E, N, K, T, top_k, seed=21)
+    w, x = torch.from_numpy(wn).to(DEV), torch.from_numpy(xn).to(DEV)
+    idt = torch.from_numpy(ids).to(DEV).contiguous()
+    y = capi.moe_a8_vec(x, w, idt, top_k, t, N, T)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    y64, _ = cpu.moe_a8_vec(wn, t, xn, ids, top_k, T)
+    assert rel_l2(y.float().cpu().numpy(), y64) <= 1e-3
+    if ref.available:
+        r = ref.ops.ggml_moe_a8_vec(x, w, idt, top_k, t, N, T)
+        assert rel_l2(y.float().cpu(), r.float().cpu()) <= 1e-4
+
+
+# ---------------------------------------------------------------- operator API (torch library) --
+
+def test_ops_api_equals_capi_and_dispatcher_end_to_end():
+    from vllm_gguf_plugin import ops
+    from vllm_gguf_plugin.quantization import linear
+
+    for name, t in TYPES.items():
+        wn, w = dev_w(t, 256, 1024, seed=t)
+        x1, x64 = dev_x(1, 1024, seed=1), dev_x(64, 1024, seed=2)
+        assert torch.equal(ops.ggml_mul_mat_vec_a8(w, x1, t, 256), capi.mul_mat_vec_a8(w, x1, t, 256))
+        assert torch.equal(ops.ggml_dequantize(w, t, 256, 1024, torch.float16), capi.dequantize(w, t, 256, 1024))
+        y = linear._fused_mul_mat_gguf(x64, w, t)
+        want = capi.mul_mat_a8(w, x64, t, 256) if name in MMQ_TYPES else capi.dequant_matmul(w, x64, t, 256)
+        assert torch.equal(y, want)
+    with pytest.raises(NotImplementedError):
+        ops.ggml_mul_mat_vec_a8(w, x1, 3, 256)
+    with pytest.raises(RuntimeError):
+        ops.ggml_mul_mat_vec_a8(w[:, :-1].contiguous(), x1, 23, 256)      # not a whole number of blocks
+
+
+def test_fused_moe_dispatcher_matches_dense_experts():
+    from vllm_gguf_plugin.quantization import fused_moe
+
+    t, E, H, I, T, top_k = 2, 8, 512, 256, 96, 2
+    w13n = np.stack([synth.make_weight(t, 2 * I, H, seed=e) for e in range(E)])
+    w2n = np.stack([synth.make_weight(t, H, I, seed=100 + e) for e in range(E)])
+    x = dev_x(T, H, seed=3)
+    tw, ids = synth.make_routing(T, E, top_k, 3)
+    w13, w2 = torch.from_numpy(w13n).to(DEV), torch.from_numpy(w2n).to(DEV)
+    out = fused_moe._fused_moe_gguf(x, w13, w2, torch.from_numpy(tw).to(DEV), torch.from_numpy(ids).to(DEV).int(), t, t, "silu")
+    # dense restatement on dequantized weights (what the reference's test_moe compares with)
+    d13 = torch.stack([capi.dequantize(w13[e], t, 2 * I, H) for e in range(E)]).float()
+    d2 = torch.stack([capi.dequantize(w2[e], t, H, I) for e in range(E)]).float()
+    want = torch.zeros(T, H, device=DEV)
+    for tok in range(T):
+        for j in range(top_k):
+            e = int(ids[tok, j])
+            h = x[tok].float() @ d13[e].T
+            h = torch.nn.functional.silu(h[:I]) * h[I:]
+            want[tok] += float(tw[tok, j]) * (h @ d2[e].T)
+    # activations are q8_1-quantized twice on the kernel path: the reference's own tolerance class
+    assert rel_l2(out.float().cpu(), want.cpu()) < 3e-2

@@ -131,6 +131,27 @@ int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, in
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
 }
 
+int gguf_b200_gemv_prepare(const void* X, int dtype, void* ws, int64_t ws_bytes, int type, int64_t M, int64_t K,
+                           void* stream) {
+  if (!type_size(type)) return E_BAD_TYPE;
+  if (!dtype_ok(dtype)) return E_BAD_DTYPE;
+  if (M < 0 || K <= 0 || K % block_size(type) != 0) return E_BAD_SHAPE;
+  if (M == 0) return E_OK;
+  if (!X || !ws || !aligned16(ws) || !aligned16(X)) return E_BAD_POINTER;
+  if (ws_bytes < q8_soa_bytes(M, K)) return E_WORKSPACE;
+  return launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int gguf_b200_gemv_prepared(const void* W, const void* ws, void* Y, int type, int dtype, int64_t M, int64_t N,
+                            int64_t K, void* stream) {
+  int rc = check_common(W, ws, Y, type, dtype, M, N, K);
+  if (rc || M == 0 || N == 0) return rc;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, static_cast<cudaStream_t>(stream));
+}
+
 int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
                          int64_t M, int64_t N, int64_t K, void* stream) {
   int rc = check_common(W, X, Y, type, dtype, M, N, K);
@@ -182,7 +203,7 @@ int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* ws, int64_t ws
   int rc = check_common(W, X, Y, type, dtype, tokens, N, K);
   if (rc) return rc;
   if (!is_mmq_type(type)) return E_BAD_TYPE;
-  if (top_k <= 0 || n_sorted < 0 || n_sorted % mmq_moe_block_size() != 0 || expert_stride_bytes % 16 != 0) return E_BAD_SHAPE;
+  if (top_k <= 0 || n_sorted < 0 || expert_stride_bytes % 16 != 0) return E_BAD_SHAPE;
   if (tokens == 0 || N == 0) return E_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t rows_out = tokens * top_k;

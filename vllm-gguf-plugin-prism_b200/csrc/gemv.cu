@@ -38,15 +38,20 @@ template <> struct GemvTraits<T_Q6_K>    { static constexpr int UPB = 4; };  // 
 template <> struct GemvTraits<T_IQ2_XXS> { static constexpr int UPB = 8; };  // 32 values each
 template <> struct GemvTraits<T_IQ4_XS>  { static constexpr int UPB = 8; };
 
+// Activations in shared memory.  The int8 codes are stored in 16-byte chunks (chunk c = values
+// 16c..16c+15) at the swizzled position c ^ ((c >> 3) & 7): lanes of a warp read chunks that are
+// 1, 2 or 4 apart (one unit per lane), and the swizzle spreads any such stride over all eight
+// 16-byte bank groups, so a 128-bit load costs its minimum of four wavefronts.
 struct XView {
-  const uint8_t* qs;   // int8 codes, vector m at qs + m*kpad
+  const uint4* qs;     // vector m at qs + m*(kpad/16)
   const float2* ds;    // {d, sum} per 32 values, vector m at ds + m*nb
-  int kpad, nb;
+  int chunks, nb;      // kpad/16, kpad/32
 };
 
+__device__ __forceinline__ int swz(int c) { return c ^ ((c >> 3) & 7); }
 __device__ __forceinline__ void load_x32(const XView& x, int m, int g, uint32_t (&u)[8]) {
-  const uint4* p = reinterpret_cast<const uint4*>(x.qs + (size_t)m * x.kpad + g * 32);
-  const uint4 a = p[0], b = p[1];
+  const uint4* p = x.qs + (size_t)m * x.chunks;
+  const uint4 a = p[swz(2 * g)], b = p[swz(2 * g + 1)];
   u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w;
   u[4] = b.x; u[5] = b.y; u[6] = b.z; u[7] = b.w;
 }
@@ -55,6 +60,12 @@ __device__ __forceinline__ int dp4a8(const uint32_t (&w)[8], const uint32_t (&u)
 #pragma unroll
   for (int i = 0; i < 8; ++i) s = __dp4a((int)w[i], (int)u[i], s);
   return s;
+}
+// unsigned bytes (weights) times signed bytes (activations)
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
 }
 // n consecutive 32-bit words from a 2-byte aligned shared address
 template <int N> __device__ __forceinline__ void lds_words_a2(const uint8_t* p, uint32_t (&w)[N]) {
@@ -97,20 +108,21 @@ template <int MT> struct Unit<T_Q8_0, MT> {   // sum_i d*d8*dot, vec_dot_q8_0_q8
 template <int MT> struct Unit<T_Q4_0, MT> {   // d4*(sumi*d8 - 8*s8), vec_dot_q4_0_q8_1
   static __device__ __forceinline__ void run(const uint8_t* blk, int, int g, const XView& x, const Tables&, int mc, float (&acc)[MT]) {
     const float d = lds_half_as_float(blk);
-    uint32_t q[4], w[8];
+    uint32_t q[4];
     lds_words_a2<4>(blk + 2, q);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w[i] = q[i] & 0x0F0F0F0Fu;             // values 4i..4i+3
-      w[4 + i] = (q[i] >> 4) & 0x0F0F0F0Fu;  // values 16+4i..
-    }
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
       if (m < mc) {
         uint32_t u[8];
         load_x32(x, m, g, u);
+        int lo = 0, hi = 0;  // hi accumulates 16 * (high-nibble dot): the nibbles stay in place
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          lo = dp4a_us(q[i] & 0x0F0F0F0Fu, u[i], lo);      // values 4i..4i+3
+          hi = dp4a_us(q[i] & 0xF0F0F0F0u, u[4 + i], hi);  // values 16+4i..
+        }
         const float2 ds = x.ds[m * x.nb + g];
-        acc[m] += d * ((float)dp4a8(w, u) * ds.x - 8.0f * ds.y);
+        acc[m] += d * ((float)(lo + (hi >> 4)) * ds.x - 8.0f * ds.y);
       }
     }
   }
@@ -118,45 +130,37 @@ template <int MT> struct Unit<T_Q4_0, MT> {   // d4*(sumi*d8 - 8*s8), vec_dot_q4
 
 template <int MT> struct Unit<T_Q4_K, MT> {   // unit p = 64 values: sub-blocks 2p (low nibbles) and 2p+1
   static __device__ __forceinline__ void run(const uint8_t* blk, int p, int g0, const XView& x, const Tables&, int mc, float (&acc)[MT]) {
-    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);  // dm | scales[12]
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);  // dm | scales[0..3] | [4..7] | [8..11]
     const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
     const float d = __low2float(dm), dmin = __high2float(dm);
-    const uint8_t* sc8 = blk + 4;
-    int sc[2], mn[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int j = 2 * p + t;
-      if (j < 4) {
-        sc[t] = sc8[j] & 63;
-        mn[t] = sc8[j + 4] & 63;
-      } else {
-        sc[t] = (sc8[j + 4] & 0xF) | ((sc8[j - 4] >> 6) << 4);
-        mn[t] = (sc8[j + 4] >> 4) | ((sc8[j] >> 6) << 4);
-      }
-    }
+    // 6-bit (scale, min) of sub-blocks j = 2p, 2p+1 (get_scale_min_k4), both selected without a branch:
+    // j < 4: sc = b[j] & 63, m = b[j+4] & 63;  j >= 4: sc = (b[j+4] & 15) | (b[j-4] >> 6) << 4, m = (b[j+4] >> 4) | (b[j] >> 6) << 4
+    const int sh = 16 * (p & 1);
+    const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, c = hdr.w >> sh;  // low 16 bits: the byte pair of interest
+    const bool low = p < 2;
+    const uint32_t sc2 = low ? (a & 0x3F3Fu) : ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u));
+    const uint32_t mn2 = low ? (b & 0x3F3Fu) : (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u));
+    const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
+    const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
     const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + 32 * p);
     const uint4 qa = qp[0], qb = qp[1];
     const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    uint32_t lo[8], hi[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      lo[i] = q[i] & 0x0F0F0F0Fu;
-      hi[i] = (q[i] >> 4) & 0x0F0F0F0Fu;
-    }
     const int g = g0 + 2 * p;
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
       if (m < mc) {
-        uint32_t u[8];
-        load_x32(x, m, g, u);
-        const float2 ds0 = x.ds[m * x.nb + g];
-        const int dot0 = dp4a8(lo, u);
-        load_x32(x, m, g + 1, u);
-        const float2 ds1 = x.ds[m * x.nb + g + 1];
-        const int dot1 = dp4a8(hi, u);
-        // ds.y holds d8*sum(q8) for this entry point (the GEMV recomputes the sum from the codes)
-        acc[m] += d * (ds0.x * (float)(dot0 * sc[0]) + ds1.x * (float)(dot1 * sc[1])) -
-                  dmin * (ds0.y * (float)mn[0] + ds1.y * (float)mn[1]);
+        uint32_t u0[8], u1[8];
+        load_x32(x, m, g, u0);
+        load_x32(x, m, g + 1, u1);
+        int dot0 = 0, dot1 = 0;  // dot1 = 16 * (high-nibble dot)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          dot0 = dp4a_us(q[i] & 0x0F0F0F0Fu, u0[i], dot0);
+          dot1 = dp4a_us(q[i] & 0xF0F0F0F0u, u1[i], dot1);
+        }
+        const float4 ds = *reinterpret_cast<const float4*>(&x.ds[m * x.nb + g]);  // d8_0, s_0, d8_1, s_1
+        // ds.y / ds.w hold d8*sum(q8) for this entry point (the GEMV recomputes the sum from the codes)
+        acc[m] += d * (ds.x * (float)(dot0 * sc0) + ds.z * (float)((dot1 >> 4) * sc1)) - dmin * (ds.y * m0 + ds.w * m1);
       }
     }
   }
@@ -172,10 +176,12 @@ template <int MT> struct Unit<T_Q6_K, MT> {   // unit u: half ip = u>>1, column 
     const int sa0 = scp[0], sa1 = scp[1], sb0 = scp[4], sb1 = scp[5];
     const float d = lds_half_as_float(blk + 208);
     uint32_t va[8], vb[8];
+    const int s2 = 2 * h;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t a = (ql[i] & 0x0F0F0F0Fu) | (((qh[i] >> (2 * h)) & 0x03030303u) << 4);
-      const uint32_t b = ((ql[i] >> 4) & 0x0F0F0F0Fu) | (((qh[i] >> (4 + 2 * h)) & 0x03030303u) << 4);
+      const uint32_t hh = qh[i] >> s2;  // bits 0-1 of each byte: group A, bits 4-5: group B
+      const uint32_t a = (ql[i] & 0x0F0F0F0Fu) | ((hh << 4) & 0x30303030u);
+      const uint32_t b = ((ql[i] >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u);
       va[i] = (a + 0x60606060u) ^ 0x80808080u;  // per byte: code - 32 as int8 (no carries: code <= 63)
       vb[i] = (b + 0x60606060u) ^ 0x80808080u;
     }
@@ -274,7 +280,7 @@ template <int MT> struct Unit<T_IQ2_XXS, MT> {   // unit ib = 32 values: 4 grid 
 
 struct GemvParams {
   const uint8_t* w;       // packed weights, N rows of row_bytes
-  int64_t w_bytes;        // N * row_bytes (bulk copies never read past w_bytes rounded down to 16)
+  int64_t w_bytes;        // total weight bytes (bulk copies never read past this rounded down to 16)
   const uint8_t* xq;      // SoA q8_1 activations of all M vectors
   int64_t m_total;        // number of vectors in xq
   int m0, mc;             // this launch handles vectors m0 .. m0+mc-1 (mc <= MT)
@@ -287,17 +293,19 @@ struct GemvParams {
   const int32_t* topk_ids;
   int64_t n_slots, top_k, expert_rows;
   int* status;
+  int debug_skip;         // tuning aid: 1 = stream the weights but skip the arithmetic
 };
 
 template <int TYPE, int MT, typename out_t>
-__global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int TS = BlockTraits<TYPE>::TS, QK = BlockTraits<TYPE>::QK, UPB = GemvTraits<TYPE>::UPB;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kpad = (int)round_up(p.k, 512), nb = kpad / 32;
+  const bool moe = p.topk_ids != nullptr;
 
   // shared layout: [x codes MT*kpad][x scales MT*nb*8][tables][rings][barriers]
-  uint8_t* s_xq = smem;
+  uint4* s_xq = reinterpret_cast<uint4*>(smem);
   float2* s_xd = reinterpret_cast<float2*>(smem + (size_t)MT * kpad);
   uint8_t* cur = smem + (size_t)MT * kpad + (size_t)MT * nb * 8;
   Tables tb;
@@ -337,40 +345,43 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const GemvPara
   fence_barrier_init();
   __syncwarp();
 
-  const int64_t total_rows = p.topk_ids ? p.n_slots * p.n : p.n;
+  // Row ownership.  Dense: rows interleaved over all warps of the grid (the 8 warps of a CTA read
+  // 8 consecutive rows).  MoE-vec: each warp owns a contiguous run, so its vector changes rarely.
+  const int64_t total_rows = moe ? p.n_slots * p.n : p.n;
   const int64_t gwarps = (int64_t)gridDim.x * GEMV_WARPS;
   const int64_t gw = (int64_t)blockIdx.x * GEMV_WARPS + warp;
-  // dense: rows interleaved over all warps (a CTA's 8 warps read 8 consecutive rows);
-  // MoE-vec: each warp owns a contiguous run of rows so that its activation vector changes rarely
   const int64_t rpw = (total_rows + gwarps - 1) / gwarps;
-  int64_t my_rows;
-  if (p.topk_ids) {
-    my_rows = total_rows - gw * rpw;
-    my_rows = my_rows < 0 ? 0 : (my_rows > rpw ? rpw : my_rows);
+  int64_t row0, row_step;
+  int my_rows;
+  if (moe) {
+    int64_t c = total_rows - gw * rpw;
+    my_rows = (int)(c < 0 ? 0 : (c > rpw ? rpw : c));
+    row0 = gw * rpw;
+    row_step = 1;
   } else {
-    my_rows = gw < total_rows ? (total_rows - gw + gwarps - 1) / gwarps : 0;
+    my_rows = gw < total_rows ? (int)((total_rows - gw + gwarps - 1) / gwarps) : 0;
+    row0 = gw;
+    row_step = gwarps;
   }
-  const int64_t n_items = my_rows * p.nseg;
-  auto row_of = [&](int64_t it) { return p.topk_ids ? gw * rpw + it / p.nseg : gw + (it / p.nseg) * gwarps; };
   const int64_t row_bytes = (int64_t)p.bpr * TS;
   const int64_t w_safe = p.w_bytes & ~int64_t(15);
+  const uint32_t n32 = (uint32_t)p.n;
 
-  // Issue the bulk copy of work item `it` (row, segment) into its stage.  Lane 0 only.
-  auto issue = [&](int64_t it) {
-    const int64_t r = row_of(it);
-    const int seg = (int)(it % p.nseg);
-    int64_t wrow = r;
-    if (p.topk_ids) {  // r = slot * N + n
-      const int64_t slot = r / p.n;
-      wrow = (int64_t)p.topk_ids[slot] * p.expert_rows + (r - slot * p.n);
-    }
+  // weight row of logical row r (MoE-vec: r = slot * N + n uses the slot's expert)
+  auto weight_row = [&](int64_t r) -> int64_t {
+    if (!moe) return r;
+    const uint32_t slot = (uint32_t)r / n32;
+    return (int64_t)p.topk_ids[slot] * p.expert_rows + (int64_t)((uint32_t)r - slot * n32);
+  };
+  // Issue the bulk copy of (row iteration ri, segment seg) into stage st.  Lane 0 only.
+  auto issue = [&](int ri, int seg, int st) {
+    const int64_t wrow = weight_row(row0 + (int64_t)ri * row_step);
     const int b0 = seg * p.seg_blocks;
     const int nbk = min(p.seg_blocks, p.bpr - b0);
     const int64_t beg = wrow * row_bytes + (int64_t)b0 * TS, end = beg + (int64_t)nbk * TS;
     const int64_t abeg = beg & ~int64_t(15);
     int64_t aend = (end + 15) & ~int64_t(15);
     if (aend > w_safe) aend = w_safe;  // the (< 16 byte) tail past w_safe is fetched with plain loads by the consumer
-    const int st = (int)(it % p.stages);
     uint8_t* dst = ring + (size_t)st * p.stage_bytes;
     const uint32_t bytes = aend > abeg ? (uint32_t)(aend - abeg) : 0u;
     if (bytes) {
@@ -381,20 +392,32 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const GemvPara
     }
   };
 
-  if (lane == 0)
-    for (int64_t it = 0; it < p.stages - 1 && it < n_items; ++it) issue(it);
+  // producer cursor (row iteration, segment, stage), advanced one item at a time: no divisions
+  int p_ri = 0, p_seg = 0, p_st = 0;
+  auto advance_producer = [&]() {
+    if (++p_seg == p.nseg) { p_seg = 0; ++p_ri; }
+    if (++p_st == p.stages) p_st = 0;
+  };
+  for (int i = 0; i < p.stages - 1; ++i) {
+    if (p_ri < my_rows) {
+      if (lane == 0) issue(p_ri, p_seg, p_st);
+      advance_producer();
+    }
+  }
 
   // Stage the activations (dense mode: vectors m0..m0+mc-1, shared by all rows).
   XView xv;
   xv.qs = s_xq;
   xv.ds = s_xd;
-  xv.kpad = kpad;
+  xv.chunks = kpad / 16;
   xv.nb = nb;
-  if (!p.topk_ids) {
+  if (!moe) {
     const uint4* src = reinterpret_cast<const uint4*>(p.xq + (size_t)p.m0 * kpad);
-    uint4* dst = reinterpret_cast<uint4*>(s_xq);
-    const int nq = p.mc * kpad / 16;
-    for (int i = threadIdx.x; i < nq; i += blockDim.x) dst[i] = __ldg(src + i);
+    const int cpv = kpad / 16;
+    for (int i = threadIdx.x; i < p.mc * cpv; i += blockDim.x) {
+      const int m = i / cpv, c = i - m * cpv;
+      s_xq[m * cpv + swz(c)] = __ldg(src + i);
+    }
     const float2* dsrc = reinterpret_cast<const float2*>(p.xq + (size_t)p.m_total * kpad) + (size_t)p.m0 * nb;
     for (int i = threadIdx.x; i < p.mc * nb; i += blockDim.x) s_xd[i] = __ldg(dsrc + i);
   }
@@ -403,82 +426,85 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const GemvPara
   float acc[MT];
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-  int64_t cur_slot = -1;
+  uint32_t cur_slot = 0xFFFFFFFFu;
+  int c_st = 0;
+  uint32_t c_phase = 0;
 
-  for (int64_t it = 0; it < n_items; ++it) {
-    if (lane == 0 && it + p.stages - 1 < n_items) issue(it + p.stages - 1);
-    const int st = (int)(it % p.stages);
-    const uint32_t parity = (uint32_t)((it / p.stages) & 1);
-    if (!mbar_wait_bounded(&bars[st], parity)) {
-      if (lane == 0) atomicExch(p.status, E_TIMEOUT);
-      return;
-    }
-    const int64_t r = row_of(it);
-    const int seg = (int)(it % p.nseg);
-    int64_t wrow = r, orow = r;
-    if (p.topk_ids) {
-      const int64_t slot = r / p.n;
-      wrow = (int64_t)p.topk_ids[slot] * p.expert_rows + (r - slot * p.n);
+  for (int ri = 0; ri < my_rows; ++ri) {
+    const int64_t r = row0 + (int64_t)ri * row_step;
+    const int64_t wrow = weight_row(r);
+    if (moe) {
+      const uint32_t slot = (uint32_t)r / n32;
       if (slot != cur_slot) {  // this warp's activation vector changes: restage it into the warp's slice
-        // MoE-vec mode keeps one vector per warp: slice `warp` of the x area (MT == GEMV_WARPS there)
-        const int64_t tok = slot / p.top_k;
+        const int64_t tok = slot / (uint32_t)p.top_k;
         const uint4* src = reinterpret_cast<const uint4*>(p.xq + (size_t)tok * kpad);
-        uint4* dst = reinterpret_cast<uint4*>(s_xq + (size_t)warp * kpad);
-        for (int i = lane; i < kpad / 16; i += 32) dst[i] = __ldg(src + i);
+        uint4* dst = s_xq + (size_t)warp * xv.chunks;
+        __syncwarp();
+        for (int i = lane; i < xv.chunks; i += 32) dst[swz(i)] = __ldg(src + i);
         const float2* dsrc = reinterpret_cast<const float2*>(p.xq + (size_t)p.m_total * kpad) + (size_t)tok * nb;
         for (int i = lane; i < nb; i += 32) s_xd[(size_t)warp * nb + i] = __ldg(dsrc + i);
         __syncwarp();
         cur_slot = slot;
       }
     }
-    const int b0 = seg * p.seg_blocks;
-    const int nbk = min(p.seg_blocks, p.bpr - b0);
-    const int64_t beg = wrow * row_bytes + (int64_t)b0 * TS;
-    uint8_t* stage = ring + (size_t)st * p.stage_bytes;
-    const uint8_t* data = stage + (beg & 15);
-    {  // tail bytes the bulk copy was not allowed to touch
-      const int64_t end = beg + (int64_t)nbk * TS;
-      if (end > w_safe) {
-        const int64_t abeg = beg & ~int64_t(15);
-        for (int64_t o = w_safe + lane; o < end; o += 32) stage[o - abeg] = p.w[o];
-        __syncwarp();
+    for (int seg = 0; seg < p.nseg; ++seg) {
+      if (p_ri < my_rows) {  // keep stages-1 copies in flight
+        if (lane == 0) issue(p_ri, p_seg, p_st);
+        advance_producer();
       }
-    }
-    const int units = nbk * UPB;
-    const int g_seg = b0 * (QK / 32);
-    if (p.topk_ids) {
-      // one vector per warp, stored in slice `warp`
-      XView xw = xv;
-      xw.qs = s_xq + (size_t)warp * kpad;
-      xw.ds = s_xd + (size_t)warp * nb;
-      float a1[1] = {acc[0]};
-      for (int u = lane; u < units; u += 32) {
-        const int b = u / UPB;
-        Unit<TYPE, 1>::run(data + b * TS, u - b * UPB, g_seg + b * (QK / 32), xw, tb, 1, a1);
+      if (!mbar_wait_bounded(&bars[c_st], c_phase)) {
+        if (lane == 0) atomicExch(p.status, E_TIMEOUT);
+        return;
       }
-      acc[0] = a1[0];
-    } else {
-      for (int u = lane; u < units; u += 32) {
-        const int b = u / UPB;
-        Unit<TYPE, MT>::run(data + b * TS, u - b * UPB, g_seg + b * (QK / 32), xv, tb, p.mc, acc);
-      }
-    }
-    if (seg == p.nseg - 1) {
-      out_t* y = static_cast<out_t*>(p.y);
-      if (p.topk_ids) {
-        const float v = warp_sum(acc[0]);
-        if (lane == 0) y[orow] = from_float<out_t>(v);
-        acc[0] = 0.f;
-      } else {
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const float v = warp_sum(acc[m]);
-          if (lane == m && m < p.mc) y[(int64_t)(p.m0 + m) * p.n + orow] = from_float<out_t>(v);
-          acc[m] = 0.f;
+      const int b0 = seg * p.seg_blocks;
+      const int nbk = min(p.seg_blocks, p.bpr - b0);
+      const int64_t beg = wrow * row_bytes + (int64_t)b0 * TS;
+      uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
+      const uint8_t* data = stage + (beg & 15);
+      {  // tail bytes the bulk copy was not allowed to touch
+        const int64_t end = beg + (int64_t)nbk * TS;
+        if (end > w_safe) {
+          const int64_t abeg = beg & ~int64_t(15);
+          for (int64_t o = w_safe + lane; o < end; o += 32) stage[o - abeg] = p.w[o];
+          __syncwarp();
         }
       }
+      const int units = nbk * UPB;
+      const int g_seg = b0 * (QK / 32);
+      if (moe) {
+        XView xw = xv;  // one vector per warp, stored in slice `warp`
+        xw.qs = s_xq + (size_t)warp * xv.chunks;
+        xw.ds = s_xd + (size_t)warp * nb;
+        float a1[1] = {acc[0]};
+        for (int u = lane; u < units; u += 32) {
+          const int b = u / UPB;
+          Unit<TYPE, 1>::run(data + b * TS, u - b * UPB, g_seg + b * (QK / 32), xw, tb, 1, a1);
+        }
+        acc[0] = a1[0];
+      } else if (!p.debug_skip) {
+        for (int u = lane; u < units; u += 32) {
+          const int b = u / UPB;
+          Unit<TYPE, MT>::run(data + b * TS, u - b * UPB, g_seg + b * (QK / 32), xv, tb, p.mc, acc);
+        }
+      } else {
+        acc[0] += (float)data[lane];
+      }
+      __syncwarp();  // all lanes are done with this stage before lane 0 refills it
+      if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
     }
-    __syncwarp();  // all lanes are done with this stage before lane 0 refills it
+    out_t* y = static_cast<out_t*>(p.y);
+    if (moe) {
+      const float v = warp_sum(acc[0]);
+      if (lane == 0) y[r] = from_float<out_t>(v);
+      acc[0] = 0.f;
+    } else {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == m && m < p.mc) y[(int64_t)(p.m0 + m) * p.n + r] = from_float<out_t>(v);
+        acc[m] = 0.f;
+      }
+    }
   }
 }
 
@@ -500,7 +526,7 @@ static int gemv_tune_int(const char* name, int dflt) {
 }
 
 static GemvPlan make_plan(int type, int64_t K, int64_t M, bool moe) {
-  static const int payload_env = gemv_tune_int("GGUF_B200_GEMV_PAYLOAD", 3072);
+  static const int payload_env = gemv_tune_int("GGUF_B200_GEMV_PAYLOAD", 2304);
   static const int stages_env = gemv_tune_int("GGUF_B200_GEMV_STAGES", 3);
   const int ts = type_size(type), qk = block_size(type);
   const int bpr = (int)(K / qk);
@@ -518,7 +544,7 @@ static GemvPlan make_plan(int type, int64_t K, int64_t M, bool moe) {
   const int64_t kpad = round_up(K, 512);
   const size_t tables = type == T_IQ2_XXS ? (256 + 128) * 8 : 0;
   const size_t rings = (size_t)GEMV_WARPS * pl.stages * pl.stage_bytes + (size_t)GEMV_WARPS * pl.stages * 8;
-  const size_t budget = 110 * 1024;  // two CTAs per SM
+  const size_t budget = 110 * 1024;  // at least two CTAs per SM
   int mt = moe ? GEMV_WARPS : 8;
   if (!moe) {
     while (mt > 1 && (mt / 2 >= M || tables + rings + (size_t)mt * (kpad + kpad / 4) > budget)) mt /= 2;
@@ -539,7 +565,7 @@ static int launch_cfg(const GemvParams& p, const GemvPlan& pl, int64_t rows, cud
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess) return E_CUDA;
     configured[dev & 63] = pl.smem;
   }
-  const int ctas_per_sm = pl.smem <= 113 * 1024 ? 2 : 1;
+  const int ctas_per_sm = (MT == 1 && pl.smem <= 74 * 1024) ? 3 : (pl.smem <= 113 * 1024 ? 2 : 1);
   int64_t grid = 148 * ctas_per_sm;
   const int64_t need = (rows + GEMV_WARPS - 1) / GEMV_WARPS;
   if (grid > need) grid = need;
@@ -586,6 +612,8 @@ static int launch_type(const GemvParams& p, const GemvPlan& pl, int out_dtype, i
 static int launch_any(GemvParams p, int type, int out_dtype, int64_t M, bool moe, cudaStream_t stream) {
   const GemvPlan pl = make_plan(type, p.k, M, moe);
   p.bpr = (int)(p.k / block_size(type));
+  static const int dbg = gemv_tune_int("GGUF_B200_GEMV_DEBUG_SKIP", 0);
+  p.debug_skip = dbg;
   p.seg_blocks = pl.seg_blocks;
   p.nseg = pl.nseg;
   p.stages = pl.stages;

@@ -127,7 +127,8 @@ Tensor ggml_moe_a8(Tensor X, Tensor W, Tensor sorted_token_ids, Tensor expert_id
   const int blk = gguf_b200_moe_block_size((int)type);
   STD_TORCH_CHECK(blk > 0, "ggml_moe_a8: type has no tensor-core MoE kernel");
   const int64_t n_sorted = sorted_token_ids.numel();
-  STD_TORCH_CHECK(n_sorted % blk == 0 && expert_ids.numel() * blk >= n_sorted,
+  // vLLM sizes sorted_token_ids as numel + E*(block-1) (not rounded) and expert_ids as its ceil-div by block
+  STD_TORCH_CHECK(expert_ids.numel() * blk >= n_sorted,
                   "ggml_moe_a8: sorted_token_ids/expert_ids were not built with block size ggml_moe_get_block_size(type)");
   const int code = dtype_code(X.scalar_type(), "ggml_moe_a8");
   Tensor Y = torch::stable::new_empty(W, {tokens * top_k, row}, X.scalar_type());  // zeroed by the C-ABI call

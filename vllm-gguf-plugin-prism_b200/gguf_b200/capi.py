@@ -30,6 +30,8 @@ SIGNATURES = {
     "gguf_b200_dequantize": (_I, [_P, _I, _P, _I, _L, _P]),
     "gguf_b200_workspace_bytes": (_L, [_I, _I, _L, _L, _L]),
     "gguf_b200_mul_mat_vec_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
+    "gguf_b200_gemv_prepare": (_I, [_P, _I, _P, _L, _I, _L, _L, _P]),
+    "gguf_b200_gemv_prepared": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_dequant_matmul": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
@@ -103,6 +105,23 @@ def _matmul(fn_name: str, op: int, W: torch.Tensor, X: torch.Tensor, qtype: int,
 
 def mul_mat_vec_a8(W, X, qtype, N):
     return _matmul("gguf_b200_mul_mat_vec_a8", OP_GEMV, W, X, qtype, N)
+
+
+def gemv_prepare(X: torch.Tensor, qtype: int) -> torch.Tensor:
+    """Quantize X once into a workspace that gemv_prepared() can reuse for several weights."""
+    M, K = X.shape
+    nbytes = lib().gguf_b200_workspace_bytes(OP_GEMV, qtype, M, 0, K)
+    ws = _ws(X, nbytes)
+    _check(lib().gguf_b200_gemv_prepare(X.data_ptr(), _DT[X.dtype], ws.data_ptr(), nbytes, qtype, M, K, _stream(X)),
+           "gemv_prepare")
+    return ws
+
+
+def gemv_prepared(W, ws, qtype, M, N, K, dtype=torch.float16, out=None):
+    Y = out if out is not None else torch.empty((M, N), dtype=dtype, device=W.device)
+    _check(lib().gguf_b200_gemv_prepared(W.data_ptr(), ws.data_ptr(), Y.data_ptr(), qtype, _DT[dtype], M, N, K, _stream(W)),
+           "gemv_prepared")
+    return Y
 
 
 def mul_mat_a8(W, X, qtype, N):
