@@ -109,6 +109,24 @@ int gguf_b200_moe_a8_vec(const void* X, const void* W, void* Y, void* workspace,
                          const int32_t* topk_ids, int64_t n_experts, int type, int dtype, int64_t tokens,
                          int64_t top_k, int64_t N, int64_t K, void* stream);
 
+/* Decode GEMV that needs no workspace from the caller and allocates nothing.  (No counterpart
+ * in the reference: its GEMV allocates its scratch tensor inside the call.)
+ * For hosts that cannot allocate: an FFI or plain-C integration that only receives W, X and Y
+ * from an engine which has already reserved the whole device (weights + KV cache), so that
+ * neither a workspace pool nor a late cudaMalloc is available to it.  Same arithmetic and
+ * result as gguf_b200_mul_mat_vec_a8; the quantized activations go to a fixed array inside the
+ * library (gguf_b200_noalloc_scratch_bytes() = 320 KiB, held by every GPU that loads the
+ * library until the process exits).
+ * Limits: M <= 8, K <= 32768; beyond them the call returns GGUF_B200_E_TOO_LARGE.
+ * The first call on each device resolves the array's device address (one runtime query, made
+ * with that device current); make that first call before starting any stream capture.
+ * All calls on a device share the one array: calls that may overlap on the GPU (different
+ * streams, or another thread) race on it -- serialise them.  Nothing in the array needs to be
+ * cleared between calls; each call rewrites all it reads. */
+int gguf_b200_mul_mat_vec_a8_noalloc(const void* W, const void* X, void* Y, int type, int dtype,
+                                     int64_t M, int64_t N, int64_t K, void* stream);
+int64_t gguf_b200_noalloc_scratch_bytes(void);
+
 /* Token-block size the caller must pass to moe_align_block_size.
  * Replaces: ggml_moe_get_block_size, gguf_kernel.cu:532-566 (4 for every type there). */
 int gguf_b200_moe_block_size(int type);

@@ -36,6 +36,8 @@ SIGNATURES = {
     "gguf_b200_dequant_matmul": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_moe_a8_vec": (_I, [_P, _P, _P, _P, _L, _P, _L, _I, _I, _L, _L, _L, _L, _P]),
+    "gguf_b200_mul_mat_vec_a8_noalloc": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
+    "gguf_b200_noalloc_scratch_bytes": (_L, []),
     "gguf_b200_moe_block_size": (_I, [_I]),
     "gguf_b200_last_status": (_I, []),
     "gguf_b200_set_q4k_contract": (None, [_I]),
@@ -152,6 +154,16 @@ def moe_a8_vec(X, W, topk_ids, top_k, qtype, N, tokens):
     _check(lib().gguf_b200_moe_a8_vec(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), nbytes,
                                       topk_ids.data_ptr(), W.shape[0], qtype, _DT[X.dtype], tokens, top_k, N, K,
                                       _stream(X)), "moe_a8_vec")
+    return Y
+
+
+def mul_mat_vec_a8_noalloc(W, X, qtype, N):
+    """GEMV through the entry point that takes no workspace (for hosts that cannot allocate one);
+    only the output tensor is created here, by the caller's own allocator."""
+    M, K = X.shape
+    Y = torch.empty((M, N), dtype=X.dtype, device=X.device)
+    _check(lib().gguf_b200_mul_mat_vec_a8_noalloc(W.data_ptr(), X.data_ptr(), Y.data_ptr(), qtype, _DT[X.dtype], M, N, K,
+                                                  _stream(X)), "mul_mat_vec_a8_noalloc")
     return Y
 
 
