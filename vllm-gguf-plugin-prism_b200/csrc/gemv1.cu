@@ -1,0 +1,507 @@
+// Single-vector decode GEMV (M = 1), the latency-critical case: Y[n] = sum_k dequant(W)[n,k] * q8_1(x)[k].
+// Same arithmetic as gemv.cu (reference: mul_mat_vec_q, mmvq.cuh:2-41 and vec_dot_*_q8_1 of
+// vecdotq.cuh), specialised so that the inner loop spends its instructions on the weights only:
+//
+//  * Lane l of a warp always works on the same K positions (units l, l+32, ... of the warp's
+//    K-slice) for every row, so the activations it needs -- int8 codes and {d, sum} -- are loaded
+//    ONCE into registers at kernel start and never touched in shared memory again.
+//  * Long rows are split into KS in {1,2,4,8} K-slices handled by different warps of the CTA so
+//    that a lane's activation slice always fits in registers; the per-slice partial sums meet in
+//    shared memory and are added in a fixed order (deterministic) every 32 row iterations.
+//  * Weights stream exactly as in gemv.cu: one 1-D bulk copy (TMA) per (row, slice) into a
+//    per-warp ring of stages, mbarrier completion, 16-byte rounded starts for the 2-byte aligned
+//    formats, bounded waits.
+//  * The unit loop is unrolled at compile time and integer dots run on independent dp4a chains.
+#include "common.cuh"
+#include "kernels.h"
+#include "tables.cuh"
+
+namespace gguf_b200 {
+
+constexpr int G1_WARPS = 8;
+constexpr int G1_BATCH = 32;   // row iterations between two flushes of the slice partials
+
+__device__ __forceinline__ int dp4a_us1(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+template <int N> __device__ __forceinline__ void lds_a2(const uint8_t* p, uint32_t (&w)[N]) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t* al = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
+  const uint32_t sh = (uint32_t)(a & 3) * 8u;
+  uint32_t r[N + 1];
+#pragma unroll
+  for (int i = 0; i <= N; ++i) r[i] = al[i];
+#pragma unroll
+  for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(r[i], r[i + 1], sh);
+}
+
+struct Tab1 {
+  const uint2* grid;
+  const uint2* smask;
+  uint32_t kv[4];
+};
+
+// Per type: UPB units per block, XW activation words and XD floats held per unit.
+template <int TYPE> struct G1;
+
+// ---- Q8_0: unit = block of 32 -----------------------------------------------------------
+template <> struct G1<T_Q8_0> {
+  static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int, uint32_t (&x)[XW], float (&xd)[XD]) {
+    const uint4* p = reinterpret_cast<const uint4*>(qs + (size_t)u * 32);
+    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    const float2 d = __ldg(ds + u);
+    xd[0] = d.x; xd[1] = d.y;
+  }
+  static __device__ __forceinline__ float unit(const uint8_t* blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = lds_half_as_float(blk);
+    uint32_t w[8];
+    lds_a2<8>(blk + 2, w);
+    int s0 = 0, s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s0 = __dp4a((int)w[2 * i], (int)x[2 * i], s0);
+      s1 = __dp4a((int)w[2 * i + 1], (int)x[2 * i + 1], s1);
+    }
+    return d * xd[0] * (float)(s0 + s1);
+  }
+};
+
+// ---- Q4_0 -------------------------------------------------------------------------------
+template <> struct G1<T_Q4_0> {
+  static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(const uint8_t* blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = lds_half_as_float(blk);
+    uint32_t q[4];
+    lds_a2<4>(blk + 2, q);
+    int lo = 0, hi = 0;  // hi = 16 * (high-nibble dot): nibbles stay in place
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo = dp4a_us1(q[i] & 0x0F0F0F0Fu, x[i], lo);
+      hi = dp4a_us1(q[i] & 0xF0F0F0F0u, x[4 + i], hi);
+    }
+    return d * ((float)(lo + (hi >> 4)) * xd[0] - 8.0f * xd[1]);
+  }
+};
+
+// ---- Q4_K: unit p = 64 values (sub-blocks 2p, 2p+1) --------------------------------------
+template <> struct G1<T_Q4_K> {
+  static constexpr int UPB = 4, XW = 16, XD = 4, UMAX = 2;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int, uint32_t (&x)[XW], float (&xd)[XD]) {
+    const uint4* p = reinterpret_cast<const uint4*>(qs + (size_t)u * 64);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 a = __ldg(p + i);
+      x[4 * i] = a.x; x[4 * i + 1] = a.y; x[4 * i + 2] = a.z; x[4 * i + 3] = a.w;
+    }
+    const float4 d = __ldg(reinterpret_cast<const float4*>(ds + 2 * u));
+    xd[0] = d.x; xd[1] = d.y; xd[2] = d.z; xd[3] = d.w;  // d8_0, d8_0*sum0, d8_1, d8_1*sum1
+  }
+  static __device__ __forceinline__ float unit(const uint8_t* blk, int p, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
+    const float d = __low2float(dm), dmin = __high2float(dm);
+    const int sh = 16 * (p & 1);
+    const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, c = hdr.w >> sh;
+    const bool low = p < 2;  // get_scale_min_k4, both cases computed, no branch
+    const uint32_t sc2 = low ? (a & 0x3F3Fu) : ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u));
+    const uint32_t mn2 = low ? (b & 0x3F3Fu) : (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u));
+    const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
+    const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
+    const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + 32 * p);
+    const uint4 qa = qp[0], qb = qp[1];
+    const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a0 = dp4a_us1(q[2 * i] & 0x0F0F0F0Fu, x[2 * i], a0);
+      a1 = dp4a_us1(q[2 * i + 1] & 0x0F0F0F0Fu, x[2 * i + 1], a1);
+      b0 = dp4a_us1(q[2 * i] & 0xF0F0F0F0u, x[8 + 2 * i], b0);
+      b1 = dp4a_us1(q[2 * i + 1] & 0xF0F0F0F0u, x[8 + 2 * i + 1], b1);
+    }
+    return d * (xd[0] * (float)((a0 + a1) * sc0) + xd[2] * (float)(((b0 + b1) >> 4) * sc1)) - dmin * (xd[1] * m0 + xd[3] * m1);
+  }
+};
+
+// ---- Q6_K: unit u4: half ip = u4>>1, column half h = u4&1 -> groups 4ip+h and 4ip+2+h -------
+// The codes stay unsigned (0..63); the "-32" is applied through the activation sums of each
+// 16-value sub-block, which are constants of the lane (xs packs them: 4 x int16 in XW words 16,17).
+template <> struct G1<T_Q6_K> {
+  static constexpr int UPB = 4, XW = 18, XD = 2, UMAX = 2;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int, uint32_t (&x)[XW], float (&xd)[XD]) {
+    const int b = u >> 2, u4 = u & 3, ip = u4 >> 1, h = u4 & 1;
+    const int ga = 8 * b + 4 * ip + h, gb = ga + 2;
+    const uint4* pa = reinterpret_cast<const uint4*>(qs + (size_t)ga * 32);
+    const uint4* pb = reinterpret_cast<const uint4*>(qs + (size_t)gb * 32);
+    const uint4 a0 = __ldg(pa), a1 = __ldg(pa + 1), b0 = __ldg(pb), b1 = __ldg(pb + 1);
+    x[0] = a0.x; x[1] = a0.y; x[2] = a0.z; x[3] = a0.w; x[4] = a1.x; x[5] = a1.y; x[6] = a1.z; x[7] = a1.w;
+    x[8] = b0.x; x[9] = b0.y; x[10] = b0.z; x[11] = b0.w; x[12] = b1.x; x[13] = b1.y; x[14] = b1.z; x[15] = b1.w;
+    int s[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[0] = __dp4a(0x01010101, (int)x[i], s[0]);
+      s[1] = __dp4a(0x01010101, (int)x[4 + i], s[1]);
+      s[2] = __dp4a(0x01010101, (int)x[8 + i], s[2]);
+      s[3] = __dp4a(0x01010101, (int)x[12 + i], s[3]);
+    }
+    x[16] = ((uint32_t)s[0] & 0xFFFFu) | ((uint32_t)s[1] << 16);
+    x[17] = ((uint32_t)s[2] & 0xFFFFu) | ((uint32_t)s[3] << 16);
+    xd[0] = __ldg(ds + ga).x;
+    xd[1] = __ldg(ds + gb).x;
+  }
+  static __device__ __forceinline__ float unit(const uint8_t* blk, int u4, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const int ip = u4 >> 1, h = u4 & 1;
+    uint32_t ql[8], qh[8];
+    lds_a2<8>(blk + 64 * ip + 32 * h, ql);
+    lds_a2<8>(blk + 128 + 32 * ip, qh);
+    const int8_t* scp = reinterpret_cast<const int8_t*>(blk + 192 + 8 * ip + 2 * h);
+    const int sa0 = scp[0], sa1 = scp[1], sb0 = scp[4], sb1 = scp[5];
+    const float d = lds_half_as_float(blk + 208);
+    const int s2 = 2 * h;
+    int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t hh = qh[i] >> s2;  // bits 0-1 of each byte: group A, bits 4-5: group B
+      const uint32_t va = (ql[i] & 0x0F0F0F0Fu) | ((hh << 4) & 0x30303030u);
+      const uint32_t vb = ((ql[i] >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u);
+      if (i < 4) {
+        a0 = dp4a_us1(va, x[i], a0);
+        b0 = dp4a_us1(vb, x[8 + i], b0);
+      } else {
+        a1 = dp4a_us1(va, x[i], a1);
+        b1 = dp4a_us1(vb, x[8 + i], b1);
+      }
+    }
+    const int xs0 = (int)(short)(x[16] & 0xFFFF), xs1 = (int)(short)(x[16] >> 16);
+    const int xs2 = (int)(short)(x[17] & 0xFFFF), xs3 = (int)(short)(x[17] >> 16);
+    const int ia = (a0 - 32 * xs0) * sa0 + (a1 - 32 * xs1) * sa1;
+    const int ib = (b0 - 32 * xs2) * sb0 + (b1 - 32 * xs3) * sb1;
+    return d * (xd[0] * (float)ia + xd[1] * (float)ib);
+  }
+};
+
+// ---- IQ4_XS: unit ib = 32 values -------------------------------------------------------------
+template <> struct G1<T_IQ4_XS> {
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ uint32_t lut(uint32_t idx, const Tab1& t) {
+    const uint32_t s = idx & 0x07070707u;
+    const uint32_t pk = s | (s >> 4);
+    const uint32_t sel = __byte_perm(pk, 0, 0x0020);
+    const uint32_t lo = __byte_perm(t.kv[0], t.kv[1], sel);
+    const uint32_t hi = __byte_perm(t.kv[2], t.kv[3], sel);
+    const uint32_t mk = ((idx & 0x08080808u) >> 3) * 0xFFu;
+    return (hi & mk) | (lo & ~mk);
+  }
+  static __device__ __forceinline__ float unit(const uint8_t* blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
+    const uint2 hdr = *reinterpret_cast<const uint2*>(blk);
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
+    const int ls = (int)(((hdr.y >> (4 * ib)) & 0xF) | ((((hdr.x >> 16) >> (2 * ib)) & 3) << 4)) - 32;
+    const uint2* qp = reinterpret_cast<const uint2*>(blk + 8 + 16 * ib);
+    const uint2 qa = qp[0], qb = qp[1];
+    const uint32_t q[4] = {qa.x, qa.y, qb.x, qb.y};
+    int s0 = 0, s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s0 = __dp4a((int)lut(q[i] & 0x0F0F0F0Fu, t), (int)x[i], s0);
+      s1 = __dp4a((int)lut((q[i] >> 4) & 0x0F0F0F0Fu, t), (int)x[4 + i], s1);
+    }
+    return d * (float)ls * xd[0] * (float)(s0 + s1);
+  }
+};
+
+// ---- IQ2_XXS: unit ib = 32 values ------------------------------------------------------------
+template <> struct G1<T_IQ2_XXS> {
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(const uint8_t* blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
+    const float d = lds_half_as_float(blk);
+    uint32_t q[2];
+    lds_a2<2>(blk + 2 + 8 * ib, q);
+    const uint32_t aux = q[1];
+    int sp = 0, sn = 0;
+#pragma unroll
+    for (int il = 0; il < 4; ++il) {
+      const uint2 gr = t.grid[(q[0] >> (8 * il)) & 0xFF];
+      const uint2 sm = t.smask[(aux >> (7 * il)) & 127];
+      sp = dp4a_us1(gr.x, x[2 * il], sp);
+      sp = dp4a_us1(gr.y, x[2 * il + 1], sp);
+      sn = dp4a_us1(gr.x & sm.x, x[2 * il], sn);
+      sn = dp4a_us1(gr.y & sm.y, x[2 * il + 1], sn);
+    }
+    return d * (0.5f + (float)(aux >> 28)) * 0.25f * xd[0] * (float)(sp - 2 * sn);
+  }
+};
+
+// ---- kernel ---------------------------------------------------------------------------------
+
+struct G1Params {
+  const uint8_t* w;
+  int64_t w_bytes;
+  const uint8_t* xq;     // SoA q8_1 of the vector: int8 qs[kpad] then float2 ds[kpad/32]
+  void* y;
+  int64_t n, k;
+  int bpr;               // blocks per row
+  int ks, rl;            // K-slices per row, rows in flight per CTA (ks * rl <= 8)
+  int slice_blocks;      // blocks per K-slice (the last slice may be shorter)
+  int stages, stage_bytes;
+  int* status;
+};
+
+template <int TYPE, typename out_t>
+__global__ void __launch_bounds__(G1_WARPS * 32, 3) gemv1_kernel(const G1Params p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using T = G1<TYPE>;
+  constexpr int TS = BlockTraits<TYPE>::TS, QK = BlockTraits<TYPE>::QK, UPB = T::UPB, UMAX = T::UMAX;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kpad = (int)round_up(p.k, 512);
+
+  uint8_t* cur = smem;
+  Tab1 tb;
+  tb.grid = nullptr;
+  tb.smask = nullptr;
+  if (TYPE == T_IQ2_XXS) {
+    uint2* g = reinterpret_cast<uint2*>(cur);
+    uint2* sm = g + 256;
+    cur += 256 * 8 + 128 * 8;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      const uint64_t v = d_iq2xxs_grid[i];
+      g[i] = make_uint2((uint32_t)v, (uint32_t)(v >> 32));
+    }
+    for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+      const uint32_t s = d_ksigns_iq2xs[i];
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= ((s >> j) & 1u) ? (0xFFu << (8 * j)) : 0u;
+        hi |= ((s >> (4 + j)) & 1u) ? (0xFFu << (8 * j)) : 0u;
+      }
+      sm[i] = make_uint2(lo, hi);
+    }
+    tb.grid = g;
+    tb.smask = sm;
+  }
+  if (TYPE == T_IQ4_XS) {
+    const uint32_t* kv = reinterpret_cast<const uint32_t*>(d_kvalues_iq4nl);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
+  }
+  float* partial = reinterpret_cast<float*>(cur);  // [G1_BATCH][rl][ks]
+  cur += (size_t)G1_BATCH * 8 * sizeof(float);
+  uint8_t* ring = cur + (size_t)warp * p.stages * p.stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(cur + (size_t)G1_WARPS * p.stages * p.stage_bytes) + warp * p.stages;
+  if (lane == 0)
+    for (int s = 0; s < p.stages; ++s) mbar_init(&bars[s], 1);
+  fence_barrier_init();
+  __syncwarp();
+
+  // warp role: row lane rl_i and K-slice ks_i; warps beyond ks*rl only join the barriers
+  const bool active = warp < p.ks * p.rl;
+  const int ks_i = warp % p.ks, rl_i = warp / p.ks;
+  const int sb0 = ks_i * p.slice_blocks;
+  const int nblk = active ? max(0, min(p.slice_blocks, p.bpr - sb0)) : 0;
+  const int units = nblk * UPB;
+  const int64_t row_bytes = (int64_t)p.bpr * TS;
+  const int64_t w_safe = p.w_bytes & ~int64_t(15);
+  const uint32_t slice_bytes = (uint32_t)nblk * TS;
+  // rows of this CTA: r = (i * gridDim.x + blockIdx.x) * rl + rl_i
+  const int64_t rows_per_iter = (int64_t)gridDim.x * p.rl;
+  const int64_t first = (int64_t)blockIdx.x * p.rl;
+  const int iters = first < p.n ? (int)((p.n - first + rows_per_iter - 1) / rows_per_iter) : 0;  // uniform over the CTA
+
+  auto row_of = [&](int i) { return first + (int64_t)i * rows_per_iter + rl_i; };
+  auto issue = [&](int i, int st) {  // lane 0
+    const int64_t beg = row_of(i) * row_bytes + (int64_t)sb0 * TS, end = beg + slice_bytes;
+    const int64_t abeg = beg & ~int64_t(15);
+    int64_t aend = (end + 15) & ~int64_t(15);
+    if (aend > w_safe) aend = w_safe;
+    const uint32_t bytes = aend > abeg ? (uint32_t)(aend - abeg) : 0u;
+    if (bytes) {
+      mbar_expect_tx(&bars[st], bytes);
+      bulk_g2s(ring + (size_t)st * p.stage_bytes, p.w + abeg, bytes, &bars[st]);
+    } else {
+      mbar_arrive(&bars[st]);
+    }
+  };
+  auto has_row = [&](int i) { return active && nblk > 0 && i < iters && row_of(i) < p.n; };
+
+  int p_i = 0, p_st = 0;
+  for (int s = 0; s < p.stages - 1; ++s) {
+    if (has_row(p_i)) {
+      if (lane == 0) issue(p_i, p_st);
+      if (++p_st == p.stages) p_st = 0;
+    }
+    ++p_i;
+  }
+
+  // this lane's activations, loaded once (unit u of the slice -> unit sb0*UPB + u of the row)
+  uint32_t xq[UMAX][T::XW];
+  float xd[UMAX][T::XD];
+  {
+    const uint8_t* qs = p.xq;
+    const float2* ds = reinterpret_cast<const float2*>(p.xq + kpad);
+#pragma unroll
+    for (int j = 0; j < UMAX; ++j) {
+      const int u = lane + 32 * j;
+      if (u < units) {
+        T::load_x(qs, ds, sb0 * UPB + u, 0, xq[j], xd[j]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < T::XW; ++i) xq[j][i] = 0;
+#pragma unroll
+        for (int i = 0; i < T::XD; ++i) xd[j][i] = 0.f;
+      }
+    }
+  }
+  if (TYPE == T_IQ2_XXS) __syncthreads();  // tables staged
+
+  out_t* y = static_cast<out_t*>(p.y);
+  int c_st = 0;
+  uint32_t c_phase = 0;
+  bool dead = false;
+  for (int i = 0; i < iters; ++i) {
+    if (has_row(p_i) && !dead) {
+      if (lane == 0) issue(p_i, p_st);
+      if (++p_st == p.stages) p_st = 0;
+    }
+    ++p_i;
+    if (has_row(i) && !dead) {
+      if (!mbar_wait_bounded(&bars[c_st], c_phase)) {
+        if (lane == 0) atomicExch(p.status, E_TIMEOUT);
+        dead = true;
+      }
+      const int64_t r = row_of(i);
+      const int64_t beg = r * row_bytes + (int64_t)sb0 * TS;
+      uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
+      const uint8_t* data = stage + (beg & 15);
+      if (beg + slice_bytes > w_safe) {  // tail bytes the bulk copy must not touch
+        const int64_t abeg = beg & ~int64_t(15);
+        for (int64_t o = w_safe + lane; o < beg + slice_bytes; o += 32) stage[o - abeg] = p.w[o];
+        __syncwarp();
+      }
+      float acc = 0.f;
+      if (!dead) {
+#pragma unroll
+        for (int j = 0; j < UMAX; ++j) {
+          const int u = lane + 32 * j;
+          if (u < units) acc += T::unit(data + (u / UPB) * TS, u % UPB, xq[j], xd[j], tb);
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) {
+        if (p.ks == 1) y[r] = from_float<out_t>(acc);
+        else partial[((i % G1_BATCH) * p.rl + rl_i) * p.ks + ks_i] = acc;
+      }
+      __syncwarp();
+      if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
+    } else if (active && p.ks > 1 && lane == 0 && i < iters && row_of(i) < p.n) {
+      partial[((i % G1_BATCH) * p.rl + rl_i) * p.ks + ks_i] = 0.f;  // empty slice (cannot happen with the planner, kept for safety)
+    }
+    if (p.ks > 1 && ((i % G1_BATCH) == G1_BATCH - 1 || i == iters - 1)) {
+      // add the slice partials in slice order and store; every warp of the CTA takes part
+      __syncthreads();
+      const int i0 = i - (i % G1_BATCH);
+      const int cnt = (i - i0 + 1) * p.rl;
+      for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
+        const int ii = i0 + t / p.rl, rr = t % p.rl;
+        const int64_t r = first + (int64_t)ii * rows_per_iter + rr;
+        if (r < p.n) {
+          float s = 0.f;
+          for (int q = 0; q < p.ks; ++q) s += partial[((ii % G1_BATCH) * p.rl + rr) * p.ks + q];
+          y[r] = from_float<out_t>(s);
+        }
+      }
+      __syncthreads();
+    }
+  }
+  (void)QK;
+}
+
+// ---- host -----------------------------------------------------------------------------------
+
+static int g1_env(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v && *v ? atoi(v) : dflt;
+}
+
+template <int TYPE, typename out_t>
+static int launch_g1(G1Params p, cudaStream_t stream) {
+  using T = G1<TYPE>;
+  constexpr int TS = BlockTraits<TYPE>::TS;
+  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 3);
+  static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 3);
+  const int cap_blocks = 32 * T::UMAX / T::UPB;  // blocks whose units fit one lane-register set
+  int ks = 1;
+  while (ks < 8 && (p.bpr + ks - 1) / ks > cap_blocks) ks *= 2;
+  if ((p.bpr + ks - 1) / ks > cap_blocks) return 1;  // row too long for this kernel: caller falls back
+  p.ks = ks;
+  p.rl = G1_WARPS / ks;
+  p.slice_blocks = (p.bpr + ks - 1) / ks;
+  p.stages = stages_env < 2 ? 2 : stages_env;
+  p.stage_bytes = (int)round_up((int64_t)p.slice_blocks * TS + 32, 16);
+  const size_t tables = TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0;
+  const size_t smem = tables + (size_t)G1_BATCH * 8 * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
+  if (smem > 227 * 1024) return 1;
+  auto kern = gemv1_kernel<TYPE, out_t>;
+  static size_t configured[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > configured[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
+    configured[dev & 63] = smem;
+  }
+  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  if (per_sm > ctas_env) per_sm = ctas_env;
+  if (per_sm < 1) per_sm = 1;
+  int64_t grid = 148 * per_sm;
+  const int64_t need = (p.n + p.rl - 1) / p.rl;
+  if (grid > need) grid = need;
+  if (grid < 1) grid = 1;
+  kern<<<(int)grid, G1_WARPS * 32, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+}
+
+template <int TYPE>
+static int launch_g1_out(const G1Params& p, int out_dtype, cudaStream_t s) {
+  switch (out_dtype) {
+    case DT_F32: return launch_g1<TYPE, float>(p, s);
+    case DT_F16: return launch_g1<TYPE, __half>(p, s);
+    case DT_BF16: return launch_g1<TYPE, __nv_bfloat16>(p, s);
+  }
+  return E_BAD_DTYPE;
+}
+
+// Returns E_OK, a negative error, or 1 when the shape is outside this kernel's reach.
+int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
+                 cudaStream_t stream) {
+  G1Params p{};
+  p.w = static_cast<const uint8_t*>(w);
+  p.bpr = (int)(K / block_size(type));
+  p.w_bytes = N * p.bpr * type_size(type);
+  p.xq = static_cast<const uint8_t*>(xq_soa);
+  p.y = y;
+  p.n = N;
+  p.k = K;
+  p.status = status;
+  switch (type) {
+    case T_Q4_0: return launch_g1_out<T_Q4_0>(p, out_dtype, stream);
+    case T_Q8_0: return launch_g1_out<T_Q8_0>(p, out_dtype, stream);
+    case T_Q4_K: return launch_g1_out<T_Q4_K>(p, out_dtype, stream);
+    case T_Q6_K: return launch_g1_out<T_Q6_K>(p, out_dtype, stream);
+    case T_IQ2_XXS: return launch_g1_out<T_IQ2_XXS>(p, out_dtype, stream);
+    case T_IQ4_XS: return launch_g1_out<T_IQ4_XS>(p, out_dtype, stream);
+  }
+  return E_BAD_TYPE;
+}
+
+}  // namespace gguf_b200

@@ -28,6 +28,10 @@ int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t
 // Y[m, n] for m in [0, M); rows of W are N x (K/QK*TS) bytes, contiguous, 16-byte aligned base.
 int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t M, int64_t N, int64_t K,
                 int* status, cudaStream_t stream);
+// Single-vector specialisation (gemv1.cu): activations in registers.  Returns 1 when the shape
+// is outside its reach (the caller then uses the general kernel).
+int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
+                 cudaStream_t stream);
 // per-(token,expert) GEMV of the small-batch MoE entry point
 int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* topk_ids, int type, int out_dtype,
                     int64_t tokens, int64_t top_k, int64_t N, int64_t K, int64_t n_experts, int* status,
