@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace gguf_b200 {
 
@@ -124,10 +125,39 @@ __device__ __forceinline__ float lds_half_as_float(const uint8_t* p) {
   return __half2float(*reinterpret_cast<const __half*>(p));
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may become resident while
+// the kernel before it in the stream is still running; pdl_wait() blocks until that kernel has
+// completed and its writes are visible (it returns at once under a normal launch), and
+// pdl_trigger() tells the runtime that the NEXT kernel in the stream may start launching.
+// Rule used throughout: before pdl_wait() a kernel touches only memory no kernel writes
+// (weights, codebooks) and its own shared memory.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
   return v;
+}
+
+// Host: launch with the programmatic-stream-serialization attribute (GGUF_B200_PDL=0 turns it off).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  static const bool enabled = [] {
+    const char* v = getenv("GGUF_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 }  // namespace gguf_b200

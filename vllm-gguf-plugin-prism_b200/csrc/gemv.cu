@@ -405,6 +405,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
     }
   }
 
+  pdl_wait();  // the weight copies above are independent of earlier kernels; the activations are not
   // Stage the activations (dense mode: vectors m0..m0+mc-1, shared by all rows).
   XView xv;
   xv.qs = s_xq;
@@ -570,8 +571,7 @@ static int launch_cfg(const GemvParams& p, const GemvPlan& pl, int64_t rows, cud
   const int64_t need = (rows + GEMV_WARPS - 1) / GEMV_WARPS;
   if (grid > need) grid = need;
   if (grid < 1) grid = 1;
-  kern<<<(int)grid, GEMV_WARPS * 32, pl.smem, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+  return launch_pdl(kern, dim3((unsigned)grid), dim3(GEMV_WARPS * 32), pl.smem, stream, p) == cudaSuccess ? E_OK : E_CUDA;
 }
 
 template <int TYPE, typename out_t>

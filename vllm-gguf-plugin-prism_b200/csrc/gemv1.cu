@@ -244,6 +244,13 @@ template <> struct G1<T_IQ2_XXS> {
 };
 
 // ---- kernel ---------------------------------------------------------------------------------
+//
+// Work item of a warp = a group of up to G1_R consecutive rows (x its K-slice).  With one slice
+// the rows of a group are contiguous in memory and arrive with ONE bulk copy; with several
+// slices each row's slice is its own copy into a padded slot of the stage.  Grouping rows
+// amortises the per-item costs (copy issue, barrier wait, address arithmetic) over G1_R rows.
+
+constexpr int G1_R = 4;
 
 struct G1Params {
   const uint8_t* w;
@@ -252,17 +259,19 @@ struct G1Params {
   void* y;
   int64_t n, k;
   int bpr;               // blocks per row
-  int ks, rl;            // K-slices per row, rows in flight per CTA (ks * rl <= 8)
+  int ks, rl;            // K-slices per row, row groups in flight per CTA (ks * rl <= 8)
   int slice_blocks;      // blocks per K-slice (the last slice may be shorter)
+  int rows_per_item;     // <= G1_R
+  int slot_bytes;        // distance between the rows of an item inside a stage
   int stages, stage_bytes;
   int* status;
 };
 
 template <int TYPE, typename out_t>
-__global__ void __launch_bounds__(G1_WARPS * 32, 3) gemv1_kernel(const G1Params p) {
+__global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
   using T = G1<TYPE>;
-  constexpr int TS = BlockTraits<TYPE>::TS, QK = BlockTraits<TYPE>::QK, UPB = T::UPB, UMAX = T::UMAX;
+  constexpr int TS = BlockTraits<TYPE>::TS, UPB = T::UPB, UMAX = T::UMAX;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kpad = (int)round_up(p.k, 512);
 
@@ -296,8 +305,8 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 3) gemv1_kernel(const G1Params 
 #pragma unroll
     for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
   }
-  float* partial = reinterpret_cast<float*>(cur);  // [G1_BATCH][rl][ks]
-  cur += (size_t)G1_BATCH * 8 * sizeof(float);
+  float* partial = reinterpret_cast<float*>(cur);  // [G1_BATCH][rl][G1_R][ks]
+  cur += (size_t)G1_BATCH * 8 * G1_R * sizeof(float);
   uint8_t* ring = cur + (size_t)warp * p.stages * p.stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cur + (size_t)G1_WARPS * p.stages * p.stage_bytes) + warp * p.stages;
   if (lane == 0)
@@ -305,54 +314,88 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 3) gemv1_kernel(const G1Params 
   fence_barrier_init();
   __syncwarp();
 
-  // warp role: row lane rl_i and K-slice ks_i; warps beyond ks*rl only join the barriers
   const bool active = warp < p.ks * p.rl;
   const int ks_i = warp % p.ks, rl_i = warp / p.ks;
   const int sb0 = ks_i * p.slice_blocks;
   const int nblk = active ? max(0, min(p.slice_blocks, p.bpr - sb0)) : 0;
   const int units = nblk * UPB;
+  const int R = p.rows_per_item;
   const int64_t row_bytes = (int64_t)p.bpr * TS;
   const int64_t w_safe = p.w_bytes & ~int64_t(15);
   const uint32_t slice_bytes = (uint32_t)nblk * TS;
-  // rows of this CTA: r = (i * gridDim.x + blockIdx.x) * rl + rl_i
-  const int64_t rows_per_iter = (int64_t)gridDim.x * p.rl;
+  const bool contiguous = p.ks == 1;
+  // row groups of this CTA: group = (i * gridDim.x + blockIdx.x) * rl + rl_i, rows [group*R, group*R + R)
+  const int64_t groups = (p.n + R - 1) / R;
+  const int64_t groups_per_iter = (int64_t)gridDim.x * p.rl;
   const int64_t first = (int64_t)blockIdx.x * p.rl;
-  const int iters = first < p.n ? (int)((p.n - first + rows_per_iter - 1) / rows_per_iter) : 0;  // uniform over the CTA
+  const int iters = first < groups ? (int)((groups - first + groups_per_iter - 1) / groups_per_iter) : 0;  // uniform over the CTA
+  const int64_t my_first = first + rl_i;
+  const int my_iters = (active && nblk > 0 && my_first < groups) ? (int)((groups - my_first + groups_per_iter - 1) / groups_per_iter) : 0;
+  const int64_t row_stride = groups_per_iter * R;      // rows between two items of this warp
+  const int64_t byte_stride = row_stride * row_bytes;
 
-  auto row_of = [&](int i) { return first + (int64_t)i * rows_per_iter + rl_i; };
-  auto issue = [&](int i, int st) {  // lane 0
-    const int64_t beg = row_of(i) * row_bytes + (int64_t)sb0 * TS, end = beg + slice_bytes;
-    const int64_t abeg = beg & ~int64_t(15);
-    int64_t aend = (end + 15) & ~int64_t(15);
-    if (aend > w_safe) aend = w_safe;
-    const uint32_t bytes = aend > abeg ? (uint32_t)(aend - abeg) : 0u;
-    if (bytes) {
-      mbar_expect_tx(&bars[st], bytes);
-      bulk_g2s(ring + (size_t)st * p.stage_bytes, p.w + abeg, bytes, &bars[st]);
+  // copy of row-range [r0, r0+cnt) (slice part) into stage st; lane 0 (contiguous) or lanes 0..cnt-1
+  auto issue = [&](int64_t r0, int st) {
+    const int64_t left_i = p.n - r0; const int cnt = (int)(left_i < R ? left_i : R);
+    uint8_t* dst = ring + (size_t)st * p.stage_bytes;
+    if (contiguous) {
+      if (lane == 0) {
+        const int64_t beg = r0 * row_bytes, end = beg + (int64_t)cnt * row_bytes;
+        const int64_t abeg = beg & ~int64_t(15);
+        int64_t aend = (end + 15) & ~int64_t(15);
+        if (aend > w_safe) aend = w_safe;
+        const uint32_t bytes = aend > abeg ? (uint32_t)(aend - abeg) : 0u;
+        if (bytes) {
+          mbar_expect_tx(&bars[st], bytes);
+          bulk_g2s(dst, p.w + abeg, bytes, &bars[st]);
+        } else {
+          mbar_arrive(&bars[st]);
+        }
+      }
     } else {
-      mbar_arrive(&bars[st]);
+      // one copy per row; lane j computes and issues row j's, lane 0 announces the byte total first
+      const int64_t beg = (r0 + lane) * row_bytes + (int64_t)sb0 * TS, end = beg + slice_bytes;
+      const int64_t abeg = beg & ~int64_t(15);
+      int64_t aend = (end + 15) & ~int64_t(15);
+      if (aend > w_safe) aend = w_safe;
+      const uint32_t bytes = (lane < cnt && aend > abeg) ? (uint32_t)(aend - abeg) : 0u;
+      uint32_t total = bytes;
+#pragma unroll
+      for (int m = 1; m < G1_R; m <<= 1) total += __shfl_xor_sync(0xffffffffu, total, m);  // lanes 0..3 hold the sum of lanes 0..3
+      if (lane == 0) {
+        if (total) mbar_expect_tx(&bars[st], total);
+        else mbar_arrive(&bars[st]);
+      }
+      __syncwarp();
+      if (bytes) bulk_g2s(dst + (size_t)lane * p.slot_bytes, p.w + abeg, bytes, &bars[st]);
     }
   };
-  auto has_row = [&](int i) { return active && nblk > 0 && i < iters && row_of(i) < p.n; };
 
-  int p_i = 0, p_st = 0;
+  int p_it = 0, p_st = 0;
+  int64_t p_row = my_first * R;
   for (int s = 0; s < p.stages - 1; ++s) {
-    if (has_row(p_i)) {
-      if (lane == 0) issue(p_i, p_st);
+    if (p_it < my_iters) {
+      issue(p_row, p_st);
+      p_row += row_stride;
+      ++p_it;
       if (++p_st == p.stages) p_st = 0;
     }
-    ++p_i;
   }
 
-  // this lane's activations, loaded once (unit u of the slice -> unit sb0*UPB + u of the row)
+  // The weight copies above touch nothing another kernel writes; everything below does.
+  pdl_wait();
+  // this lane's units (block offset inside the slice, sub-unit) and their activations
   uint32_t xq[UMAX][T::XW];
   float xd[UMAX][T::XD];
+  int uoff[UMAX], usub[UMAX];
   {
     const uint8_t* qs = p.xq;
     const float2* ds = reinterpret_cast<const float2*>(p.xq + kpad);
 #pragma unroll
     for (int j = 0; j < UMAX; ++j) {
       const int u = lane + 32 * j;
+      uoff[j] = (u / UPB) * TS;
+      usub[j] = u % UPB;
       if (u < units) {
         T::load_x(qs, ds, sb0 * UPB + u, 0, xq[j], xd[j]);
       } else {
@@ -364,67 +407,84 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 3) gemv1_kernel(const G1Params 
     }
   }
   if (TYPE == T_IQ2_XXS) __syncthreads();  // tables staged
+  pdl_trigger();  // activations are in registers: the next kernel may be scheduled behind this one
 
   out_t* y = static_cast<out_t*>(p.y);
   int c_st = 0;
   uint32_t c_phase = 0;
   bool dead = false;
+  int64_t c_row = my_first * R;
   for (int i = 0; i < iters; ++i) {
-    if (has_row(p_i) && !dead) {
-      if (lane == 0) issue(p_i, p_st);
-      if (++p_st == p.stages) p_st = 0;
-    }
-    ++p_i;
-    if (has_row(i) && !dead) {
+    const bool mine = i < my_iters && !dead;
+    if (mine) {
+      if (p_it < my_iters) {
+        issue(p_row, p_st);
+        p_row += row_stride;
+        ++p_it;
+        if (++p_st == p.stages) p_st = 0;
+      }
       if (!mbar_wait_bounded(&bars[c_st], c_phase)) {
         if (lane == 0) atomicExch(p.status, E_TIMEOUT);
         dead = true;
       }
-      const int64_t r = row_of(i);
-      const int64_t beg = r * row_bytes + (int64_t)sb0 * TS;
+    }
+    if (mine && !dead) {
+      const int64_t left_c = p.n - c_row; const int cnt = (int)(left_c < R ? left_c : R);
       uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
-      const uint8_t* data = stage + (beg & 15);
-      if (beg + slice_bytes > w_safe) {  // tail bytes the bulk copy must not touch
-        const int64_t abeg = beg & ~int64_t(15);
-        for (int64_t o = w_safe + lane; o < beg + slice_bytes; o += 32) stage[o - abeg] = p.w[o];
+      const int64_t beg0 = c_row * row_bytes + (int64_t)sb0 * TS;
+      const int64_t last_end = (c_row + cnt - 1) * row_bytes + (int64_t)sb0 * TS + slice_bytes;
+      if (last_end > w_safe) {  // tail bytes the bulk copy must not touch: fetched with plain loads
+        const int64_t lbeg = contiguous ? beg0 : last_end - slice_bytes;
+        const int64_t abeg = lbeg & ~int64_t(15);
+        uint8_t* base = contiguous ? stage : stage + (size_t)(cnt - 1) * p.slot_bytes;
+        for (int64_t o = w_safe + lane; o < last_end; o += 32) base[o - abeg] = p.w[o];
         __syncwarp();
       }
-      float acc = 0.f;
-      if (!dead) {
+      float acc[G1_R];
 #pragma unroll
-        for (int j = 0; j < UMAX; ++j) {
-          const int u = lane + 32 * j;
-          if (u < units) acc += T::unit(data + (u / UPB) * TS, u % UPB, xq[j], xd[j], tb);
+      for (int rr = 0; rr < G1_R; ++rr) {
+        acc[rr] = 0.f;
+        if (rr < cnt) {
+          const uint8_t* data = contiguous ? stage + (beg0 & 15) + (size_t)rr * row_bytes
+                                           : stage + (size_t)rr * p.slot_bytes + ((beg0 + rr * row_bytes) & 15);
+#pragma unroll
+          for (int j = 0; j < UMAX; ++j)
+            if (lane + 32 * j < units) acc[rr] += T::unit(data + uoff[j], usub[j], xq[j], xd[j], tb);
         }
       }
-      acc = warp_sum(acc);
-      if (lane == 0) {
-        if (p.ks == 1) y[r] = from_float<out_t>(acc);
-        else partial[((i % G1_BATCH) * p.rl + rl_i) * p.ks + ks_i] = acc;
+#pragma unroll
+      for (int rr = 0; rr < G1_R; ++rr) {
+        if (rr < cnt) {
+          const float v = warp_sum(acc[rr]);
+          if (lane == 0) {
+            if (p.ks == 1) y[c_row + rr] = from_float<out_t>(v);
+            else partial[(((i % G1_BATCH) * p.rl + rl_i) * G1_R + rr) * p.ks + ks_i] = v;
+          }
+        }
       }
       __syncwarp();
       if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
-    } else if (active && p.ks > 1 && lane == 0 && i < iters && row_of(i) < p.n) {
-      partial[((i % G1_BATCH) * p.rl + rl_i) * p.ks + ks_i] = 0.f;  // empty slice (cannot happen with the planner, kept for safety)
+      c_row += row_stride;
     }
     if (p.ks > 1 && ((i % G1_BATCH) == G1_BATCH - 1 || i == iters - 1)) {
       // add the slice partials in slice order and store; every warp of the CTA takes part
       __syncthreads();
       const int i0 = i - (i % G1_BATCH);
-      const int cnt = (i - i0 + 1) * p.rl;
+      const int cnt = (i - i0 + 1) * p.rl * G1_R;
       for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
-        const int ii = i0 + t / p.rl, rr = t % p.rl;
-        const int64_t r = first + (int64_t)ii * rows_per_iter + rr;
-        if (r < p.n) {
+        const int rr = t % G1_R, g2 = t / G1_R;
+        const int ii = i0 + g2 / p.rl, gl = g2 % p.rl;
+        const int64_t r = (first + (int64_t)ii * groups_per_iter + gl) * R + rr;
+        if (rr < R && r < p.n) {
           float s = 0.f;
-          for (int q = 0; q < p.ks; ++q) s += partial[((ii % G1_BATCH) * p.rl + rr) * p.ks + q];
+          for (int q = 0; q < p.ks; ++q) s += partial[(((ii % G1_BATCH) * p.rl + gl) * G1_R + rr) * p.ks + q];
           y[r] = from_float<out_t>(s);
         }
       }
       __syncthreads();
     }
   }
-  (void)QK;
+  (void)byte_stride;
 }
 
 // ---- host -----------------------------------------------------------------------------------
@@ -438,8 +498,10 @@ template <int TYPE, typename out_t>
 static int launch_g1(G1Params p, cudaStream_t stream) {
   using T = G1<TYPE>;
   constexpr int TS = BlockTraits<TYPE>::TS;
-  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 3);
-  static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 3);
+  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 2);
+  static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
+  static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
+  static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 6000);
   const int cap_blocks = 32 * T::UMAX / T::UPB;  // blocks whose units fit one lane-register set
   int ks = 1;
   while (ks < 8 && (p.bpr + ks - 1) / ks > cap_blocks) ks *= 2;
@@ -447,10 +509,15 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   p.ks = ks;
   p.rl = G1_WARPS / ks;
   p.slice_blocks = (p.bpr + ks - 1) / ks;
+  const int slice_bytes = p.slice_blocks * TS;
+  int R = rows_env < 1 ? 1 : (rows_env > G1_R ? G1_R : rows_env);
+  while (R > 1 && (int64_t)R * slice_bytes > item_env) --R;
+  p.rows_per_item = R;
+  p.slot_bytes = ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16);
   p.stages = stages_env < 2 ? 2 : stages_env;
-  p.stage_bytes = (int)round_up((int64_t)p.slice_blocks * TS + 32, 16);
+  p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
   const size_t tables = TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0;
-  const size_t smem = tables + (size_t)G1_BATCH * 8 * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
+  const size_t smem = tables + (size_t)G1_BATCH * 8 * G1_R * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
   if (smem > 227 * 1024) return 1;
   auto kern = gemv1_kernel<TYPE, out_t>;
   static size_t configured[64] = {0};
@@ -464,11 +531,11 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   if (per_sm > ctas_env) per_sm = ctas_env;
   if (per_sm < 1) per_sm = 1;
   int64_t grid = 148 * per_sm;
-  const int64_t need = (p.n + p.rl - 1) / p.rl;
+  const int64_t groups = (p.n + R - 1) / R;
+  const int64_t need = (groups + p.rl - 1) / p.rl;
   if (grid > need) grid = need;
   if (grid < 1) grid = 1;
-  kern<<<(int)grid, G1_WARPS * 32, smem, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+  return launch_pdl(kern, dim3((unsigned)grid), dim3(G1_WARPS * 32), smem, stream, p) == cudaSuccess ? E_OK : E_CUDA;
 }
 
 template <int TYPE>

@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
                                                             int64_t M, int64_t K, int64_t kpad, int sum_mode,
                                                             int64_t ldb, int corr_mode, const int32_t* __restrict__ gather_ids,
                                                             int64_t gather_div, int64_t gather_limit) {
+  pdl_trigger();  // the consumer kernel may start its weight prefetch now; it waits for this grid before reading
+  pdl_wait();     // the activations (and the scratch we overwrite) belong to earlier kernels
   const int lane = threadIdx.x & 31;
   const int64_t nbr = kpad / 32;                                   // blocks per row
   const int64_t total = M * nbr;
@@ -136,13 +138,13 @@ static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t
   uint8_t* o = static_cast<uint8_t*>(out);
   switch (x_dtype) {
     case DT_F32:
-      quantize_q8_1_kernel<float, MODE><<<blocks, 256, 0, stream>>>((const float*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      launch_pdl(quantize_q8_1_kernel<float, MODE>, dim3(blocks), dim3(256), 0, stream, (const float*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
       break;
     case DT_F16:
-      quantize_q8_1_kernel<__half, MODE><<<blocks, 256, 0, stream>>>((const __half*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      launch_pdl(quantize_q8_1_kernel<__half, MODE>, dim3(blocks), dim3(256), 0, stream, (const __half*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
       break;
     case DT_BF16:
-      quantize_q8_1_kernel<__nv_bfloat16, MODE><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      launch_pdl(quantize_q8_1_kernel<__nv_bfloat16, MODE>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
       break;
     default:
       return E_BAD_DTYPE;
