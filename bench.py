@@ -141,16 +141,41 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_ncu_case(spec: str):
+    """Six back-to-back calls of one entry point on distinct weight copies, nothing timed."""
+    import torch
+
+    from gguf_b200 import capi, synth
+
+    op, t, n, k, m = spec.split(",")
+    t, n, k, m = int(t), int(n), int(k), int(m)
+    base = synth.make_weight(t, n, k, seed=1)
+    ws = [torch.from_numpy(base).to("cuda") for _ in range(6)]
+    x = torch.from_numpy(synth.make_activation(m, k, seed=0)).to("cuda")
+    fn = {"gemv": capi.mul_mat_vec_a8, "mmq": capi.mul_mat_a8, "dqmm": capi.dequant_matmul}.get(op)
+    for w in ws:
+        if op == "dequantize":
+            capi.dequantize(w, t, n, k)
+        else:
+            fn(w, x, t, n)
+    torch.cuda.synchronize()
+    print("ncu case done, device status", capi.last_status())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ncu-case", default=None,
+                    help="op,type,N,K,M: run six plain calls of one kernel and exit (a small target for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.ncu_case:
+        return run_ncu_case(args.ncu_case)
 
     import torch
     import torch.distributed as dist
@@ -296,7 +321,7 @@ def main():
             bytes_per_launch = total_bytes / g / calls_per_step
             achieved = bytes_per_launch / t_k / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None, "peak_source": which, "kernel": "gemv_kernel<Q4_K, 1 vector>",
+                    "traffic": None, "peak_source": which, "kernel": "gemv1_kernel<Q4_K> (single-vector GEMV)",
                     "us_per_launch": t_k * 1e6, "algorithmic_bytes_per_launch": bytes_per_launch}
     if world > 1:
         dist.barrier()
