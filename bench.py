@@ -321,10 +321,35 @@ def main():
             bytes_per_launch = total_bytes / g / calls_per_step
             achieved = bytes_per_launch / t_k / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None, "peak_source": which, "kernel": "gemv1_kernel<Q4_K> (single-vector GEMV)",
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu capture
+                    # (profiles/gemv1_q4k_llama8b_decode.md); both shapes move the same 33.03 MB of weights
+                    "traffic": 33082500 // g, "peak_source": which, "kernel": "gemv1_kernel<Q4_K> (single-vector GEMV)",
                     "us_per_launch": t_k * 1e6, "algorithmic_bytes_per_launch": bytes_per_launch}
     if world > 1:
         dist.barrier()
+
+    # ---- secondary figure (N = 1 only): the prefill GEMM of the same configuration, M = 512 -----
+    extras = None
+    if world == 1:
+        with torch.cuda.stream(stream):
+            xm = torch.randn(512, SHAPES[0][1], device=dev, dtype=torch.float16)
+            for c in range(3):
+                capi.mul_mat_a8(weights[0][c], xm, Q4_K, SHAPES[0][0])
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for c in range(COPIES):
+                capi.mul_mat_a8(weights[0][c], xm, Q4_K, SHAPES[0][0])
+            e1.record(stream)
+            stream.synchronize()
+            t_mm = e0.elapsed_time(e1) / 1e3 / COPIES
+        flops = 2.0 * 512 * SHAPES[0][0] * SHAPES[0][1]
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+        extras = {"prefill_gemm_q4k_m512_14336x4096": {
+            "us_per_call": t_mm * 1e6, "tflops": flops / t_mm / 1e12, "bound": "tensor (fp16 operands, fp32 accumulate)",
+            "frac_of_measured_16bit_peak": flops / t_mm / 1e12 / tf_peak, "frac_of_2x_that_as_int8_proxy": flops / t_mm / 1e12 / (2 * tf_peak),
+            "includes": "q8_1 quantization of the 512x4096 activations + tcgen05 GEMM"}}
 
     status = capi.last_status()
     if rank != 0:
@@ -368,6 +393,7 @@ def main():
         "gpu_launches": args.steps * calls_per_step * 2,
         "roofline": roof, "cpu_baseline": cpu_base, "clocks": clocks.summary(),
         "parity": {"rel_l2_vs_oracle": rel, "device_status": status},
+        "extras": extras,
     }
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -152,6 +152,10 @@ int gguf_b200_gemv_prepared(const void* W, const void* ws, void* Y, int type, in
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, static_cast<cudaStream_t>(stream));
 }
 
+// Below this many tokens the op is bound by reading the weights once, which the GEMV kernel does
+// best; it then runs with the tiled kernels' formulas (Q4_K min term from the stored fp16 sum).
+static const int64_t kMmqGemvMaxTokens = 16;
+
 int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
                          int64_t M, int64_t N, int64_t K, void* stream) {
   int rc = check_common(W, X, Y, type, dtype, M, N, K);
@@ -159,10 +163,15 @@ int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_
   if (!is_mmq_type(type)) return E_BAD_TYPE;
   if (!ws || !aligned16(ws)) return E_BAD_POINTER;
   const int64_t ldb = mmq_ldb(type, K);
-  if (ws_bytes < M * ldb * 2) return E_WORKSPACE;
+  if (ws_bytes < M * ldb * 2) return E_WORKSPACE;   // (always >= the GEMV scratch of the same M, K)
   int* st = status_ptr();
   if (!st) return E_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M <= kMmqGemvMaxTokens) {
+    rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, 0, 0, CORR_NONE, nullptr, 1, 0, s);
+    if (rc) return rc;
+    return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
+  }
   rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), nullptr, 1, 0, s);
   if (rc) return rc;
   MmqArgs a{};

@@ -19,10 +19,11 @@
 // Tile: 128 weight rows (UMMA M) x TN tokens (UMMA N, 16..256) x 64 values per stage, both
 // operands K-major in shared memory with the 128-byte swizzle.  Weight rows sit on the M axis
 // so that small token counts (M = 8, MoE blocks) do not waste the 128-row instruction.
-// Warp roles:  warps 0-3 decode weights into the A stage (one row per thread) and later run
-// the epilogue (tcgen05.ld, one TMEM lane = one weight row per thread); warp 4 issues the TMA
-// loads of the B tile (tiled 2-D tensor map, no multicast) and owns the TMEM allocation;
-// warp 5 lane 0 issues tcgen05.mma and commits stage releases.  A 4-deep mbarrier ring
+// Warp roles:  warps 0-7 decode weights into the A stage (two threads per row, 32 values each,
+// raw bytes prefetched two stages ahead in registers) and later run the epilogue (tcgen05.ld,
+// one TMEM lane = one weight row; the two threads of a row split the token columns); warp 8
+// issues the TMA loads of the B tile (tiled 2-D tensor map, no multicast) and owns the TMEM
+// allocation; warp 9 lane 0 issues tcgen05.mma and commits stage releases.  A 4-deep mbarrier ring
 // decouples them.  Every wait is bounded and reports through the status word.
 #include <cuda.h>
 
@@ -30,14 +31,17 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "mmq_decode.cuh"
 #include "tables.cuh"
 
 namespace gguf_b200 {
 
 constexpr int MMQ_ROWS = 128;
 constexpr int MMQ_BK = 64;
-constexpr int MMQ_STAGES = 4;
-constexpr int MMQ_THREADS = 192;
+__host__ __device__ constexpr int mmq_stages(int tn) { return tn > 128 ? 3 : 4; }
+constexpr int MMQ_PRODUCER_WARPS = 8;   // two threads per weight row of a stage: 32 values each
+constexpr int MMQ_THREADS = (MMQ_PRODUCER_WARPS + 3) * 32;   // + B loader, MMA issuer, raw-weight loader
+constexpr int MMQ_MAX_RAW = 6;
 constexpr int MMQ_A_STAGE = MMQ_ROWS * MMQ_BK * 2;  // 16 KB
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
@@ -94,237 +98,6 @@ __host__ __device__ inline uint32_t umma_idesc(int m, int n, int fmt) {
   return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// ---- weight decoders: 64 consecutive values of one row -> 32 packed 16-bit pairs --------
-
-template <typename ab_t> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(a)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(b)) << 16);
-}
-__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
-// (1024 + a, 1024 + b) as half2 for small unsigned a, b: exact integers, so subtracting
-// 1024 + bias afterwards yields (a - bias, b - bias) without any rounding.
-__device__ __forceinline__ __half2 ints_plus_1024(uint32_t a, uint32_t b) { return u32_as_h2(0x64006400u | a | (b << 16)); }
-__device__ __forceinline__ __half2 hmul2_rn(__half2 a, __half2 b) { return __hmul2_rn(a, b); }
-
-__device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
-
-struct DecodeCtx {
-  const uint64_t* grid;   // IQ2_XXS tables in shared memory
-  const uint8_t* signs;
-  const int8_t* kv;       // IQ4_XS levels in shared memory
-};
-
-template <int TYPE, typename ab_t> struct Decoder;
-
-// Q4_0: value = half((q - 8) * d), dequantize_q4_0 (dequantize.cuh:3-15)
-template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
-  static __device__ __forceinline__ void slab(const uint8_t* row, int s, int64_t K, const DecodeCtx&, uint32_t (&out)[32]) {
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      const int64_t blk_i = 2 * (int64_t)s + b;
-      if (blk_i * 32 >= K) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) out[16 * b + i] = 0;
-        continue;
-      }
-      const uint8_t* blk = row + blk_i * 18;
-      const uint32_t du = ldg16(blk);
-      const __half2 d2 = u32_as_h2(du | (du << 16));
-      const __half2 off = __floats2half2_rn(1032.f, 1032.f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t t = ldg16(blk + 2 + 2 * i);  // qs[2i], qs[2i+1]
-        out[16 * b + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(t & 0xF, (t >> 8) & 0xF), off), d2));
-        out[16 * b + 8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((t >> 4) & 0xF, (t >> 12) & 0xF), off), d2));
-      }
-    }
-  }
-  // correction columns: A'[n, g] = d of block g (pairs with 8*(d8*sum(q8) - s8) on the B side)
-  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[32]) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int64_t g = 64 * (int64_t)c + 2 * i;
-      const uint32_t a = g * 32 < K ? ldg16(row + g * 18) : 0u;
-      const uint32_t b = (g + 1) * 32 < K ? ldg16(row + (g + 1) * 18) : 0u;
-      out[i] = a | (b << 16);
-    }
-  }
-};
-
-// Q8_0: value = half(q * d), dequantize_q8_0 (dequantize.cuh:69-78)
-template <typename ab_t> struct Decoder<T_Q8_0, ab_t> {
-  static __device__ __forceinline__ void slab(const uint8_t* row, int s, int64_t K, const DecodeCtx&, uint32_t (&out)[32]) {
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      const int64_t blk_i = 2 * (int64_t)s + b;
-      if (blk_i * 32 >= K) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) out[16 * b + i] = 0;
-        continue;
-      }
-      const uint8_t* blk = row + blk_i * 34;
-      const uint32_t du = ldg16(blk);
-      const __half2 d2 = u32_as_h2(du | (du << 16));
-      const __half2 off = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t t = ldg16(blk + 2 + 2 * i) ^ 0x8080u;  // int8 -> biased unsigned
-        out[16 * b + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(t & 0xFF, t >> 8), off), d2));
-      }
-    }
-  }
-  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[32]) {}
-};
-
-// 6-bit (scale, min) pair j of a Q4_K super-block from its 12 packed bytes held in three
-// registers (bytes 0-3, 4-7, 8-11); same packing as get_scale_min_k4, dequantize.cuh:156-163.
-__device__ __forceinline__ void q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, int& sc, int& m) {
-  if (j < 4) {
-    sc = (w0 >> (8 * j)) & 63;
-    m = (w1 >> (8 * j)) & 63;
-  } else {
-    const int sh = 8 * (j - 4);
-    const uint32_t b = (w2 >> sh) & 0xFF;
-    sc = (b & 0xF) | ((((w0 >> sh) & 0xFF) >> 6) << 4);
-    m = (b >> 4) | ((((w1 >> sh) & 0xFF) >> 6) << 4);
-  }
-}
-
-// Q4_K: A = half(d1 * q) with d1 = half(d * sc); the -dmin*m part is a correction column
-template <typename ab_t> struct Decoder<T_Q4_K, ab_t> {
-  static __device__ __forceinline__ void slab(const uint8_t* row, int s, int64_t, const DecodeCtx&, uint32_t (&out)[32]) {
-    const uint8_t* blk = row + (int64_t)(s >> 2) * 144;
-    const int p = s & 3;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-    const __half dall = __ushort_as_half((unsigned short)(hdr.x & 0xffff));
-    int sc0, sc1, m0, m1;
-    q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * p, sc0, m0);
-    q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * p + 1, sc1, m1);
-    (void)m0;
-    (void)m1;
-    const __half d1 = __hmul_rn(dall, __int2half_rn(sc0)), d2 = __hmul_rn(dall, __int2half_rn(sc1));
-    const __half2 d1v = __half2half2(d1), d2v = __half2half2(d2);
-    const __half2 off = __floats2half2_rn(1024.f, 1024.f);
-    const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + 32 * p);
-    const uint4 qa = __ldg(qp), qb = __ldg(qp + 1);
-    const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {  // word i: bytes 4i..4i+3 -> values 4i.. (low nibbles) and 32+4i.. (high)
-      const uint32_t w = q[i];
-      out[2 * i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(w & 0xF, (w >> 8) & 0xF), off), d1v));
-      out[2 * i + 1] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((w >> 16) & 0xF, (w >> 24) & 0xF), off), d1v));
-      out[16 + 2 * i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((w >> 4) & 0xF, (w >> 12) & 0xF), off), d2v));
-      out[16 + 2 * i + 1] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((w >> 20) & 0xF, (w >> 28) & 0xF), off), d2v));
-    }
-  }
-  // correction columns: A'[n, g] = half(dmin * m_g)  (pairs with -s8 on the B side)
-  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[32]) {
-#pragma unroll
-    for (int sb = 0; sb < 8; ++sb) {
-      const int64_t sbi = 8 * (int64_t)c + sb;  // super-block index: 8 groups each
-      if (sbi * 256 >= K) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[4 * sb + i] = 0;
-        continue;
-      }
-      const uint8_t* blk = row + sbi * 144;
-      const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-      const __half dmin = __ushort_as_half((unsigned short)(hdr.x >> 16));
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        int sc, ma, mb;
-        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * i, sc, ma);
-        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * i + 1, sc, mb);
-        out[4 * sb + i] = (uint32_t)__half_as_ushort(__hmul_rn(dmin, __int2half_rn(ma))) |
-                          ((uint32_t)__half_as_ushort(__hmul_rn(dmin, __int2half_rn(mb))) << 16);
-      }
-    }
-  }
-};
-
-// Q6_K: value = half(d * half(sc * (code - 32))), dequantize_block_q6_K (dequantize.cuh:232-256)
-template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
-  static __device__ __forceinline__ void slab(const uint8_t* row, int s, int64_t, const DecodeCtx&, uint32_t (&out)[32]) {
-    const uint8_t* blk = row + (int64_t)(s >> 2) * 210;
-    const int ip = (s >> 1) & 1, odd = s & 1;
-    const uint32_t du = ldg16(blk + 208);
-    const __half2 d2 = u32_as_h2(du | (du << 16));
-    const __half2 off = __floats2half2_rn(1056.f, 1056.f);  // 1024 + 32
-    const uint8_t* ql = blk + 64 * ip;
-    const uint8_t* qh = blk + 128 + 32 * ip;
-    const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192 + 8 * ip + 4 * odd);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {  // pair i: values 2i, 2i+1 of the slab
-      const int j = 2 * i;          // ql byte index 64ip + j; qh byte 32ip + j%32, shift 2q, q = 2*odd + j/32
-      const uint32_t l = ldg16(ql + j) >> (4 * odd);
-      const uint32_t h = ldg16(qh + (j & 31)) >> (2 * (2 * odd + (j >> 5)));
-      const uint32_t c0 = (l & 0xF) | ((h & 3) << 4), c1 = ((l >> 8) & 0xF) | (((h >> 8) & 3) << 4);
-      const int scv = (int)__ldg(sc + 2 * (j >> 5) + ((j & 31) >> 4));
-      const __half2 s2 = __half2half2(__int2half_rn(scv));
-      out[i] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(ints_plus_1024(c0, c1), off))));
-    }
-  }
-  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[32]) {}
-};
-
-// IQ4_XS: fp32 d*(ls-32)*level rounded once to ab_t, dequantize_block_iq4_xs (dequantize.cuh:420-435)
-template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
-  static __device__ __forceinline__ void slab(const uint8_t* row, int s, int64_t, const DecodeCtx& cx, uint32_t (&out)[32]) {
-    const uint8_t* blk = row + (int64_t)(s >> 2) * 136;
-    const uint2 hdr = __ldg(reinterpret_cast<const uint2*>(blk));
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int ib = 2 * (s & 3) + t;
-      const int ls = (int)(((hdr.y >> (4 * ib)) & 0xF) | ((((hdr.x >> 16) >> (2 * ib)) & 3) << 4)) - 32;
-      const float dl = d * (float)ls;
-      const uint2* qp = reinterpret_cast<const uint2*>(blk + 8 + 16 * ib);
-      const uint2 qa = __ldg(qp), qb = __ldg(qp + 1);
-      const uint32_t q[4] = {qa.x, qa.y, qb.x, qb.y};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {  // bytes 4i..4i+3: values 4i.. (low) and 16+4i.. (high)
-        const uint32_t w = q[i];
-        out[16 * t + 2 * i] = pack2<ab_t>(dl * (float)cx.kv[w & 0xF], dl * (float)cx.kv[(w >> 8) & 0xF]);
-        out[16 * t + 2 * i + 1] = pack2<ab_t>(dl * (float)cx.kv[(w >> 16) & 0xF], dl * (float)cx.kv[(w >> 24) & 0xF]);
-        out[16 * t + 8 + 2 * i] = pack2<ab_t>(dl * (float)cx.kv[(w >> 4) & 0xF], dl * (float)cx.kv[(w >> 12) & 0xF]);
-        out[16 * t + 8 + 2 * i + 1] = pack2<ab_t>(dl * (float)cx.kv[(w >> 20) & 0xF], dl * (float)cx.kv[(w >> 28) & 0xF]);
-      }
-    }
-  }
-  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[32]) {}
-};
-
-// IQ2_XXS: fp32 d*(0.5+s)*0.25*grid*sign rounded once, dequantize_block_iq2_xxs (dequantize.cuh:258-275)
-template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
-  static __device__ __forceinline__ void slab(const uint8_t* row, int s, int64_t, const DecodeCtx& cx, uint32_t (&out)[32]) {
-    const uint8_t* blk = row + (int64_t)(s >> 2) * 66;
-    const float dh = __half2float(__ushort_as_half((unsigned short)ldg16(blk)));
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const uint8_t* q2 = blk + 2 + 8 * (2 * (s & 3) + t);
-      const uint32_t idx = ldg16(q2) | (ldg16(q2 + 2) << 16);
-      const uint32_t aux = ldg16(q2 + 4) | (ldg16(q2 + 6) << 16);
-      const float d = dh * (0.5f + (float)(aux >> 28)) * 0.25f;
-#pragma unroll
-      for (int il = 0; il < 4; ++il) {
-        const uint64_t g = cx.grid[(idx >> (8 * il)) & 0xFF];
-        const uint32_t sg = cx.signs[(aux >> (7 * il)) & 127];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = d * (float)((uint32_t)(g >> (16 * j)) & 0xFF) * ((sg >> (2 * j)) & 1 ? -1.f : 1.f);
-          const float b = d * (float)((uint32_t)(g >> (16 * j + 8)) & 0xFF) * ((sg >> (2 * j + 1)) & 1 ? -1.f : 1.f);
-          out[16 * t + 4 * il + j] = pack2<ab_t>(a, b);
-        }
-      }
-    }
-  }
-  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[32]) {}
-};
-
 // ---- kernel -----------------------------------------------------------------------------
 
 struct MmqParams {
@@ -339,17 +112,30 @@ struct MmqParams {
   const int32_t* n_post_pad;
   int64_t expert_stride_bytes, rows_out;
   int* status;
+  int debug;   // tuning aid (bit mask): 1 no decode, 2 no A store, 4 no MMA, 8 no B load
+  int raw_tma;            // 1: raw weight chunks arrive by 2-D TMA boxes (wmap), 0: by cp.async pieces
+  int raw_stages;         // depth of the raw ring
+  int64_t w_row0;         // first row of this matrix in wmap (MoE: added to expert * N)
 };
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE>
-__global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const MmqParams p) {
+__global__ void __launch_bounds__(MMQ_THREADS, (TN <= 64 ? 2 : 1)) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const MmqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
+  constexpr int MMQ_STAGES = mmq_stages(TN);
+  // raw ring geometry: dense TMA boxes or padded cp.async slots
+  const int kc = p.raw_tma ? TmaGeom<TYPE>::KC_T : RawGeom<TYPE>::KC;
+  const int rbc = kc / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;
+  const int slot = p.raw_tma ? rbc : RawGeom<TYPE>::SLOT;
+  const int RAW_STAGE = MMQ_ROWS * slot;
   uint8_t* sA = smem;
   uint8_t* sB = smem + MMQ_STAGES * MMQ_A_STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB + MMQ_STAGES * B_STAGE);
+  uint8_t* sRaw = sB + MMQ_STAGES * B_STAGE + 4096;   // barriers and codebooks take the 4 KB in between
+  uint64_t* raw_full = bars + 3 * MMQ_STAGES + 2 + 256 + 16 + 2;   // after tmem slot, grid, signs, levels
+  uint64_t* raw_empty = raw_full + MMQ_MAX_RAW;
   uint64_t* full_a = bars;
   uint64_t* full_b = bars + MMQ_STAGES;
   uint64_t* empty = bars + 2 * MMQ_STAGES;
@@ -374,11 +160,15 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MMQ_STAGES; ++s) {
-      mbar_init(&full_a[s], 4);
+      mbar_init(&full_a[s], MMQ_PRODUCER_WARPS);
       mbar_init(&full_b[s], 1);
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
+    for (int s = 0; s < MMQ_MAX_RAW; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], MMQ_PRODUCER_WARPS);
+    }
     fence_barrier_init();
   }
   if (TYPE == T_IQ2_XXS) {
@@ -386,7 +176,7 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
     for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = d_ksigns_iq2xs[i];
   }
   if (TYPE == T_IQ4_XS && threadIdx.x < 16) s_kv[threadIdx.x] = d_kvalues_iq4nl[threadIdx.x];
-  if (warp == 4) {
+  if (warp == MMQ_PRODUCER_WARPS) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -396,45 +186,125 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
 
-  if (warp < 4) {
-    // ---------------- A producers: thread r decodes row n0 + r ----------------
-    const int r = threadIdx.x;
+  if (warp < MMQ_PRODUCER_WARPS) {
+    // ---------------- A producers: threads r and r+128 decode the two 32-value halves of row n0 + r ----------------
+    const int r = threadIdx.x & 127, half = threadIdx.x >> 7;
     const int64_t n = n0 + r;
     const bool live = n < p.N;
     const uint8_t* row = wbase + (live ? n : 0) * p.row_bytes;
     DecodeCtx cx{s_grid, s_signs, s_kv};
     const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-    for (int i = 0; i < nk && ok; ++i) {
+    const int nunits = (int)((p.K + 31) / 32);   // 32-value units of a row that exist
+    // Raw weight bytes reach shared memory in chunks of KC values per row: warp w copies rows
+    // w, w+8, ... of the tile, one coalesced 16-byte cp.async per lane and row (a row's chunk is
+    // 66..272 contiguous bytes), one chunk ahead of the decode.  Thread-per-row global loads
+    // would touch 32 cache lines per warp instruction and stall on the L1 tag stage instead.
+    const int SPC = kc / MMQ_BK;                  // MMA stages per chunk
+    const int nchunks = (p.nmain + SPC - 1) / SPC;
+    const int64_t tile_end = (int64_t)p.N * p.row_bytes;   // bytes of this weight matrix (expert)
+    auto issue_chunk = [&](int c) {
+      uint8_t* slot0 = sRaw + (size_t)(c % 2) * RAW_STAGE;
+      for (int rr = warp; rr < MMQ_ROWS; rr += MMQ_PRODUCER_WARPS) {
+        const int64_t nn = n0 + rr;
+        if (nn >= p.N) break;
+        const int64_t beg = nn * p.row_bytes + (int64_t)c * rbc;
+        int64_t end = beg + rbc;
+        const int64_t row_end = (nn + 1) * p.row_bytes;
+        if (end > row_end) end = row_end;
+        const int64_t a0 = beg & ~int64_t(15);
+        const int64_t off = a0 + 16 * (int64_t)lane;
+        if (off < end) {
+          uint8_t* dst = slot0 + (size_t)rr * slot + 16 * lane;
+          if (off + 16 <= tile_end) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(wbase + off) : "memory");
+          } else {  // last bytes of the buffer: never read past its end
+            for (int64_t o = off; o < tile_end; o += 2)
+              *reinterpret_cast<uint16_t*>(dst + (o - off)) = *reinterpret_cast<const uint16_t*>(wbase + o);
+          }
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // row pointer such that (pointer + byte offset in the row) lands in this thread's slot of chunk c
+    auto row_in_chunk = [&](int c) -> const uint8_t* {
+      const int64_t beg = n * p.row_bytes + (int64_t)c * rbc;
+      const int st = p.raw_tma ? c % p.raw_stages : c % 2;
+      return sRaw + (size_t)st * RAW_STAGE + (size_t)r * slot + (p.raw_tma ? 0 : (beg & 15)) - (int64_t)c * rbc;
+    };
+    if (!p.raw_tma) issue_chunk(0);
+    for (int c = 0; c < nchunks; ++c) {   // runs to the end even after a time-out: all 256 threads must meet at the barrier
+      if (p.raw_tma) {
+        if (ok) ok = mbar_wait_bounded(&raw_full[c % p.raw_stages], (uint32_t)((c / p.raw_stages) & 1));
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");   // chunk c landed for everyone; chunk c-1 fully decoded
+        if (c + 1 < nchunks) issue_chunk(c + 1);
+      }
+      const uint8_t* srow = row_in_chunk(c);
+      for (int i = c * SPC; i < (c + 1) * SPC && i < p.nmain && ok; ++i) {
+        const int s = i % MMQ_STAGES;
+        const uint32_t round = (uint32_t)(i / MMQ_STAGES);
+        const int u = 2 * i + half;
+        uint32_t v[16];
+        if (live && u < nunits && !(p.debug & 1)) {
+          constexpr int RW = Decoder<TYPE, ab_t>::RW;
+          uint32_t raw[RW];
+          Decoder<TYPE, ab_t>::load(srow, u, raw);
+          Decoder<TYPE, ab_t>::decode(srow, u, raw, cx, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0;
+        }
+        ok = mbar_wait_bounded(&empty[s], (round & 1u) ^ 1u);
+        if (!ok) break;
+        uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
+        if (!(p.debug & 2)) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+          *reinterpret_cast<uint4*>(dst + (((4 * half + cc) ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
+        fence_proxy_async();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_a[s]);
+      }
+      if (p.raw_tma) {   // this warp is done reading the raw chunk: hand the slot back to the loader
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[c % p.raw_stages]);
+      }
+    }
+    // correction columns (Q4_0 / Q4_K): a few stages at the end, straight from global memory
+    for (int i = p.nmain; i < nk && ok; ++i) {
       const int s = i % MMQ_STAGES;
       const uint32_t round = (uint32_t)(i / MMQ_STAGES);
-      uint32_t v[32];
-      if (!live) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0;
-      } else if (i < p.nmain) {
-        Decoder<TYPE, ab_t>::slab(row, i, p.K, cx, v);
+      uint32_t v[16];
+      if (live) {
+        Decoder<TYPE, ab_t>::corr(row, 2 * (i - p.nmain) + half, p.K, v);
       } else {
-        Decoder<TYPE, ab_t>::corr(row, i - p.nmain, p.K, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0;
       }
       ok = mbar_wait_bounded(&empty[s], (round & 1u) ^ 1u);
       if (!ok) break;
       uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      for (int cc = 0; cc < 4; ++cc)
+        *reinterpret_cast<uint4*>(dst + (((4 * half + cc) ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
     }
-    // ---------------- epilogue: TMEM lane r = weight row n0 + r ----------------
+    // ---------------- epilogue: TMEM lane r = weight row n0 + r; the two threads of a row split the columns ----------------
     if (ok) ok = mbar_wait_bounded(accum, 0);
     if (ok) {
       tc_fence_after();
       out_t* y = static_cast<out_t*>(p.y);
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+      const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
       const int64_t npp = MOE ? (int64_t)p.n_post_pad[0] : 0;
+      constexpr int CHALF = TN >= 32 ? TN / 2 : TN;          // columns per thread of a row pair
+      const int cbeg = TN >= 32 ? half * CHALF : 0;
+      const int cend = TN >= 32 ? cbeg + CHALF : (half == 0 ? TN : 0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 16) {
+      for (int c0 = cbeg; c0 < cend; c0 += 16) {
         uint32_t acc[16];
         tmem_ld16(lane_addr + (uint32_t)c0, acc);
         tmem_ld_wait();
@@ -451,7 +321,7 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == MMQ_PRODUCER_WARPS) {
     // ---------------- B loader: one TMA box (64 k x TN rows) per stage ----------------
     if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
@@ -459,11 +329,27 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
         const uint32_t round = (uint32_t)(i / MMQ_STAGES);
         if (!mbar_wait_bounded(&empty[s], (round & 1u) ^ 1u)) { ok = false; break; }
         const int64_t col = i < p.nmain ? (int64_t)i * MMQ_BK : p.kpad + (int64_t)(i - p.nmain) * MMQ_BK;
+        if (p.debug & 8) { mbar_arrive(&full_b[s]); continue; }
         mbar_expect_tx(&full_b[s], (uint32_t)B_STAGE);
         tma_load_2d(sB + (size_t)s * B_STAGE, &bmap, (int)col, (int)t0, &full_b[s]);
       }
     }
-  } else {
+  } else if (warp == MMQ_PRODUCER_WARPS + 2) {
+    // ---------------- raw-weight loader: one 2-D TMA box (chunk bytes x 128 rows) per chunk ----------------
+    if (lane == 0 && p.raw_tma) {
+      const int SPC = kc / MMQ_BK;
+      const int nchunks = (p.nmain + SPC - 1) / SPC;
+      int64_t wrow = p.w_row0 + n0;
+      if (MOE) wrow += (int64_t)p.expert_ids[blockIdx.y] * p.N;
+      for (int c = 0; c < nchunks; ++c) {
+        const int st = c % p.raw_stages;
+        const uint32_t round = (uint32_t)(c / p.raw_stages);
+        if (!mbar_wait_bounded(&raw_empty[st], (round & 1u) ^ 1u)) { ok = false; break; }
+        mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
+        tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, c * (rbc / 4), (int)wrow, &raw_full[st]);
+      }
+    }
+  } else if (warp == MMQ_PRODUCER_WARPS + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(MMQ_ROWS, TN, sizeof(ab_t) == 2 && std::is_same<ab_t, __nv_bfloat16>::value ? 1 : 0);
@@ -474,6 +360,7 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
         tc_fence_after();
         const uint64_t ad = umma_desc_sw128(smem_u32(sA + (size_t)s * MMQ_A_STAGE));
         const uint64_t bd = umma_desc_sw128(smem_u32(sB + (size_t)s * B_STAGE));
+        if (!(p.debug & 4))
 #pragma unroll
         for (int kk = 0; kk < MMQ_BK / 16; ++kk)  // 16 values = 32 bytes = +2 in the descriptor's 16-byte units
           umma_f16(tmem_base, ad + 2 * kk, bd + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
@@ -485,7 +372,7 @@ __global__ void __launch_bounds__(MMQ_THREADS, 1) mmq_kernel(const __grid_consta
   if (!ok && lane == 0) atomicExch(p.status, E_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == MMQ_PRODUCER_WARPS) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -528,17 +415,47 @@ static int launch_tn(const MmqArgs& a, const MmqParams& p, int64_t b_rows, cudaS
   if (enc(&map, dt, 2, const_cast<void*>(a.b), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return E_CUDA;
+  // Raw weight bytes: 2-D TMA boxes when the geometry allows (row bytes a multiple of 16 and, for
+  // MoE, experts stored back to back with whole tiles per expert so that a box never leaves the
+  // caller's buffer), else cp.async pieces issued by the decode warps.
+  MmqParams pp = p;
+  CUtensorMap wmap = map;   // placeholder when unused
+  static const char* no_tma = getenv("GGUF_B200_MMQ_NO_RAW_TMA");
+  bool raw_tma = TmaGeom<TYPE>::OK && a.K % 32 == 0 && pp.row_bytes % 16 == 0 && !(no_tma && no_tma[0] == '1');
+  int64_t map_rows = a.N;
+  if (MOE) {
+    raw_tma = raw_tma && a.expert_stride_bytes == a.N * pp.row_bytes && a.N % MMQ_ROWS == 0;
+    map_rows = a.N * 256;   // expert ids are limited to [0, 255]; boxes only touch experts that are routed to
+  }
+  if (raw_tma) {
+    const cuuint64_t wd[2] = {(cuuint64_t)(pp.row_bytes / 4), (cuuint64_t)map_rows};
+    const cuuint64_t ws[1] = {(cuuint64_t)pp.row_bytes};
+    const cuuint32_t wb[2] = {(cuuint32_t)(TmaGeom<TYPE>::RBC_T / 4), (cuuint32_t)MMQ_ROWS};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.w), wd, ws, wb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      raw_tma = false;
+  }
+  const size_t ab_bytes = 1024 + (size_t)mmq_stages(TN) * (MMQ_A_STAGE + TN * MMQ_BK * 2) + 4096;
+  const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
+  const size_t budget = (TN <= 64 ? 113 : 226) * 1024;   // two CTAs per SM for small token tiles
+  int rs = raw_tma ? (int)((budget - ab_bytes) / raw_stage) : 2;
+  if (rs > MMQ_MAX_RAW) rs = MMQ_MAX_RAW;
+  if (rs < 2) rs = 2;
+  pp.raw_tma = raw_tma ? 1 : 0;
+  pp.raw_stages = rs;
+  pp.w_row0 = 0;
+  const size_t smem = ab_bytes + (size_t)rs * raw_stage;
+  if (smem > 227 * 1024) return E_TOO_LARGE;
   auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE>;
-  const size_t smem = 1024 + (size_t)MMQ_STAGES * (MMQ_A_STAGE + TN * MMQ_BK * 2) + (3 * MMQ_STAGES + 2) * 8 + 2048 + 128 + 16;
-  static bool configured[64] = {false};
+  static size_t configured[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
+  if (smem > configured[dev & 63]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
-    configured[dev & 63] = true;
+    configured[dev & 63] = smem;
   }
   dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), 1);
-  kern<<<grid, MMQ_THREADS, smem, stream>>>(map, p);
+  kern<<<grid, MMQ_THREADS, smem, stream>>>(map, wmap, pp);
   return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
 }
 
@@ -582,6 +499,8 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
   p.expert_stride_bytes = a.expert_stride_bytes;
   p.rows_out = a.rows_out;
   p.status = a.status;
+  static const char* dbg = getenv("GGUF_B200_MMQ_DEBUG");
+  p.debug = dbg ? atoi(dbg) : 0;
   const bool bf = a.b_dtype == DT_BF16;
   switch (a.type) {
     case T_Q4_0: return bf ? E_BAD_DTYPE : launch_out<T_Q4_0, __half>(a, p, stream);

@@ -1,0 +1,299 @@
+// Weight decoders of the tensor-core GEMM (mmq.cu): one 32-value group of one weight row
+// ("unit" u = values 32u..32u+31) -> 16 packed 16-bit pairs = 64 bytes of the row in the A tile.
+// Two threads share a row of a 64-value stage, so 256 threads decode a 128 x 64 stage.
+//
+// Each decoder is split in two so that the producer threads can keep global loads in flight:
+//   load()   issues the loads of a unit's raw bytes into registers (no use of the data),
+//   decode() turns those registers into fp16/bf16 values.
+// The kernel calls load() for the unit two stages ahead before decode() of the current one.
+//
+// Values are bit-identical to the reference's standalone dequantize for the types that are fed
+// to the MMA as dequantized weights (Q4_0, Q8_0, Q6_K: dequantize.cuh:3-15, 69-78, 232-256;
+// IQ4_XS, IQ2_XXS: dequantize.cuh:420-435, 258-275).  Q4_K feeds half(d*sc*q) and carries its
+// min term in the correction columns (see mmq.cu).
+//
+// Blocks of Q4_0 / Q8_0 / Q6_K / IQ2_XXS are only 2-byte aligned: raw bytes are fetched as the
+// aligned 32-bit words that cover them and realigned with funnel shifts.
+#pragma once
+
+#include "common.cuh"
+
+namespace gguf_b200 {
+
+template <typename ab_t> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(a)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(b)) << 16);
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+// (1024 + a, 1024 + b) as half2 for small unsigned a, b: exact integers, so subtracting
+// 1024 + bias afterwards yields (a - bias, b - bias) without any rounding.
+__device__ __forceinline__ __half2 ints_plus_1024(uint32_t a, uint32_t b) { return u32_as_h2(0x64006400u | a | (b << 16)); }
+__device__ __forceinline__ __half2 hmul2_rn(__half2 a, __half2 b) { return __hmul2_rn(a, b); }
+__device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
+
+// N aligned words covering `len` bytes from the (2-byte aligned) address p; words that hold no
+// needed byte are not loaded (no read past the end of the buffer).  Plain loads: the pointer may
+// be global memory or the shared-memory staging area of the raw weight bytes.
+template <int N> __device__ __forceinline__ void ldg_cover(const uint8_t* p, int len, uint32_t* r) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t* al = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
+  const int need = (len + (int)(a & 3) + 3) >> 2;
+#pragma unroll
+  for (int i = 0; i < N; ++i) r[i] = i < need ? al[i] : 0u;
+}
+// word i of the byte stream that starts `sh` bits into r[0]
+__device__ __forceinline__ uint32_t word_at(const uint32_t* r, int i, uint32_t sh) { return __funnelshift_r(r[i], r[i + 1], sh); }
+__device__ __forceinline__ uint32_t shift_of(const uint8_t* p) { return (uint32_t)(reinterpret_cast<uintptr_t>(p) & 3) * 8u; }
+
+struct DecodeCtx {
+  const uint64_t* grid;   // IQ2_XXS tables in shared memory
+  const uint8_t* signs;
+  const int8_t* kv;       // IQ4_XS levels in shared memory
+};
+
+template <int TYPE, typename ab_t> struct Decoder;
+
+// Raw-byte staging of the tensor-core kernel: KC values of every row of the tile are copied to
+// shared memory at once (coalesced 16-byte pieces), RBC bytes per row, in slots of SLOT bytes.
+// SLOT leaves room for the 16-byte rounding of the start and is an odd multiple of 16 so that
+// the 128 rows of a tile spread over all shared-memory banks.
+// TMA variant of the staging (row bytes a multiple of 16 and chunk starts 16-byte aligned): a
+// chunk of KC_T values per row is one 2-D box of RBC_T bytes x 128 rows, stored densely.  RBC_T
+// is 16 mod 128 for every supported type, so dense rows are bank-conflict free as well.
+template <int TYPE> struct TmaGeom {
+  static constexpr bool OK = TYPE == T_Q4_0 || TYPE == T_Q8_0 || TYPE == T_Q4_K || TYPE == T_IQ4_XS;
+  static constexpr int KC_T = TYPE == T_IQ4_XS ? 512 : 256;
+  static constexpr int RBC_T = KC_T / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;   // 144 or 272
+};
+template <int TYPE> struct RawGeom {
+  static constexpr int KC = (TYPE == T_Q8_0) ? 128 : (TYPE == T_IQ2_XXS ? 512 : 256);
+  static constexpr int RBC = KC / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;
+  static constexpr int S16 = (RBC + 30) / 16 + 1;
+  static constexpr int SLOT = (S16 % 2 ? S16 : S16 + 1) * 16;
+};
+
+// ---- Q4_0: value = half((q - 8) * d); unit = one 18-byte block ------------------------------
+template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
+  static constexpr int RW = 7;   // 18 bytes at 2-byte alignment: <= 6 words (+1 for the shifts)
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    ldg_cover<RW - 1>(row + (int64_t)u * 18, 18, raw);
+    raw[RW - 1] = 0;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const uint32_t sh = shift_of(row + (int64_t)u * 18);
+    const __half2 off = __floats2half2_rn(1032.f, 1032.f);
+    const uint32_t du = word_at(raw, 0, sh) & 0xFFFFu;
+    const __half2 d2 = u32_as_h2(du | (du << 16));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // stream half-word 1+i holds qs[2i], qs[2i+1]
+      const int h = 1 + i;
+      const uint32_t wv = word_at(raw, h >> 1, sh);
+      const uint32_t t = (h & 1) ? (wv >> 16) : (wv & 0xFFFFu);
+      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(t & 0xF, (t >> 8) & 0xF), off), d2));
+      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((t >> 4) & 0xF, (t >> 12) & 0xF), off), d2));
+    }
+  }
+  // correction columns [32c, 32c+32): A'[n, g] = d of block g (pairs with 8*(d8*sum(q8) - s8) on the B side)
+  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t g = 32 * (int64_t)c + 2 * i;
+      const uint32_t a = g * 32 < K ? ldg16(row + g * 18) : 0u;
+      const uint32_t b = (g + 1) * 32 < K ? ldg16(row + (g + 1) * 18) : 0u;
+      out[i] = a | (b << 16);
+    }
+  }
+};
+
+// ---- Q8_0: value = half(q * d); unit = one 34-byte block ---------------------------------------
+template <typename ab_t> struct Decoder<T_Q8_0, ab_t> {
+  static constexpr int RW = 11;  // 34 bytes: <= 10 words (+1)
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    ldg_cover<RW - 1>(row + (int64_t)u * 34, 34, raw);
+    raw[RW - 1] = 0;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const uint32_t sh = shift_of(row + (int64_t)u * 34);
+    const __half2 off = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128
+    const uint32_t du = word_at(raw, 0, sh) & 0xFFFFu;
+    const __half2 d2 = u32_as_h2(du | (du << 16));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int h = 1 + i;
+      const uint32_t wv = word_at(raw, h >> 1, sh);
+      const uint32_t t = ((h & 1) ? (wv >> 16) : (wv & 0xFFFFu)) ^ 0x8080u;  // int8 -> biased unsigned
+      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(t & 0xFF, t >> 8), off), d2));
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+// 6-bit (scale, min) pair j of a Q4_K super-block from its 12 packed bytes held in three
+// registers (bytes 0-3, 4-7, 8-11); same packing as get_scale_min_k4, dequantize.cuh:156-163.
+__device__ __forceinline__ void q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, int& sc, int& m) {
+  if (j < 4) {
+    sc = (w0 >> (8 * j)) & 63;
+    m = (w1 >> (8 * j)) & 63;
+  } else {
+    const int sh = 8 * (j - 4);
+    const uint32_t b = (w2 >> sh) & 0xFF;
+    sc = (b & 0xF) | ((((w0 >> sh) & 0xFF) >> 6) << 4);
+    m = (b >> 4) | ((((w1 >> sh) & 0xFF) >> 6) << 4);
+  }
+}
+
+// ---- Q4_K: A = half(d1 * q) with d1 = half(d * sc); the -dmin*m part is a correction column ----
+// unit u: super-block u>>3, sub-block j = u&7: nibble (j&1) of the 32 bytes qs[32*(j>>1) ..]
+template <typename ab_t> struct Decoder<T_Q4_K, ab_t> {
+  static constexpr int RW = 12;  // header (16 bytes) + 32 bytes of nibbles, all 16-byte aligned
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 144;
+    const uint4 h = *reinterpret_cast<const uint4*>(blk);
+    const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + 32 * ((u >> 1) & 3));
+    const uint4 a = qp[0], b = qp[1];
+    raw[0] = h.x; raw[1] = h.y; raw[2] = h.z; raw[3] = h.w;
+    raw[4] = a.x; raw[5] = a.y; raw[6] = a.z; raw[7] = a.w; raw[8] = b.x; raw[9] = b.y; raw[10] = b.z; raw[11] = b.w;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t*, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const int j = u & 7, sh = 4 * (j & 1);
+    const __half dall = __ushort_as_half((unsigned short)(raw[0] & 0xffff));
+    int sc, m;
+    q4k_scale_min(raw[1], raw[2], raw[3], j, sc, m);
+    (void)m;
+    const __half2 dv = __half2half2(__hmul_rn(dall, __int2half_rn(sc)));
+    const __half2 off = __floats2half2_rn(1024.f, 1024.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // word i: bytes 4i..4i+3 -> values 4i..4i+3 of this sub-block
+      const uint32_t w = raw[4 + i] >> sh;
+      out[2 * i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(w & 0xF, (w >> 8) & 0xF), off), dv));
+      out[2 * i + 1] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((w >> 16) & 0xF, (w >> 24) & 0xF), off), dv));
+    }
+  }
+  // correction columns [32c, 32c+32): A'[n, g] = half(dmin * m_g)  (pairs with -s8 on the B side)
+  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int sb = 0; sb < 4; ++sb) {
+      const int64_t sbi = 4 * (int64_t)c + sb;  // super-block index: 8 groups each
+      if (sbi * 256 >= K) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[4 * sb + i] = 0;
+        continue;
+      }
+      const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(row + sbi * 144));
+      const __half dmin = __ushort_as_half((unsigned short)(hdr.x >> 16));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int sc, ma, mb;
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * i, sc, ma);
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * i + 1, sc, mb);
+        out[4 * sb + i] = (uint32_t)__half_as_ushort(__hmul_rn(dmin, __int2half_rn(ma))) |
+                          ((uint32_t)__half_as_ushort(__hmul_rn(dmin, __int2half_rn(mb))) << 16);
+      }
+    }
+  }
+};
+
+// ---- Q6_K: value = half(d * half(sc * (code - 32))) ------------------------------------------
+// unit u: super-block u>>3, group g = u&7: ip = g>>2 (128-value half), q = g&3:
+//   low 4 bits = nibble (q>>1) of ql[64ip + 32(q&1) + l], high 2 bits = bits 2q.. of qh[32ip + l], l = 0..31,
+//   scales sc[8ip + 2q] (l < 16) and sc[8ip + 2q + 1].
+// Raw: [0..9] 32 bytes of ql (+ cover), [10..19] 32 bytes of qh (+ cover), [20..21] scale half-word, [22] d.
+template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
+  static constexpr int RW = 23;
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 210;
+    const int g = u & 7, ip = g >> 2, q = g & 3;
+    ldg_cover<9>(blk + 64 * ip + 32 * (q & 1), 32, raw);
+    raw[9] = 0;
+    ldg_cover<9>(blk + 128 + 32 * ip, 32, raw + 10);
+    raw[19] = 0;
+    ldg_cover<1>(blk + 192 + 8 * ip + 2 * q, 2, raw + 20);
+    raw[21] = 0;
+    ldg_cover<1>(blk + 208, 2, raw + 22);
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 210;
+    const int g = u & 7, ip = g >> 2, q = g & 3;
+    const uint32_t sh_l = shift_of(blk + 64 * ip + 32 * (q & 1)), sh_h = shift_of(blk + 128 + 32 * ip);
+    const uint32_t sc2 = (raw[20] >> shift_of(blk + 192 + 8 * ip + 2 * q)) & 0xFFFFu;   // two int8 scales
+    const uint32_t du = (raw[22] >> shift_of(blk + 208)) & 0xFFFFu;
+    const __half2 d2 = u32_as_h2(du | (du << 16));
+    const __half2 off = __floats2half2_rn(1056.f, 1056.f);  // 1024 + 32
+    const __half2 s_lo = __half2half2(__int2half_rn((int)(int8_t)(sc2 & 0xFF)));
+    const __half2 s_hi = __half2half2(__int2half_rn((int)(int8_t)(sc2 >> 8)));
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) {             // word wi: values 4wi..4wi+3 of the unit
+      const uint32_t l = word_at(raw, wi, sh_l) >> (4 * (q >> 1));
+      const uint32_t h = word_at(raw + 10, wi, sh_h) >> (2 * q);
+      const __half2 s2 = wi < 4 ? s_lo : s_hi;
+      const uint32_t c0 = (l & 0xF) | ((h & 3) << 4), c1 = ((l >> 8) & 0xF) | (((h >> 8) & 3) << 4);
+      const uint32_t c2 = ((l >> 16) & 0xF) | (((h >> 16) & 3) << 4), c3 = ((l >> 24) & 0xF) | (((h >> 24) & 3) << 4);
+      out[2 * wi] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(ints_plus_1024(c0, c1), off))));
+      out[2 * wi + 1] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(ints_plus_1024(c2, c3), off))));
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+// ---- IQ4_XS: fp32 d*(ls-32)*level rounded once to ab_t; unit = 32-value group ib = u&7 -----------
+template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
+  static constexpr int RW = 6;   // header (8 bytes) + 16 index bytes, 8-byte aligned
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 136;
+    const uint2 h = *reinterpret_cast<const uint2*>(blk);
+    const uint2* qp = reinterpret_cast<const uint2*>(blk + 8 + 16 * (u & 7));
+    const uint2 a = qp[0], b = qp[1];
+    raw[0] = h.x; raw[1] = h.y; raw[2] = a.x; raw[3] = a.y; raw[4] = b.x; raw[5] = b.y;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t*, int u, const uint32_t (&raw)[RW], const DecodeCtx& cx, uint32_t (&out)[16]) {
+    const int ib = u & 7;
+    const float d = __half2float(__ushort_as_half((unsigned short)(raw[0] & 0xffff)));
+    const int ls = (int)(((raw[1] >> (4 * ib)) & 0xF) | ((((raw[0] >> 16) >> (2 * ib)) & 3) << 4)) - 32;
+    const float dl = d * (float)ls;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // bytes 4i..4i+3: values 4i.. (low nibbles) and 16+4i.. (high)
+      const uint32_t w = raw[2 + i];
+      out[2 * i] = pack2<ab_t>(dl * (float)cx.kv[w & 0xF], dl * (float)cx.kv[(w >> 8) & 0xF]);
+      out[2 * i + 1] = pack2<ab_t>(dl * (float)cx.kv[(w >> 16) & 0xF], dl * (float)cx.kv[(w >> 24) & 0xF]);
+      out[8 + 2 * i] = pack2<ab_t>(dl * (float)cx.kv[(w >> 4) & 0xF], dl * (float)cx.kv[(w >> 12) & 0xF]);
+      out[8 + 2 * i + 1] = pack2<ab_t>(dl * (float)cx.kv[(w >> 20) & 0xF], dl * (float)cx.kv[(w >> 28) & 0xF]);
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+// ---- IQ2_XXS: fp32 d*(0.5+s)*0.25*grid*sign rounded once; unit = 32-value group ib = u&7 ----------
+template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
+  static constexpr int RW = 5;   // [0] word holding d, [1..3] the group's 8 bytes (+ cover), [4] pad
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 66;
+    ldg_cover<1>(blk, 2, raw);
+    ldg_cover<3>(blk + 2 + 8 * (u & 7), 8, raw + 1);
+    raw[4] = 0;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx& cx, uint32_t (&out)[16]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 66;
+    const float dh = __half2float(__ushort_as_half((unsigned short)((raw[0] >> shift_of(blk)) & 0xFFFFu)));
+    const uint32_t sh = shift_of(blk + 2 + 8 * (u & 7));
+    const uint32_t idx = word_at(raw + 1, 0, sh), aux = word_at(raw + 1, 1, sh);
+    const float d = dh * (0.5f + (float)(aux >> 28)) * 0.25f;
+#pragma unroll
+    for (int il = 0; il < 4; ++il) {
+      const uint64_t g = cx.grid[(idx >> (8 * il)) & 0xFF];
+      const uint32_t sg = cx.signs[(aux >> (7 * il)) & 127];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = d * (float)((uint32_t)(g >> (16 * j)) & 0xFF) * ((sg >> (2 * j)) & 1 ? -1.f : 1.f);
+        const float b = d * (float)((uint32_t)(g >> (16 * j + 8)) & 0xFF) * ((sg >> (2 * j + 1)) & 1 ? -1.f : 1.f);
+        out[4 * il + j] = pack2<ab_t>(a, b);
+      }
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+}  // namespace gguf_b200
