@@ -352,9 +352,30 @@ def main():
             "includes": "q8_1 quantization of the 512x4096 activations + tcgen05 GEMM"}}
 
     status = capi.last_status()
+
+    def shutdown():
+        """Leave without waiting on NCCL: a communicator that a live CUDA graph still references
+        does not tear down, so the graph goes first and a watchdog ends the process regardless."""
+        nonlocal graph
+        if world == 1:
+            return
+        sys.stdout.flush()
+        sys.stderr.flush()
+        import threading
+
+        dog = threading.Timer(20.0, lambda: os._exit(0))
+        dog.daemon = True
+        dog.start()
+        try:
+            torch.cuda.synchronize()
+            if graph is not None:
+                graph.reset()
+                graph = None
+        finally:
+            os._exit(0)
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        shutdown()
         return
 
     # parity spot check of what was just timed (host oracle, tiny: first 64 rows of one copy)
@@ -396,8 +417,7 @@ def main():
         "extras": extras,
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown()
 
 
 if __name__ == "__main__":

@@ -172,9 +172,11 @@ int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_
     if (rc) return rc;
     return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
   }
-  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), nullptr, 1, 0, s);
+  const int perm = mmq_perm(type, N, K, false, 0);
+  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), nullptr, 1, 0, s, perm);
   if (rc) return rc;
   MmqArgs a{};
+  a.perm = perm;
   a.w = W; a.b = ws; a.y = Y;
   a.type = type; a.out_dtype = dtype; a.b_dtype = DT_F16;
   a.M = M; a.N = N; a.K = K; a.ldb = ldb;
@@ -227,10 +229,12 @@ int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* ws, int64_t ws
   int* st = status_ptr();
   if (!st) return E_CUDA;
   // quantize + gather: row p of the fp16 matrix = activations of token sorted_token_ids[p] / top_k
+  const int perm = mmq_perm(type, N, K, true, expert_stride_bytes);
   rc = launch_quantize_q8_1(X, dtype, ws, n_sorted, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), sorted_token_ids, top_k,
-                            rows_out, s);
+                            rows_out, s, perm);
   if (rc) return rc;
   MmqArgs a{};
+  a.perm = perm;
   a.w = W; a.b = ws; a.y = Y;
   a.type = type; a.out_dtype = dtype; a.b_dtype = DT_F16;
   a.M = n_sorted; a.N = N; a.K = K; a.ldb = ldb;

@@ -97,17 +97,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Every wait in this library is bounded: after `limit` polls the caller records a status
-// word and leaves, so a lost completion can never wedge the GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 20000000u) {
-  for (uint32_t i = 0; i < limit; ++i)
+// non-blocking probe of a phase (try_wait may park the thread; this never does)
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Every wait in this library is bounded in time: a poll may itself suspend the thread for a
+// while, so the limit is counted in SM clock cycles (about a quarter of a second), after which
+// the caller records a status word and leaves.  A lost completion can then never wedge the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, long long limit_cycles = 500000000ll) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  do {
     if (mbar_try_wait(bar, parity)) return true;
+  } while (clock64() - t0 < limit_cycles);
   return false;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// 1-D bulk copy global -> shared (no multicast); src, dst and bytes multiples of 16.
+// 1-D bulk copy global -> shared of this CTA; src, dst and bytes multiples of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),

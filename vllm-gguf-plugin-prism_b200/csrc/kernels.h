@@ -16,10 +16,12 @@ enum : int { CORR_NONE = 0, CORR_Q4_0 = 1, CORR_MIN = 2 };
 // input row gather_ids[r] / gather_div; ids outside [0, gather_limit) give a zero row.
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream);
+                         cudaStream_t stream, int perm = 0);
 // leading dimension (elements) of the fp16 activation matrix of the tensor-core kernels
 int64_t mmq_ldb(int type, int64_t K);
 int mmq_corr_mode(int type);
+// value order the tensor-core kernel will expect in the fp16 activation matrix for this problem
+int mmq_perm(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_bytes);
 
 int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t n_elems, int q4k_contract,
                       cudaStream_t stream);
@@ -48,6 +50,7 @@ struct MmqArgs {
   int64_t ldb;              // leading dimension of b in elements
   int64_t kext;             // contraction length in elements incl. correction columns (multiple of 64)
   int corr_mode;            // which correction the appended columns hold
+  int perm;                 // value order inside each group of four of b: 0 natural, 1 = (0,2,1,3) (see mmq_perm)
   // MoE gather (null sorted_ids = dense)
   const int32_t* sorted_ids;
   const int32_t* expert_ids;

@@ -22,7 +22,7 @@
 // Warp roles:  warps 0-7 decode weights into the A stage (two threads per row, 32 values each,
 // raw bytes prefetched two stages ahead in registers) and later run the epilogue (tcgen05.ld,
 // one TMEM lane = one weight row; the two threads of a row split the token columns); warp 8
-// issues the TMA loads of the B tile (tiled 2-D tensor map, no multicast) and owns the TMEM
+// issues the TMA loads of the B tile (tiled 2-D tensor map, one CTA per box) and owns the TMEM
 // allocation; warp 9 lane 0 issues tcgen05.mma and commits stage releases.  A 4-deep mbarrier ring
 // decouples them.  Every wait is bounded and reports through the status word.
 #include <cuda.h>
@@ -38,9 +38,16 @@ namespace gguf_b200 {
 
 constexpr int MMQ_ROWS = 128;
 constexpr int MMQ_BK = 64;
-__host__ __device__ constexpr int mmq_stages(int tn) { return tn > 128 ? 3 : 4; }
-constexpr int MMQ_PRODUCER_WARPS = 8;   // two threads per weight row of a stage: 32 values each
-constexpr int MMQ_THREADS = (MMQ_PRODUCER_WARPS + 3) * 32;   // + B loader, MMA issuer, raw-weight loader
+// Ring depths.  The A ring (16 KB slots) is never shallower than the number of producer groups:
+// a group that runs ahead may be at most one use of a slot ahead of the MMA warp, or the
+// one-bit phase parity of the slot's barrier would alias.  The B ring (TN * 128 bytes per slot)
+// only has to cover the TMA latency.
+__host__ __device__ constexpr int mmq_a_stages(int tn) { return 4; }
+__host__ __device__ constexpr int mmq_b_stages(int tn) { return tn > 128 ? 3 : 4; }
+// producer groups of 128 threads (one thread per weight row) that take the K stages in turn;
+// one CTA per SM
+__host__ __device__ constexpr int mmq_groups(int tn) { return 4; }
+__host__ __device__ constexpr int mmq_threads(int tn) { return (4 * mmq_groups(tn) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
 constexpr int MMQ_MAX_RAW = 6;
 constexpr int MMQ_A_STAGE = MMQ_ROWS * MMQ_BK * 2;  // 16 KB
 
@@ -64,6 +71,12 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// one lane of a converged warp (the same one every time)
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -99,6 +112,16 @@ __host__ __device__ inline uint32_t umma_idesc(int m, int n, int fmt) {
 }
 
 // ---- kernel -----------------------------------------------------------------------------
+__device__ unsigned long long g_mmq_trace[7][128];
+__device__ int g_mmq_where[8];   // first wait that gave up: code, stage, block x, block y, thread
+__device__ __forceinline__ bool wait_or_note(uint64_t* bar, uint32_t parity, int code, int i) {
+  if (mbar_wait_bounded(bar, parity)) return true;
+  if (atomicCAS(&g_mmq_where[0], 0, code) == 0) {
+    g_mmq_where[1] = i; g_mmq_where[2] = (int)blockIdx.x; g_mmq_where[3] = (int)blockIdx.y; g_mmq_where[4] = (int)threadIdx.x;
+  }
+  return false;
+}
+#define TRACE(role, i) do { if ((p.debug & 64) && blockIdx.x == 0 && blockIdx.y == 0 && (i) < 128) g_mmq_trace[role][i] = clock64(); } while (0)
 
 struct MmqParams {
   const uint8_t* w;
@@ -116,36 +139,47 @@ struct MmqParams {
   int raw_tma;            // 1: raw weight chunks arrive by 2-D TMA boxes (wmap), 0: by cp.async pieces
   int raw_stages;         // depth of the raw ring
   int64_t w_row0;         // first row of this matrix in wmap (MoE: added to expert * N)
+  int y_tma;              // 1: the output tile leaves through shared memory and one TMA store (ymap)
 };
 
-template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE>
-__global__ void __launch_bounds__(MMQ_THREADS, (TN <= 64 ? 2 : 1)) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const MmqParams p) {
+template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
+__global__ void __launch_bounds__(mmq_threads(TN), 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
-  constexpr int MMQ_STAGES = mmq_stages(TN);
+  constexpr int SA = mmq_a_stages(TN), SB = mmq_b_stages(TN);
+  static_assert(mmq_groups(TN) <= SA, "a producer group may not lap the A ring");
+  constexpr int NG = mmq_groups(TN);
+  constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
   // raw ring geometry: dense TMA boxes or padded cp.async slots
-  const int kc = p.raw_tma ? TmaGeom<TYPE>::KC_T : RawGeom<TYPE>::KC;
+  const bool tma = FAST || p.raw_tma;
+  const int kc = tma ? TmaGeom<TYPE>::KC_T : RawGeom<TYPE>::KC;
   const int rbc = kc / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;
-  const int slot = p.raw_tma ? rbc : RawGeom<TYPE>::SLOT;
+  const int slot = tma ? rbc : RawGeom<TYPE>::SLOT;
   const int RAW_STAGE = MMQ_ROWS * slot;
+  const int SPC = kc / MMQ_BK;                  // MMA stages per chunk (a multiple of NG)
+  const int nchunks = (p.nmain + SPC - 1) / SPC;
   uint8_t* sA = smem;
-  uint8_t* sB = smem + MMQ_STAGES * MMQ_A_STAGE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + MMQ_STAGES * B_STAGE);
-  uint8_t* sRaw = sB + MMQ_STAGES * B_STAGE + 4096;   // barriers and codebooks take the 4 KB in between
-  uint64_t* raw_full = bars + 3 * MMQ_STAGES + 2 + 256 + 16 + 2;   // after tmem slot, grid, signs, levels
-  uint64_t* raw_empty = raw_full + MMQ_MAX_RAW;
-  uint64_t* full_a = bars;
-  uint64_t* full_b = bars + MMQ_STAGES;
-  uint64_t* empty = bars + 2 * MMQ_STAGES;
-  uint64_t* accum = bars + 3 * MMQ_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * MMQ_STAGES + 1);
-  uint64_t* s_grid = reinterpret_cast<uint64_t*>(bars + 3 * MMQ_STAGES + 2);
+  uint8_t* sB = smem + SA * MMQ_A_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + SB * B_STAGE);
+  uint8_t* sRaw = sB + SB * B_STAGE + 4096;   // barriers and codebooks take the 4 KB in between
+  // One "full" and one "empty" barrier per A slot serve both operands of a stage, so the MMA
+  // thread polls and commits once per stage: full[i % SA] collects the warps of the group that
+  // decoded stage i plus the B loader's expect-tx arrival and bytes; empty[i % SA] is the
+  // tcgen05.commit after stage i, which frees A slot i % SA and B slot i % SB alike.
+  uint64_t* full_a = bars;                    // [8]
+  uint64_t* empty_a = bars + 16;              // [8]
+  uint64_t* accum = bars + 32;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 33);
+  uint64_t* raw_full = bars + 34;             // [MMQ_MAX_RAW]
+  uint64_t* raw_empty = bars + 34 + MMQ_MAX_RAW;
+  uint64_t* s_grid = bars + 48;
   uint8_t* s_signs = reinterpret_cast<uint8_t*>(s_grid + 256);
   int8_t* s_kv = reinterpret_cast<int8_t*>(s_signs + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TRACE(6, 0);
   const int64_t n0 = (int64_t)blockIdx.x * MMQ_ROWS;
   const int64_t t0 = (int64_t)blockIdx.y * TN;
   const uint8_t* wbase = p.w;
@@ -159,10 +193,9 @@ __global__ void __launch_bounds__(MMQ_THREADS, (TN <= 64 ? 2 : 1)) mmq_kernel(co
   const int nk = p.nmain + p.ncorr;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < MMQ_STAGES; ++s) {
-      mbar_init(&full_a[s], MMQ_PRODUCER_WARPS);
-      mbar_init(&full_b[s], 1);
-      mbar_init(&empty[s], 1);
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(&full_a[s], MMQ_PRODUCER_WARPS / NG + 1);   // the warps of the one group that fills the stage + the B loader
+      mbar_init(&empty_a[s], 1);
     }
     mbar_init(accum, 1);
     for (int s = 0; s < MMQ_MAX_RAW; ++s) {
@@ -185,23 +218,23 @@ __global__ void __launch_bounds__(MMQ_THREADS, (TN <= 64 ? 2 : 1)) mmq_kernel(co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  if (threadIdx.x == 0) TRACE(6, 1);
 
   if (warp < MMQ_PRODUCER_WARPS) {
-    // ---------------- A producers: threads r and r+128 decode the two 32-value halves of row n0 + r ----------------
-    const int r = threadIdx.x & 127, half = threadIdx.x >> 7;
+    // ---------------- A producers ----------------
+    // Thread r of group g decodes all 64 values of row n0 + r for the stages i = g, g + NG, ...:
+    // the groups work on different stages at the same time, which hides the latency of one
+    // thread's decode chain behind the other group's.
+    const int r = threadIdx.x & 127, g = threadIdx.x >> 7;
     const int64_t n = n0 + r;
     const bool live = n < p.N;
     const uint8_t* row = wbase + (live ? n : 0) * p.row_bytes;
     DecodeCtx cx{s_grid, s_signs, s_kv};
     const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
     const int nunits = (int)((p.K + 31) / 32);   // 32-value units of a row that exist
-    // Raw weight bytes reach shared memory in chunks of KC values per row: warp w copies rows
-    // w, w+8, ... of the tile, one coalesced 16-byte cp.async per lane and row (a row's chunk is
-    // 66..272 contiguous bytes), one chunk ahead of the decode.  Thread-per-row global loads
-    // would touch 32 cache lines per warp instruction and stall on the L1 tag stage instead.
-    const int SPC = kc / MMQ_BK;                  // MMA stages per chunk
-    const int nchunks = (p.nmain + SPC - 1) / SPC;
     const int64_t tile_end = (int64_t)p.N * p.row_bytes;   // bytes of this weight matrix (expert)
+    // cp.async staging (shapes the TMA boxes cannot serve): warp w copies rows w, w+8, ... of the
+    // tile, one coalesced 16-byte piece per lane and row, one chunk ahead of the decode.
     auto issue_chunk = [&](int c) {
       uint8_t* slot0 = sRaw + (size_t)(c % 2) * RAW_STAGE;
       for (int rr = warp; rr < MMQ_ROWS; rr += MMQ_PRODUCER_WARPS) {
@@ -225,84 +258,146 @@ __global__ void __launch_bounds__(MMQ_THREADS, (TN <= 64 ? 2 : 1)) mmq_kernel(co
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    // row pointer such that (pointer + byte offset in the row) lands in this thread's slot of chunk c
-    auto row_in_chunk = [&](int c) -> const uint8_t* {
-      const int64_t beg = n * p.row_bytes + (int64_t)c * rbc;
-      const int st = p.raw_tma ? c % p.raw_stages : c % 2;
-      return sRaw + (size_t)st * RAW_STAGE + (size_t)r * slot + (p.raw_tma ? 0 : (beg & 15)) - (int64_t)c * rbc;
-    };
-    if (!p.raw_tma) issue_chunk(0);
-    for (int c = 0; c < nchunks; ++c) {   // runs to the end even after a time-out: all 256 threads must meet at the barrier
-      if (p.raw_tma) {
-        if (ok) ok = mbar_wait_bounded(&raw_full[c % p.raw_stages], (uint32_t)((c / p.raw_stages) & 1));
-      } else {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("bar.sync 1, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");   // chunk c landed for everyone; chunk c-1 fully decoded
-        if (c + 1 < nchunks) issue_chunk(c + 1);
-      }
-      const uint8_t* srow = row_in_chunk(c);
-      for (int i = c * SPC; i < (c + 1) * SPC && i < p.nmain && ok; ++i) {
-        const int s = i % MMQ_STAGES;
-        const uint32_t round = (uint32_t)(i / MMQ_STAGES);
-        const int u = 2 * i + half;
-        uint32_t v[16];
-        if (live && u < nunits && !(p.debug & 1)) {
-          constexpr int RW = Decoder<TYPE, ab_t>::RW;
-          uint32_t raw[RW];
-          Decoder<TYPE, ab_t>::load(srow, u, raw);
-          Decoder<TYPE, ab_t>::decode(srow, u, raw, cx, v);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0;
-        }
-        ok = mbar_wait_bounded(&empty[s], (round & 1u) ^ 1u);
-        if (!ok) break;
-        uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
-        if (!(p.debug & 2)) {
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc)
-          *reinterpret_cast<uint4*>(dst + (((4 * half + cc) ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
-        fence_proxy_async();
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_a[s]);
-      }
-      if (p.raw_tma) {   // this warp is done reading the raw chunk: hand the slot back to the loader
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[c % p.raw_stages]);
-      }
-    }
-    // correction columns (Q4_0 / Q4_K): a few stages at the end, straight from global memory
-    for (int i = p.nmain; i < nk && ok; ++i) {
-      const int s = i % MMQ_STAGES;
-      const uint32_t round = (uint32_t)(i / MMQ_STAGES);
-      uint32_t v[16];
-      if (live) {
-        Decoder<TYPE, ab_t>::corr(row, 2 * (i - p.nmain) + half, p.K, v);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0;
-      }
-      ok = mbar_wait_bounded(&empty[s], (round & 1u) ^ 1u);
-      if (!ok) break;
+    int s = g;                 // A slot of this group's next stage and its phase
+    uint32_t ph = 0;
+    while (s >= SA) { s -= SA; ph ^= 1u; }
+    auto publish = [&](const uint32_t (&v)[32], int i) -> bool {   // wait for the slot, store the row, signal the MMA warp
+      if (threadIdx.x == 0) TRACE(0, i);
+      if (!wait_or_note(&empty_a[s], ph ^ 1u, 2, i)) return false;
+      if (threadIdx.x == 0) TRACE(1, i);
       uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
+      if (!(p.debug & 2)) {
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc)
-        *reinterpret_cast<uint4*>(dst + (((4 * half + cc) ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
-      fence_proxy_async();
+        for (int cc = 0; cc < 8; ++cc)
+          *reinterpret_cast<uint4*>(dst + ((cc ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
+        fence_proxy_async();
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
+      if (threadIdx.x == 0) TRACE(2, i);
+      s += NG;
+      while (s >= SA) { s -= SA; ph ^= 1u; }
+      return true;
+    };
+    int rs = 0;                // raw ring slot and phase (TMA staging)
+    uint32_t rph = 0;
+    auto run = [&](auto G) {
+      constexpr int GI = decltype(G)::value;
+      if (!tma) issue_chunk(0);
+      for (int c = 0; c < nchunks; ++c) {   // runs to the end even after a time-out: the cp.async path meets at a barrier
+        if (tma) {
+          if (ok && !wait_or_note(&raw_full[rs], rph, 1, c)) ok = false;
+        } else {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");   // chunk c landed for everyone; chunk c-1 fully decoded
+          if (c + 1 < nchunks) issue_chunk(c + 1);
+        }
+        if constexpr (FAST) {
+          const uint8_t* chunk = sRaw + (size_t)rs * RAW_STAGE + (size_t)r * TmaGeom<TYPE>::RBC_T;
+          auto stage = [&](auto SCc) {
+            constexpr int SC = decltype(SCc)::value;
+            const int i = c * 4 + SC;
+            if (i < p.nmain && ok) {
+              uint32_t v[32];
+              if (!(p.debug & 1)) {
+                Stage64<TYPE, ab_t>::template decode<SC>(chunk, v);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0;
+              }
+              ok = publish(v, i);
+            }
+          };
+          stage(std::integral_constant<int, GI>{});
+          if constexpr (NG == 2) stage(std::integral_constant<int, GI + 2>{});
+        } else {
+          // row pointer such that (pointer + byte offset in the row) lands in this thread's slot of chunk c
+          const int64_t beg = n * p.row_bytes + (int64_t)c * rbc;
+          const uint8_t* srow = sRaw + (size_t)(tma ? rs : (c & 1)) * RAW_STAGE + (size_t)r * slot + (tma ? 0 : (beg & 15)) - (int64_t)c * rbc;
+          for (int i = c * SPC + GI; i < (c + 1) * SPC && i < p.nmain && ok; i += NG) {
+            uint32_t v[32];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int u = 2 * i + h;
+              uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
+              if (live && u < nunits && !(p.debug & 1)) {
+                constexpr int RW = Decoder<TYPE, ab_t>::RW;
+                uint32_t raw[RW];
+                Decoder<TYPE, ab_t>::load(srow, u, raw);
+                Decoder<TYPE, ab_t>::decode(srow, u, raw, cx, vh);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) vh[j] = 0;
+              }
+            }
+            ok = publish(v, i);
+          }
+        }
+        if (tma) {   // this warp is done reading the raw chunk: hand the slot back to the loader
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[rs]);
+          if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
+        }
+      }
+      // correction columns (Q4_0 / Q4_K): a few stages at the end, straight from global memory
+      int i0 = p.nmain;
+      while ((i0 % NG) != GI) ++i0;
+      for (int i = i0; i < nk && ok; i += NG) {
+        uint32_t v[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
+          if (live) {
+            Decoder<TYPE, ab_t>::corr(row, 2 * (i - p.nmain) + h, p.K, vh);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) vh[j] = 0;
+          }
+        }
+        ok = publish(v, i);
+      }
+    };
+    if (g == 0) run(std::integral_constant<int, 0>{});
+    else if (g == 1) run(std::integral_constant<int, 1>{});
+    else if constexpr (NG == 4) {
+      if (g == 2) run(std::integral_constant<int, 2>{});
+      else run(std::integral_constant<int, 3>{});
     }
-    // ---------------- epilogue: TMEM lane r = weight row n0 + r; the two threads of a row split the columns ----------------
-    if (ok) ok = mbar_wait_bounded(accum, 0);
-    if (ok) {
-      tc_fence_after();
-      out_t* y = static_cast<out_t*>(p.y);
-      const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-      const int64_t npp = MOE ? (int64_t)p.n_post_pad[0] : 0;
-      constexpr int CHALF = TN >= 32 ? TN / 2 : TN;          // columns per thread of a row pair
-      const int cbeg = TN >= 32 ? half * CHALF : 0;
-      const int cend = TN >= 32 ? cbeg + CHALF : (half == 0 ? TN : 0);
+    // ---------------- epilogue: TMEM lane r = weight row n0 + r; the NG threads of a row split the columns ----------------
+    if (threadIdx.x == 0) TRACE(6, 2);
+    if (ok) ok = wait_or_note(accum, 0, 3, 0);
+    if (threadIdx.x == 0) TRACE(6, 3);
+    tc_fence_after();
+    out_t* y = static_cast<out_t*>(p.y);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const int64_t npp = MOE ? (int64_t)p.n_post_pad[0] : 0;
+    constexpr int CH = TN / NG;          // columns per thread of the NG threads that share a row (a multiple of 16)
+    const int cbeg = g * CH, cend = cbeg + CH;
+    if (!MOE && p.y_tma) {
+      // Stage the tile as [token][128 rows] in the (now idle) operand stages and let one TMA
+      // store write it: full lines to global memory, edges clipped by the tensor map.
+      out_t* so = reinterpret_cast<out_t*>(smem);
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = cbeg; c0 < cend; c0 += 16) {
+          uint32_t acc[16];
+          tmem_ld16(lane_addr + (uint32_t)c0, acc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) so[(c0 + j) * MMQ_ROWS + r] = from_float<out_t>(__uint_as_float(acc[j]));
+        }
+        fence_proxy_async();
+      }
+      // every producer thread arrives here, also after a time-out, so the barrier cannot hang
+      asm volatile("bar.sync 2, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");
+      if (threadIdx.x == 0 && ok) {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&ymap), "r"(smem_u32(so)),
+                     "r"((int)n0), "r"((int)t0)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+    } else if (ok) {
 #pragma unroll 1
       for (int c0 = cbeg; c0 < cend; c0 += 16) {
         uint32_t acc[16];
@@ -321,58 +416,88 @@ __global__ void __launch_bounds__(MMQ_THREADS, (TN <= 64 ? 2 : 1)) mmq_kernel(co
         }
       }
     }
+    if (threadIdx.x == 0) TRACE(6, 4);
   } else if (warp == MMQ_PRODUCER_WARPS) {
     // ---------------- B loader: one TMA box (64 k x TN rows) per stage ----------------
     if (lane == 0) {
+      // B slot i % SB held stage i - SB: wait for that stage's commit (on its A slot's barrier)
+      int sa = 0, sb = 0;             // slots of stage i
+      int se = 0;                     // A slot of stage i - SB and the phase of that use
+      uint32_t phe = 0;
       for (int i = 0; i < nk; ++i) {
-        const int s = i % MMQ_STAGES;
-        const uint32_t round = (uint32_t)(i / MMQ_STAGES);
-        if (!mbar_wait_bounded(&empty[s], (round & 1u) ^ 1u)) { ok = false; break; }
+        if (i >= SB) {
+          if (!wait_or_note(&empty_a[se], phe, 4, i)) { ok = false; break; }
+          if (++se == SA) { se = 0; phe ^= 1u; }
+        }
         const int64_t col = i < p.nmain ? (int64_t)i * MMQ_BK : p.kpad + (int64_t)(i - p.nmain) * MMQ_BK;
-        if (p.debug & 8) { mbar_arrive(&full_b[s]); continue; }
-        mbar_expect_tx(&full_b[s], (uint32_t)B_STAGE);
-        tma_load_2d(sB + (size_t)s * B_STAGE, &bmap, (int)col, (int)t0, &full_b[s]);
+        if (p.debug & 8) {
+          mbar_arrive(&full_a[sa]);
+        } else {
+          mbar_expect_tx(&full_a[sa], (uint32_t)B_STAGE);
+          tma_load_2d(sB + (size_t)sb * B_STAGE, &bmap, (int)col, (int)t0, &full_a[sa]);
+        }
+        TRACE(4, i);
+        if (++sa == SA) sa = 0;
+        if (++sb == SB) sb = 0;
       }
     }
   } else if (warp == MMQ_PRODUCER_WARPS + 2) {
     // ---------------- raw-weight loader: one 2-D TMA box (chunk bytes x 128 rows) per chunk ----------------
-    if (lane == 0 && p.raw_tma) {
-      const int SPC = kc / MMQ_BK;
-      const int nchunks = (p.nmain + SPC - 1) / SPC;
+    if (lane == 0 && tma) {
       int64_t wrow = p.w_row0 + n0;
       if (MOE) wrow += (int64_t)p.expert_ids[blockIdx.y] * p.N;
+      int st = 0;
+      uint32_t sph = 0;
       for (int c = 0; c < nchunks; ++c) {
-        const int st = c % p.raw_stages;
-        const uint32_t round = (uint32_t)(c / p.raw_stages);
-        if (!mbar_wait_bounded(&raw_empty[st], (round & 1u) ^ 1u)) { ok = false; break; }
+        if (!wait_or_note(&raw_empty[st], sph ^ 1u, 5, c)) { ok = false; break; }
         mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
         tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, c * (rbc / 4), (int)wrow, &raw_full[st]);
+        if (++st == p.raw_stages) { st = 0; sph ^= 1u; }
       }
     }
   } else if (warp == MMQ_PRODUCER_WARPS + 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop with uniform control flow (slot counters and descriptors stay
+    // warp-uniform values); one elected lane issues the tcgen05 instructions.
+    {
       const uint32_t idesc = umma_idesc(MMQ_ROWS, TN, sizeof(ab_t) == 2 && std::is_same<ab_t, __nv_bfloat16>::value ? 1 : 0);
+      int sa = 0, sb = 0;
+      uint32_t pha = 0;
+      const uint64_t ad0 = umma_desc_sw128(smem_u32(sA)), bd0 = umma_desc_sw128(smem_u32(sB));
       for (int i = 0; i < nk; ++i) {
-        const int s = i % MMQ_STAGES;
-        const uint32_t round = (uint32_t)(i / MMQ_STAGES);
-        if (!mbar_wait_bounded(&full_a[s], round & 1u) || !mbar_wait_bounded(&full_b[s], round & 1u)) { ok = false; break; }
+        // lane 0 spins on the non-blocking probe (lowest latency once the stage is ready); the warp follows
+        int got = 1;
+        if (lane == 0) {
+          got = 0;
+          for (int spin = 0; spin < 4096 && !got; ++spin) got = mbar_test_wait(&full_a[sa], pha);
+          if (!got) got = wait_or_note(&full_a[sa], pha, 6, i);
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) { ok = false; break; }
+        if (lane == 0) TRACE(3, i);
         tc_fence_after();
-        const uint64_t ad = umma_desc_sw128(smem_u32(sA + (size_t)s * MMQ_A_STAGE));
-        const uint64_t bd = umma_desc_sw128(smem_u32(sB + (size_t)s * B_STAGE));
-        if (!(p.debug & 4))
+        const uint64_t ad = ad0 + (uint64_t)(sa * (MMQ_A_STAGE >> 4)), bd = bd0 + (uint64_t)(sb * (B_STAGE >> 4));
+        if (elect_one()) {
+          if (!(p.debug & 4))
 #pragma unroll
-        for (int kk = 0; kk < MMQ_BK / 16; ++kk)  // 16 values = 32 bytes = +2 in the descriptor's 16-byte units
-          umma_f16(tmem_base, ad + 2 * kk, bd + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&empty[s]);
+          for (int kk = 0; kk < MMQ_BK / 16; ++kk)  // 16 values = 32 bytes = +2 in the descriptor's 16-byte units
+            umma_f16(tmem_base, ad + 2 * kk, bd + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&empty_a[sa]);
+        }
+        __syncwarp();
+        if (lane == 0) TRACE(5, i);
+        if (++sa == SA) { sa = 0; pha ^= 1u; }
+        if (++sb == SB) sb = 0;
       }
-      if (ok) umma_commit(accum);
+      if (ok && elect_one()) umma_commit(accum);
+      __syncwarp();
     }
   }
   if (!ok && lane == 0) atomicExch(p.status, E_TIMEOUT);
   tc_fence_before();
   __syncthreads();
   if (warp == MMQ_PRODUCER_WARPS) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0) TRACE(6, 5);
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -393,13 +518,95 @@ static EncodeTiledFn encode_fn() {
 }
 
 int mmq_moe_block_size() { return 64; }
+extern "C" __attribute__((visibility("default"))) int gguf_b200_debug_read_trace(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_mmq_trace, sizeof(g_mmq_trace));
+}
+extern "C" __attribute__((visibility("default"))) int gguf_b200_debug_read_where(int* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_mmq_where, sizeof(g_mmq_where));
+}
 
 static int pick_tn(int64_t M) {
-  if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
   if (M <= 128) return 128;
   return 256;
+}
+
+// Whether the raw weight bytes of this problem can arrive as 2-D TMA boxes: row bytes a multiple
+// of 16 and, for MoE, experts stored back to back with whole 128-row tiles per expert so that a
+// box never leaves the caller's buffer.  One decision, shared by the activation quantizer (which
+// must know the value order of the stage) and the launch.
+static bool raw_tma_ok(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_bytes) {
+  static const char* no_tma = getenv("GGUF_B200_MMQ_NO_RAW_TMA");
+  if (no_tma && no_tma[0] == '1') return false;
+  if (!(type == T_Q4_0 || type == T_Q8_0 || type == T_Q4_K || type == T_IQ4_XS)) return false;
+  const int64_t row_bytes = K / block_size(type) * type_size(type);
+  if (K % 32 != 0 || row_bytes % 16 != 0) return false;
+  if (moe && (expert_stride_bytes != N * row_bytes || N % MMQ_ROWS != 0)) return false;
+  return true;
+}
+int mmq_perm(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_bytes) {
+  if (!raw_tma_ok(type, N, K, moe, expert_stride_bytes)) return 0;
+  switch (type) {
+    case T_Q4_0: return Stage64<T_Q4_0, __half>::PERM;
+    case T_Q4_K: return Stage64<T_Q4_K, __half>::PERM;
+    case T_Q8_0: return Stage64<T_Q8_0, __half>::PERM;
+  }
+  return 0;
+}
+
+template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
+static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap& map, int64_t b_rows, bool raw_tma, cudaStream_t stream) {
+  EncodeTiledFn enc = encode_fn();
+  MmqParams pp = p;
+  CUtensorMap wmap = map;   // placeholder when unused
+  if (raw_tma) {
+    const int64_t map_rows = MOE ? a.N * 256 : a.N;   // expert ids are limited to [0, 255]; boxes only touch experts that are routed to
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint64_t wd[2] = {(cuuint64_t)(pp.row_bytes / 4), (cuuint64_t)map_rows};
+    const cuuint64_t ws[1] = {(cuuint64_t)pp.row_bytes};
+    const cuuint32_t wb[2] = {(cuuint32_t)(TmaGeom<TYPE>::RBC_T / 4), (cuuint32_t)MMQ_ROWS};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.w), wd, ws, wb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return E_CUDA;
+  }
+  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TN) * TN * MMQ_BK * 2 + 4096;
+  const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
+  const size_t budget = 226 * 1024;
+  int rs = raw_tma ? (int)((budget - ab_bytes) / raw_stage) : 2;
+  if (rs > MMQ_MAX_RAW) rs = MMQ_MAX_RAW;
+  if (rs < 2) rs = 2;
+  pp.raw_tma = raw_tma ? 1 : 0;
+  pp.raw_stages = rs;
+  pp.w_row0 = 0;
+  const size_t smem = ab_bytes + (size_t)rs * raw_stage;
+  if (smem > 227 * 1024) return E_TOO_LARGE;
+  // output tile through shared memory + TMA store when the rows of y allow a tensor map
+  CUtensorMap ymap = map;
+  pp.y_tma = 0;
+  static const char* no_ytma = getenv("GGUF_B200_MMQ_NO_Y_TMA");
+  if (!MOE && (a.N * sizeof(out_t)) % 16 == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && !(no_ytma && no_ytma[0] == '1')) {
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint64_t yd[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
+    const cuuint64_t ys[1] = {(cuuint64_t)a.N * sizeof(out_t)};
+    const cuuint32_t yb[2] = {(cuuint32_t)MMQ_ROWS, (cuuint32_t)TN};
+    const CUtensorMapDataType ydt = std::is_same<out_t, float>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                    : (std::is_same<out_t, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    if (enc(&ymap, ydt, 2, a.y, yd, ys, yb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+      pp.y_tma = 1;
+  }
+  auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE, FAST>;
+  static size_t configured[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > configured[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
+    configured[dev & 63] = smem;
+  }
+  dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), 1);
+  kern<<<grid, mmq_threads(TN), smem, stream>>>(map, wmap, ymap, pp);
+  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
 }
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE>
@@ -415,59 +622,27 @@ static int launch_tn(const MmqArgs& a, const MmqParams& p, int64_t b_rows, cudaS
   if (enc(&map, dt, 2, const_cast<void*>(a.b), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return E_CUDA;
-  // Raw weight bytes: 2-D TMA boxes when the geometry allows (row bytes a multiple of 16 and, for
-  // MoE, experts stored back to back with whole tiles per expert so that a box never leaves the
-  // caller's buffer), else cp.async pieces issued by the decode warps.
-  MmqParams pp = p;
-  CUtensorMap wmap = map;   // placeholder when unused
-  static const char* no_tma = getenv("GGUF_B200_MMQ_NO_RAW_TMA");
-  bool raw_tma = TmaGeom<TYPE>::OK && a.K % 32 == 0 && pp.row_bytes % 16 == 0 && !(no_tma && no_tma[0] == '1');
-  int64_t map_rows = a.N;
-  if (MOE) {
-    raw_tma = raw_tma && a.expert_stride_bytes == a.N * pp.row_bytes && a.N % MMQ_ROWS == 0;
-    map_rows = a.N * 256;   // expert ids are limited to [0, 255]; boxes only touch experts that are routed to
+  const bool raw_tma = raw_tma_ok(TYPE, a.N, a.K, MOE, a.expert_stride_bytes);
+  if constexpr (Stage64<TYPE, ab_t>::FAST) {
+    // the whole-stage decoders need the TMA boxes and the activation order they were quantized in
+    if (raw_tma && a.perm == Stage64<TYPE, ab_t>::PERM) return launch_kernel<TYPE, ab_t, out_t, TN, MOE, true>(a, p, map, b_rows, true, stream);
   }
-  if (raw_tma) {
-    const cuuint64_t wd[2] = {(cuuint64_t)(pp.row_bytes / 4), (cuuint64_t)map_rows};
-    const cuuint64_t ws[1] = {(cuuint64_t)pp.row_bytes};
-    const cuuint32_t wb[2] = {(cuuint32_t)(TmaGeom<TYPE>::RBC_T / 4), (cuuint32_t)MMQ_ROWS};
-    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.w), wd, ws, wb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      raw_tma = false;
-  }
-  const size_t ab_bytes = 1024 + (size_t)mmq_stages(TN) * (MMQ_A_STAGE + TN * MMQ_BK * 2) + 4096;
-  const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
-  const size_t budget = (TN <= 64 ? 113 : 226) * 1024;   // two CTAs per SM for small token tiles
-  int rs = raw_tma ? (int)((budget - ab_bytes) / raw_stage) : 2;
-  if (rs > MMQ_MAX_RAW) rs = MMQ_MAX_RAW;
-  if (rs < 2) rs = 2;
-  pp.raw_tma = raw_tma ? 1 : 0;
-  pp.raw_stages = rs;
-  pp.w_row0 = 0;
-  const size_t smem = ab_bytes + (size_t)rs * raw_stage;
-  if (smem > 227 * 1024) return E_TOO_LARGE;
-  auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE>;
-  static size_t configured[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (smem > configured[dev & 63]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
-    configured[dev & 63] = smem;
-  }
-  dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), 1);
-  kern<<<grid, MMQ_THREADS, smem, stream>>>(map, wmap, pp);
-  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+  if (a.perm != 0) return E_BAD_SHAPE;
+  return launch_kernel<TYPE, ab_t, out_t, TN, MOE, false>(a, p, map, b_rows, raw_tma, stream);
 }
 
 template <int TYPE, typename ab_t, typename out_t>
 static int launch_shape(const MmqArgs& a, const MmqParams& p, cudaStream_t s) {
   if (a.sorted_ids) return launch_tn<TYPE, ab_t, out_t, 64, true>(a, p, a.n_sorted, s);
   switch (pick_tn(a.M)) {
-    case 16: return launch_tn<TYPE, ab_t, out_t, 16, false>(a, p, a.M, s);
     case 32: return launch_tn<TYPE, ab_t, out_t, 32, false>(a, p, a.M, s);
     case 64: return launch_tn<TYPE, ab_t, out_t, 64, false>(a, p, a.M, s);
     case 128: return launch_tn<TYPE, ab_t, out_t, 128, false>(a, p, a.M, s);
-    default: return launch_tn<TYPE, ab_t, out_t, 256, false>(a, p, a.M, s);
+    default: {
+      const int rc = launch_tn<TYPE, ab_t, out_t, 256, false>(a, p, a.M, s);
+      // (padded cp.async staging of the widest rows does not fit beside three 256-token stages)
+      return rc == E_TOO_LARGE ? launch_tn<TYPE, ab_t, out_t, 128, false>(a, p, a.M, s) : rc;
+    }
   }
 }
 
@@ -507,8 +682,13 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
     case T_Q8_0: return bf ? E_BAD_DTYPE : launch_out<T_Q8_0, __half>(a, p, stream);
     case T_Q4_K: return bf ? E_BAD_DTYPE : launch_out<T_Q4_K, __half>(a, p, stream);
     case T_Q6_K: return bf ? E_BAD_DTYPE : launch_out<T_Q6_K, __half>(a, p, stream);
-    case T_IQ2_XXS: return bf ? launch_out<T_IQ2_XXS, __nv_bfloat16>(a, p, stream) : launch_out<T_IQ2_XXS, __half>(a, p, stream);
-    case T_IQ4_XS: return bf ? launch_out<T_IQ4_XS, __nv_bfloat16>(a, p, stream) : launch_out<T_IQ4_XS, __half>(a, p, stream);
+    // the dequantize-then-matmul route computes and returns in the activations' own 16-bit type
+    case T_IQ2_XXS:
+      if (a.out_dtype != a.b_dtype) return E_BAD_DTYPE;
+      return bf ? launch_shape<T_IQ2_XXS, __nv_bfloat16, __nv_bfloat16>(a, p, stream) : launch_shape<T_IQ2_XXS, __half, __half>(a, p, stream);
+    case T_IQ4_XS:
+      if (a.out_dtype != a.b_dtype) return E_BAD_DTYPE;
+      return bf ? launch_shape<T_IQ4_XS, __nv_bfloat16, __nv_bfloat16>(a, p, stream) : launch_shape<T_IQ4_XS, __half, __half>(a, p, stream);
   }
   return E_BAD_TYPE;
 }

@@ -70,7 +70,7 @@ template <int TYPE> struct TmaGeom {
   static constexpr int RBC_T = KC_T / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;   // 144 or 272
 };
 template <int TYPE> struct RawGeom {
-  static constexpr int KC = (TYPE == T_Q8_0) ? 128 : (TYPE == T_IQ2_XXS ? 512 : 256);
+  static constexpr int KC = TYPE == T_IQ2_XXS ? 512 : 256;   // multiples of 256: every producer group meets every chunk
   static constexpr int RBC = KC / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;
   static constexpr int S16 = (RBC + 30) / 16 + 1;
   static constexpr int SLOT = (S16 % 2 ? S16 : S16 + 1) * 16;
@@ -294,6 +294,137 @@ template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
     }
   }
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+// =============================================================================================
+// Whole-stage decoders: one thread turns the 64 values of one weight row of one K stage into
+// the 128 bytes of that row in the A tile (out[4c..4c+3] = 16-byte piece c of the row).
+//
+// The specialised ("fast") forms read a dense 256-value chunk of the row from shared memory
+// (the 2-D TMA box of mmq.cu) with 16-byte loads at compile-time offsets and build fp16 pairs
+// with the mantissa trick: OR-ing a small unsigned integer n into the mantissa of 1024.0
+// (0x6400) gives exactly 1024 + n, into bits 4-7 of 64.0 (0x5400) exactly 64 + n.  Values are
+// the same as the 32-value decoders above produce (one rounding, in the final multiply).
+//
+// PERM: order of the 64 values inside the stage.  0 = natural.  1 = within every group of four
+// consecutive values the middle two are swapped (0,2,1,3): the two low nibbles that sit 16 bits
+// apart in a 32-bit word of packed bytes become one fp16 pair with a single AND/OR.  The
+// activation matrix is written in the same order (quantize_q8_1.cu), so the contraction is
+// unchanged.
+// =============================================================================================
+template <int TYPE, typename ab_t> struct Stage64 {
+  static constexpr bool FAST = false;
+  static constexpr int PERM = 0;
+};
+
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ __half2 h2const(float v) { return __floats2half2_rn(v, v); }
+
+// ---- Q4_K: chunk = one 144-byte super-block; stage SC = sub-blocks 2SC (low nibbles) and 2SC+1 ----
+template <> struct Stage64<T_Q4_K, __half> {
+  static constexpr bool FAST = true;
+  static constexpr int PERM = 1;
+  template <int SC> static __device__ __forceinline__ void decode(const uint8_t* blk, uint32_t (&out)[32]) {
+    const uint4 h = lds128(blk);
+    const uint4 qa = lds128(blk + 16 + 32 * SC), qb = lds128(blk + 32 + 32 * SC);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const __half dall = __ushort_as_half((unsigned short)(h.x & 0xffff));
+    int sc0, sc1, m;
+    q4k_scale_min(h.y, h.z, h.w, 2 * SC, sc0, m);
+    q4k_scale_min(h.y, h.z, h.w, 2 * SC + 1, sc1, m);
+    const __half d0 = __hmul_rn(dall, __int2half_rn(sc0)), d1 = __hmul_rn(dall, __int2half_rn(sc1));
+    const __half2 s0 = __half2half2(d0), s1 = __half2half2(d1);
+    const float big = fmaxf(fabsf(__half2float(d0)), fabsf(__half2float(d1)));
+    if (big < 32.f) {
+      // (1024 + n) * s - 1024 * s: the product term is exact, so this is n * s rounded once
+      const __half2 c0 = __hmul2_rn(s0, h2const(-1024.f)), c1 = __hmul2_rn(s1, h2const(-64.f));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t a = w[j], b = w[j] >> 8;
+        out[2 * j] = h2_as_u32(__hfma2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), s0, c0));
+        out[2 * j + 1] = h2_as_u32(__hfma2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), s0, c0));
+        out[16 + 2 * j] = h2_as_u32(__hfma2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), s1, c1));
+        out[16 + 2 * j + 1] = h2_as_u32(__hfma2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), s1, c1));
+      }
+    } else {  // 1024 * s would overflow fp16: subtract the offset first (exact), then scale
+      const __half2 o0 = h2const(1024.f), o1 = h2const(64.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t a = w[j], b = w[j] >> 8;
+        out[2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), o0), s0));
+        out[2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), o0), s0));
+        out[16 + 2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), o1), s1));
+        out[16 + 2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), o1), s1));
+      }
+    }
+  }
+};
+
+// ---- Q4_0: chunk = 8 blocks of 18 bytes; stage SC = blocks 2SC, 2SC+1 at byte 36*SC ----------------
+template <> struct Stage64<T_Q4_0, __half> {
+  static constexpr bool FAST = true;
+  static constexpr int PERM = 1;
+  static __device__ __forceinline__ void block(const uint32_t (&q)[4], __half2 d2, uint32_t* out) {
+    const __half2 o0 = h2const(1032.f), o1 = h2const(72.f);   // 1024 + 8, 64 + 8
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {   // bytes 4j..4j+3: low nibbles = values 4j.., high nibbles = values 16+4j..
+      const uint32_t a = q[j], b = q[j] >> 8;
+      out[2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), o0), d2));
+      out[2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), o0), d2));
+      out[8 + 2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), o1), d2));
+      out[8 + 2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), o1), d2));
+    }
+  }
+  template <int SC> static __device__ __forceinline__ void decode(const uint8_t* chunk, uint32_t (&out)[32]) {
+    constexpr int A0 = (36 * SC) & ~15, O = (36 * SC - A0) / 4;   // aligned start, word offset of block 2SC
+    uint32_t W[12];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const uint4 v = lds128(chunk + A0 + 16 * i);
+      W[4 * i] = v.x; W[4 * i + 1] = v.y; W[4 * i + 2] = v.z; W[4 * i + 3] = v.w;
+    }
+    // block 2SC starts at word O (d in the low half, nibbles 2 bytes in); block 2SC+1 at word O+4, upper half
+    const uint32_t da = W[O] & 0xFFFFu, db = W[O + 4] >> 16;
+    const uint32_t qa[4] = {__funnelshift_r(W[O], W[O + 1], 16), __funnelshift_r(W[O + 1], W[O + 2], 16),
+                            __funnelshift_r(W[O + 2], W[O + 3], 16), __funnelshift_r(W[O + 3], W[O + 4], 16)};
+    const uint32_t qb[4] = {W[O + 5], W[O + 6], W[O + 7], W[O + 8]};
+    block(qa, u32_as_h2(da | (da << 16)), out);
+    block(qb, u32_as_h2(db | (db << 16)), out + 16);
+  }
+};
+
+// ---- Q8_0: chunk = 8 blocks of 34 bytes; stage SC = blocks 2SC, 2SC+1 at byte 68*SC ----------------
+template <> struct Stage64<T_Q8_0, __half> {
+  static constexpr bool FAST = true;
+  static constexpr int PERM = 0;
+  // two int8 codes (already biased by +128) -> (1024 + u0, 1024 + u1) -> (u - 128) * d
+  static __device__ __forceinline__ uint32_t pair(uint32_t w, uint32_t sel, __half2 d2) {
+    const __half2 o = h2const(1152.f);
+    return h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(w, 0x64646464u, sel)), o), d2));
+  }
+  template <int SC> static __device__ __forceinline__ void decode(const uint8_t* chunk, uint32_t (&out)[32]) {
+    constexpr int A0 = (68 * SC) & ~15, O = (68 * SC - A0) / 4;
+    uint32_t W[20];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      const uint4 v = lds128(chunk + A0 + 16 * i);
+      W[4 * i] = v.x; W[4 * i + 1] = v.y; W[4 * i + 2] = v.z; W[4 * i + 3] = v.w;
+    }
+    const uint32_t da = W[O] & 0xFFFFu, db = W[O + 8] >> 16;
+    const __half2 d2a = u32_as_h2(da | (da << 16)), d2b = u32_as_h2(db | (db << 16));
+    // block 2SC: codes start in the upper half of word O; pair t = codes 2t, 2t+1 = half-word 1+t of the block
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const uint32_t wv = W[O + ((1 + t) >> 1)] ^ 0x80808080u;
+      out[t] = pair(wv, ((1 + t) & 1) ? 0x4342u : 0x4140u, d2a);
+    }
+    // block 2SC+1: codes start at word O+9, aligned
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const uint32_t wv = W[O + 9 + (t >> 1)] ^ 0x80808080u;
+      out[16 + t] = pair(wv, (t & 1) ? 0x4342u : 0x4140u, d2b);
+    }
+  }
 };
 
 }  // namespace gguf_b200

@@ -128,6 +128,102 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
   }
 }
 
+
+// F16 layout, eight inputs per thread (16-byte loads and stores): four lanes own one block of 32.
+// The reference's butterfly adds element i to element i^16, then i^8, i^4, i^2, i^1; with lane
+// t of a quad holding elements 8t..8t+7 the first two levels are shuffles across the quad (lane
+// ^2, lane ^1) and the last three are adds inside the thread, in the same order, so the fp32 sum
+// has the same bits.  perm = 1 stores every group of four values in the order (0,2,1,3) (see
+// Stage64 in mmq_decode.cuh).
+template <typename in_t>
+__global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restrict__ x, __half* __restrict__ xb, int64_t M, int64_t K,
+                                                             int64_t kpad, int64_t ldb, int corr_mode, int perm,
+                                                             const int32_t* __restrict__ gather_ids, int64_t gather_div,
+                                                             int64_t gather_limit) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, t = lane & 3;
+  const int64_t nbr = kpad / 32;                                   // blocks per row
+  const int64_t total = M * nbr;                                   // blocks in all
+  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 2);
+  // every lane of a warp runs the same number of iterations (the shuffles need all of them)
+  const int64_t first = (int64_t)blockIdx.x * (blockDim.x >> 2) + (threadIdx.x >> 5) * 8;
+  for (int64_t b0 = first; b0 < total; b0 += stride) {
+    const int64_t b = b0 + (lane >> 2);
+    const bool inb = b < total;
+    const int64_t row = inb ? b / nbr : 0, kb = inb ? b - row * nbr : 0;
+    const int64_t k = kb * 32 + 8 * t;
+    int64_t src = row;
+    bool have = inb;
+    if (gather_ids && inb) {
+      const int64_t id = gather_ids[row];
+      have = id >= 0 && id < gather_limit;
+      src = have ? id / gather_div : 0;
+    }
+    float v[8];
+    if (have && k + 8 <= K) {
+      if (sizeof(in_t) == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(x + src * K + k), c = *reinterpret_cast<const float4*>(x + src * K + k + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+      } else {
+        const uint4 a = *reinterpret_cast<const uint4*>(x + src * K + k);
+        const in_t* e = reinterpret_cast<const in_t*>(&a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = to_float<in_t>(e[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (have && k + j < K) ? to_float<in_t>(x[src * K + k + j]) : 0.0f;
+    }
+    float amax = 0.f, sm[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      amax = fmaxf(amax, fabsf(v[j]));
+      sm[j] = v[j] + __shfl_xor_sync(0xffffffffu, v[j], 2, 32);          // i ^ 16
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm[j] += __shfl_xor_sync(0xffffffffu, sm[j], 1, 32);   // i ^ 8
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2, 32));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1, 32));
+    float s4[4], s2[2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s4[j] = sm[j] + sm[j + 4];               // i ^ 4
+#pragma unroll
+    for (int j = 0; j < 2; ++j) s2[j] = s4[j] + s4[j + 2];               // i ^ 2
+    const float sum = s2[0] + s2[1];                                      // i ^ 1
+    const float d = amax / 127;
+    const __half hd = __float2half(d), hs = __float2half(sum);
+    const float d8 = __half2float(hd);
+    int q[8], qs = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int8_t qq = amax == 0.0f ? 0 : roundf(v[j] / d);
+      q[j] = qq;
+      qs += q[j];
+    }
+    if (inb) {
+      __half o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int jj = perm ? ((j & 4) | ((j & 1) << 1) | ((j >> 1) & 1)) : j;   // position jj holds value j
+        o[jj] = __float2half_rn(d8 * (float)q[j]);
+      }
+      *reinterpret_cast<uint4*>(xb + row * ldb + k) = *reinterpret_cast<const uint4*>(o);
+    }
+    if (corr_mode != CORR_NONE) {
+      qs += __shfl_xor_sync(0xffffffffu, qs, 2, 32);
+      qs += __shfl_xor_sync(0xffffffffu, qs, 1, 32);
+      if (inb && t == 0) {
+        const float s8 = __half2float(hs);
+        const float c = corr_mode == CORR_Q4_0 ? 8.0f * (d8 * (float)qs - s8) : -s8;   // see quantize_q8_1_kernel
+        xb[row * ldb + kpad + kb] = __float2half_rn(c);
+      }
+      if (inb && kb == 0)
+        for (int64_t c = kpad + nbr + t; c < ldb; c += 4) xb[row * ldb + c] = __float2half_rn(0.f);
+    }
+  }
+}
+
 template <int MODE>
 static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int sum_mode, int64_t ldb,
                        int corr_mode, const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream) {
@@ -152,9 +248,39 @@ static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t
   return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
 }
 
+static int launch_f16x8(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int64_t ldb, int corr_mode, int perm,
+                        const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream) {
+  if (M <= 0 || K <= 0) return M < 0 || K < 0 ? E_BAD_SHAPE : E_OK;
+  const int64_t kpad = round_up(K, 512);
+  const int64_t total = M * (kpad / 32);
+  const int64_t want = (total + 63) / 64;                 // 64 blocks of 32 per CTA pass
+  const int blocks = (int)(want > 148 * 8 ? 148 * 8 : want);
+  __half* o = static_cast<__half*>(out);
+  switch (x_dtype) {
+    case DT_F32:
+      launch_pdl(quantize_f16x8_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim);
+      break;
+    case DT_F16:
+      launch_pdl(quantize_f16x8_kernel<__half>, dim3(blocks), dim3(256), 0, stream, (const __half*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim);
+      break;
+    case DT_BF16:
+      launch_pdl(quantize_f16x8_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim);
+      break;
+    default:
+      return E_BAD_DTYPE;
+  }
+  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+}
+
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int perm) {
+  if (mode == Q8_MODE_F16) {
+    // rows of x and of the output start on 16-byte boundaries when K and ldb are multiples of 8
+    const bool aligned = K % 8 == 0 && ldb % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    if (aligned) return launch_f16x8(x, x_dtype, out, M, K, ldb, corr_mode, perm, gather_ids, gather_div, gather_limit, stream);
+    if (perm) return E_BAD_POINTER;
+  }
   switch (mode) {
     case Q8_MODE_REF: return launch_mode<Q8_MODE_REF>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
     case Q8_MODE_SOA: return launch_mode<Q8_MODE_SOA>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
