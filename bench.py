@@ -214,6 +214,18 @@ def main():
     outs_full = [torch.empty((COPIES, n_rows), dtype=torch.float16, device=dev) for (n_rows, _) in SHAPES]
     outs_host = [torch.empty((COPIES, n_rows), dtype=torch.float16).pin_memory() for (n_rows, _) in SHAPES]
     gathers = [torch.empty((COPIES, g, n_rows // g), dtype=torch.float16, device=dev) for (n_rows, _) in SHAPES] if g > 1 else None
+    # N > 1: the GEMV kernel stores its slice into every rank's output vector over NVLink and raises a
+    # flag (no collective call per GEMV); NCCL all-gather only if peer-mapped memory cannot be set up
+    fused = None
+    if g > 1 and os.environ.get("GGUF_B200_BENCH_NCCL_GATHER", "0") != "1":
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
+        try:
+            from gguf_b200.tp import FusedGatherGemv
+
+            fused = FusedGatherGemv(max(n for n, _ in SHAPES), len(SHAPES) * COPIES, torch.float16, dev)
+        except Exception as exc:
+            print(f"[bench] peer-mapped output unavailable ({type(exc).__name__}: {exc}); using NCCL all-gather", file=sys.stderr)
+            fused = None
 
     ys = [[None] * COPIES for _ in SHAPES]
 
@@ -221,6 +233,13 @@ def main():
         """One pass: every weight copy of both shapes meets its activation vector once."""
         for si, (n_rows, k) in enumerate(SHAPES):
             for c in range(COPIES):
+                if fused is not None:
+                    # a decode chain: each call's quantizer waits for the previous call's gather
+                    slot = si * COPIES + c
+                    ys[si][c] = fused(slot, weights[si][c], xs_dev[si][c:c + 1], Q4_K, wait_slot=slot - 1, wait=False)[:, :n_rows]
+                    if slot == len(SHAPES) * COPIES - 1:
+                        fused.wait(slot)
+                    continue
                 y = ops.ggml_mul_mat_vec_a8(weights[si][c], xs_dev[si][c:c + 1], Q4_K, n_rows // g)
                 ys[si][c] = y
                 if g > 1:
@@ -280,7 +299,7 @@ def main():
                 xd.copy_(xh, non_blocking=True)
             run_step()
             for si in range(len(SHAPES)):
-                if g > 1:
+                if g > 1 and fused is None:
                     src = gathers[si].view(COPIES, -1)
                 else:  # one gather kernel per shape: the step's outputs as one buffer
                     src = torch.cat(ys[si], dim=0, out=outs_full[si])
@@ -363,7 +382,7 @@ def main():
         sys.stderr.flush()
         import threading
 
-        dog = threading.Timer(20.0, lambda: os._exit(0))
+        dog = threading.Timer(120.0, lambda: os._exit(0))
         dog.daemon = True
         dog.start()
         try:
@@ -371,6 +390,9 @@ def main():
             if graph is not None:
                 graph.reset()
                 graph = None
+            # ranks leave together, idle: nobody exits while a peer may still touch mapped memory
+            dist.barrier()
+            torch.cuda.synchronize()
         finally:
             os._exit(0)
 
@@ -383,7 +405,7 @@ def main():
 
     w0 = synth.make_weight(Q4_K, SHAPES[0][0], SHAPES[0][1], seed=0)[:64]
     want, _ = cpu.matmul_a8(w0, Q4_K, xs_host[0][0:1].numpy(), "float16", mmq=False)
-    got = (gathers[0][0].view(-1) if g > 1 else ys[0][0].view(-1))[:64].float().cpu().numpy()
+    got = (gathers[0][0].view(-1) if (g > 1 and fused is None) else ys[0][0].view(-1))[:64].float().cpu().numpy()
     rel = float(np.linalg.norm(got - want[0]) / np.linalg.norm(want[0]))
 
     cpu_base = None
@@ -407,11 +429,12 @@ def main():
         "config": {"workload": "Q4_K GEMV M=1, Llama-3-8B shapes 14336x4096 and 4096x14336, 16 weight copies each per step",
                    "l2": "inputs larger than L2: 1.06 GB of weights per step, each copy read once",
                    "launch": "CUDA graph of one step" if use_graph else "eager",
-                   "parallelism": f"tp{g} column-sharded + NCCL all-gather" if g > 1 else "single GPU",
+                   "parallelism": (f"tp{g} column-sharded, all-gather fused into the GEMV (peer stores over NVLink + flags)" if fused is not None
+                                   else f"tp{g} column-sharded + NCCL all-gather") if g > 1 else "single GPU",
                    "weights_resident": True},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": t_e2e / args.steps * 1e3},
-        "gpu_launches": args.steps * calls_per_step * 2,
+        "gpu_launches": args.steps * (calls_per_step * 2 + (1 if fused is not None else 0)),
         "roofline": roof, "cpu_baseline": cpu_base, "clocks": clocks.summary(),
         "parity": {"rel_l2_vs_oracle": rel, "device_status": status},
         "extras": extras,

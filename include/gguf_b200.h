@@ -127,6 +127,34 @@ int gguf_b200_mul_mat_vec_a8_noalloc(const void* W, const void* X, void* Y, int 
                                      int64_t M, int64_t N, int64_t K, void* stream);
 int64_t gguf_b200_noalloc_scratch_bytes(void);
 
+/* Tensor-parallel decode GEMV (one activation vector) with the all-gather fused into the kernel.
+ * (No counterpart in the reference: there each rank computes its row shard -- the weight loader
+ * shards dim 0, quantization/params.py:229-231 -- and the serving engine's column-parallel linear
+ * layer all-gathers the outputs with a separate collective.)
+ * Rank `rank` of `world` (<= 8) holds rows [rank*N_local, (rank+1)*N_local) of the weight.  The
+ * kernel writes its N_local results to y_peers[r] + rank*N_local for EVERY r: y_peers is a host
+ * array of `world` device pointers to each rank's full output vector (world*N_local elements of
+ * `dtype`), peer-mapped into this process (symmetric memory or CUDA IPC mappings).  When the last
+ * CTA is done it increments epochs_local[slot] (this rank's own launch counter) and then
+ * flag_peers[r][slot] on every rank.  flag_peers[r] / epochs_local are arrays of uint32 counters,
+ * zero before first use, that only ever grow (captured graphs can be replayed without a reset).
+ * wait_slot >= 0: X was computed from the vector gathered in that slot, so the activation
+ * quantizer first waits (bounded, about a second, then GGUF_B200_E_TIMEOUT in the status word)
+ * until flag_peers[rank][wait_slot] >= world * epochs_local[wait_slot]; -1: no wait.
+ * A slot's vector may be rewritten only after every rank has consumed it.  Calls that can
+ * overlap on one GPU must use different slots (slot % 64 selects internal state).  Every rank
+ * issues the same sequence of calls.  X, ws as in gguf_b200_mul_mat_vec_a8.
+ * Returns GGUF_B200_E_TOO_LARGE when the rows are too long for the single-vector kernel. */
+int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* y_peers, uint32_t* const* flag_peers,
+                                uint32_t* epochs_local, int slot, int wait_slot, void* ws, int64_t ws_bytes, int type,
+                                int dtype, int64_t N_local, int64_t K, int rank, int world, void* stream);
+/* Completes the gather of `slot` on this rank for consumers that are not one of the calls above:
+ * a one-thread kernel that waits, for at most about a second, until
+ * flags_local[slot] >= world * epochs_local[slot]; a time-out sets the status word
+ * (gguf_b200_last_status) to GGUF_B200_E_TIMEOUT.  Work queued on `stream` behind it may read the
+ * full output vector. */
+int gguf_b200_tp_wait(const uint32_t* flags_local, const uint32_t* epochs_local, int slot, int world, void* stream);
+
 /* Token-block size the caller must pass to moe_align_block_size.
  * Replaces: ggml_moe_get_block_size, gguf_kernel.cu:532-566 (4 for every type there). */
 int gguf_b200_moe_block_size(int type);

@@ -346,3 +346,35 @@ def test_fused_moe_dispatcher_matches_dense_experts():
             want[tok] += float(tw[tok, j]) * (h @ d2[e].T)
     # activations are q8_1-quantized twice on the kernel path: the reference's own tolerance class
     assert rel_l2(out.float().cpu(), want.cpu()) < 3e-2
+
+
+# ---------------------------------------------------------------- fused gather (tensor parallel) --
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q8_0", "IQ4_XS"])
+def test_tp_gemv_peer_stores_one_gpu(name):
+    """Two ranks emulated on one GPU, one after the other on one stream (nothing ever waits on a
+    kernel that has not been launched): each writes its row slice into both output vectors and
+    raises both flags; the wait kernels then find the flags complete.  Result = unsharded GEMV."""
+    t = TYPES[name]
+    N, K = 1024, 2048
+    wn, w = dev_w(t, N, K, seed=5)
+    x = dev_x(1, K, seed=5)
+    want = capi.mul_mat_vec_a8(w, x, t, N)
+    ys = [torch.zeros(N, dtype=torch.float16, device=DEV) for _ in range(2)]
+    flags = [torch.zeros(1024, dtype=torch.int32, device=DEV) for _ in range(2)]
+    epochs = [torch.zeros(1024, dtype=torch.int32, device=DEV) for _ in range(2)]
+    slot = 3
+    for rep in range(2):
+        for y in ys:
+            y.zero_()
+        for r in range(2):
+            capi.mul_mat_vec_a8_tp(w[r * N // 2:(r + 1) * N // 2].contiguous(), x, [y.data_ptr() for y in ys],
+                                   [f.data_ptr() for f in flags], epochs[r], slot, t, r,
+                                   wait_slot=slot if rep else -1)   # second round: the quantizer checks round one's flags
+        for r in range(2):
+            capi.tp_wait(flags[r], epochs[r], slot, 2)
+        torch.cuda.synchronize()
+        assert capi.last_status() == 0
+        for r in range(2):
+            assert int(flags[r][slot]) == 2 * (rep + 1) and int(epochs[r][slot]) == rep + 1
+            assert torch.equal(ys[r].view(1, N), want)

@@ -131,6 +131,51 @@ int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, in
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
 }
 
+int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* y_peers, uint32_t* const* flag_peers,
+                                uint32_t* epochs_local, int slot, int wait_slot, void* ws, int64_t ws_bytes, int type, int dtype,
+                                int64_t N_local, int64_t K, int rank, int world, void* stream) {
+  if (!y_peers || !flag_peers || !epochs_local) return E_BAD_POINTER;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0) return E_BAD_SHAPE;
+  int rc = check_common(W, X, y_peers[rank], type, dtype, 1, N_local, K);
+  if (rc || N_local == 0) return rc;
+  if (!ws || !aligned16(ws)) return E_BAD_POINTER;
+  if (ws_bytes < q8_soa_bytes(1, K)) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  GemvTp tp{};
+  tp.world = world;
+  tp.slot = slot;
+  tp.rank = rank;
+  tp.epoch = epochs_local;
+  tp.y_off = (int64_t)rank * N_local;
+  for (int r = 0; r < world; ++r) {
+    if (!y_peers[r] || !flag_peers[r]) return E_BAD_POINTER;
+    tp.y_peer[r] = y_peers[r];
+    tp.flag_peer[r] = flag_peers[r];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Q8Wait wt{};
+  if (wait_slot >= 0) {   // X derives from the vector gathered in wait_slot: the quantizer waits for it
+    wt.flag = flag_peers[rank] + wait_slot;
+    wt.epoch = epochs_local + wait_slot;
+    wt.world = world;
+    wt.status = st;
+  }
+  rc = launch_quantize_q8_1(X, dtype, ws, 1, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s, 0,
+                            wait_slot >= 0 ? &wt : nullptr);
+  if (rc) return rc;
+  rc = launch_gemv1(W, ws, nullptr, type, dtype, N_local, K, st, s, &tp);
+  return rc == 1 ? E_TOO_LARGE : rc;   // rows too long for the single-vector kernel
+}
+
+int gguf_b200_tp_wait(const uint32_t* flags_local, const uint32_t* epochs_local, int slot, int world, void* stream) {
+  if (!flags_local || !epochs_local) return E_BAD_POINTER;
+  if (world < 1 || world > 8 || slot < 0) return E_BAD_SHAPE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  return launch_tp_wait(flags_local, epochs_local, slot, world, st, static_cast<cudaStream_t>(stream));
+}
+
 int gguf_b200_gemv_prepare(const void* X, int dtype, void* ws, int64_t ws_bytes, int type, int64_t M, int64_t K,
                            void* stream) {
   if (!type_size(type)) return E_BAD_TYPE;

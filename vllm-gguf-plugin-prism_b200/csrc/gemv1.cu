@@ -251,6 +251,8 @@ template <> struct G1<T_IQ2_XXS> {
 // amortises the per-item costs (copy issue, barrier wait, address arithmetic) over G1_R rows.
 
 constexpr int G1_R = 4;
+constexpr int G1_MAX_WORLD = 8;
+constexpr int G1_TP_SLOTS = 64;
 
 struct G1Params {
   const uint8_t* w;
@@ -265,7 +267,25 @@ struct G1Params {
   int slot_bytes;        // distance between the rows of an item inside a stage
   int stages, stage_bytes;
   int* status;
+  // tensor-parallel output (world > 0): every result goes to y_peer[r][y_off + row] for all r,
+  // then flag_peer[r][slot] is raised once per launch (see the end of the kernel)
+  int world, slot, rank;
+  unsigned* epoch;
+  int64_t y_off;
+  void* y_peer[G1_MAX_WORLD];
+  unsigned* flag_peer[G1_MAX_WORLD];
 };
+
+// launches in flight per call slot: CTAs of one launch that have finished (reset by the last one)
+__device__ unsigned g_tp_done[G1_TP_SLOTS];
+
+template <typename out_t>
+__device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v) {
+  // tensor-parallel launches write this rank's own copy of the full vector first; the last CTA
+  // forwards the finished slice to the peers in one coalesced pass (end of the kernel)
+  out_t* y = p.world == 0 ? static_cast<out_t*>(p.y) : static_cast<out_t*>(p.y_peer[p.rank]) + p.y_off;
+  y[row] = from_float<out_t>(v);
+}
 
 template <int TYPE, typename out_t>
 __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params p) {
@@ -409,7 +429,6 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   if (TYPE == T_IQ2_XXS) __syncthreads();  // tables staged
   pdl_trigger();  // activations are in registers: the next kernel may be scheduled behind this one
 
-  out_t* y = static_cast<out_t*>(p.y);
   int c_st = 0;
   uint32_t c_phase = 0;
   bool dead = false;
@@ -457,7 +476,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         if (rr < cnt) {
           const float v = warp_sum(acc[rr]);
           if (lane == 0) {
-            if (p.ks == 1) y[c_row + rr] = from_float<out_t>(v);
+            if (p.ks == 1) store_result<out_t>(p, c_row + rr, v);
             else partial[(((i % G1_BATCH) * p.rl + rl_i) * G1_R + rr) * p.ks + ks_i] = v;
           }
         }
@@ -478,13 +497,76 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         if (rr < R && r < p.n) {
           float s = 0.f;
           for (int q = 0; q < p.ks; ++q) s += partial[(((ii % G1_BATCH) * p.rl + gl) * G1_R + rr) * p.ks + q];
-          y[r] = from_float<out_t>(s);
+          store_result<out_t>(p, r, s);
         }
       }
       __syncthreads();
     }
   }
   (void)byte_stride;
+  if (p.world > 0) {
+    // All-gather completion.  Every CTA publishes its results at GPU scope (CTA barrier, then
+    // thread 0's fence -- the pattern of a grid-wide barrier) and counts itself off; the last
+    // CTA copies the finished slice from this rank's vector into every peer's with 16-byte
+    // stores over NVLink (one coalesced pass instead of a 2-byte remote store per row), fences
+    // system-wide and raises this launch's flag on every rank.  The flags only ever grow (one
+    // increment per rank and launch), so replays of a captured graph need no reset; a consumer
+    // waits for world * (this rank's own launch count).
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      unsigned* done = &g_tp_done[p.slot % G1_TP_SLOTS];
+      const unsigned prev = atomicAdd(done, 1u);
+      s_last = prev == gridDim.x - 1;
+      if (s_last) *done = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();   // acquire side of the count-off: the other CTAs' results are visible
+      const out_t* src = static_cast<const out_t*>(p.y_peer[p.rank]) + p.y_off;
+      const int64_t bytes = p.n * (int64_t)sizeof(out_t);
+      const bool vec = ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)bytes) & 15) == 0;
+      for (int r = 0; r < p.world; ++r) {
+        if (r == p.rank) continue;
+        out_t* dst = static_cast<out_t*>(p.y_peer[r]) + p.y_off;
+        if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          const uint4* s4 = reinterpret_cast<const uint4*>(src);
+          uint4* d4 = reinterpret_cast<uint4*>(dst);
+          for (int64_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) d4[i] = __ldcg(s4 + i);
+        } else {
+          for (int64_t i = threadIdx.x; i < p.n; i += blockDim.x) dst[i] = __ldcg(src + i);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        p.epoch[p.slot] += 1;      // read by this rank's later kernels (stream order)
+        __threadfence_system();
+        for (int r = 0; r < p.world; ++r) atomicAdd_system(p.flag_peer[r] + p.slot, 1u);
+      }
+    }
+  }
+}
+
+// One thread waits (bounded) until all `world` ranks have raised flag[slot] for this launch.
+__global__ void tp_wait_kernel(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status) {
+  pdl_trigger();   // whatever follows may be scheduled; it waits for this grid before it reads
+  pdl_wait();      // this rank's own GEMV has finished
+  const unsigned want = epoch[slot] * (unsigned)world;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag + slot) : "memory");
+    if ((int)(v - want) >= 0) return;
+    if (clock64() - t0 > 2000000000ll) {   // about a second: a rank is missing
+      atomicExch(status, E_TIMEOUT);
+      return;
+    }
+  }
+}
+
+int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status, cudaStream_t stream) {
+  return launch_pdl(tp_wait_kernel, dim3(1), dim3(1), 0, stream, flag, epoch, slot, world, status) == cudaSuccess ? E_OK : E_CUDA;
 }
 
 // ---- host -----------------------------------------------------------------------------------
@@ -550,8 +632,20 @@ static int launch_g1_out(const G1Params& p, int out_dtype, cudaStream_t s) {
 
 // Returns E_OK, a negative error, or 1 when the shape is outside this kernel's reach.
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, const GemvTp* tp) {
   G1Params p{};
+  if (tp) {
+    if (tp->world < 1 || tp->world > G1_MAX_WORLD || tp->slot < 0) return E_BAD_SHAPE;
+    p.world = tp->world;
+    p.slot = tp->slot;
+    p.rank = tp->rank;
+    p.epoch = tp->epoch;
+    p.y_off = tp->y_off;
+    for (int r = 0; r < tp->world; ++r) {
+      p.y_peer[r] = tp->y_peer[r];
+      p.flag_peer[r] = tp->flag_peer[r];
+    }
+  }
   p.w = static_cast<const uint8_t*>(w);
   p.bpr = (int)(K / block_size(type));
   p.w_bytes = N * p.bpr * type_size(type);

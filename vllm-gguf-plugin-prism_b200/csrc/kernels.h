@@ -12,11 +12,20 @@ enum : int { Q8_MODE_REF = 0, Q8_MODE_SOA = 1, Q8_MODE_F16 = 2 };
 // correction column appended to the fp16 activation matrix of the tensor-core kernels
 enum : int { CORR_NONE = 0, CORR_Q4_0 = 1, CORR_MIN = 2 };
 
+// Optional wait of the SoA quantizer (tensor-parallel consumer): before reading x, wait until
+// *flag >= *epoch * world (flag raised by every rank's fused-gather GEMV, epoch counted by this
+// rank's own); a time-out sets *status.
+struct Q8Wait {
+  const unsigned* flag = nullptr;
+  const unsigned* epoch = nullptr;
+  int world = 0;
+  int* status = nullptr;
+};
 // M = number of OUTPUT rows.  gather_ids (F16 mode only, may be null): output row r quantizes
 // input row gather_ids[r] / gather_div; ids outside [0, gather_limit) give a zero row.
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream, int perm = 0);
+                         cudaStream_t stream, int perm = 0, const Q8Wait* wait = nullptr);
 // leading dimension (elements) of the fp16 activation matrix of the tensor-core kernels
 int64_t mmq_ldb(int type, int64_t K);
 int mmq_corr_mode(int type);
@@ -32,8 +41,19 @@ int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dt
                 int* status, cudaStream_t stream);
 // Single-vector specialisation (gemv1.cu): activations in registers.  Returns 1 when the shape
 // is outside its reach (the caller then uses the general kernel).
+// Tensor-parallel output of the single-vector kernel: results go to y_peer[r] + y_off for every
+// rank r (peer-mapped pointers), then flag_peer[r][slot] is incremented once per launch.
+struct GemvTp {
+  int world, slot, rank;
+  unsigned* epoch;          // this rank's launch counters: epoch[slot] is incremented by the last CTA
+  int64_t y_off;
+  void* y_peer[8];
+  unsigned* flag_peer[8];
+};
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream);
+                 cudaStream_t stream, const GemvTp* tp = nullptr);
+// waits until flag[slot] has reached world * epoch[slot]; sets *status on a time-out
+int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status, cudaStream_t stream);
 // per-(token,expert) GEMV of the small-batch MoE entry point
 int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* topk_ids, int type, int out_dtype,
                     int64_t tokens, int64_t top_k, int64_t N, int64_t K, int64_t n_experts, int* status,

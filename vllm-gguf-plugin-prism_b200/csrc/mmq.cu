@@ -38,16 +38,19 @@ namespace gguf_b200 {
 
 constexpr int MMQ_ROWS = 128;
 constexpr int MMQ_BK = 64;
+// Producer groups of 128 threads (one thread per weight row) that take the K stages in turn; one
+// CTA per SM.  The whole-stage decoders are short enough for four groups (16 warps) to fit the
+// register file; the generic 32-value decoders need more registers per thread and measured
+// faster with two groups (IQ2_XXS, the longest decode, still gains from four).
+__host__ __device__ constexpr int mmq_groups(int type, bool fast) { return (fast || type == T_IQ2_XXS) ? 4 : 2; }
+__host__ __device__ constexpr int mmq_threads(int type, bool fast) { return (4 * mmq_groups(type, fast) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
 // Ring depths.  The A ring (16 KB slots) is never shallower than the number of producer groups:
 // a group that runs ahead may be at most one use of a slot ahead of the MMA warp, or the
 // one-bit phase parity of the slot's barrier would alias.  The B ring (TN * 128 bytes per slot)
-// only has to cover the TMA latency.
-__host__ __device__ constexpr int mmq_a_stages(int tn) { return 4; }
+// only has to cover the TMA latency.  With 256-token tiles the two-group kernels keep a 3-deep
+// A ring so that two padded raw chunks of the widest rows (34 KB each) still fit.
 __host__ __device__ constexpr int mmq_b_stages(int tn) { return tn > 128 ? 3 : 4; }
-// producer groups of 128 threads (one thread per weight row) that take the K stages in turn;
-// one CTA per SM
-__host__ __device__ constexpr int mmq_groups(int tn) { return 4; }
-__host__ __device__ constexpr int mmq_threads(int tn) { return (4 * mmq_groups(tn) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
+__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, int tn) { return (mmq_groups(type, fast) <= 3 && tn > 128) ? 3 : 4; }
 constexpr int MMQ_MAX_RAW = 6;
 constexpr int MMQ_A_STAGE = MMQ_ROWS * MMQ_BK * 2;  // 16 KB
 
@@ -143,14 +146,14 @@ struct MmqParams {
 };
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
-__global__ void __launch_bounds__(mmq_threads(TN), 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
+__global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
-  constexpr int SA = mmq_a_stages(TN), SB = mmq_b_stages(TN);
-  static_assert(mmq_groups(TN) <= SA, "a producer group may not lap the A ring");
-  constexpr int NG = mmq_groups(TN);
+  constexpr int SA = mmq_a_stages(TYPE, FAST, TN), SB = mmq_b_stages(TN);
+  constexpr int NG = mmq_groups(TYPE, FAST);
+  static_assert(NG <= SA, "a producer group may not lap the A ring");
   constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
   // raw ring geometry: dense TMA boxes or padded cp.async slots
   const bool tma = FAST || p.raw_tma;
@@ -465,15 +468,8 @@ __global__ void __launch_bounds__(mmq_threads(TN), 1) mmq_kernel(const __grid_co
       uint32_t pha = 0;
       const uint64_t ad0 = umma_desc_sw128(smem_u32(sA)), bd0 = umma_desc_sw128(smem_u32(sB));
       for (int i = 0; i < nk; ++i) {
-        // lane 0 spins on the non-blocking probe (lowest latency once the stage is ready); the warp follows
-        int got = 1;
-        if (lane == 0) {
-          got = 0;
-          for (int spin = 0; spin < 4096 && !got; ++spin) got = mbar_test_wait(&full_a[sa], pha);
-          if (!got) got = wait_or_note(&full_a[sa], pha, 6, i);
-        }
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) { ok = false; break; }
+        const bool got = wait_or_note(&full_a[sa], pha, 6, i);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         if (lane == 0) TRACE(3, i);
         tc_fence_after();
         const uint64_t ad = ad0 + (uint64_t)(sa * (MMQ_A_STAGE >> 4)), bd = bd0 + (uint64_t)(sb * (B_STAGE >> 4));
@@ -570,7 +566,7 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return E_CUDA;
   }
-  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TN) * TN * MMQ_BK * 2 + 4096;
+  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TN) * TN * MMQ_BK * 2 + 4096;
   const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
   const size_t budget = 226 * 1024;
   int rs = raw_tma ? (int)((budget - ab_bytes) / raw_stage) : 2;
@@ -605,7 +601,7 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
     configured[dev & 63] = smem;
   }
   dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), 1);
-  kern<<<grid, mmq_threads(TN), smem, stream>>>(map, wmap, ymap, pp);
+  kern<<<grid, mmq_threads(TYPE, FAST), smem, stream>>>(map, wmap, ymap, pp);
   return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
 }
 

@@ -60,9 +60,27 @@ template <typename in_t, int MODE>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restrict__ x, uint8_t* __restrict__ out,
                                                             int64_t M, int64_t K, int64_t kpad, int sum_mode,
                                                             int64_t ldb, int corr_mode, const int32_t* __restrict__ gather_ids,
-                                                            int64_t gather_div, int64_t gather_limit) {
+                                                            int64_t gather_div, int64_t gather_limit, Q8Wait wt) {
   pdl_trigger();  // the consumer kernel may start its weight prefetch now; it waits for this grid before reading
   pdl_wait();     // the activations (and the scratch we overwrite) belong to earlier kernels
+  if (wt.flag) {
+    // tensor-parallel consumer: the activations derive from a vector that all ranks' GEMV kernels
+    // wrote into this rank's memory; wait (bounded) until every rank has raised its flag for it
+    if (threadIdx.x == 0) {
+      const unsigned want = *wt.epoch * (unsigned)wt.world;
+      const long long t0 = clock64();
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wt.flag) : "memory");
+        if ((int)(v - want) >= 0) break;
+        if (clock64() - t0 > 2000000000ll) {   // about a second: a rank is missing
+          atomicExch(wt.status, E_TIMEOUT);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
   const int lane = threadIdx.x & 31;
   const int64_t nbr = kpad / 32;                                   // blocks per row
   const int64_t total = M * nbr;
@@ -226,7 +244,7 @@ __global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restr
 
 template <int MODE>
 static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int sum_mode, int64_t ldb,
-                       int corr_mode, const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream) {
+                       int corr_mode, const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream, Q8Wait wt = Q8Wait{}) {
   if (M <= 0 || K <= 0) return M < 0 || K < 0 ? E_BAD_SHAPE : E_OK;
   const int64_t kpad = round_up(K, 512);
   const int64_t total = M * (kpad / 32);
@@ -234,13 +252,13 @@ static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t
   uint8_t* o = static_cast<uint8_t*>(out);
   switch (x_dtype) {
     case DT_F32:
-      launch_pdl(quantize_q8_1_kernel<float, MODE>, dim3(blocks), dim3(256), 0, stream, (const float*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      launch_pdl(quantize_q8_1_kernel<float, MODE>, dim3(blocks), dim3(256), 0, stream, (const float*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim, wt);
       break;
     case DT_F16:
-      launch_pdl(quantize_q8_1_kernel<__half, MODE>, dim3(blocks), dim3(256), 0, stream, (const __half*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      launch_pdl(quantize_q8_1_kernel<__half, MODE>, dim3(blocks), dim3(256), 0, stream, (const __half*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim, wt);
       break;
     case DT_BF16:
-      launch_pdl(quantize_q8_1_kernel<__nv_bfloat16, MODE>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim);
+      launch_pdl(quantize_q8_1_kernel<__nv_bfloat16, MODE>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, o, M, K, kpad, sum_mode, ldb, corr_mode, gid, gdiv, glim, wt);
       break;
     default:
       return E_BAD_DTYPE;
@@ -274,7 +292,7 @@ static int launch_f16x8(const void* x, int x_dtype, void* out, int64_t M, int64_
 
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream, int perm) {
+                         cudaStream_t stream, int perm, const Q8Wait* wait) {
   if (mode == Q8_MODE_F16) {
     // rows of x and of the output start on 16-byte boundaries when K and ldb are multiples of 8
     const bool aligned = K % 8 == 0 && ldb % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
@@ -283,7 +301,7 @@ int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64
   }
   switch (mode) {
     case Q8_MODE_REF: return launch_mode<Q8_MODE_REF>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
-    case Q8_MODE_SOA: return launch_mode<Q8_MODE_SOA>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
+    case Q8_MODE_SOA: return launch_mode<Q8_MODE_SOA>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream, wait ? *wait : Q8Wait{});
     case Q8_MODE_F16:
       return launch_mode<Q8_MODE_F16>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, gather_ids, gather_div, gather_limit, stream);
   }

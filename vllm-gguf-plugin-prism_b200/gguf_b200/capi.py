@@ -37,6 +37,8 @@ SIGNATURES = {
     "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_moe_a8_vec": (_I, [_P, _P, _P, _P, _L, _P, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_vec_a8_noalloc": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
+    "gguf_b200_mul_mat_vec_a8_tp": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
+    "gguf_b200_tp_wait": (_I, [_P, _P, _I, _I, _P]),
     "gguf_b200_noalloc_scratch_bytes": (_L, []),
     "gguf_b200_moe_block_size": (_I, [_I]),
     "gguf_b200_last_status": (_I, []),
@@ -165,6 +167,29 @@ def mul_mat_vec_a8_noalloc(W, X, qtype, N):
     _check(lib().gguf_b200_mul_mat_vec_a8_noalloc(W.data_ptr(), X.data_ptr(), Y.data_ptr(), qtype, _DT[X.dtype], M, N, K,
                                                   _stream(X)), "mul_mat_vec_a8_noalloc")
     return Y
+
+
+def mul_mat_vec_a8_tp(W_local, X, y_ptrs, flag_ptrs, epochs_local, slot, qtype, rank, wait_slot=-1):
+    """Rank `rank`'s rows of the GEMV, written into every rank's output vector (y_ptrs: device
+    addresses of the full vectors, one per rank); then epochs_local[slot] += 1 and
+    flag_ptrs[r][slot] += 1 on every rank.  wait_slot >= 0: the quantizer first waits for that
+    slot's gather (X derives from it)."""
+    world = len(y_ptrs)
+    K = X.shape[1]
+    n_local = W_local.shape[0]
+    nbytes = lib().gguf_b200_workspace_bytes(OP_GEMV, qtype, 1, n_local, K)
+    ws = _ws(X, nbytes)
+    ya = (ctypes.c_void_p * world)(*[int(p) for p in y_ptrs])
+    fa = (ctypes.c_void_p * world)(*[int(p) for p in flag_ptrs])
+    _check(lib().gguf_b200_mul_mat_vec_a8_tp(W_local.data_ptr(), X.data_ptr(), ctypes.cast(ya, ctypes.c_void_p),
+                                             ctypes.cast(fa, ctypes.c_void_p), epochs_local.data_ptr(), int(slot),
+                                             int(wait_slot), ws.data_ptr(), nbytes, qtype, _DT[X.dtype], n_local, K,
+                                             int(rank), world, _stream(X)), "mul_mat_vec_a8_tp")
+
+
+def tp_wait(flags_local: torch.Tensor, epochs_local: torch.Tensor, slot: int, world: int):
+    _check(lib().gguf_b200_tp_wait(flags_local.data_ptr(), epochs_local.data_ptr(), int(slot), int(world),
+                                   _stream(flags_local)), "tp_wait")
 
 
 def last_status() -> int:
