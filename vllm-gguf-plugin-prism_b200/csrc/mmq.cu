@@ -115,16 +115,12 @@ __host__ __device__ inline uint32_t umma_idesc(int m, int n, int fmt) {
 }
 
 // ---- kernel -----------------------------------------------------------------------------
-__device__ unsigned long long g_mmq_trace[7][128];
-__device__ int g_mmq_where[8];   // first wait that gave up: code, stage, block x, block y, thread
+// bounded wait; `code` and `i` name the waiter and its stage for whoever instruments a time-out
 __device__ __forceinline__ bool wait_or_note(uint64_t* bar, uint32_t parity, int code, int i) {
-  if (mbar_wait_bounded(bar, parity)) return true;
-  if (atomicCAS(&g_mmq_where[0], 0, code) == 0) {
-    g_mmq_where[1] = i; g_mmq_where[2] = (int)blockIdx.x; g_mmq_where[3] = (int)blockIdx.y; g_mmq_where[4] = (int)threadIdx.x;
-  }
-  return false;
+  (void)code;
+  (void)i;
+  return mbar_wait_bounded(bar, parity);
 }
-#define TRACE(role, i) do { if ((p.debug & 64) && blockIdx.x == 0 && blockIdx.y == 0 && (i) < 128) g_mmq_trace[role][i] = clock64(); } while (0)
 
 struct MmqParams {
   const uint8_t* w;
@@ -182,7 +178,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
   int8_t* s_kv = reinterpret_cast<int8_t*>(s_signs + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) TRACE(6, 0);
   const int64_t n0 = (int64_t)blockIdx.x * MMQ_ROWS;
   const int64_t t0 = (int64_t)blockIdx.y * TN;
   const uint8_t* wbase = p.w;
@@ -221,7 +216,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
-  if (threadIdx.x == 0) TRACE(6, 1);
 
   if (warp < MMQ_PRODUCER_WARPS) {
     // ---------------- A producers ----------------
@@ -265,9 +259,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
     uint32_t ph = 0;
     while (s >= SA) { s -= SA; ph ^= 1u; }
     auto publish = [&](const uint32_t (&v)[32], int i) -> bool {   // wait for the slot, store the row, signal the MMA warp
-      if (threadIdx.x == 0) TRACE(0, i);
       if (!wait_or_note(&empty_a[s], ph ^ 1u, 2, i)) return false;
-      if (threadIdx.x == 0) TRACE(1, i);
       uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
       if (!(p.debug & 2)) {
 #pragma unroll
@@ -277,7 +269,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
-      if (threadIdx.x == 0) TRACE(2, i);
       s += NG;
       while (s >= SA) { s -= SA; ph ^= 1u; }
       return true;
@@ -367,9 +358,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
       else run(std::integral_constant<int, 3>{});
     }
     // ---------------- epilogue: TMEM lane r = weight row n0 + r; the NG threads of a row split the columns ----------------
-    if (threadIdx.x == 0) TRACE(6, 2);
     if (ok) ok = wait_or_note(accum, 0, 3, 0);
-    if (threadIdx.x == 0) TRACE(6, 3);
     tc_fence_after();
     out_t* y = static_cast<out_t*>(p.y);
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
@@ -419,7 +408,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
         }
       }
     }
-    if (threadIdx.x == 0) TRACE(6, 4);
   } else if (warp == MMQ_PRODUCER_WARPS) {
     // ---------------- B loader: one TMA box (64 k x TN rows) per stage ----------------
     if (lane == 0) {
@@ -439,7 +427,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
           mbar_expect_tx(&full_a[sa], (uint32_t)B_STAGE);
           tma_load_2d(sB + (size_t)sb * B_STAGE, &bmap, (int)col, (int)t0, &full_a[sa]);
         }
-        TRACE(4, i);
         if (++sa == SA) sa = 0;
         if (++sb == SB) sb = 0;
       }
@@ -470,7 +457,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
       for (int i = 0; i < nk; ++i) {
         const bool got = wait_or_note(&full_a[sa], pha, 6, i);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-        if (lane == 0) TRACE(3, i);
         tc_fence_after();
         const uint64_t ad = ad0 + (uint64_t)(sa * (MMQ_A_STAGE >> 4)), bd = bd0 + (uint64_t)(sb * (B_STAGE >> 4));
         if (elect_one()) {
@@ -481,7 +467,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
           umma_commit(&empty_a[sa]);
         }
         __syncwarp();
-        if (lane == 0) TRACE(5, i);
         if (++sa == SA) { sa = 0; pha ^= 1u; }
         if (++sb == SB) sb = 0;
       }
@@ -493,7 +478,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
   tc_fence_before();
   __syncthreads();
   if (warp == MMQ_PRODUCER_WARPS) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (threadIdx.x == 0) TRACE(6, 5);
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -514,12 +498,6 @@ static EncodeTiledFn encode_fn() {
 }
 
 int mmq_moe_block_size() { return 64; }
-extern "C" __attribute__((visibility("default"))) int gguf_b200_debug_read_trace(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_mmq_trace, sizeof(g_mmq_trace));
-}
-extern "C" __attribute__((visibility("default"))) int gguf_b200_debug_read_where(int* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_mmq_where, sizeof(g_mmq_where));
-}
 
 static int pick_tn(int64_t M) {
   if (M <= 32) return 32;
