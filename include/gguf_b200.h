@@ -61,7 +61,10 @@ int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int6
  * written, so the caller need not zero-fill. */
 int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream);
 
-/* Scratch bytes needed by an op for the given sizes (rows = M, or tokens for the MoE ops). */
+/* Scratch bytes an op wants for the given sizes (rows = M, or tokens for the MoE ops).  For the
+ * dense GEMM ops this includes room for fp32 partial tiles when the problem is split over K
+ * (few output tiles, long rows); a smaller workspace that still holds the activations is
+ * accepted and merely disables the split. */
 int64_t gguf_b200_workspace_bytes(int op, int type, int64_t M, int64_t N, int64_t K);
 
 /* Decode GEMV: Y[M][N] = q8_1(X) . dequant(W)^T, weights read once for up to 8 vectors.

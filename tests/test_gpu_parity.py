@@ -378,3 +378,29 @@ def test_tp_gemv_peer_stores_one_gpu(name):
         for r in range(2):
             assert int(flags[r][slot]) == 2 * (rep + 1) and int(epochs[r][slot]) == rep + 1
             assert torch.equal(ys[r].view(1, N), want)
+
+
+def test_mmq_split_k_matches_unsplit():
+    """Few output tiles and long rows: the GEMM splits K over CTAs (fp32 partial tiles in the
+    workspace, added in slice order).  With a workspace that only holds the activations the same
+    call runs unsplit; both must agree to fp16 rounding and match the oracle."""
+    t = TYPES["Q4_K"]
+    N, K, M = 512, 8192, 130
+    wn, w = dev_w(t, N, K, seed=11)
+    x = dev_x(M, K, seed=11)
+    y_split = capi.mul_mat_a8(w, x, t, N)
+    L = capi.lib()
+    full = L.gguf_b200_workspace_bytes(1, t, M, N, K)
+    kpad = (K + 511) // 512 * 512
+    small = M * (kpad + (kpad // 32 + 63) // 64 * 64) * 2          # the activation matrix alone
+    assert full > small
+    ws = torch.empty(small, dtype=torch.uint8, device=DEV)
+    y_one = torch.empty_like(y_split)
+    rc = L.gguf_b200_mul_mat_a8(w.data_ptr(), x.data_ptr(), y_one.data_ptr(), ws.data_ptr(), small, t, 1, M, N, K,
+                                torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and capi.last_status() == 0
+    assert rel_l2(y_split.float().cpu(), y_one.float().cpu()) <= 3e-4
+    y64, _ = cpu.matmul_a8(wn, t, x.cpu().numpy(), "float16", mmq=True)
+    assert rel_l2(y_split.float().cpu().numpy(), y64) <= REL_L2_TOL
+    assert rel_l2(y_one.float().cpu().numpy(), y64) <= REL_L2_TOL

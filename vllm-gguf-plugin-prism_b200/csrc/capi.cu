@@ -103,15 +103,22 @@ int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int6
   return launch_dequantize(W, type, out, out_dtype, n_elems, g_q4k_contract, static_cast<cudaStream_t>(stream));
 }
 
+// Below this many tokens the op is bound by reading the weights once, which the GEMV kernel does
+// best; it then runs with the tiled kernels' formulas (Q4_K min term from the stored fp16 sum).
+static const int64_t kMmqGemvMaxTokens = 16;
+
+// activation matrix of the tensor-core kernels, rounded so that what follows it stays aligned
+static int64_t mmq_b_bytes(int type, int64_t M, int64_t K) { return round_up(M * mmq_ldb(type, K) * 2, 256); }
+
 int64_t gguf_b200_workspace_bytes(int op, int type, int64_t M, int64_t N, int64_t K) {
-  (void)N;
   if (!type_size(type) || M < 0 || K <= 0) return 0;
   switch (op) {
     case GGUF_B200_OP_GEMV:
     case GGUF_B200_OP_MOE_VEC: return q8_soa_bytes(M, K);
-    case GGUF_B200_OP_MMQ:
-    case GGUF_B200_OP_MOE: return M * mmq_ldb(type, K) * 2;  /* MOE: M = length of sorted_token_ids */
-    case GGUF_B200_OP_DEQUANT_MATMUL: return 0;
+    /* dense GEMM: + room for the fp32 partial tiles of a split over K (small N, long K) */
+    case GGUF_B200_OP_MMQ: return M <= kMmqGemvMaxTokens ? M * mmq_ldb(type, K) * 2 : mmq_b_bytes(type, M, K) + mmq_split_scratch_bytes(M, N > 0 ? N : 0, K);
+    case GGUF_B200_OP_MOE: return M * mmq_ldb(type, K) * 2;  /* M = length of sorted_token_ids */
+    case GGUF_B200_OP_DEQUANT_MATMUL: return mmq_split_scratch_bytes(M, N > 0 ? N : 0, K);
   }
   return 0;
 }
@@ -197,10 +204,6 @@ int gguf_b200_gemv_prepared(const void* W, const void* ws, void* Y, int type, in
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, static_cast<cudaStream_t>(stream));
 }
 
-// Below this many tokens the op is bound by reading the weights once, which the GEMV kernel does
-// best; it then runs with the tiled kernels' formulas (Q4_K min term from the stored fp16 sum).
-static const int64_t kMmqGemvMaxTokens = 16;
-
 int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
                          int64_t M, int64_t N, int64_t K, void* stream) {
   int rc = check_common(W, X, Y, type, dtype, M, N, K);
@@ -228,13 +231,17 @@ int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_
   a.corr_mode = mmq_corr_mode(type);
   a.rows_out = M;
   a.status = st;
+  // whatever the caller gave beyond the activation matrix may hold split-K partial tiles
+  const int64_t used = mmq_b_bytes(type, M, K);
+  if (ws_bytes > used) {
+    a.part = static_cast<uint8_t*>(ws) + used;
+    a.part_bytes = ws_bytes - used;
+  }
   return launch_mmq(a, s);
 }
 
 int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* ws, int64_t ws_bytes, int type, int dtype,
                              int64_t M, int64_t N, int64_t K, void* stream) {
-  (void)ws;
-  (void)ws_bytes;
   int rc = check_common(W, X, Y, type, dtype, M, N, K);
   if (rc || M == 0 || N == 0) return rc;
   if (type != T_IQ2_XXS && type != T_IQ4_XS) return E_BAD_TYPE;
@@ -249,6 +256,10 @@ int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* ws, in
   a.corr_mode = CORR_NONE;
   a.rows_out = M;
   a.status = st;
+  if (ws && aligned16(ws) && ws_bytes > 0) {   // optional: room for split-K partial tiles
+    a.part = ws;
+    a.part_bytes = ws_bytes;
+  }
   return launch_mmq(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -78,7 +78,11 @@ struct MmqArgs {
   int64_t n_sorted, expert_stride_bytes, top_k, rows_out;
   int moe_block;
   int* status;
+  void* part;               // optional fp32 scratch for split-K partial tiles (16-byte aligned), part_bytes long
+  int64_t part_bytes;
 };
+// bytes of fp32 scratch a dense M x N x K problem can use for split K (0: it never splits)
+int64_t mmq_split_scratch_bytes(int64_t M, int64_t N, int64_t K);
 int launch_mmq(const MmqArgs& a, cudaStream_t stream);
 int mmq_moe_block_size();
 

@@ -139,6 +139,7 @@ struct MmqParams {
   int raw_stages;         // depth of the raw ring
   int64_t w_row0;         // first row of this matrix in wmap (MoE: added to expert * N)
   int y_tma;              // 1: the output tile leaves through shared memory and one TMA store (ymap)
+  int ksplit, sps;        // K slices (grid.z) and main stages per slice; > 1: fp32 partial tiles go to ymap slice z
 };
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
@@ -158,7 +159,15 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
   const int slot = tma ? rbc : RawGeom<TYPE>::SLOT;
   const int RAW_STAGE = MMQ_ROWS * slot;
   const int SPC = kc / MMQ_BK;                  // MMA stages per chunk (a multiple of NG)
-  const int nchunks = (p.nmain + SPC - 1) / SPC;
+  // Split K: CTA z of p.ksplit works on the stages [i_begin, i_begin + nmain) of the row (a
+  // multiple of 8, so chunk boundaries and the stage -> group assignment are unchanged); the
+  // last one also takes the correction columns.  Below, i and c count from this CTA's first
+  // stage / chunk; i_begin and c_begin are added wherever an address is formed.
+  const int i_begin = (int)blockIdx.z * p.sps;
+  const int nmain = min(p.nmain - i_begin, p.sps);
+  const int ncorr = (int)blockIdx.z == p.ksplit - 1 ? p.ncorr : 0;
+  const int c_begin = i_begin / SPC;
+  const int nchunks = (nmain + SPC - 1) / SPC;
   uint8_t* sA = smem;
   uint8_t* sB = smem + SA * MMQ_A_STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB + SB * B_STAGE);
@@ -188,7 +197,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
     wbase += (int64_t)e * p.expert_stride_bytes;
   }
   constexpr uint32_t TMEM_COLS = TN < 32 ? 32 : TN;
-  const int nk = p.nmain + p.ncorr;
+  const int nk = nmain + ncorr;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SA; ++s) {
@@ -237,7 +246,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
       for (int rr = warp; rr < MMQ_ROWS; rr += MMQ_PRODUCER_WARPS) {
         const int64_t nn = n0 + rr;
         if (nn >= p.N) break;
-        const int64_t beg = nn * p.row_bytes + (int64_t)c * rbc;
+        const int64_t beg = nn * p.row_bytes + (int64_t)(c + c_begin) * rbc;
         int64_t end = beg + rbc;
         const int64_t row_end = (nn + 1) * p.row_bytes;
         if (end > row_end) end = row_end;
@@ -291,7 +300,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
           auto stage = [&](auto SCc) {
             constexpr int SC = decltype(SCc)::value;
             const int i = c * 4 + SC;
-            if (i < p.nmain && ok) {
+            if (i < nmain && ok) {
               uint32_t v[32];
               if (!(p.debug & 1)) {
                 Stage64<TYPE, ab_t>::template decode<SC>(chunk, v);
@@ -306,13 +315,13 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
           if constexpr (NG == 2) stage(std::integral_constant<int, GI + 2>{});
         } else {
           // row pointer such that (pointer + byte offset in the row) lands in this thread's slot of chunk c
-          const int64_t beg = n * p.row_bytes + (int64_t)c * rbc;
-          const uint8_t* srow = sRaw + (size_t)(tma ? rs : (c & 1)) * RAW_STAGE + (size_t)r * slot + (tma ? 0 : (beg & 15)) - (int64_t)c * rbc;
-          for (int i = c * SPC + GI; i < (c + 1) * SPC && i < p.nmain && ok; i += NG) {
+          const int64_t beg = n * p.row_bytes + (int64_t)(c + c_begin) * rbc;
+          const uint8_t* srow = sRaw + (size_t)(tma ? rs : (c & 1)) * RAW_STAGE + (size_t)r * slot + (tma ? 0 : (beg & 15)) - (int64_t)(c + c_begin) * rbc;
+          for (int i = c * SPC + GI; i < (c + 1) * SPC && i < nmain && ok; i += NG) {
             uint32_t v[32];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              const int u = 2 * i + h;
+              const int u = 2 * (i + i_begin) + h;
               uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
               if (live && u < nunits && !(p.debug & 1)) {
                 constexpr int RW = Decoder<TYPE, ab_t>::RW;
@@ -334,7 +343,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
         }
       }
       // correction columns (Q4_0 / Q4_K): a few stages at the end, straight from global memory
-      int i0 = p.nmain;
+      int i0 = nmain;
       while ((i0 % NG) != GI) ++i0;
       for (int i = i0; i < nk && ok; i += NG) {
         uint32_t v[32];
@@ -342,7 +351,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
         for (int h = 0; h < 2; ++h) {
           uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
           if (live) {
-            Decoder<TYPE, ab_t>::corr(row, 2 * (i - p.nmain) + h, p.K, vh);
+            Decoder<TYPE, ab_t>::corr(row, 2 * (i - nmain) + h, p.K, vh);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) vh[j] = 0;
@@ -369,22 +378,28 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
       // Stage the tile as [token][128 rows] in the (now idle) operand stages and let one TMA
       // store write it: full lines to global memory, edges clipped by the tensor map.
       out_t* so = reinterpret_cast<out_t*>(smem);
+      float* sf = reinterpret_cast<float*>(smem);       // split K: the partial tile stays fp32
       if (ok) {
 #pragma unroll 1
         for (int c0 = cbeg; c0 < cend; c0 += 16) {
           uint32_t acc[16];
           tmem_ld16(lane_addr + (uint32_t)c0, acc);
           tmem_ld_wait();
+          if (p.ksplit > 1) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) so[(c0 + j) * MMQ_ROWS + r] = from_float<out_t>(__uint_as_float(acc[j]));
+            for (int j = 0; j < 16; ++j) sf[(c0 + j) * MMQ_ROWS + r] = __uint_as_float(acc[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) so[(c0 + j) * MMQ_ROWS + r] = from_float<out_t>(__uint_as_float(acc[j]));
+          }
         }
         fence_proxy_async();
       }
       // every producer thread arrives here, also after a time-out, so the barrier cannot hang
       asm volatile("bar.sync 2, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");
       if (threadIdx.x == 0 && ok) {
-        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&ymap), "r"(smem_u32(so)),
-                     "r"((int)n0), "r"((int)t0)
+        asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&ymap), "r"(smem_u32(so)),
+                     "r"((int)n0), "r"((int)t0), "r"((int)blockIdx.z)
                      : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -420,7 +435,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
           if (!wait_or_note(&empty_a[se], phe, 4, i)) { ok = false; break; }
           if (++se == SA) { se = 0; phe ^= 1u; }
         }
-        const int64_t col = i < p.nmain ? (int64_t)i * MMQ_BK : p.kpad + (int64_t)(i - p.nmain) * MMQ_BK;
+        const int64_t col = i < nmain ? (int64_t)(i + i_begin) * MMQ_BK : p.kpad + (int64_t)(i - nmain) * MMQ_BK;
         if (p.debug & 8) {
           mbar_arrive(&full_a[sa]);
         } else {
@@ -441,7 +456,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const _
       for (int c = 0; c < nchunks; ++c) {
         if (!wait_or_note(&raw_empty[st], sph ^ 1u, 5, c)) { ok = false; break; }
         mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
-        tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, c * (rbc / 4), (int)wrow, &raw_full[st]);
+        tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, (c + c_begin) * (rbc / 4), (int)wrow, &raw_full[st]);
         if (++st == p.raw_stages) { st = 0; sph ^= 1u; }
       }
     }
@@ -529,6 +544,39 @@ int mmq_perm(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_byt
   return 0;
 }
 
+// K slices for a problem of `tiles` output tiles and `nmain` 64-value stages per row: as many as
+// keep every slice at least 16 stages long and the grid within one wave of 148 SMs.
+static int mmq_pick_split(int tiles, int nmain) {
+  static const char* env = getenv("GGUF_B200_MMQ_SPLIT");
+  if (env && env[0] == '0') return 1;
+  for (int s = 4; s >= 2; --s)
+    if ((int64_t)tiles * s <= 148 && nmain / s >= 16) return s;
+  return 1;
+}
+// bytes of fp32 scratch the split may use for an M x N output (0 when it can never split)
+int64_t mmq_split_scratch_bytes(int64_t M, int64_t N, int64_t K) {
+  const int tn = pick_tn(M);
+  const int tiles = (int)(((N + MMQ_ROWS - 1) / MMQ_ROWS) * ((M + tn - 1) / tn));
+  const int s = mmq_pick_split(tiles, (int)((K + MMQ_BK - 1) / MMQ_BK));
+  return s > 1 ? (int64_t)s * M * N * 4 : 0;
+}
+
+// y = sum of the fp32 partial slices, added in slice order (deterministic), rounded once
+template <typename out_t>
+__global__ void __launch_bounds__(256) add_partials_kernel(const float4* __restrict__ part, out_t* __restrict__ y, int64_t n4, int slices) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 s = part[i];
+    for (int z = 1; z < slices; ++z) {
+      const float4 v = part[(int64_t)z * n4 + i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    y[4 * i] = from_float<out_t>(s.x);
+    y[4 * i + 1] = from_float<out_t>(s.y);
+    y[4 * i + 2] = from_float<out_t>(s.z);
+    y[4 * i + 3] = from_float<out_t>(s.w);
+  }
+}
+
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
 static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap& map, int64_t b_rows, bool raw_tma, cudaStream_t stream) {
   EncodeTiledFn enc = encode_fn();
@@ -555,20 +603,37 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
   pp.w_row0 = 0;
   const size_t smem = ab_bytes + (size_t)rs * raw_stage;
   if (smem > 227 * 1024) return E_TOO_LARGE;
-  // output tile through shared memory + TMA store when the rows of y allow a tensor map
+  // Output tile through shared memory + one TMA store when the rows of y allow a tensor map.
+  // Split K (few tiles, long rows): grid.z CTAs per tile each write an fp32 partial tile to slice
+  // z of the caller's scratch through the same store; a second kernel adds the slices in order.
   CUtensorMap ymap = map;
   pp.y_tma = 0;
+  pp.ksplit = 1;
+  pp.sps = pp.nmain;
   static const char* no_ytma = getenv("GGUF_B200_MMQ_NO_Y_TMA");
   if (!MOE && (a.N * sizeof(out_t)) % 16 == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && !(no_ytma && no_ytma[0] == '1')) {
-    const cuuint32_t estr[2] = {1, 1};
-    const cuuint64_t yd[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
-    const cuuint64_t ys[1] = {(cuuint64_t)a.N * sizeof(out_t)};
-    const cuuint32_t yb[2] = {(cuuint32_t)MMQ_ROWS, (cuuint32_t)TN};
-    const CUtensorMapDataType ydt = std::is_same<out_t, float>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+    const int tiles = (int)(((a.N + MMQ_ROWS - 1) / MMQ_ROWS) * ((b_rows + TN - 1) / TN));
+    int split = mmq_pick_split(tiles, pp.nmain);
+    if (!a.part || a.part_bytes < (int64_t)split * a.M * a.N * 4 || (reinterpret_cast<uintptr_t>(a.part) & 15)) split = 1;
+    if (split > 1) {
+      pp.sps = ((pp.nmain + split - 1) / split + 7) / 8 * 8;
+      pp.ksplit = (pp.nmain + pp.sps - 1) / pp.sps;
+    }
+    const bool part = pp.ksplit > 1;
+    const size_t es = part ? 4 : sizeof(out_t);
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const cuuint64_t yd[3] = {(cuuint64_t)a.N, (cuuint64_t)a.M, (cuuint64_t)pp.ksplit};
+    const cuuint64_t ys[2] = {(cuuint64_t)a.N * es, (cuuint64_t)a.N * a.M * es};
+    const cuuint32_t yb[3] = {(cuuint32_t)MMQ_ROWS, (cuuint32_t)TN, 1};
+    const CUtensorMapDataType ydt = (part || std::is_same<out_t, float>::value) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                     : (std::is_same<out_t, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-    if (enc(&ymap, ydt, 2, a.y, yd, ys, yb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+    if (enc(&ymap, ydt, 3, part ? a.part : a.y, yd, ys, yb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
       pp.y_tma = 1;
+    } else {
+      pp.ksplit = 1;
+      pp.sps = pp.nmain;
+    }
   }
   auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE, FAST>;
   static size_t configured[64] = {0};
@@ -578,9 +643,16 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
     configured[dev & 63] = smem;
   }
-  dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), 1);
+  dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), (unsigned)pp.ksplit);
   kern<<<grid, mmq_threads(TYPE, FAST), smem, stream>>>(map, wmap, ymap, pp);
-  return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  if (pp.ksplit > 1) {
+    const int64_t n4 = a.M * a.N / 4;
+    const int blocks = (int)((n4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n4 + 255) / 256);
+    add_partials_kernel<out_t><<<blocks, 256, 0, stream>>>(static_cast<const float4*>(a.part), static_cast<out_t*>(a.y), n4, pp.ksplit);
+    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  }
+  return E_OK;
 }
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE>
