@@ -38,19 +38,27 @@ namespace gguf_b200 {
 
 constexpr int MMQ_ROWS = 128;
 constexpr int MMQ_BK = 64;
-// Producer groups of 128 threads (one thread per weight row) that take the K stages in turn; one
-// CTA per SM.  The whole-stage decoders are short enough for four groups (16 warps) to fit the
-// register file; the generic 32-value decoders need more registers per thread and measured
-// faster with two groups (IQ2_XXS, the longest decode, still gains from four).
-__host__ __device__ constexpr int mmq_groups(int type, bool fast) { return (fast || type == T_IQ2_XXS) ? 4 : 2; }
-__host__ __device__ constexpr int mmq_threads(int type, bool fast) { return (4 * mmq_groups(type, fast) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
+// Producer groups of 128 threads (one thread per weight row) that take the K stages in turn.
+// The whole-stage decoders are short enough for four groups (16 warps) to fit the register
+// file; the generic 32-value decoders need more registers per thread and measured faster with
+// two groups (IQ2_XXS, the longest decode, still gains from four).  Token tiles of 64 or less
+// with a whole-stage decoder run TWO CTAs of two groups per SM instead of one CTA of four: the
+// tensor work per stage is small there and the per-stage cost of one MMA-issuing warp is the
+// limit, so two independent pipelines per SM raise the rate -- when the grid has enough CTAs to
+// put two on every SM (MoE, many row tiles); with fewer CTAs than SMs the one-CTA form keeps
+// all 16 decode warps on the tile (`two` is chosen per launch).
+__host__ __device__ constexpr int mmq_groups(int type, bool fast, bool two) { return two ? 2 : ((fast || type == T_IQ2_XXS) ? 4 : 2); }
+__host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two) { return (4 * mmq_groups(type, fast, two) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
 // Ring depths.  The A ring (16 KB slots) is never shallower than the number of producer groups:
 // a group that runs ahead may be at most one use of a slot ahead of the MMA warp, or the
 // one-bit phase parity of the slot's barrier would alias.  The B ring (TN * 128 bytes per slot)
 // only has to cover the TMA latency.  With 256-token tiles the two-group kernels keep a 3-deep
-// A ring so that two padded raw chunks of the widest rows (34 KB each) still fit.
-__host__ __device__ constexpr int mmq_b_stages(int tn) { return tn > 128 ? 3 : 4; }
-__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, int tn) { return (mmq_groups(type, fast) <= 3 && tn > 128) ? 3 : 4; }
+// A ring so that two padded raw chunks of the widest rows (34 KB each) still fit; the
+// two-CTA-per-SM kernels have half the shared memory each and run 3-deep rings as well.
+__host__ __device__ constexpr int mmq_b_stages(bool two, int tn) { return (tn > 128 || two) ? 3 : 4; }
+__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) {
+  return (two || (mmq_groups(type, fast, two) <= 3 && tn > 128)) ? 3 : 4;
+}
 constexpr int MMQ_MAX_RAW = 6;
 constexpr int MMQ_A_STAGE = MMQ_ROWS * MMQ_BK * 2;  // 16 KB
 
@@ -142,14 +150,14 @@ struct MmqParams {
   int ksplit, sps;        // K slices (grid.z) and main stages per slice; > 1: fp32 partial tiles go to ymap slice z
 };
 
-template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
-__global__ void __launch_bounds__(mmq_threads(TYPE, FAST), 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
+template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST, bool TWO>
+__global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
-  constexpr int SA = mmq_a_stages(TYPE, FAST, TN), SB = mmq_b_stages(TN);
-  constexpr int NG = mmq_groups(TYPE, FAST);
+  constexpr int SA = mmq_a_stages(TYPE, FAST, TWO, TN), SB = mmq_b_stages(TWO, TN);
+  constexpr int NG = mmq_groups(TYPE, FAST, TWO);
   static_assert(NG <= SA, "a producer group may not lap the A ring");
   constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
   // raw ring geometry: dense TMA boxes or padded cp.async slots
@@ -577,7 +585,7 @@ __global__ void __launch_bounds__(256) add_partials_kernel(const float4* __restr
   }
 }
 
-template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST>
+template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST, bool TWO>
 static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap& map, int64_t b_rows, bool raw_tma, cudaStream_t stream) {
   EncodeTiledFn enc = encode_fn();
   MmqParams pp = p;
@@ -592,9 +600,9 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return E_CUDA;
   }
-  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TN) * TN * MMQ_BK * 2 + 4096;
+  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TWO, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TWO, TN) * TN * MMQ_BK * 2 + 4096;
   const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
-  const size_t budget = 226 * 1024;
+  const size_t budget = (TWO ? 113 : 226) * 1024;   // two CTAs share the SM's 228 KB (1 KB each is reserved)
   int rs = raw_tma ? (int)((budget - ab_bytes) / raw_stage) : 2;
   if (rs > MMQ_MAX_RAW) rs = MMQ_MAX_RAW;
   if (rs < 2) rs = 2;
@@ -635,7 +643,7 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
       pp.sps = pp.nmain;
     }
   }
-  auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE, FAST>;
+  auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE, FAST, TWO>;
   static size_t configured[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -644,7 +652,7 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
     configured[dev & 63] = smem;
   }
   dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), (unsigned)pp.ksplit);
-  kern<<<grid, mmq_threads(TYPE, FAST), smem, stream>>>(map, wmap, ymap, pp);
+  kern<<<grid, mmq_threads(TYPE, FAST, TWO), smem, stream>>>(map, wmap, ymap, pp);
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   if (pp.ksplit > 1) {
     const int64_t n4 = a.M * a.N / 4;
@@ -671,10 +679,17 @@ static int launch_tn(const MmqArgs& a, const MmqParams& p, int64_t b_rows, cudaS
   const bool raw_tma = raw_tma_ok(TYPE, a.N, a.K, MOE, a.expert_stride_bytes);
   if constexpr (Stage64<TYPE, ab_t>::FAST) {
     // the whole-stage decoders need the TMA boxes and the activation order they were quantized in
-    if (raw_tma && a.perm == Stage64<TYPE, ab_t>::PERM) return launch_kernel<TYPE, ab_t, out_t, TN, MOE, true>(a, p, map, b_rows, true, stream);
+    if (raw_tma && a.perm == Stage64<TYPE, ab_t>::PERM) {
+      if constexpr (TN <= 64) {
+        // two small CTAs per SM once the grid can put two on every SM (before any split of K)
+        const int64_t ctas = ((a.N + MMQ_ROWS - 1) / MMQ_ROWS) * ((b_rows + TN - 1) / TN);
+        if (ctas >= 2 * 148) return launch_kernel<TYPE, ab_t, out_t, TN, MOE, true, true>(a, p, map, b_rows, true, stream);
+      }
+      return launch_kernel<TYPE, ab_t, out_t, TN, MOE, true, false>(a, p, map, b_rows, true, stream);
+    }
   }
   if (a.perm != 0) return E_BAD_SHAPE;
-  return launch_kernel<TYPE, ab_t, out_t, TN, MOE, false>(a, p, map, b_rows, raw_tma, stream);
+  return launch_kernel<TYPE, ab_t, out_t, TN, MOE, false, false>(a, p, map, b_rows, raw_tma, stream);
 }
 
 template <int TYPE, typename ab_t, typename out_t>
