@@ -33,7 +33,8 @@ GEMV_CASES = [(Q4_K, 57344, 4096, 1), (Q8_0, 3072, 1024, 1), (Q4_K, 14336, 4096,
               (IQ2_XXS, 28672, 8192, 1), (IQ2_XXS, 8192, 28672, 1), (Q4_0, 2048, 2048, 1), (Q4_0, 16384, 4096, 1),
               (Q4_K, 14336, 4096, 2), (Q4_K, 14336, 4096, 4), (Q4_K, 14336, 4096, 8)]
 GEMM_CASES = [("mmq", Q4_K, 14336, 4096, 2048), ("mmq", Q4_K, 14336, 4096, 512), ("mmq", Q4_K, 4096, 14336, 512),
-              ("mmq", Q4_K, 14336, 4096, 64), ("mmq", Q4_K, 4096, 14336, 64), ("mmq", Q4_K, 14336, 4096, 8),
+              ("mmq", Q4_K, 14336, 4096, 64), ("mmq", Q4_K, 4096, 14336, 64), ("mmq", Q4_K, 14336, 4096, 8), ("mmq", Q4_K, 4096, 14336, 8),
+              ("mmq", Q4_K, 14336, 4096, 4), ("mmq", Q4_K, 14336, 4096, 16),
               ("mmq", Q6_K, 37888, 3584, 256), ("mmq", Q8_0, 14336, 4096, 512), ("mmq", Q4_0, 14336, 4096, 512),
               ("dqmm", IQ2_XXS, 28672, 8192, 128), ("dqmm", IQ2_XXS, 8192, 28672, 128), ("dqmm", IQ4_XS, 37888, 3584, 256)]
 

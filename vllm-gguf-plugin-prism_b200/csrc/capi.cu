@@ -103,9 +103,12 @@ int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int6
   return launch_dequantize(W, type, out, out_dtype, n_elems, g_q4k_contract, static_cast<cudaStream_t>(stream));
 }
 
-// Below this many tokens the op is bound by reading the weights once, which the GEMV kernel does
+// Up to this many tokens the op is bound by reading the weights once, which the GEMV kernel does
 // best; it then runs with the tiled kernels' formulas (Q4_K min term from the stored fp16 sum).
-static const int64_t kMmqGemvMaxTokens = 16;
+// Measured cross-over on 14336x4096: the types with whole-stage tensor-core decoders win from 5
+// tokens on (Q4_K, 8 tokens: 26.9 us against 37.3 us through the GEMV); the others keep the GEMV
+// up to 16.
+static int64_t mmq_gemv_max_tokens(int type) { return (type == T_Q4_K || type == T_Q4_0 || type == T_Q8_0) ? 4 : 16; }
 
 // activation matrix of the tensor-core kernels, rounded so that what follows it stays aligned
 static int64_t mmq_b_bytes(int type, int64_t M, int64_t K) { return round_up(M * mmq_ldb(type, K) * 2, 256); }
@@ -116,7 +119,7 @@ int64_t gguf_b200_workspace_bytes(int op, int type, int64_t M, int64_t N, int64_
     case GGUF_B200_OP_GEMV:
     case GGUF_B200_OP_MOE_VEC: return q8_soa_bytes(M, K);
     /* dense GEMM: + room for the fp32 partial tiles of a split over K (small N, long K) */
-    case GGUF_B200_OP_MMQ: return M <= kMmqGemvMaxTokens ? M * mmq_ldb(type, K) * 2 : mmq_b_bytes(type, M, K) + mmq_split_scratch_bytes(M, N > 0 ? N : 0, K);
+    case GGUF_B200_OP_MMQ: return M <= mmq_gemv_max_tokens(type) ? M * mmq_ldb(type, K) * 2 : mmq_b_bytes(type, M, K) + mmq_split_scratch_bytes(M, N > 0 ? N : 0, K);
     case GGUF_B200_OP_MOE: return M * mmq_ldb(type, K) * 2;  /* M = length of sorted_token_ids */
     case GGUF_B200_OP_DEQUANT_MATMUL: return mmq_split_scratch_bytes(M, N > 0 ? N : 0, K);
   }
@@ -215,7 +218,7 @@ int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_
   int* st = status_ptr();
   if (!st) return E_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (M <= kMmqGemvMaxTokens) {
+  if (M <= mmq_gemv_max_tokens(type)) {
     rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, 0, 0, CORR_NONE, nullptr, 1, 0, s);
     if (rc) return rc;
     return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
