@@ -11,11 +11,13 @@ Two fixtures, both produced by code that is NOT this repository's:
 * golden_routing.json -- which operator the reference's dispatcher
   ``_fused_mul_mat_gguf`` (vllm_gguf_plugin/quantization/linear.py:35-58) calls for each
   (type, batch, rows), recorded by importing the reference module from its checkout with its
-  ``ops`` functions replaced by recorders.  Needs /root/reference and vLLM; skipped if absent.
+  ``ops`` functions replaced by recorders.  Needs the reference checkout (GGUF_REFERENCE_ROOT) and
+  vLLM; skipped if absent.
 """
 from __future__ import annotations
 
 import importlib
+import os
 import json
 import sys
 import types
@@ -48,7 +50,7 @@ def gguf_py_fixture():
     print("wrote golden_gguf_py.npz")
 
 
-def routing_fixture(ref_root=Path("/root/reference")):
+def routing_fixture(ref_root=Path(os.environ.get("GGUF_REFERENCE_ROOT", "/root/reference"))):
     if not (ref_root / "vllm_gguf_plugin").exists():
         print("reference checkout absent: golden_routing.json not regenerated")
         return
