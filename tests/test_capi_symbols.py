@@ -55,6 +55,33 @@ def test_geometry_and_error_codes(native_libs):
     assert lib.gguf_b200_dequantize(p, 12, p, 1, 100, null) == -3
     assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 0, 12, 1, 0, 8, 256, null) == 0          # empty batch
     assert b"workspace" in lib.gguf_b200_error_string(-5)
+    # dense GEMM workspace: activations (+ fp32 partial tiles when few tiles and long rows split K)
+    act = lambda m, k: (m * (k + (k // 32 + 63) // 64 * 64) * 2 + 255) // 256 * 256
+    assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 12, 512, 14336, 4096) == act(512, 4096)              # 224 tiles: no split
+    assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 12, 512, 4096, 14336) == act(512, 14336) + 2 * 512 * 4096 * 4
+    assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 12, 64, 4096, 14336) == act(64, 14336) + 4 * 64 * 4096 * 4
+    assert lib.gguf_b200_workspace_bytes(capi.OP_DEQUANT_MATMUL, 16, 128, 28672, 8192) == 0
+    assert lib.gguf_b200_workspace_bytes(capi.OP_DEQUANT_MATMUL, 16, 128, 8192, 28672) == 2 * 128 * 8192 * 4
+
+
+def test_tensor_parallel_entry_points_validate_arguments(native_libs):
+    from gguf_b200 import capi
+
+    lib = capi.lib()
+    null = ctypes.c_void_p(0)
+    p = ctypes.c_void_p(4096)
+    two = (ctypes.c_void_p * 2)(4096, 8192)
+    ptrs = ctypes.cast(two, ctypes.c_void_p)
+    args = lambda **kw: [kw.get("W", p), p, kw.get("y", ptrs), kw.get("f", ptrs), kw.get("e", p), kw.get("slot", 0), -1, p, 1 << 20,
+                         kw.get("type", 12), 1, 64, 256, kw.get("rank", 0), kw.get("world", 2), null]
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(y=null)) == -4
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(e=null)) == -4
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(world=9)) == -3
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(rank=2)) == -3
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(slot=-1)) == -3
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(type=3)) == -1
+    assert lib.gguf_b200_tp_wait(null, p, 0, 2, null) == -4
+    assert lib.gguf_b200_tp_wait(p, p, 0, 0, null) == -3
 
 
 def test_ops_module_fails_loudly_without_extension(tmp_path, monkeypatch):
