@@ -103,7 +103,7 @@ def test_q4k_contraction_knob_selects_oracle_mode():
 
 # ---------------------------------------------------------------- GEMV -----------------------
 
-GEMV_SHAPES = [(3072, 1024, 1), (520, 4096, 1), (257, 2048, 3), (128, 14336, 2), (96, 28672, 1), (64, 3584, 8), (40, 4096, 11)]
+GEMV_SHAPES = [(3072, 1024, 1), (520, 4096, 1), (257, 2048, 3), (128, 14336, 2), (1001, 4096, 2), (300, 1024, 2), (96, 28672, 1), (64, 3584, 8), (40, 4096, 11)]
 
 
 @pytest.mark.parametrize("shape", GEMV_SHAPES)

@@ -633,9 +633,9 @@ int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dt
                 int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return E_OK;
   static const int use_g1 = gemv_tune_int("GGUF_B200_GEMV1", 1);
-  if (M == 1 && use_g1) {
-    const int rc = launch_gemv1(w, xq_soa, y, type, out_dtype, N, K, status, stream);
-    if (rc <= 0) return rc;  // done or failed; 1 = shape outside the single-vector kernel's reach
+  if (M <= 2 && use_g1) {
+    const int rc = launch_gemv1(w, xq_soa, y, type, out_dtype, N, K, status, stream, nullptr, (int)M);
+    if (rc <= 0) return rc;  // done or failed; 1 = shape outside the register-resident kernel's reach
   }
   GemvParams p{};
   p.w = static_cast<const uint8_t*>(w);

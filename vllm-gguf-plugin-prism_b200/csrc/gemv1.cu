@@ -280,18 +280,22 @@ struct G1Params {
 __device__ unsigned g_tp_done[G1_TP_SLOTS];
 
 template <typename out_t>
-__device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v) {
+__device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v, int m = 0) {
   // tensor-parallel launches write this rank's own copy of the full vector first; the last CTA
   // forwards the finished slice to the peers in one coalesced pass (end of the kernel)
-  out_t* y = p.world == 0 ? static_cast<out_t*>(p.y) : static_cast<out_t*>(p.y_peer[p.rank]) + p.y_off;
+  out_t* y = p.world == 0 ? static_cast<out_t*>(p.y) + (int64_t)m * p.n : static_cast<out_t*>(p.y_peer[p.rank]) + p.y_off;
   y[row] = from_float<out_t>(v);
 }
 
-template <int TYPE, typename out_t>
+// MV activation vectors share one pass over the weights (MV = 1 or 2): a lane keeps the
+// activations of MV vectors for UMAX / MV units, so rows are cut into MV times as many K-slices
+// and the register budget stays that of one vector.
+template <int TYPE, typename out_t, int MV>
 __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
   using T = G1<TYPE>;
-  constexpr int TS = BlockTraits<TYPE>::TS, UPB = T::UPB, UMAX = T::UMAX;
+  static_assert(T::UMAX % MV == 0, "units per lane must divide by the vector count");
+  constexpr int TS = BlockTraits<TYPE>::TS, UPB = T::UPB, UMAX = T::UMAX / MV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kpad = (int)round_up(p.k, 512);
 
@@ -325,8 +329,8 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
 #pragma unroll
     for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
   }
-  float* partial = reinterpret_cast<float*>(cur);  // [G1_BATCH][rl][G1_R][ks]
-  cur += (size_t)G1_BATCH * 8 * G1_R * sizeof(float);
+  float* partial = reinterpret_cast<float*>(cur);  // [G1_BATCH][rl][G1_R][MV][ks]
+  cur += (size_t)G1_BATCH * 8 * G1_R * MV * sizeof(float);
   uint8_t* ring = cur + (size_t)warp * p.stages * p.stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cur + (size_t)G1_WARPS * p.stages * p.stage_bytes) + warp * p.stages;
   if (lane == 0)
@@ -405,24 +409,25 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   // The weight copies above touch nothing another kernel writes; everything below does.
   pdl_wait();
   // this lane's units (block offset inside the slice, sub-unit) and their activations
-  uint32_t xq[UMAX][T::XW];
-  float xd[UMAX][T::XD];
+  uint32_t xq[MV][UMAX][T::XW];
+  float xd[MV][UMAX][T::XD];
   int uoff[UMAX], usub[UMAX];
-  {
-    const uint8_t* qs = p.xq;
-    const float2* ds = reinterpret_cast<const float2*>(p.xq + kpad);
+#pragma unroll
+  for (int m = 0; m < MV; ++m) {   // SoA scratch: int8 codes [MV][kpad], then float2 {d, sum} [MV][kpad / 32]
+    const uint8_t* qs = p.xq + (size_t)m * kpad;
+    const float2* ds = reinterpret_cast<const float2*>(p.xq + (size_t)MV * kpad) + (size_t)m * (kpad / 32);
 #pragma unroll
     for (int j = 0; j < UMAX; ++j) {
       const int u = lane + 32 * j;
       uoff[j] = (u / UPB) * TS;
       usub[j] = u % UPB;
       if (u < units) {
-        T::load_x(qs, ds, sb0 * UPB + u, 0, xq[j], xd[j]);
+        T::load_x(qs, ds, sb0 * UPB + u, 0, xq[m][j], xd[m][j]);
       } else {
 #pragma unroll
-        for (int i = 0; i < T::XW; ++i) xq[j][i] = 0;
+        for (int i = 0; i < T::XW; ++i) xq[m][j][i] = 0;
 #pragma unroll
-        for (int i = 0; i < T::XD; ++i) xd[j][i] = 0.f;
+        for (int i = 0; i < T::XD; ++i) xd[m][j][i] = 0.f;
       }
     }
   }
@@ -459,25 +464,32 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         for (int64_t o = w_safe + lane; o < last_end; o += 32) base[o - abeg] = p.w[o];
         __syncwarp();
       }
-      float acc[G1_R];
+      float acc[MV][G1_R];
 #pragma unroll
       for (int rr = 0; rr < G1_R; ++rr) {
-        acc[rr] = 0.f;
+#pragma unroll
+        for (int m = 0; m < MV; ++m) acc[m][rr] = 0.f;
         if (rr < cnt) {
           const uint8_t* data = contiguous ? stage + (beg0 & 15) + (size_t)rr * row_bytes
                                            : stage + (size_t)rr * p.slot_bytes + ((beg0 + rr * row_bytes) & 15);
 #pragma unroll
           for (int j = 0; j < UMAX; ++j)
-            if (lane + 32 * j < units) acc[rr] += T::unit(data + uoff[j], usub[j], xq[j], xd[j], tb);
+            if (lane + 32 * j < units) {
+#pragma unroll
+              for (int m = 0; m < MV; ++m) acc[m][rr] += T::unit(data + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+            }
         }
       }
 #pragma unroll
       for (int rr = 0; rr < G1_R; ++rr) {
         if (rr < cnt) {
-          const float v = warp_sum(acc[rr]);
-          if (lane == 0) {
-            if (p.ks == 1) store_result<out_t>(p, c_row + rr, v);
-            else partial[(((i % G1_BATCH) * p.rl + rl_i) * G1_R + rr) * p.ks + ks_i] = v;
+#pragma unroll
+          for (int m = 0; m < MV; ++m) {
+            const float v = warp_sum(acc[m][rr]);
+            if (lane == 0) {
+              if (p.ks == 1) store_result<out_t>(p, c_row + rr, v, m);
+              else partial[((((i % G1_BATCH) * p.rl + rl_i) * G1_R + rr) * MV + m) * p.ks + ks_i] = v;
+            }
           }
         }
       }
@@ -489,15 +501,16 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       // add the slice partials in slice order and store; every warp of the CTA takes part
       __syncthreads();
       const int i0 = i - (i % G1_BATCH);
-      const int cnt = (i - i0 + 1) * p.rl * G1_R;
+      const int cnt = (i - i0 + 1) * p.rl * G1_R * MV;
       for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
-        const int rr = t % G1_R, g2 = t / G1_R;
+        const int m = t % MV, t2 = t / MV;
+        const int rr = t2 % G1_R, g2 = t2 / G1_R;
         const int ii = i0 + g2 / p.rl, gl = g2 % p.rl;
         const int64_t r = (first + (int64_t)ii * groups_per_iter + gl) * R + rr;
         if (rr < R && r < p.n) {
           float s = 0.f;
-          for (int q = 0; q < p.ks; ++q) s += partial[(((ii % G1_BATCH) * p.rl + gl) * G1_R + rr) * p.ks + q];
-          store_result<out_t>(p, r, s);
+          for (int q = 0; q < p.ks; ++q) s += partial[((((ii % G1_BATCH) * p.rl + gl) * G1_R + rr) * MV + m) * p.ks + q];
+          store_result<out_t>(p, r, s, m);
         }
       }
       __syncthreads();
@@ -576,7 +589,7 @@ static int g1_env(const char* name, int dflt) {
   return v && *v ? atoi(v) : dflt;
 }
 
-template <int TYPE, typename out_t>
+template <int TYPE, typename out_t, int MV>
 static int launch_g1(G1Params p, cudaStream_t stream) {
   using T = G1<TYPE>;
   constexpr int TS = BlockTraits<TYPE>::TS;
@@ -584,7 +597,7 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
   static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
   static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 6000);
-  const int cap_blocks = 32 * T::UMAX / T::UPB;  // blocks whose units fit one lane-register set
+  const int cap_blocks = 32 * (T::UMAX / MV) / T::UPB;  // blocks whose units fit one lane-register set
   int ks = 1;
   while (ks < 8 && (p.bpr + ks - 1) / ks > cap_blocks) ks *= 2;
   if ((p.bpr + ks - 1) / ks > cap_blocks) return 1;  // row too long for this kernel: caller falls back
@@ -599,9 +612,9 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   p.stages = stages_env < 2 ? 2 : stages_env;
   p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
   const size_t tables = TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0;
-  const size_t smem = tables + (size_t)G1_BATCH * 8 * G1_R * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
+  const size_t smem = tables + (size_t)G1_BATCH * 8 * G1_R * MV * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
   if (smem > 227 * 1024) return 1;
-  auto kern = gemv1_kernel<TYPE, out_t>;
+  auto kern = gemv1_kernel<TYPE, out_t, MV>;
   static size_t configured[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -621,19 +634,28 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
 }
 
 template <int TYPE>
-static int launch_g1_out(const G1Params& p, int out_dtype, cudaStream_t s) {
+static int launch_g1_out(const G1Params& p, int out_dtype, int mv, cudaStream_t s) {
+  if (mv == 2) {
+    switch (out_dtype) {
+      case DT_F32: return launch_g1<TYPE, float, 2>(p, s);
+      case DT_F16: return launch_g1<TYPE, __half, 2>(p, s);
+      case DT_BF16: return launch_g1<TYPE, __nv_bfloat16, 2>(p, s);
+    }
+    return E_BAD_DTYPE;
+  }
   switch (out_dtype) {
-    case DT_F32: return launch_g1<TYPE, float>(p, s);
-    case DT_F16: return launch_g1<TYPE, __half>(p, s);
-    case DT_BF16: return launch_g1<TYPE, __nv_bfloat16>(p, s);
+    case DT_F32: return launch_g1<TYPE, float, 1>(p, s);
+    case DT_F16: return launch_g1<TYPE, __half, 1>(p, s);
+    case DT_BF16: return launch_g1<TYPE, __nv_bfloat16, 1>(p, s);
   }
   return E_BAD_DTYPE;
 }
 
 // Returns E_OK, a negative error, or 1 when the shape is outside this kernel's reach.
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp) {
+                 cudaStream_t stream, const GemvTp* tp, int vectors) {
   G1Params p{};
+  if (vectors != 1 && (vectors != 2 || tp)) return 1;
   if (tp) {
     if (tp->world < 1 || tp->world > G1_MAX_WORLD || tp->slot < 0) return E_BAD_SHAPE;
     p.world = tp->world;
@@ -655,12 +677,12 @@ int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_d
   p.k = K;
   p.status = status;
   switch (type) {
-    case T_Q4_0: return launch_g1_out<T_Q4_0>(p, out_dtype, stream);
-    case T_Q8_0: return launch_g1_out<T_Q8_0>(p, out_dtype, stream);
-    case T_Q4_K: return launch_g1_out<T_Q4_K>(p, out_dtype, stream);
-    case T_Q6_K: return launch_g1_out<T_Q6_K>(p, out_dtype, stream);
-    case T_IQ2_XXS: return launch_g1_out<T_IQ2_XXS>(p, out_dtype, stream);
-    case T_IQ4_XS: return launch_g1_out<T_IQ4_XS>(p, out_dtype, stream);
+    case T_Q4_0: return launch_g1_out<T_Q4_0>(p, out_dtype, vectors, stream);
+    case T_Q8_0: return launch_g1_out<T_Q8_0>(p, out_dtype, vectors, stream);
+    case T_Q4_K: return launch_g1_out<T_Q4_K>(p, out_dtype, vectors, stream);
+    case T_Q6_K: return launch_g1_out<T_Q6_K>(p, out_dtype, vectors, stream);
+    case T_IQ2_XXS: return launch_g1_out<T_IQ2_XXS>(p, out_dtype, vectors, stream);
+    case T_IQ4_XS: return launch_g1_out<T_IQ4_XS>(p, out_dtype, vectors, stream);
   }
   return E_BAD_TYPE;
 }

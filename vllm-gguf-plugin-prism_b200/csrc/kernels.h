@@ -39,8 +39,8 @@ int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t
 // Y[m, n] for m in [0, M); rows of W are N x (K/QK*TS) bytes, contiguous, 16-byte aligned base.
 int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t M, int64_t N, int64_t K,
                 int* status, cudaStream_t stream);
-// Single-vector specialisation (gemv1.cu): activations in registers.  Returns 1 when the shape
-// is outside its reach (the caller then uses the general kernel).
+// One- and two-vector specialisation (gemv1.cu): activations in registers.  Returns 1 when the
+// shape is outside its reach (the caller then uses the general kernel).
 // Tensor-parallel output of the single-vector kernel: results go to y_peer[r] + y_off for every
 // rank r (peer-mapped pointers), then flag_peer[r][slot] is incremented once per launch.
 struct GemvTp {
@@ -51,7 +51,7 @@ struct GemvTp {
   unsigned* flag_peer[8];
 };
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp = nullptr);
+                 cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1);
 // waits until flag[slot] has reached world * epoch[slot]; sets *status on a time-out
 int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status, cudaStream_t stream);
 // per-(token,expert) GEMV of the small-batch MoE entry point
