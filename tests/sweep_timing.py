@@ -153,6 +153,17 @@ def sweep_moe(ref):
         r2 = graph_time([lambda: ref.ggml_moe_a8(x2, w2, s4, e4, n4, t, hid, 1, tokens * top_k)] * 2, reps=3)
         r.update(us_reference_gate_up=r1 * 1e6, us_reference_down=r2 * 1e6)
     print(json.dumps(r), flush=True)
+    # decode: a few tokens, every (token, expert) pair is one GEMV (ggml_moe_a8_vec)
+    for tk in (1, 4, 16):
+        xs = x1[:tk].contiguous()
+        tid = torch.from_numpy(np.ascontiguousarray(ids[:tk])).to(DEV).to(torch.int32)
+        tv = graph_time([lambda: capi.moe_a8_vec(xs, w13, tid, top_k, t, 2 * inter, tk)] * 4)
+        rv = dict(op="moe_a8_vec Q4_0 gate/up", tokens=tk, us=tv * 1e6,
+                  weight_GBs=tk * top_k * 2 * inter * (hid // 32 * 18) / tv / 1e9, status=capi.last_status())
+        if ref is not None:
+            rr = graph_time([lambda: ref.ggml_moe_a8_vec(xs, w13, tid, top_k, t, 2 * inter, tk)] * 2, reps=3)
+            rv.update(us_reference=rr * 1e6)
+        print(json.dumps(rv), flush=True)
 
 
 def main():

@@ -654,6 +654,12 @@ int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* t
                     int64_t tokens, int64_t top_k, int64_t N, int64_t K, int64_t n_experts, int* status,
                     cudaStream_t stream) {
   if (tokens == 0 || N == 0 || top_k == 0) return E_OK;
+  static const int use_g1 = gemv_tune_int("GGUF_B200_GEMV1", 1);
+  if (use_g1) {   // every (token, expert) pair as a register-resident single-vector GEMV
+    GemvMoe moe{topk_ids, tokens, top_k, n_experts, tokens * top_k};
+    const int rc = launch_gemv1(w, xq_soa, y, type, out_dtype, N, K, status, stream, nullptr, 1, &moe);
+    if (rc <= 0) return rc;
+  }
   GemvParams p{};
   p.w = static_cast<const uint8_t*>(w);
   p.w_bytes = n_experts * N * (K / block_size(type)) * type_size(type);

@@ -267,6 +267,12 @@ struct G1Params {
   int slot_bytes;        // distance between the rows of an item inside a stage
   int stages, stage_bytes;
   int* status;
+  // MoE decode (topk_ids != null, one vector): blockIdx.y is an output row s of y; it uses the
+  // weights of expert topk_ids[s] (experts back to back, expert_bytes apart) and the activation
+  // vector s / top_k of the xq_vecs quantized ones
+  const int32_t* topk_ids;
+  int top_k, n_experts, xq_vecs, moe_slots;
+  int64_t expert_bytes;
   // tensor-parallel output (world > 0): every result goes to y_peer[r][y_off + row] for all r,
   // then flag_peer[r][slot] is raised once per launch (see the end of the kernel)
   int world, slot, rank;
@@ -281,6 +287,7 @@ __device__ unsigned g_tp_done[G1_TP_SLOTS];
 
 template <typename out_t>
 __device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v, int m = 0) {
+  if (p.topk_ids) m = (int)blockIdx.y;   // MoE decode: one output row of y per (token, expert) pair
   // tensor-parallel launches write this rank's own copy of the full vector first; the last CTA
   // forwards the finished slice to the peers in one coalesced pass (end of the kernel)
   out_t* y = p.world == 0 ? static_cast<out_t*>(p.y) + (int64_t)m * p.n : static_cast<out_t*>(p.y_peer[p.rank]) + p.y_off;
@@ -298,6 +305,14 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   constexpr int TS = BlockTraits<TYPE>::TS, UPB = T::UPB, UMAX = T::UMAX / MV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kpad = (int)round_up(p.k, 512);
+  const uint8_t* wb = p.w;      // this CTA's weight matrix
+  int vec0 = 0;                 // its first activation vector
+  if (p.topk_ids) {
+    const int e = p.topk_ids[blockIdx.y];
+    if (e < 0 || e >= p.n_experts) return;   // not a valid expert: the row is left as it is
+    wb += (int64_t)e * p.expert_bytes;
+    vec0 = (int)blockIdx.y / p.top_k;
+  }
 
   uint8_t* cur = smem;
   Tab1 tb;
@@ -371,7 +386,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         const uint32_t bytes = aend > abeg ? (uint32_t)(aend - abeg) : 0u;
         if (bytes) {
           mbar_expect_tx(&bars[st], bytes);
-          bulk_g2s(dst, p.w + abeg, bytes, &bars[st]);
+          bulk_g2s(dst, wb + abeg, bytes, &bars[st]);
         } else {
           mbar_arrive(&bars[st]);
         }
@@ -391,7 +406,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         else mbar_arrive(&bars[st]);
       }
       __syncwarp();
-      if (bytes) bulk_g2s(dst + (size_t)lane * p.slot_bytes, p.w + abeg, bytes, &bars[st]);
+      if (bytes) bulk_g2s(dst + (size_t)lane * p.slot_bytes, wb + abeg, bytes, &bars[st]);
     }
   };
 
@@ -414,8 +429,8 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   int uoff[UMAX], usub[UMAX];
 #pragma unroll
   for (int m = 0; m < MV; ++m) {   // SoA scratch: int8 codes [MV][kpad], then float2 {d, sum} [MV][kpad / 32]
-    const uint8_t* qs = p.xq + (size_t)m * kpad;
-    const float2* ds = reinterpret_cast<const float2*>(p.xq + (size_t)MV * kpad) + (size_t)m * (kpad / 32);
+    const uint8_t* qs = p.xq + (size_t)(vec0 + m) * kpad;
+    const float2* ds = reinterpret_cast<const float2*>(p.xq + (size_t)p.xq_vecs * kpad) + (size_t)(vec0 + m) * (kpad / 32);
 #pragma unroll
     for (int j = 0; j < UMAX; ++j) {
       const int u = lane + 32 * j;
@@ -461,7 +476,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         const int64_t lbeg = contiguous ? beg0 : last_end - slice_bytes;
         const int64_t abeg = lbeg & ~int64_t(15);
         uint8_t* base = contiguous ? stage : stage + (size_t)(cnt - 1) * p.slot_bytes;
-        for (int64_t o = w_safe + lane; o < last_end; o += 32) base[o - abeg] = p.w[o];
+        for (int64_t o = w_safe + lane; o < last_end; o += 32) base[o - abeg] = wb[o];
         __syncwarp();
       }
       float acc[MV][G1_R];
@@ -630,7 +645,13 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   const int64_t need = (groups + p.rl - 1) / p.rl;
   if (grid > need) grid = need;
   if (grid < 1) grid = 1;
-  return launch_pdl(kern, dim3((unsigned)grid), dim3(G1_WARPS * 32), smem, stream, p) == cudaSuccess ? E_OK : E_CUDA;
+  unsigned gy = 1;
+  if (p.topk_ids) {   // MoE decode: the CTAs are shared out over the (token, expert) pairs
+    gy = (unsigned)p.moe_slots;
+    const int64_t per_pair = (148 * per_sm + gy - 1) / gy;
+    if (grid > per_pair) grid = per_pair;
+  }
+  return launch_pdl(kern, dim3((unsigned)grid, gy), dim3(G1_WARPS * 32), smem, stream, p) == cudaSuccess ? E_OK : E_CUDA;
 }
 
 template <int TYPE>
@@ -653,9 +674,21 @@ static int launch_g1_out(const G1Params& p, int out_dtype, int mv, cudaStream_t 
 
 // Returns E_OK, a negative error, or 1 when the shape is outside this kernel's reach.
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp, int vectors) {
+                 cudaStream_t stream, const GemvTp* tp, int vectors, const GemvMoe* moe) {
   G1Params p{};
-  if (vectors != 1 && (vectors != 2 || tp)) return 1;
+  if (vectors != 1 && (vectors != 2 || tp || moe)) return 1;
+  p.xq_vecs = vectors;
+  if (moe) {
+    if (tp) return 1;
+    const int64_t eb = N * (K / block_size(type)) * type_size(type);
+    if (eb % 16 != 0 || moe->slots > 65535) return 1;   // experts must start on 16-byte boundaries; grid.y limit
+    p.topk_ids = moe->topk_ids;
+    p.top_k = (int)moe->top_k;
+    p.n_experts = (int)moe->n_experts;
+    p.xq_vecs = (int)moe->tokens;
+    p.moe_slots = (int)moe->slots;
+    p.expert_bytes = eb;
+  }
   if (tp) {
     if (tp->world < 1 || tp->world > G1_MAX_WORLD || tp->slot < 0) return E_BAD_SHAPE;
     p.world = tp->world;

@@ -50,8 +50,14 @@ struct GemvTp {
   void* y_peer[8];
   unsigned* flag_peer[8];
 };
+// MoE decode through the same kernel: y row s = weights of expert topk_ids[s] (N x K each, back
+// to back) times activation vector s / top_k of the `tokens` quantized ones
+struct GemvMoe {
+  const int32_t* topk_ids;
+  int64_t tokens, top_k, n_experts, slots;
+};
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1);
+                 cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1, const GemvMoe* moe = nullptr);
 // waits until flag[slot] has reached world * epoch[slot]; sets *status on a time-out
 int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status, cudaStream_t stream);
 // per-(token,expert) GEMV of the small-batch MoE entry point
