@@ -404,3 +404,67 @@ def test_mmq_split_k_matches_unsplit():
     y64, _ = cpu.matmul_a8(wn, t, x.cpu().numpy(), "float16", mmq=True)
     assert rel_l2(y_split.float().cpu().numpy(), y64) <= REL_L2_TOL
     assert rel_l2(y_one.float().cpu().numpy(), y64) <= REL_L2_TOL
+
+
+# ---------------------------------------------------------------- full benchmark sizes -----------
+
+def test_mmq_full_size_deterministic_linear_and_close_to_reference(ref):
+    """Q4_K 14336x4096 at 512 tokens (the prefill benchmark shape): two runs give identical bits;
+    doubling every d and dmin (exact in fp16) doubles the output exactly; the reference's own
+    tiled kernel, when it was built, agrees within the tolerance."""
+    t, N, K, M = 12, 14336, 4096, 512
+    wn = synth.make_weight(t, N, K, seed=3)
+    w = torch.from_numpy(wn).to(DEV)
+    x = dev_x(M, K, seed=3)
+    y1 = capi.mul_mat_a8(w, x, t, N)
+    y2 = capi.mul_mat_a8(w, x, t, N)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert torch.equal(y1, y2)
+    blocks = wn.reshape(-1, 144).copy()
+    d = blocks[:, 0:4].copy().view(np.float16) * np.float16(2)
+    blocks[:, 0:4] = d.view(np.uint8)
+    y3 = capi.mul_mat_a8(torch.from_numpy(blocks.reshape(N, -1)).to(DEV), x, t, N)
+    assert torch.equal(y3.float(), 2 * y1.float())
+    if ref.available:
+        r = ref.ops.ggml_mul_mat_a8(w, x, t, N)
+        assert rel_l2(y1.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+
+
+def test_mmq_split_k_full_size_close_to_reference(ref):
+    """Q4_K 4096x14336 at 64 tokens: 32 output tiles, so K is split over four CTAs per tile."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    t, N, K, M = 12, 4096, 14336, 64
+    wn, w = dev_w(t, N, K, seed=5)
+    x = dev_x(M, K, seed=5)
+    y = capi.mul_mat_a8(w, x, t, N)
+    r = ref.ops.ggml_mul_mat_a8(w, x, t, N)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+
+
+def test_moe_full_size_close_to_reference(ref):
+    """The MoE benchmark configuration (64 experts, top-8, hidden 2048 -> 2 x 1024, Q4_0, 256 tokens):
+    both expert GEMMs against the reference's kernels, and the decode form for 4 tokens."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    t, E, top_k, hid, inter, T = 2, 64, 8, 2048, 1024, 256
+    w13 = torch.from_numpy(np.stack([synth.make_weight(t, 2 * inter, hid, seed=100 + e) for e in range(E)])).to(DEV)
+    x = torch.from_numpy(synth.make_activation(T, hid, seed=1)).to(DEV)
+    _, ids = synth.make_routing(T, E, top_k, 0)
+    blk = capi.lib().gguf_b200_moe_block_size(t)
+    s, e, n = [torch.from_numpy(a).to(DEV) for a in synth.moe_align_block_size(ids, blk, E)]
+    s4, e4, n4 = [torch.from_numpy(a).to(DEV) for a in synth.moe_align_block_size(ids, 4, E)]
+    y = capi.moe_a8(x, w13, s, e, n, t, 2 * inter, top_k, T)
+    r = ref.ops.ggml_moe_a8(x, w13, s4, e4, n4, t, 2 * inter, top_k, T)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+    tid = torch.from_numpy(np.ascontiguousarray(ids[:4])).to(DEV).to(torch.int32)
+    yv = capi.moe_a8_vec(x[:4].contiguous(), w13, tid, top_k, t, 2 * inter, 4)
+    rv = ref.ops.ggml_moe_a8_vec(x[:4].contiguous(), w13, tid, top_k, t, 2 * inter, 4)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(yv.float().cpu(), rv.float().cpu()) <= REL_L2_TOL
