@@ -3,6 +3,7 @@
     python tests/sweep_timing.py gemv [--ref]     decode GEMV, all block types
     python tests/sweep_timing.py gemm [--ref]     tensor-core GEMM (ggml_mul_mat_a8 / dequantize-matmul route)
     python tests/sweep_timing.py moe  [--ref]     OLMoE-shaped ggml_moe_a8 (gate/up and down GEMMs)
+    python tests/sweep_timing.py dequant [--ref]  standalone ggml_dequantize (all types) and the q8_1 quantizer
 
 One JSON line per case.  Every case rotates over enough seeded weight copies that a launch reads
 its weights cold (> 300 MB per graph); "us" is the mean per call.  With --ref the reference
@@ -166,10 +167,33 @@ def sweep_moe(ref):
         print(json.dumps(rv), flush=True)
 
 
+def sweep_dequant(ref):
+    hbm, _ = peaks()
+    for (t, n, k) in [(Q4_K, 14336, 4096), (Q4_0, 14336, 4096), (Q8_0, 14336, 4096), (Q6_K, 37888, 3584),
+                      (IQ4_XS, 37888, 3584), (IQ2_XXS, 28672, 8192)]:
+        wb, ws = copies(t, n, k, 200e6)
+        ws = ws[:4]
+        td = graph_time([lambda w=w: capi.dequantize(w, t, n, k, torch.float16) for w in ws])
+        moved = wb + n * k * 2      # packed weights in, fp16 values out
+        r = dict(op="dequantize->f16", type=synth.NAMES[t], N=n, K=k, us=td * 1e6, GBs=moved / td / 1e9,
+                 frac_of_measured_hbm=moved / td / 1e9 / hbm)
+        if ref is not None:
+            tr = graph_time([lambda w=w: ref.ggml_dequantize(w, t, n, k, torch.float16) for w in ws], reps=5)
+            r.update(us_reference=tr * 1e6, speedup=tr / td)
+        print(json.dumps(r), flush=True)
+        del ws
+        torch.cuda.empty_cache()
+    for (m, k) in [(1, 4096), (512, 4096), (2048, 4096)]:
+        x = torch.from_numpy(synth.make_activation(m, k, seed=0)).to(DEV)
+        tq = graph_time([lambda: capi.quantize_q8_1(x)] * 8)
+        moved = m * k * 2 + m * k // 32 * 36
+        print(json.dumps(dict(op="quantize_q8_1 (36-byte blocks)", M=m, K=k, us=tq * 1e6, GBs=moved / tq / 1e9)), flush=True)
+
+
 def main():
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     ref = load_ref() if "--ref" in sys.argv else None
-    {"gemv": sweep_gemv, "gemm": sweep_gemm, "moe": sweep_moe}[what](ref)
+    {"gemv": sweep_gemv, "gemm": sweep_gemm, "moe": sweep_moe, "dequant": sweep_dequant}[what](ref)
 
 
 if __name__ == "__main__":

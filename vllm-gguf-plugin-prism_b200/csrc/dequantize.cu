@@ -193,7 +193,7 @@ template <int TYPE, typename out_t>
 static int launch_t(const void* w, void* out, int64_t n, int q4k_contract, cudaStream_t s) {
   const int64_t chunks = (n + 255) / 256;
   int64_t ctas = (chunks + 7) / 8;
-  const int64_t cap = 148 * 8;  // 8 resident CTAs of 256 threads per SM
+  const int64_t cap = 148 * 32;  // four rounds of the 8 resident CTAs per SM measured best (148*8: -5 %, one CTA per 8 chunks: -25 %)
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
   if (TYPE == T_Q4_K && q4k_contract)
