@@ -16,15 +16,21 @@
 // "sum" terms the reference's tiled kernels use (Q4_0: -8*d*s8, Q4_K: -dmin*m*s8, with s8 the
 // fp16 sum of the *unquantized* activations) ride along as K/32 extra contraction columns.
 //
-// Tile: 128 weight rows (UMMA M) x TN tokens (UMMA N, 16..256) x 64 values per stage, both
+// Tile: 128 weight rows (UMMA M) x TN tokens (UMMA N, 32..256) x 64 values per stage, both
 // operands K-major in shared memory with the 128-byte swizzle.  Weight rows sit on the M axis
-// so that small token counts (M = 8, MoE blocks) do not waste the 128-row instruction.
-// Warp roles:  warps 0-7 decode weights into the A stage (two threads per row, 32 values each,
-// raw bytes prefetched two stages ahead in registers) and later run the epilogue (tcgen05.ld,
-// one TMEM lane = one weight row; the two threads of a row split the token columns); warp 8
-// issues the TMA loads of the B tile (tiled 2-D tensor map, one CTA per box) and owns the TMEM
-// allocation; warp 9 lane 0 issues tcgen05.mma and commits stage releases.  A 4-deep mbarrier ring
-// decouples them.  Every wait is bounded and reports through the status word.
+// so that small token counts (MoE blocks) do not waste the 128-row instruction.
+// Warp roles (P = 4 * groups producer warps, groups = 2 or 4):
+//   warps 0..P-1  producers: group g = 128 threads, one per weight row, decodes all 64 values of
+//                 its row for the stages i = g, g + groups, ... from the raw-byte ring into the A
+//                 slot; afterwards the epilogue (tcgen05.ld, one TMEM lane = one weight row, the
+//                 threads of a row split the token columns; tile staged in shared memory and
+//                 written by one TMA store, or stored directly for MoE)
+//   warp P        B loader: one TMA box of activations per stage; owns the TMEM allocation
+//   warp P+1      MMA issuer: warp-uniform loop, an elected lane issues 4 tcgen05.mma + 1 commit per stage
+//   warp P+2      raw-weight loader: one 2-D TMA box (256-value chunk x 128 rows) per chunk
+// One full/empty mbarrier pair per A slot serves both operands.  K may be split over grid.z
+// (fp32 partial tiles, added by add_partials_kernel).  Every wait is bounded in time and
+// reports through the status word.
 #include <cuda.h>
 
 #include <type_traits>
