@@ -1,4 +1,6 @@
-// Single-vector decode GEMV (M = 1), the latency-critical case: Y[n] = sum_k dequant(W)[n,k] * q8_1(x)[k].
+// Decode GEMV for one or two activation vectors, the latency-critical case:
+// Y[m][n] = sum_k dequant(W)[n,k] * q8_1(x_m)[k].  Also serves MoE decode (one grid row per
+// (token, expert) pair) and the tensor-parallel form that forwards its slice to peer GPUs.
 // Same arithmetic as gemv.cu (reference: mul_mat_vec_q, mmvq.cuh:2-41 and vec_dot_*_q8_1 of
 // vecdotq.cuh), specialised so that the inner loop spends its instructions on the weights only:
 //

@@ -1,11 +1,11 @@
 // Weight decoders of the tensor-core GEMM (mmq.cu): one 32-value group of one weight row
 // ("unit" u = values 32u..32u+31) -> 16 packed 16-bit pairs = 64 bytes of the row in the A tile.
-// Two threads share a row of a 64-value stage, so 256 threads decode a 128 x 64 stage.
+// A producer thread owns one row of a 64-value stage and calls a decoder for its two units
+// (the whole-stage decoders at the end of this file replace that for Q4_K / Q4_0 / Q8_0).
 //
-// Each decoder is split in two so that the producer threads can keep global loads in flight:
-//   load()   issues the loads of a unit's raw bytes into registers (no use of the data),
+// Each decoder is split in two:
+//   load()   fetches a unit's raw bytes (from the shared-memory raw ring) into registers,
 //   decode() turns those registers into fp16/bf16 values.
-// The kernel calls load() for the unit two stages ahead before decode() of the current one.
 //
 // Values are bit-identical to the reference's standalone dequantize for the types that are fed
 // to the MMA as dequantized weights (Q4_0, Q8_0, Q6_K: dequantize.cuh:3-15, 69-78, 232-256;
