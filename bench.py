@@ -370,6 +370,43 @@ def main():
             "frac_of_measured_16bit_peak": flops / t_mm / 1e12 / tf_peak, "frac_of_2x_that_as_int8_proxy": flops / t_mm / 1e12 / (2 * tf_peak),
             "includes": "q8_1 quantization of the 512x4096 activations + tcgen05 GEMM"}}
 
+        # ---- secondary figure: the linear layers of one Llama-3-8B decode step, batch 1 -----------
+        # 32 layers x (qkv 6144x4096, o 4096x4096, gate+up 28672x4096, down 4096x14336), Q4_K;
+        # four seeded layer copies (488 MB > L2) are walked round-robin inside one CUDA graph.
+        layer_shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+        n_layers, n_copies = 32, 4
+        with torch.cuda.stream(stream):
+            lw = [[torch.from_numpy(synth.make_weight(Q4_K, n, k, seed=7000 + 10 * c + j)).to(dev)
+                   for j, (n, k) in enumerate(layer_shapes)] for c in range(n_copies)]
+            lx = {k: torch.randn(1, k, device=dev, dtype=torch.float16) for k in (4096, 14336)}
+
+            def decode_step():
+                for layer in range(n_layers):
+                    for j, (n, k) in enumerate(layer_shapes):
+                        ops.ggml_mul_mat_vec_a8(lw[layer % n_copies][j], lx[k], Q4_K, n)
+
+            decode_step()
+            stream.synchronize()
+            dg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(dg, stream=stream):
+                decode_step()
+            for _ in range(3):
+                dg.replay()
+            stream.synchronize()
+            e0.record(stream)
+            reps = 20
+            for _ in range(reps):
+                dg.replay()
+            e1.record(stream)
+            stream.synchronize()
+            t_tok = e0.elapsed_time(e1) / 1e3 / reps
+        layer_bytes = sum(n * (k // 256) * 144 for n, k in layer_shapes)
+        extras["decode_linear_layers_llama3_8b_q4k_batch1"] = {
+            "ms_per_token": t_tok * 1e3, "tokens_per_s": 1.0 / t_tok, "weight_GBs": n_layers * layer_bytes / t_tok / 1e9,
+            "covers": "the 128 quantized GEMVs (with their activation quantizers) of one decode step; attention, norms, "
+                      "embedding and lm_head are outside this path"}
+        del lw
+
     status = capi.last_status()
 
     def shutdown():
