@@ -99,11 +99,15 @@ int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* worksp
  *   X [tokens][K]; W [E][N][K/QK*type_size] with expert_stride_bytes between experts;
  *   sorted_token_ids[n_sorted], expert_ids[ceil(n_sorted/block)], num_tokens_post_padded[1] on device,
  *   as produced by moe_align_block_size with block = gguf_b200_moe_block_size(type);
- *   Y [tokens*top_k][N]: row t = sorted id; rows that receive no token are set to zero. */
+ *   Y [tokens*top_k][N]: row t = sorted id; rows that receive no token are set to zero.
+ *   n_experts (1..256) = experts stored in W: a block whose expert id is outside [0, n_experts) is
+ *   skipped, so no id can make the kernel read past W (the reference only guards [0, 255],
+ *   moe.cuh:33). */
 int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* workspace, int64_t workspace_bytes,
                      const int32_t* sorted_token_ids, const int32_t* expert_ids,
                      const int32_t* num_tokens_post_padded, int64_t n_sorted, int64_t expert_stride_bytes,
-                     int type, int dtype, int64_t tokens, int64_t top_k, int64_t N, int64_t K, void* stream);
+                     int64_t n_experts, int type, int dtype, int64_t tokens, int64_t top_k, int64_t N, int64_t K,
+                     void* stream);
 
 /* Small-batch MoE: one GEMV per (token, expert) pair.
  * Replaces: ggml_moe_a8_vec, gguf_kernel.cu:395-530 (+ moe_vec.cuh:3-53).
@@ -130,33 +134,60 @@ int gguf_b200_mul_mat_vec_a8_noalloc(const void* W, const void* X, void* Y, int 
                                      int64_t M, int64_t N, int64_t K, void* stream);
 int64_t gguf_b200_noalloc_scratch_bytes(void);
 
-/* Tensor-parallel decode GEMV (one activation vector) with the all-gather fused into the kernel.
- * (No counterpart in the reference: there each rank computes its row shard -- the weight loader
- * shards dim 0, quantization/params.py:229-231 -- and the serving engine's column-parallel linear
- * layer all-gathers the outputs with a separate collective.)
- * Rank `rank` of `world` (<= 8) holds rows [rank*N_local, (rank+1)*N_local) of the weight.  The
- * kernel writes its N_local results to y_peers[r] + rank*N_local for EVERY r: y_peers is a host
- * array of `world` device pointers to each rank's full output vector (world*N_local elements of
- * `dtype`), peer-mapped into this process (symmetric memory or CUDA IPC mappings).  When the last
- * CTA is done it increments epochs_local[slot] (this rank's own launch counter) and then
- * flag_peers[r][slot] on every rank.  flag_peers[r] / epochs_local are arrays of uint32 counters,
- * zero before first use, that only ever grow (captured graphs can be replayed without a reset).
- * wait_slot >= 0: X was computed from the vector gathered in that slot, so the activation
- * quantizer first waits (bounded, about a second, then GGUF_B200_E_TIMEOUT in the status word)
- * until flag_peers[rank][wait_slot] >= world * epochs_local[wait_slot]; -1: no wait.
- * A slot's vector may be rewritten only after every rank has consumed it.  Calls that can
- * overlap on one GPU must use different slots (slot % 64 selects internal state).  Every rank
- * issues the same sequence of calls.  X, ws as in gguf_b200_mul_mat_vec_a8.
+/* ---- column-sharded tensor parallelism (1..8 GPUs of one NVLink domain) -------------------------
+ * No counterpart in the reference: there each rank computes its row shard (the weight loader
+ * narrows dim 0, quantization/params.py:227-236) and the serving engine's column-parallel linear
+ * layer all-gathers the outputs with a separate NCCL collective.  Here the all-gather is part of
+ * the kernels: every rank writes its share of the result straight into ALL ranks' output buffers
+ * over NVLink (peer-mapped pointers: symmetric memory or CUDA IPC mappings; plain st.global, no
+ * multimem, no TMA).  Rank `rank` of `world` (<= 8) holds rows [rank*N_local, (rank+1)*N_local)
+ * of the weight; every rank issues the same sequence of calls.  Calls that can overlap on one GPU
+ * must use different slots.  A slot may be reused only after every rank has consumed its previous
+ * contents.  Waits on other GPUs are bounded (gguf_b200_set_wait_limit_cycles) and report
+ * GGUF_B200_E_TIMEOUT through the status word.
+ *
+ * Decode, one activation vector.  The gathered vector of call slot `slot` lives on every rank as
+ * PACKETS: element i is one naturally aligned word {value, tag} -- 4 bytes {16-bit value, 16-bit
+ * tag} for f16/bf16, 8 bytes {f32 value, 32-bit tag} for f32 -- at packet index
+ * slot*slot_packets + i of the rank's packet arena (packet_peers[r] = base of rank r's arena,
+ * 16-byte aligned, zero before first use; slot_packets >= world*N_local).  tag = number of the
+ * launch that wrote it = epochs_local[slot] (uint32 per slot, zero before first use, incremented
+ * once per call by this entry point on the device, so captured graphs replay without a reset).
+ * A reader that finds the expected tag has the value: no fence, no flag, one NVLink crossing.
+ * Activations: x'[k] = X[k] + add_scale * gathered[add_slot][k] rounded to `dtype` (add_slot < 0:
+ * x' = X; X may be null when add_slot >= 0) -- the quantizer of this call polls the packets of
+ * add_slot itself, so a chain of dependent decode GEMVs needs no collective or wait kernel at all.
  * Returns GGUF_B200_E_TOO_LARGE when the rows are too long for the single-vector kernel. */
-int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* y_peers, uint32_t* const* flag_peers,
-                                uint32_t* epochs_local, int slot, int wait_slot, void* ws, int64_t ws_bytes, int type,
-                                int dtype, int64_t N_local, int64_t K, int rank, int world, void* stream);
-/* Completes the gather of `slot` on this rank for consumers that are not one of the calls above:
- * a one-thread kernel that waits, for at most about a second, until
- * flags_local[slot] >= world * epochs_local[slot]; a time-out sets the status word
- * (gguf_b200_last_status) to GGUF_B200_E_TIMEOUT.  Work queued on `stream` behind it may read the
- * full output vector. */
+int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* packet_peers, uint32_t* epochs_local,
+                                int slot, int add_slot, float add_scale, int64_t slot_packets, void* ws,
+                                int64_t ws_bytes, int type, int dtype, int64_t N_local, int64_t K, int rank, int world,
+                                void* stream);
+/* Packets -> plain vectors, for consumers that are not one of the calls above: out[s][0..n) =
+ * values of slot slot0+s (s < nslots, out rows out_stride elements apart), each packet polled
+ * until its tag equals epochs_local[slot0+s]. */
+int gguf_b200_tp_unpack(const void* packets_local, const uint32_t* epochs_local, int slot0, int nslots,
+                        int64_t slot_packets, int64_t n, void* out, int64_t out_stride, int dtype, void* stream);
+
+/* Prefill, M activation rows: op = GGUF_B200_OP_MMQ (q8_1-quantized activations, types 2/8/12/14)
+ * or GGUF_B200_OP_DEQUANT_MATMUL (IQ types, f16/bf16).  y_peers[r] = rank r's gathered output
+ * [M][world*N_local] in `dtype` (16-byte aligned; N_local a multiple of 8): the tensor-core kernel's
+ * tile epilogue (or, when K is split over CTAs, the kernel that adds the partial tiles) stores this
+ * rank's column block [rank*N_local, ...) into every rank's matrix with 16-byte stores.  The last
+ * CTA then increments epochs_local[slot] and flag_peers[r][slot] on every rank (uint32 counters,
+ * zero before first use, only ever growing).  Workspace: gguf_b200_workspace_bytes(op, type, M,
+ * N_local, K). */
+int gguf_b200_matmul_tp(int op, const void* W, const void* X, void* const* y_peers, uint32_t* const* flag_peers,
+                        uint32_t* epochs_local, int slot, void* ws, int64_t ws_bytes, int type, int dtype, int64_t M,
+                        int64_t N_local, int64_t K, int rank, int world, void* stream);
+/* Completes the gather of a gguf_b200_matmul_tp call on this rank: a one-thread kernel that waits
+ * until flags_local[slot] >= world * epochs_local[slot]; work queued on `stream` behind it may
+ * read the full output matrix. */
 int gguf_b200_tp_wait(const uint32_t* flags_local, const uint32_t* epochs_local, int slot, int world, void* stream);
+
+/* Limit of every wait on another GPU (packet polls, flag waits), in SM clock cycles; <= 0 restores
+ * the default of 2e9 (about a second).  When a wait runs out the kernel stores
+ * GGUF_B200_E_TIMEOUT in the status word and returns; the result of that call is invalid. */
+void gguf_b200_set_wait_limit_cycles(int64_t cycles);
 
 /* Token-block size the caller must pass to moe_align_block_size.
  * Replaces: ggml_moe_get_block_size, gguf_kernel.cu:532-566 (4 for every type there). */

@@ -62,6 +62,7 @@ def test_geometry_and_error_codes(native_libs):
     assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 12, 64, 4096, 14336) == act(64, 14336) + 4 * 64 * 4096 * 4
     assert lib.gguf_b200_workspace_bytes(capi.OP_DEQUANT_MATMUL, 16, 128, 28672, 8192) == 0
     assert lib.gguf_b200_workspace_bytes(capi.OP_DEQUANT_MATMUL, 16, 128, 8192, 28672) == 2 * 128 * 8192 * 4
+    assert lib.gguf_b200_workspace_bytes(capi.OP_DEQUANT_MATMUL, 16, 128, 1024, 28672) == 16 * 128 * 1024 * 4   # 8 tiles: 16 K slices
 
 
 def test_tensor_parallel_entry_points_validate_arguments(native_libs):
@@ -72,16 +73,33 @@ def test_tensor_parallel_entry_points_validate_arguments(native_libs):
     p = ctypes.c_void_p(4096)
     two = (ctypes.c_void_p * 2)(4096, 8192)
     ptrs = ctypes.cast(two, ctypes.c_void_p)
-    args = lambda **kw: [kw.get("W", p), p, kw.get("y", ptrs), kw.get("f", ptrs), kw.get("e", p), kw.get("slot", 0), -1, p, 1 << 20,
-                         kw.get("type", 12), 1, 64, 256, kw.get("rank", 0), kw.get("world", 2), null]
+    # decode: W, X, packet arenas, epochs, slot, add_slot, add_scale, slot_packets, ws, ws_bytes, type, dtype, N_local, K, rank, world, stream
+    args = lambda **kw: [kw.get("W", p), kw.get("X", p), kw.get("y", ptrs), kw.get("e", p), kw.get("slot", 0), kw.get("add", -1), 0.0,
+                         kw.get("sp", 1024), p, 1 << 20, kw.get("type", 12), 1, 64, 256, kw.get("rank", 0), kw.get("world", 2), null]
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(y=null)) == -4
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(e=null)) == -4
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(X=null)) == -4          # no activations at all
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(world=9)) == -3
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(rank=2)) == -3
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(slot=-1)) == -3
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(sp=100)) == -3          # slot too small for world * N_local
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(add=0)) == -3           # a call cannot consume its own slot
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(type=3)) == -1
+    assert lib.gguf_b200_tp_unpack(null, p, 0, 1, 1024, 64, p, 64, 1, null) == -4
+    assert lib.gguf_b200_tp_unpack(p, p, 0, 1, 1024, 2048, p, 2048, 1, null) == -3   # n beyond the slot
+    assert lib.gguf_b200_tp_unpack(p, p, 0, 1, 1024, 64, p, 64, 9, null) == -2
+    # prefill: op, W, X, outputs, flags, epochs, slot, ws, ws_bytes, type, dtype, M, N_local, K, rank, world, stream
+    margs = lambda **kw: [kw.get("op", capi.OP_MMQ), p, p, kw.get("y", ptrs), ptrs, p, 0, p, 1 << 30, kw.get("type", 12),
+                          kw.get("dtype", 1), 32, 64, 256, 0, kw.get("world", 2), null]
+    assert lib.gguf_b200_matmul_tp(*margs(y=null)) == -4
+    assert lib.gguf_b200_matmul_tp(*margs(op=capi.OP_GEMV)) == -3
+    assert lib.gguf_b200_matmul_tp(*margs(world=0)) == -3
+    assert lib.gguf_b200_matmul_tp(*margs(type=16)) == -1                # IQ types go through OP_DEQUANT_MATMUL
+    assert lib.gguf_b200_matmul_tp(*margs(op=capi.OP_DEQUANT_MATMUL, type=12)) == -1
+    assert lib.gguf_b200_matmul_tp(*margs(op=capi.OP_DEQUANT_MATMUL, type=16, dtype=0)) == -2
     assert lib.gguf_b200_tp_wait(null, p, 0, 2, null) == -4
     assert lib.gguf_b200_tp_wait(p, p, 0, 0, null) == -3
+    lib.gguf_b200_set_wait_limit_cycles(0)                                # restores the default; no device call
 
 
 def test_ops_module_fails_loudly_without_extension(tmp_path, monkeypatch):

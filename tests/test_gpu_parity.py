@@ -103,7 +103,9 @@ def test_q4k_contraction_knob_selects_oracle_mode():
 
 # ---------------------------------------------------------------- GEMV -----------------------
 
-GEMV_SHAPES = [(3072, 1024, 1), (520, 4096, 1), (257, 2048, 3), (128, 14336, 2), (1001, 4096, 2), (300, 1024, 2), (96, 28672, 1), (64, 3584, 8), (40, 4096, 11)]
+GEMV_SHAPES = [(3072, 1024, 1), (520, 4096, 1), (257, 2048, 3), (128, 14336, 2), (1001, 4096, 2), (300, 1024, 2), (96, 28672, 1), (64, 3584, 8), (40, 4096, 11),
+               # K whose blocks do not divide evenly into the K-slices of the two-vector kernel
+               (300, 8960, 2), (70, 8448, 2), (33, 12544, 2), (50, 10752, 1), (7, 18944, 1), (5000, 512, 1)]
 
 
 @pytest.mark.parametrize("shape", GEMV_SHAPES)
@@ -349,35 +351,110 @@ def test_fused_moe_dispatcher_matches_dense_experts():
 
 
 # ---------------------------------------------------------------- fused gather (tensor parallel) --
+# Two ranks emulated on ONE GPU, one after the other on one stream, so nothing ever waits on a
+# kernel that has not been launched.  The real 2/4/8-GPU runs are in tests/test_tp_multi_gpu.py.
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q8_0", "IQ4_XS"])
-def test_tp_gemv_peer_stores_one_gpu(name):
-    """Two ranks emulated on one GPU, one after the other on one stream (nothing ever waits on a
-    kernel that has not been launched): each writes its row slice into both output vectors and
-    raises both flags; the wait kernels then find the flags complete.  Result = unsharded GEMV."""
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("name", ["Q4_K", "Q8_0", "IQ4_XS", "IQ2_XXS"])
+def test_tp_gemv_packets_one_gpu(name, dtype):
+    """Each rank sends its row slice as tagged packets into both packet arenas; unpacking either
+    arena gives the unsharded GEMV bit for bit.  A second call whose activations are
+    x + s * (vector gathered by the first) reads the packets in its own quantizer."""
     t = TYPES[name]
-    N, K = 1024, 2048
+    N, K, world = 1024, 2048, 2
     wn, w = dev_w(t, N, K, seed=5)
-    x = dev_x(1, K, seed=5)
+    x = dev_x(1, K, seed=5, dtype=dtype)
     want = capi.mul_mat_vec_a8(w, x, t, N)
-    ys = [torch.zeros(N, dtype=torch.float16, device=DEV) for _ in range(2)]
-    flags = [torch.zeros(1024, dtype=torch.int32, device=DEV) for _ in range(2)]
-    epochs = [torch.zeros(1024, dtype=torch.int32, device=DEV) for _ in range(2)]
-    slot = 3
+    psz = 8 if dtype == torch.float32 else 4
+    slots, slot_packets = 4, 2048
+    arenas = [torch.zeros(slots * slot_packets * psz, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    epochs = [torch.zeros(slots, dtype=torch.int32, device=DEV) for _ in range(world)]
+    ptrs = [a.data_ptr() for a in arenas]
+    shards = [w[r * N // world:(r + 1) * N // world].contiguous() for r in range(world)]
+    for rep in range(3):   # later rounds find the previous round's packets in place: only the tag tells them apart
+        for r in range(world):
+            capi.mul_mat_vec_a8_tp(shards[r], x, ptrs, epochs[r], 1, slot_packets, t, r)
+        for r in range(world):
+            got = capi.tp_unpack(arenas[r], epochs[r], 1, 1, slot_packets, N, dtype)
+            assert torch.equal(got, want)
+            assert int(epochs[r][1]) == rep + 1
+    # chained call: x2 = x + s * y(slot 1)[:K], rounded to the activation type, into slot 2
+    s = 2.0 ** -9
+    x2 = (x.float() + s * want[:, :K].float()).to(dtype)
+    want2 = capi.mul_mat_vec_a8(w, x2, t, N)
+    for r in range(world):
+        capi.mul_mat_vec_a8_tp(shards[r], x, ptrs, epochs[r], 2, slot_packets, t, r, add_slot=1, add_scale=s)
+    for r in range(world):
+        assert torch.equal(capi.tp_unpack(arenas[r], epochs[r], 2, 1, slot_packets, N, dtype), want2)
+    # both slots at once
+    both = capi.tp_unpack(arenas[0], epochs[0], 1, 2, slot_packets, N, dtype)
+    assert torch.equal(both[0:1], want) and torch.equal(both[1:2], want2)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+
+
+@pytest.mark.parametrize("case", [("Q4_K", 12, 1, 512, 2048, 96), ("Q6_K", 14, 1, 256, 8192, 130), ("IQ2_XXS", 16, 4, 512, 4096, 128),
+                                  ("IQ4_XS", 23, 4, 1024, 1024, 40)])
+def test_tp_matmul_tiles_one_gpu(case):
+    """Prefill GEMM, two emulated ranks: each stores its column block into both gathered outputs
+    (tile epilogue, or the partial-tile adder when K is split) and raises both flags."""
+    name, t, op, N, K, M = case
+    world = 2
+    wn, w = dev_w(t, N, K, seed=7)
+    x = dev_x(M, K, seed=7)
+    want = capi.mul_mat_a8(w, x, t, N) if op == capi.OP_MMQ else capi.dequant_matmul(w, x, t, N)
+    ys = [torch.zeros((M, N), dtype=torch.float16, device=DEV) for _ in range(world)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(world)]
+    epochs = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(world)]
+    slot = 5
     for rep in range(2):
         for y in ys:
             y.zero_()
-        for r in range(2):
-            capi.mul_mat_vec_a8_tp(w[r * N // 2:(r + 1) * N // 2].contiguous(), x, [y.data_ptr() for y in ys],
-                                   [f.data_ptr() for f in flags], epochs[r], slot, t, r,
-                                   wait_slot=slot if rep else -1)   # second round: the quantizer checks round one's flags
-        for r in range(2):
-            capi.tp_wait(flags[r], epochs[r], slot, 2)
+        for r in range(world):
+            capi.matmul_tp(op, w[r * N // world:(r + 1) * N // world].contiguous(), x, [y.data_ptr() for y in ys],
+                           [f.data_ptr() for f in flags], epochs[r], slot, t, r)
+        for r in range(world):
+            capi.tp_wait(flags[r], epochs[r], slot, world)
         torch.cuda.synchronize()
         assert capi.last_status() == 0
-        for r in range(2):
-            assert int(flags[r][slot]) == 2 * (rep + 1) and int(epochs[r][slot]) == rep + 1
-            assert torch.equal(ys[r].view(1, N), want)
+        for r in range(world):
+            assert int(flags[r][slot]) == world * (rep + 1) and int(epochs[r][slot]) == rep + 1
+            # same arithmetic per element; only a different split of K may reorder the fp32 sums
+            assert rel_l2(ys[r].float().cpu(), want.float().cpu()) <= 3e-4
+        assert torch.equal(ys[0], ys[1])
+
+
+def test_waits_on_other_gpus_run_out_and_report():
+    """A packet that nobody sends and a flag that nobody raises: with a limit of about a millisecond
+    the waiting kernels give up by themselves, the status word reads E_TIMEOUT (-8) and the
+    context stays usable."""
+    capi.set_wait_limit_cycles(2_000_000)
+    try:
+        arena = torch.zeros(4 * 256 * 4, dtype=torch.uint8, device=DEV)
+        epochs = torch.ones(4, dtype=torch.int32, device=DEV)        # expects launch 1 of every slot: never sent
+        out = capi.tp_unpack(arena, epochs, 0, 1, 256, 256, torch.float16)
+        torch.cuda.synchronize()
+        assert capi.last_status() == -8
+        assert capi.last_status() == 0                               # reading clears it
+        flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+        capi.tp_wait(flags, epochs, 0, 2)
+        torch.cuda.synchronize()
+        assert capi.last_status() == -8
+        # the quantizer's packet poll of a chained decode call gives up the same way
+        t, N, K = 12, 64, 1024
+        _, w = dev_w(t, N, K, seed=1)
+        x = dev_x(1, K, seed=1)
+        big = torch.zeros(4 * 1024 * 4, dtype=torch.uint8, device=DEV)
+        ep = torch.zeros(4, dtype=torch.int32, device=DEV)
+        ep[0] = 1
+        capi.mul_mat_vec_a8_tp(w, x, [big.data_ptr()], ep, 1, 1024, t, 0, add_slot=0, add_scale=1.0)
+        torch.cuda.synchronize()
+        assert capi.last_status() == -8
+    finally:
+        capi.set_wait_limit_cycles(0)
+    y = capi.mul_mat_vec_a8(w, x, t, N)                              # the device still works
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0 and bool(torch.isfinite(y).all())
 
 
 def test_mmq_split_k_matches_unsplit():

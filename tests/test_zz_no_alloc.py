@@ -39,6 +39,21 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(native_libs):
     assert capi.last_status() == 0
 
 
+def test_noalloc_at_its_limits(native_libs):
+    """The largest case the fixed array admits (8 vectors of K = 32768 fill it to the last byte)
+    and a 5..8-vector case at moderate K, bit for bit against the regular entry point.  A bounded
+    wait that expired inside these kernels would show in the same status word as everywhere else."""
+    w, x = case(synth.Q8_0, 64, 32768, 8, seed=3)
+    assert capi.lib().gguf_b200_workspace_bytes(capi.OP_GEMV, synth.Q8_0, 8, 64, 32768) == capi.lib().gguf_b200_noalloc_scratch_bytes()
+    y = capi.mul_mat_vec_a8_noalloc(w, x, synth.Q8_0, 64)
+    assert torch.equal(y, capi.mul_mat_vec_a8(w, x, synth.Q8_0, 64))
+    for m in (5, 7, 8):
+        w2, x2 = case(synth.Q4_K, 200, 4096, m, seed=m)
+        assert torch.equal(capi.mul_mat_vec_a8_noalloc(w2, x2, synth.Q4_K, 200), capi.mul_mat_vec_a8(w2, x2, synth.Q4_K, 200))
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+
+
 def test_noalloc_rejects_sizes_beyond_its_array(native_libs):
     lib = capi.lib()
     assert lib.gguf_b200_noalloc_scratch_bytes() == 8 * (32768 + 8192)

@@ -13,8 +13,11 @@ namespace gguf_b200 {
 // Device-side status word written by kernels whose bounded waits expire.
 static __device__ int g_status_word;
 static int g_q4k_contract = 1;  // the reference binary fuses the pair (established on B200 against it)
+// limit of the waits on other GPUs (packets, flags), in SM clock cycles: about a second by default
+static const long long kDefaultWaitLimit = 2000000000ll;
+static long long g_wait_limit_cycles = kDefaultWaitLimit;
 
-static int* status_ptr() {
+int* status_word_ptr() {
   static int* ptrs[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
@@ -26,6 +29,8 @@ static int* status_ptr() {
   }
   return p;
 }
+
+static int* status_ptr() { return status_word_ptr(); }
 
 int mmq_corr_mode(int type) { return type == T_Q4_0 ? CORR_Q4_0 : (type == T_Q4_K ? CORR_MIN : CORR_NONE); }
 int64_t mmq_ldb(int type, int64_t K) {
@@ -73,6 +78,8 @@ int gguf_b200_block_size(int type) { return block_size(type); }
 int64_t gguf_b200_q8_1_row_bytes(int64_t K) { return round_up(K, 512) / 32 * 36; }
 void gguf_b200_set_q4k_contract(int fused) { g_q4k_contract = fused ? 1 : 0; }
 int gguf_b200_moe_block_size(int type) { return is_mmq_type(type) ? mmq_moe_block_size() : 0; }
+
+void gguf_b200_set_wait_limit_cycles(int64_t cycles) { g_wait_limit_cycles = cycles > 0 ? cycles : kDefaultWaitLimit; }
 
 int gguf_b200_last_status(void) {
   int* p = status_ptr();
@@ -141,41 +148,115 @@ int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, in
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
 }
 
-int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* y_peers, uint32_t* const* flag_peers,
-                                uint32_t* epochs_local, int slot, int wait_slot, void* ws, int64_t ws_bytes, int type, int dtype,
-                                int64_t N_local, int64_t K, int rank, int world, void* stream) {
-  if (!y_peers || !flag_peers || !epochs_local) return E_BAD_POINTER;
-  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0) return E_BAD_SHAPE;
-  int rc = check_common(W, X, y_peers[rank], type, dtype, 1, N_local, K);
+int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* packet_peers, uint32_t* epochs_local, int slot,
+                                int add_slot, float add_scale, int64_t slot_packets, void* ws, int64_t ws_bytes, int type,
+                                int dtype, int64_t N_local, int64_t K, int rank, int world, void* stream) {
+  if (!packet_peers || !epochs_local) return E_BAD_POINTER;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0 || slot_packets <= 0) return E_BAD_SHAPE;
+  if (!X && add_slot < 0) return E_BAD_POINTER;
+  int rc = check_common(W, X ? X : W, packet_peers[rank], type, dtype, 1, N_local, K);
   if (rc || N_local == 0) return rc;
+  if ((int64_t)world * N_local > slot_packets || (add_slot >= 0 && K > slot_packets) || add_slot == slot) return E_BAD_SHAPE;
   if (!ws || !aligned16(ws)) return E_BAD_POINTER;
   if (ws_bytes < q8_soa_bytes(1, K)) return E_WORKSPACE;
   int* st = status_ptr();
   if (!st) return E_CUDA;
+  const int64_t psz = dtype == DT_F32 ? 8 : 4;   // bytes per packet
   GemvTp tp{};
   tp.world = world;
   tp.slot = slot;
-  tp.rank = rank;
   tp.epoch = epochs_local;
   tp.y_off = (int64_t)rank * N_local;
   for (int r = 0; r < world; ++r) {
-    if (!y_peers[r] || !flag_peers[r]) return E_BAD_POINTER;
-    tp.y_peer[r] = y_peers[r];
-    tp.flag_peer[r] = flag_peers[r];
+    if (!packet_peers[r] || (reinterpret_cast<uintptr_t>(packet_peers[r]) & 15)) return E_BAD_POINTER;
+    tp.ll_peer[r] = static_cast<uint8_t*>(packet_peers[r]) + (int64_t)slot * slot_packets * psz;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  Q8Wait wt{};
-  if (wait_slot >= 0) {   // X derives from the vector gathered in wait_slot: the quantizer waits for it
-    wt.flag = flag_peers[rank] + wait_slot;
-    wt.epoch = epochs_local + wait_slot;
-    wt.world = world;
-    wt.status = st;
+  Q8Tp qt{};
+  qt.bump = epochs_local + slot;    // this launch's number, read by the GEMV kernel behind the quantizer
+  qt.status = st;
+  qt.limit_cycles = g_wait_limit_cycles;
+  if (add_slot >= 0) {   // x' = x + add_scale * (vector gathered in add_slot): the quantizer polls its packets
+    qt.add = static_cast<const uint8_t*>(packet_peers[rank]) + (int64_t)add_slot * slot_packets * psz;
+    qt.add_epoch = epochs_local + add_slot;
+    qt.add_scale = add_scale;
   }
-  rc = launch_quantize_q8_1(X, dtype, ws, 1, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s, 0,
-                            wait_slot >= 0 ? &wt : nullptr);
+  rc = launch_quantize_q8_1(X, dtype, ws, 1, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s, 0, &qt);
   if (rc) return rc;
   rc = launch_gemv1(W, ws, nullptr, type, dtype, N_local, K, st, s, &tp);
   return rc == 1 ? E_TOO_LARGE : rc;   // rows too long for the single-vector kernel
+}
+
+int gguf_b200_tp_unpack(const void* packets_local, const uint32_t* epochs_local, int slot0, int nslots, int64_t slot_packets,
+                        int64_t n, void* out, int64_t out_stride, int dtype, void* stream) {
+  if (!packets_local || !epochs_local || !out) return E_BAD_POINTER;
+  if (!dtype_ok(dtype)) return E_BAD_DTYPE;
+  if (slot0 < 0 || nslots < 0 || n < 0 || n > slot_packets || out_stride < n) return E_BAD_SHAPE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  return launch_tp_unpack(packets_local, epochs_local, slot0, nslots, slot_packets, n, out, out_stride, dtype, g_wait_limit_cycles,
+                          st, static_cast<cudaStream_t>(stream));
+}
+
+int gguf_b200_matmul_tp(int op, const void* W, const void* X, void* const* y_peers, uint32_t* const* flag_peers,
+                        uint32_t* epochs_local, int slot, void* ws, int64_t ws_bytes, int type, int dtype, int64_t M,
+                        int64_t N_local, int64_t K, int rank, int world, void* stream) {
+  if (!y_peers || !flag_peers || !epochs_local) return E_BAD_POINTER;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0) return E_BAD_SHAPE;
+  if (op != GGUF_B200_OP_MMQ && op != GGUF_B200_OP_DEQUANT_MATMUL) return E_BAD_SHAPE;
+  int rc = check_common(W, X, y_peers[rank], type, dtype, M, N_local, K);
+  if (rc || M == 0 || N_local == 0) return rc;
+  if (op == GGUF_B200_OP_DEQUANT_MATMUL) {
+    if (type != T_IQ2_XXS && type != T_IQ4_XS) return E_BAD_TYPE;
+    if (dtype != DT_F16 && dtype != DT_BF16) return E_BAD_DTYPE;
+    if (K % 64 != 0) return E_BAD_SHAPE;
+  } else if (!is_mmq_type(type)) {
+    return E_BAD_TYPE;
+  }
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MmqTp tp{};
+  tp.world = world;
+  tp.slot = slot;
+  tp.col_off = (int64_t)rank * N_local;
+  tp.ld = (int64_t)world * N_local;
+  tp.epoch = epochs_local;
+  for (int r = 0; r < world; ++r) {
+    tp.y_peer[r] = y_peers[r];
+    tp.flag_peer[r] = flag_peers[r];
+  }
+  MmqArgs a{};
+  a.w = W; a.y = nullptr;
+  a.type = type; a.out_dtype = dtype;
+  a.M = M; a.N = N_local; a.K = K;
+  a.rows_out = M;
+  a.status = st;
+  a.tp = &tp;
+  if (op == GGUF_B200_OP_DEQUANT_MATMUL) {
+    a.b = X; a.b_dtype = dtype; a.ldb = K;
+    a.corr_mode = CORR_NONE;
+    if (ws && aligned16(ws) && ws_bytes > 0) {
+      a.part = ws;
+      a.part_bytes = ws_bytes;
+    }
+    return launch_mmq(a, s);
+  }
+  if (!ws || !aligned16(ws)) return E_BAD_POINTER;
+  const int64_t ldb = mmq_ldb(type, K);
+  if (ws_bytes < M * ldb * 2) return E_WORKSPACE;
+  const int perm = mmq_perm(type, N_local, K, false, 0);
+  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), nullptr, 1, 0, s, perm);
+  if (rc) return rc;
+  a.perm = perm;
+  a.b = ws; a.b_dtype = DT_F16; a.ldb = ldb;
+  a.corr_mode = mmq_corr_mode(type);
+  const int64_t used = mmq_b_bytes(type, M, K);
+  if (ws_bytes > used) {
+    a.part = static_cast<uint8_t*>(ws) + used;
+    a.part_bytes = ws_bytes - used;
+  }
+  return launch_mmq(a, s);
 }
 
 int gguf_b200_tp_wait(const uint32_t* flags_local, const uint32_t* epochs_local, int slot, int world, void* stream) {
@@ -183,7 +264,7 @@ int gguf_b200_tp_wait(const uint32_t* flags_local, const uint32_t* epochs_local,
   if (world < 1 || world > 8 || slot < 0) return E_BAD_SHAPE;
   int* st = status_ptr();
   if (!st) return E_CUDA;
-  return launch_tp_wait(flags_local, epochs_local, slot, world, st, static_cast<cudaStream_t>(stream));
+  return launch_tp_wait(flags_local, epochs_local, slot, world, g_wait_limit_cycles, st, static_cast<cudaStream_t>(stream));
 }
 
 int gguf_b200_gemv_prepare(const void* X, int dtype, void* ws, int64_t ws_bytes, int type, int64_t M, int64_t K,
@@ -268,12 +349,13 @@ int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* ws, in
 
 int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* ws, int64_t ws_bytes, const int32_t* sorted_token_ids,
                      const int32_t* expert_ids, const int32_t* num_tokens_post_padded, int64_t n_sorted,
-                     int64_t expert_stride_bytes, int type, int dtype, int64_t tokens, int64_t top_k, int64_t N,
-                     int64_t K, void* stream) {
+                     int64_t expert_stride_bytes, int64_t n_experts, int type, int dtype, int64_t tokens, int64_t top_k,
+                     int64_t N, int64_t K, void* stream) {
   int rc = check_common(W, X, Y, type, dtype, tokens, N, K);
   if (rc) return rc;
   if (!is_mmq_type(type)) return E_BAD_TYPE;
-  if (top_k <= 0 || n_sorted < 0 || expert_stride_bytes % 16 != 0) return E_BAD_SHAPE;
+  if (top_k <= 0 || n_sorted < 0 || expert_stride_bytes % 16 != 0 || n_experts <= 0) return E_BAD_SHAPE;
+  if (n_experts > 256) return E_TOO_LARGE;
   if (tokens == 0 || N == 0) return E_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t rows_out = tokens * top_k;
@@ -305,6 +387,7 @@ int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* ws, int64_t ws
   a.expert_stride_bytes = expert_stride_bytes;
   a.top_k = top_k;
   a.rows_out = rows_out;
+  a.n_experts = n_experts;
   a.moe_block = mmq_moe_block_size();
   a.status = st;
   return launch_mmq(a, s);

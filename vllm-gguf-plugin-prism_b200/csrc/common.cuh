@@ -111,7 +111,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 }
 // Every wait in this library is bounded in time: a poll may itself suspend the thread for a
 // while, so the limit is counted in SM clock cycles (about a quarter of a second), after which
-// the caller records a status word and leaves.  A lost completion can then never wedge the GPU.
+// the caller records a status word and leaves, so a lost completion cannot wedge the GPU.  A
+// thread that gives up still has asynchronous work in flight (bulk copies into its shared memory,
+// tensor-core instructions): it calls drain_pause() -- and the tensor-core kernel also waits for
+// its last commit -- before its CTA may retire.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, long long limit_cycles = 500000000ll) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
@@ -119,6 +122,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return true;
   } while (clock64() - t0 < limit_cycles);
   return false;
+}
+// Pause of about a tenth of a millisecond, far longer than any bulk copy takes to land.
+__device__ __forceinline__ void drain_pause() {
+  for (int i = 0; i < 64; ++i) __nanosleep(2000);
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -139,6 +146,45 @@ __device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t* p) {
 }
 __device__ __forceinline__ float lds_half_as_float(const uint8_t* p) {
   return __half2float(*reinterpret_cast<const __half*>(p));
+}
+
+// ---- packets of a gathered vector (tensor-parallel decode) ---------------------------------
+// One element travels as ONE naturally aligned store that carries the value and the number of
+// the launch that produced it: 32 bits {16-bit value, 16-bit tag} for f16 / bf16, 64 bits
+// {f32 value, 32-bit tag} for f32.  A reader polls the word until the tag is the one it expects;
+// the value then is that launch's, with no fence and no separate flag.  The poll is bounded.
+template <typename T> __device__ __forceinline__ bool packet_read(const void* base, int64_t i, unsigned want, long long limit_cycles, float& out) {
+  if (sizeof(T) == 2) {
+    const uint32_t* p = static_cast<const uint32_t*>(base) + i;
+    want &= 0xFFFFu;
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    bool ok = (v >> 16) == want;
+    if (!ok) {
+      const long long t0 = clock64();
+      do {
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+        ok = (v >> 16) == want;
+      } while (!ok && clock64() - t0 < limit_cycles);
+    }
+    const unsigned short b = (unsigned short)(v & 0xFFFFu);
+    out = to_float<T>(*reinterpret_cast<const T*>(&b));
+    return ok;
+  } else {
+    const unsigned long long* p = static_cast<const unsigned long long*>(base) + i;
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    bool ok = (unsigned)(v >> 32) == want;
+    if (!ok) {
+      const long long t0 = clock64();
+      do {
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+        ok = (unsigned)(v >> 32) == want;
+      } while (!ok && clock64() - t0 < limit_cycles);
+    }
+    out = __uint_as_float((unsigned)(v & 0xFFFFFFFFull));
+    return ok;
+  }
 }
 
 // Programmatic dependent launch.  A kernel launched with launch_pdl() may become resident while

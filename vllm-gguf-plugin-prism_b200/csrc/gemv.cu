@@ -291,9 +291,8 @@ struct GemvParams {
   int stages, stage_bytes;
   // MoE-vec mode (topk_ids != null): output row s uses weights of expert topk_ids[s], vector s/top_k
   const int32_t* topk_ids;
-  int64_t n_slots, top_k, expert_rows;
+  int64_t n_slots, top_k, expert_rows, n_experts;
   int* status;
-  int debug_skip;         // tuning aid: 1 = stream the weights but skip the arithmetic
 };
 
 template <int TYPE, int MT, typename out_t>
@@ -367,11 +366,14 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
   const int64_t w_safe = p.w_bytes & ~int64_t(15);
   const uint32_t n32 = (uint32_t)p.n;
 
-  // weight row of logical row r (MoE-vec: r = slot * N + n uses the slot's expert)
+  // weight row of logical row r (MoE-vec: r = slot * N + n uses the slot's expert); -1 when the
+  // slot's expert id is not in [0, n_experts): such rows are neither read nor written
   auto weight_row = [&](int64_t r) -> int64_t {
     if (!moe) return r;
     const uint32_t slot = (uint32_t)r / n32;
-    return (int64_t)p.topk_ids[slot] * p.expert_rows + (int64_t)((uint32_t)r - slot * n32);
+    const int64_t e = p.topk_ids[slot];
+    if (e < 0 || e >= p.n_experts) return -1;
+    return e * p.expert_rows + (int64_t)((uint32_t)r - slot * n32);
   };
   // Issue the bulk copy of (row iteration ri, segment seg) into stage st.  Lane 0 only.
   auto issue = [&](int ri, int seg, int st) {
@@ -383,7 +385,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
     int64_t aend = (end + 15) & ~int64_t(15);
     if (aend > w_safe) aend = w_safe;  // the (< 16 byte) tail past w_safe is fetched with plain loads by the consumer
     uint8_t* dst = ring + (size_t)st * p.stage_bytes;
-    const uint32_t bytes = aend > abeg ? (uint32_t)(aend - abeg) : 0u;
+    const uint32_t bytes = (wrow >= 0 && aend > abeg) ? (uint32_t)(aend - abeg) : 0u;
     if (bytes) {
       mbar_expect_tx(&bars[st], bytes);
       bulk_g2s(dst, p.w + abeg, bytes, &bars[st]);
@@ -455,6 +457,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
       }
       if (!mbar_wait_bounded(&bars[c_st], c_phase)) {
         if (lane == 0) atomicExch(p.status, E_TIMEOUT);
+        drain_pause();   // copies this warp still has in flight land before its CTA can retire
         return;
       }
       const int b0 = seg * p.seg_blocks;
@@ -464,13 +467,13 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
       const uint8_t* data = stage + (beg & 15);
       {  // tail bytes the bulk copy was not allowed to touch
         const int64_t end = beg + (int64_t)nbk * TS;
-        if (end > w_safe) {
+        if (wrow >= 0 && end > w_safe) {
           const int64_t abeg = beg & ~int64_t(15);
           for (int64_t o = w_safe + lane; o < end; o += 32) stage[o - abeg] = p.w[o];
           __syncwarp();
         }
       }
-      const int units = nbk * UPB;
+      const int units = wrow >= 0 ? nbk * UPB : 0;
       const int g_seg = b0 * (QK / 32);
       if (moe) {
         XView xw = xv;  // one vector per warp, stored in slice `warp`
@@ -482,13 +485,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
           Unit<TYPE, 1>::run(data + b * TS, u - b * UPB, g_seg + b * (QK / 32), xw, tb, 1, a1);
         }
         acc[0] = a1[0];
-      } else if (!p.debug_skip) {
+      } else {
         for (int u = lane; u < units; u += 32) {
           const int b = u / UPB;
           Unit<TYPE, MT>::run(data + b * TS, u - b * UPB, g_seg + b * (QK / 32), xv, tb, p.mc, acc);
         }
-      } else {
-        acc[0] += (float)data[lane];
       }
       __syncwarp();  // all lanes are done with this stage before lane 0 refills it
       if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
@@ -496,7 +497,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, MT == 1 ? 3 : 2) gemv_kernel(
     out_t* y = static_cast<out_t*>(p.y);
     if (moe) {
       const float v = warp_sum(acc[0]);
-      if (lane == 0) y[r] = from_float<out_t>(v);
+      if (lane == 0 && wrow >= 0) y[r] = from_float<out_t>(v);
       acc[0] = 0.f;
     } else {
 #pragma unroll
@@ -612,8 +613,6 @@ static int launch_type(const GemvParams& p, const GemvPlan& pl, int out_dtype, i
 static int launch_any(GemvParams p, int type, int out_dtype, int64_t M, bool moe, cudaStream_t stream) {
   const GemvPlan pl = make_plan(type, p.k, M, moe);
   p.bpr = (int)(p.k / block_size(type));
-  static const int dbg = gemv_tune_int("GGUF_B200_GEMV_DEBUG_SKIP", 0);
-  p.debug_skip = dbg;
   p.seg_blocks = pl.seg_blocks;
   p.nseg = pl.nseg;
   p.stages = pl.stages;
@@ -674,6 +673,7 @@ int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* t
   p.n_slots = tokens * top_k;
   p.top_k = top_k;
   p.expert_rows = N;
+  p.n_experts = n_experts;
   p.status = status;
   return launch_any(p, type, out_dtype, tokens, true, stream);
 }

@@ -22,6 +22,7 @@ namespace gguf_b200 {
 
 constexpr int G1_WARPS = 8;
 constexpr int G1_BATCH = 32;   // row iterations between two flushes of the slice partials
+constexpr int G1_TAB_COPIES = 16;   // bank-conflict-free copies of the IQ2_XXS code books (see the kernel)
 
 __device__ __forceinline__ int dp4a_us1(uint32_t a, uint32_t b, int c) {
   int d;
@@ -234,8 +235,8 @@ template <> struct G1<T_IQ2_XXS> {
     int sp = 0, sn = 0;
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
-      const uint2 gr = t.grid[(q[0] >> (8 * il)) & 0xFF];
-      const uint2 sm = t.smask[(aux >> (7 * il)) & 127];
+      const uint2 gr = t.grid[((q[0] >> (8 * il)) & 0xFF) * G1_TAB_COPIES];     // this lane's copy of the entry
+      const uint2 sm = t.smask[((aux >> (7 * il)) & 127) * G1_TAB_COPIES];
       sp = dp4a_us1(gr.x, x[2 * il], sp);
       sp = dp4a_us1(gr.y, x[2 * il + 1], sp);
       sn = dp4a_us1(gr.x & sm.x, x[2 * il], sn);
@@ -251,10 +252,16 @@ template <> struct G1<T_IQ2_XXS> {
 // the rows of a group are contiguous in memory and arrive with ONE bulk copy; with several
 // slices each row's slice is its own copy into a padded slot of the stage.  Grouping rows
 // amortises the per-item costs (copy issue, barrier wait, address arithmetic) over G1_R rows.
+//
+// Rows are shared out over the grid's "row lanes" (a row lane = the ks warps of a CTA that work
+// on the same rows; rl lanes per CTA) in one of two ways:
+//   contiguous   lane w owns rows [w*q + min(w, r), ...) with q = N / lanes, r = N % lanes: every
+//                lane gets q or q+1 rows, so no lane runs a whole extra pass, a lane streams one
+//                contiguous byte range, and the rows of a CTA are one contiguous range;
+//   round-robin  row groups are dealt to the lanes in turn (group = pass * lanes + lane).
 
 constexpr int G1_R = 4;
 constexpr int G1_MAX_WORLD = 8;
-constexpr int G1_TP_SLOTS = 64;
 
 struct G1Params {
   const uint8_t* w;
@@ -263,11 +270,12 @@ struct G1Params {
   void* y;
   int64_t n, k;
   int bpr;               // blocks per row
-  int ks, rl;            // K-slices per row, row groups in flight per CTA (ks * rl <= 8)
-  int slice_blocks;      // blocks per K-slice (the last slice may be shorter)
+  int ks, rl;            // K-slices per row, row lanes per CTA (ks * rl <= 8)
+  int slice_q, slice_r;  // slice i holds slice_q + (i < slice_r) blocks, so no slice is ever empty
   int rows_per_item;     // <= G1_R
   int slot_bytes;        // distance between the rows of an item inside a stage
   int stages, stage_bytes;
+  int contig;            // 1: contiguous row ranges per lane, 0: round-robin row groups
   int* status;
   // MoE decode (topk_ids != null, one vector): blockIdx.y is an output row s of y; it uses the
   // weights of expert topk_ids[s] (experts back to back, expert_bytes apart) and the activation
@@ -275,25 +283,39 @@ struct G1Params {
   const int32_t* topk_ids;
   int top_k, n_experts, xq_vecs, moe_slots;
   int64_t expert_bytes;
-  // tensor-parallel output (world > 0): every result goes to y_peer[r][y_off + row] for all r,
-  // then flag_peer[r][slot] is raised once per launch (see the end of the kernel)
-  int world, slot, rank;
-  unsigned* epoch;
+  // Tensor-parallel output (world > 0): every result is sent to ALL ranks (this one included) as
+  // a packet {value, tag} written with one store into ll_peer[r][y_off + row]; tag = epoch[slot],
+  // this launch's number, which the activation quantizer queued just before this kernel has
+  // already incremented.  A reader that finds the tag it expects has the value: no fence, no flag.
+  int world, slot;
+  const unsigned* epoch;
   int64_t y_off;
-  void* y_peer[G1_MAX_WORLD];
-  unsigned* flag_peer[G1_MAX_WORLD];
+  void* ll_peer[G1_MAX_WORLD];
 };
 
-// launches in flight per call slot: CTAs of one launch that have finished (reset by the last one)
-__device__ unsigned g_tp_done[G1_TP_SLOTS];
-
 template <typename out_t>
-__device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v, int m = 0) {
-  if (p.topk_ids) m = (int)blockIdx.y;   // MoE decode: one output row of y per (token, expert) pair
-  // tensor-parallel launches write this rank's own copy of the full vector first; the last CTA
-  // forwards the finished slice to the peers in one coalesced pass (end of the kernel)
-  out_t* y = p.world == 0 ? static_cast<out_t*>(p.y) + (int64_t)m * p.n : static_cast<out_t*>(p.y_peer[p.rank]) + p.y_off;
-  y[row] = from_float<out_t>(v);
+__device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v, int m, unsigned tag) {
+  if (p.world == 0) {
+    if (p.topk_ids) m = (int)blockIdx.y;   // MoE decode: one output row of y per (token, expert) pair
+    static_cast<out_t*>(p.y)[(int64_t)m * p.n + row] = from_float<out_t>(v);
+    return;
+  }
+  const out_t o = from_float<out_t>(v);
+  if (sizeof(out_t) == 2) {
+    const uint32_t pk = (uint32_t)(*reinterpret_cast<const uint16_t*>(&o)) | (tag << 16);
+#pragma unroll 1
+    for (int r = 0; r < p.world; ++r) {
+      uint32_t* dst = static_cast<uint32_t*>(p.ll_peer[r]) + p.y_off + row;
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(pk) : "memory");
+    }
+  } else {
+    const unsigned long long pk = (unsigned long long)(*reinterpret_cast<const uint32_t*>(&o)) | ((unsigned long long)tag << 32);
+#pragma unroll 1
+    for (int r = 0; r < p.world; ++r) {
+      unsigned long long* dst = static_cast<unsigned long long*>(p.ll_peer[r]) + p.y_off + row;
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(pk) : "memory");
+    }
+  }
 }
 
 // MV activation vectors share one pass over the weights (MV = 1 or 2): a lane keeps the
@@ -321,15 +343,20 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   tb.grid = nullptr;
   tb.smask = nullptr;
   if (TYPE == T_IQ2_XXS) {
+    // Both code books are stored G1_TAB_COPIES times, copy c in the 8-byte column c of every
+    // 128-byte line: lane l reads copy l % 16, and since a 64-bit shared load is served one
+    // half-warp at a time, the 16 lanes of a half-warp hit 16 different bank pairs whatever
+    // entries they ask for.  (One copy costs a 3- to 4-way bank conflict on almost every look-up:
+    // 32 unrelated 8-byte entries per load.)
     uint2* g = reinterpret_cast<uint2*>(cur);
-    uint2* sm = g + 256;
-    cur += 256 * 8 + 128 * 8;
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-      const uint64_t v = d_iq2xxs_grid[i];
+    uint2* sm = g + 256 * G1_TAB_COPIES;
+    cur += (256 + 128) * 8 * G1_TAB_COPIES;
+    for (int i = threadIdx.x; i < 256 * G1_TAB_COPIES; i += blockDim.x) {
+      const uint64_t v = d_iq2xxs_grid[i / G1_TAB_COPIES];
       g[i] = make_uint2((uint32_t)v, (uint32_t)(v >> 32));
     }
-    for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-      const uint32_t s = d_ksigns_iq2xs[i];
+    for (int i = threadIdx.x; i < 128 * G1_TAB_COPIES; i += blockDim.x) {
+      const uint32_t s = d_ksigns_iq2xs[i / G1_TAB_COPIES];
       uint32_t lo = 0, hi = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -338,15 +365,15 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       }
       sm[i] = make_uint2(lo, hi);
     }
-    tb.grid = g;
-    tb.smask = sm;
+    tb.grid = g + (lane & (G1_TAB_COPIES - 1));
+    tb.smask = sm + (lane & (G1_TAB_COPIES - 1));
   }
   if (TYPE == T_IQ4_XS) {
     const uint32_t* kv = reinterpret_cast<const uint32_t*>(d_kvalues_iq4nl);
 #pragma unroll
     for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
   }
-  float* partial = reinterpret_cast<float*>(cur);  // [G1_BATCH][rl][G1_R][MV][ks]
+  float* partial = reinterpret_cast<float*>(cur);  // [rl][G1_BATCH][G1_R][MV][ks]
   cur += (size_t)G1_BATCH * 8 * G1_R * MV * sizeof(float);
   uint8_t* ring = cur + (size_t)warp * p.stages * p.stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cur + (size_t)G1_WARPS * p.stages * p.stage_bytes) + warp * p.stages;
@@ -357,27 +384,52 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
 
   const bool active = warp < p.ks * p.rl;
   const int ks_i = warp % p.ks, rl_i = warp / p.ks;
-  const int sb0 = ks_i * p.slice_blocks;
-  const int nblk = active ? max(0, min(p.slice_blocks, p.bpr - sb0)) : 0;
+  const int sb0 = ks_i * p.slice_q + min(ks_i, p.slice_r);
+  const int nblk = active ? p.slice_q + (ks_i < p.slice_r ? 1 : 0) : 0;
   const int units = nblk * UPB;
   const int R = p.rows_per_item;
   const int64_t row_bytes = (int64_t)p.bpr * TS;
   const int64_t w_safe = p.w_bytes & ~int64_t(15);
   const uint32_t slice_bytes = (uint32_t)nblk * TS;
   const bool contiguous = p.ks == 1;
-  // row groups of this CTA: group = (i * gridDim.x + blockIdx.x) * rl + rl_i, rows [group*R, group*R + R)
-  const int64_t groups = (p.n + R - 1) / R;
-  const int64_t groups_per_iter = (int64_t)gridDim.x * p.rl;
-  const int64_t first = (int64_t)blockIdx.x * p.rl;
-  const int iters = first < groups ? (int)((groups - first + groups_per_iter - 1) / groups_per_iter) : 0;  // uniform over the CTA
-  const int64_t my_first = first + rl_i;
-  const int my_iters = (active && nblk > 0 && my_first < groups) ? (int)((groups - my_first + groups_per_iter - 1) / groups_per_iter) : 0;
-  const int64_t row_stride = groups_per_iter * R;      // rows between two items of this warp
-  const int64_t byte_stride = row_stride * row_bytes;
+  const bool staged = p.ks > 1 || p.world > 0;   // results meet in shared memory before they are stored
 
-  // copy of row-range [r0, r0+cnt) (slice part) into stage st; lane 0 (contiguous) or lanes 0..cnt-1
-  auto issue = [&](int64_t r0, int st) {
-    const int64_t left_i = p.n - r0; const int cnt = (int)(left_i < R ? left_i : R);
+  // ---- which rows: lane_first(l) = first row of row lane l of this CTA, lane_count(l) its rows
+  // (contiguous), or first group / number of passes (round-robin) -------------------------------
+  const int64_t lanes = (int64_t)gridDim.x * p.rl;
+  const int64_t q_rows = p.n / lanes, r_rows = p.n % lanes;
+  const int64_t groups = (p.n + R - 1) / R;
+  auto lane_row0 = [&](int l) -> int64_t {
+    const int64_t wl = (int64_t)blockIdx.x * p.rl + l;
+    return wl * q_rows + (wl < r_rows ? wl : r_rows);
+  };
+  auto lane_rows = [&](int l) -> int {
+    const int64_t wl = (int64_t)blockIdx.x * p.rl + l;
+    return (int)(q_rows + (wl < r_rows ? 1 : 0));
+  };
+  // first row and row count of item i of row lane l
+  auto item = [&](int l, int i, int64_t& row, int& cnt) {
+    if (p.contig) {
+      const int left = lane_rows(l) - i * R;
+      row = lane_row0(l) + (int64_t)i * R;
+      cnt = left < R ? (left > 0 ? left : 0) : R;
+    } else {
+      const int64_t g = ((int64_t)i * gridDim.x + blockIdx.x) * p.rl + l;
+      row = g * R;
+      const int64_t left = p.n - row;
+      cnt = g < groups ? (int)(left < R ? left : R) : 0;
+    }
+  };
+  auto lane_iters = [&](int l) -> int {
+    if (p.contig) return (lane_rows(l) + R - 1) / R;
+    const int64_t f = (int64_t)blockIdx.x * p.rl + l;
+    return f < groups ? (int)((groups - f + lanes - 1) / lanes) : 0;
+  };
+  const int iters = lane_iters(0);   // lane 0 of a CTA never has fewer passes than the others: uniform over the CTA
+  const int my_iters = (active && nblk > 0) ? lane_iters(rl_i) : 0;
+
+  // copy of the rows [r0, r0 + cnt) (this warp's slice of them) into stage st
+  auto issue = [&](int64_t r0, int cnt, int st) {
     uint8_t* dst = ring + (size_t)st * p.stage_bytes;
     if (contiguous) {
       if (lane == 0) {
@@ -413,11 +465,12 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   };
 
   int p_it = 0, p_st = 0;
-  int64_t p_row = my_first * R;
   for (int s = 0; s < p.stages - 1; ++s) {
     if (p_it < my_iters) {
-      issue(p_row, p_st);
-      p_row += row_stride;
+      int64_t r0;
+      int cnt;
+      item(rl_i, p_it, r0, cnt);
+      issue(r0, cnt, p_st);
       ++p_it;
       if (++p_st == p.stages) p_st = 0;
     }
@@ -425,6 +478,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
 
   // The weight copies above touch nothing another kernel writes; everything below does.
   pdl_wait();
+  const unsigned tag = p.world > 0 ? (sizeof(out_t) == 2 ? (p.epoch[p.slot] & 0xFFFFu) : p.epoch[p.slot]) : 0u;
   // this lane's units (block offset inside the slice, sub-unit) and their activations
   uint32_t xq[MV][UMAX][T::XW];
   float xd[MV][UMAX][T::XD];
@@ -454,13 +508,14 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   int c_st = 0;
   uint32_t c_phase = 0;
   bool dead = false;
-  int64_t c_row = my_first * R;
   for (int i = 0; i < iters; ++i) {
     const bool mine = i < my_iters && !dead;
     if (mine) {
       if (p_it < my_iters) {
-        issue(p_row, p_st);
-        p_row += row_stride;
+        int64_t r0;
+        int cnt;
+        item(rl_i, p_it, r0, cnt);
+        issue(r0, cnt, p_st);
         ++p_it;
         if (++p_st == p.stages) p_st = 0;
       }
@@ -470,7 +525,9 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       }
     }
     if (mine && !dead) {
-      const int64_t left_c = p.n - c_row; const int cnt = (int)(left_c < R ? left_c : R);
+      int64_t c_row;
+      int cnt;
+      item(rl_i, i, c_row, cnt);
       uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
       const int64_t beg0 = c_row * row_bytes + (int64_t)sb0 * TS;
       const int64_t last_end = (c_row + cnt - 1) * row_bytes + (int64_t)sb0 * TS + slice_bytes;
@@ -504,99 +561,40 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
           for (int m = 0; m < MV; ++m) {
             const float v = warp_sum(acc[m][rr]);
             if (lane == 0) {
-              if (p.ks == 1) store_result<out_t>(p, c_row + rr, v, m);
-              else partial[((((i % G1_BATCH) * p.rl + rl_i) * G1_R + rr) * MV + m) * p.ks + ks_i] = v;
+              if (!staged) store_result<out_t>(p, c_row + rr, v, m, 0u);
+              else partial[(((rl_i * G1_BATCH + (i % G1_BATCH)) * G1_R + rr) * MV + m) * p.ks + ks_i] = v;
             }
           }
         }
       }
       __syncwarp();
       if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
-      c_row += row_stride;
     }
-    if (p.ks > 1 && ((i % G1_BATCH) == G1_BATCH - 1 || i == iters - 1)) {
-      // add the slice partials in slice order and store; every warp of the CTA takes part
+    if (staged && ((i % G1_BATCH) == G1_BATCH - 1 || i == iters - 1)) {
+      // add the slice partials in slice order and store; every warp of the CTA takes part.
+      // Consecutive threads take consecutive rows of one row lane, so the stores (and the
+      // packets sent to the other GPUs) leave as runs of adjacent addresses.
       __syncthreads();
       const int i0 = i - (i % G1_BATCH);
-      const int cnt = (i - i0 + 1) * p.rl * G1_R * MV;
+      const int per_lane = (i - i0 + 1) * G1_R;
+      const int cnt = per_lane * p.rl * MV;
       for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
-        const int m = t % MV, t2 = t / MV;
-        const int rr = t2 % G1_R, g2 = t2 / G1_R;
-        const int ii = i0 + g2 / p.rl, gl = g2 % p.rl;
-        const int64_t r = (first + (int64_t)ii * groups_per_iter + gl) * R + rr;
-        if (rr < R && r < p.n) {
+        const int m = t / (per_lane * p.rl), t2 = t - m * per_lane * p.rl;
+        const int gl = t2 / per_lane, t3 = t2 - gl * per_lane;
+        const int ii = i0 + t3 / G1_R, rr = t3 % G1_R;
+        int64_t r0;
+        int c;
+        item(gl, ii, r0, c);
+        if (rr < c) {
           float s = 0.f;
-          for (int q = 0; q < p.ks; ++q) s += partial[((((ii % G1_BATCH) * p.rl + gl) * G1_R + rr) * MV + m) * p.ks + q];
-          store_result<out_t>(p, r, s, m);
+          for (int q = 0; q < p.ks; ++q) s += partial[(((gl * G1_BATCH + (ii % G1_BATCH)) * G1_R + rr) * MV + m) * p.ks + q];
+          store_result<out_t>(p, r0 + rr, s, m, tag);
         }
       }
       __syncthreads();
     }
   }
-  (void)byte_stride;
-  if (p.world > 0) {
-    // All-gather completion.  Every CTA publishes its results at GPU scope (CTA barrier, then
-    // thread 0's fence -- the pattern of a grid-wide barrier) and counts itself off; the last
-    // CTA copies the finished slice from this rank's vector into every peer's with 16-byte
-    // stores over NVLink (one coalesced pass instead of a 2-byte remote store per row), fences
-    // system-wide and raises this launch's flag on every rank.  The flags only ever grow (one
-    // increment per rank and launch), so replays of a captured graph need no reset; a consumer
-    // waits for world * (this rank's own launch count).
-    __shared__ int s_last;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      unsigned* done = &g_tp_done[p.slot % G1_TP_SLOTS];
-      const unsigned prev = atomicAdd(done, 1u);
-      s_last = prev == gridDim.x - 1;
-      if (s_last) *done = 0;
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();   // acquire side of the count-off: the other CTAs' results are visible
-      const out_t* src = static_cast<const out_t*>(p.y_peer[p.rank]) + p.y_off;
-      const int64_t bytes = p.n * (int64_t)sizeof(out_t);
-      const bool vec = ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)bytes) & 15) == 0;
-      for (int r = 0; r < p.world; ++r) {
-        if (r == p.rank) continue;
-        out_t* dst = static_cast<out_t*>(p.y_peer[r]) + p.y_off;
-        if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-          const uint4* s4 = reinterpret_cast<const uint4*>(src);
-          uint4* d4 = reinterpret_cast<uint4*>(dst);
-          for (int64_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) d4[i] = __ldcg(s4 + i);
-        } else {
-          for (int64_t i = threadIdx.x; i < p.n; i += blockDim.x) dst[i] = __ldcg(src + i);
-        }
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        p.epoch[p.slot] += 1;      // read by this rank's later kernels (stream order)
-        __threadfence_system();
-        for (int r = 0; r < p.world; ++r) atomicAdd_system(p.flag_peer[r] + p.slot, 1u);
-      }
-    }
-  }
-}
-
-// One thread waits (bounded) until all `world` ranks have raised flag[slot] for this launch.
-__global__ void tp_wait_kernel(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status) {
-  pdl_trigger();   // whatever follows may be scheduled; it waits for this grid before it reads
-  pdl_wait();      // this rank's own GEMV has finished
-  const unsigned want = epoch[slot] * (unsigned)world;
-  const long long t0 = clock64();
-  for (;;) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag + slot) : "memory");
-    if ((int)(v - want) >= 0) return;
-    if (clock64() - t0 > 2000000000ll) {   // about a second: a rank is missing
-      atomicExch(status, E_TIMEOUT);
-      return;
-    }
-  }
-}
-
-int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status, cudaStream_t stream) {
-  return launch_pdl(tp_wait_kernel, dim3(1), dim3(1), 0, stream, flag, epoch, slot, world, status) == cudaSuccess ? E_OK : E_CUDA;
+  if (dead) drain_pause();   // copies this warp still has in flight land before its CTA can retire
 }
 
 // ---- host -----------------------------------------------------------------------------------
@@ -614,21 +612,27 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
   static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
   static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 6000);
+  static const int contig_env = g1_env("GGUF_B200_GEMV1_CONTIG", 1);
+  p.contig = (contig_env || p.world > 0) ? 1 : 0;
   const int cap_blocks = 32 * (T::UMAX / MV) / T::UPB;  // blocks whose units fit one lane-register set
   int ks = 1;
   while (ks < 8 && (p.bpr + ks - 1) / ks > cap_blocks) ks *= 2;
   if ((p.bpr + ks - 1) / ks > cap_blocks) return 1;  // row too long for this kernel: caller falls back
   p.ks = ks;
   p.rl = G1_WARPS / ks;
-  p.slice_blocks = (p.bpr + ks - 1) / ks;
-  const int slice_bytes = p.slice_blocks * TS;
+  // balanced split (bpr >= ks always holds: ks > 1 only when bpr exceeds cap_blocks >= 4)
+  p.slice_q = p.bpr / ks;
+  p.slice_r = p.bpr % ks;
+  const int slice_bytes = (p.slice_q + (p.slice_r ? 1 : 0)) * TS;   // the longest slice
   int R = rows_env < 1 ? 1 : (rows_env > G1_R ? G1_R : rows_env);
-  while (R > 1 && (int64_t)R * slice_bytes > item_env) --R;
+  // (the 16 copies of the IQ2_XXS code books take 48 KB: smaller items keep two CTAs on an SM)
+  const int item_cap = TYPE == T_IQ2_XXS && item_env > 3900 ? 3900 : item_env;
+  while (R > 1 && (int64_t)R * (ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16)) > item_cap) --R;
   p.rows_per_item = R;
   p.slot_bytes = ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16);
   p.stages = stages_env < 2 ? 2 : stages_env;
   p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
-  const size_t tables = TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0;
+  const size_t tables = TYPE == T_IQ2_XXS ? (size_t)(256 + 128) * 8 * G1_TAB_COPIES : 0;
   const size_t smem = tables + (size_t)G1_BATCH * 8 * G1_R * MV * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
   if (smem > 227 * 1024) return 1;
   auto kern = gemv1_kernel<TYPE, out_t, MV>;
@@ -695,13 +699,9 @@ int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_d
     if (tp->world < 1 || tp->world > G1_MAX_WORLD || tp->slot < 0) return E_BAD_SHAPE;
     p.world = tp->world;
     p.slot = tp->slot;
-    p.rank = tp->rank;
     p.epoch = tp->epoch;
     p.y_off = tp->y_off;
-    for (int r = 0; r < tp->world; ++r) {
-      p.y_peer[r] = tp->y_peer[r];
-      p.flag_peer[r] = tp->flag_peer[r];
-    }
+    for (int r = 0; r < tp->world; ++r) p.ll_peer[r] = tp->ll_peer[r];
   }
   p.w = static_cast<const uint8_t*>(w);
   p.bpr = (int)(K / block_size(type));

@@ -12,20 +12,26 @@ enum : int { Q8_MODE_REF = 0, Q8_MODE_SOA = 1, Q8_MODE_F16 = 2 };
 // correction column appended to the fp16 activation matrix of the tensor-core kernels
 enum : int { CORR_NONE = 0, CORR_Q4_0 = 1, CORR_MIN = 2 };
 
-// Optional wait of the SoA quantizer (tensor-parallel consumer): before reading x, wait until
-// *flag >= *epoch * world (flag raised by every rank's fused-gather GEMV, epoch counted by this
-// rank's own); a time-out sets *status.
-struct Q8Wait {
-  const unsigned* flag = nullptr;
-  const unsigned* epoch = nullptr;
-  int world = 0;
+// Tensor-parallel input of the SoA quantizer (one vector).  A gathered vector lives on every rank
+// as "packets": one 32-bit word {16-bit value, 16-bit tag} per element for f16/bf16 outputs, one
+// 64-bit word {f32 value, 32-bit tag} for f32, each written by a single store of the producing
+// GEMV (possibly on another GPU).  The quantizer reads x'[k] = x[k] + add_scale * value(add[k])
+// (x may be null), polling every packet until its tag equals *add_epoch (bounded by limit_cycles,
+// then *status = E_TIMEOUT).  bump != null: thread 0 of the grid increments *bump first -- the
+// launch number of the GEMV that follows, which that GEMV uses as the tag of its own packets.
+struct Q8Tp {
+  const void* add = nullptr;        // packets of the vector to add (element type = the x dtype), or null
+  const unsigned* add_epoch = nullptr;
+  float add_scale = 0.f;
+  unsigned* bump = nullptr;
+  long long limit_cycles = 0;
   int* status = nullptr;
 };
 // M = number of OUTPUT rows.  gather_ids (F16 mode only, may be null): output row r quantizes
 // input row gather_ids[r] / gather_div; ids outside [0, gather_limit) give a zero row.
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream, int perm = 0, const Q8Wait* wait = nullptr);
+                         cudaStream_t stream, int perm = 0, const Q8Tp* tp = nullptr);
 // leading dimension (elements) of the fp16 activation matrix of the tensor-core kernels
 int64_t mmq_ldb(int type, int64_t K);
 int mmq_corr_mode(int type);
@@ -41,14 +47,13 @@ int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dt
                 int* status, cudaStream_t stream);
 // One- and two-vector specialisation (gemv1.cu): activations in registers.  Returns 1 when the
 // shape is outside its reach (the caller then uses the general kernel).
-// Tensor-parallel output of the single-vector kernel: results go to y_peer[r] + y_off for every
-// rank r (peer-mapped pointers), then flag_peer[r][slot] is incremented once per launch.
+// Tensor-parallel output of the single-vector kernel: every result is sent to all `world` ranks
+// as a packet at ll_peer[r] + y_off + row (see Q8Tp), tagged with epoch[slot].
 struct GemvTp {
-  int world, slot, rank;
-  unsigned* epoch;          // this rank's launch counters: epoch[slot] is incremented by the last CTA
+  int world, slot;
+  const unsigned* epoch;    // this rank's launch counters (incremented by the quantizer before the launch)
   int64_t y_off;
-  void* y_peer[8];
-  unsigned* flag_peer[8];
+  void* ll_peer[8];
 };
 // MoE decode through the same kernel: y row s = weights of expert topk_ids[s] (N x K each, back
 // to back) times activation vector s / top_k of the `tokens` quantized ones
@@ -58,14 +63,30 @@ struct GemvMoe {
 };
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
                  cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1, const GemvMoe* moe = nullptr);
-// waits until flag[slot] has reached world * epoch[slot]; sets *status on a time-out
-int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, int* status, cudaStream_t stream);
+// Packets of `nslots` gathered vectors (slot_packets apart) -> plain vectors out[s][0..n) (out_stride
+// elements apart); every packet is polled until its tag equals epoch[slot0 + s] (bounded).
+// one thread waits (bounded) until flag[slot] has reached world * epoch[slot]
+int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int world, long long limit_cycles, int* status,
+                   cudaStream_t stream);
+int launch_tp_unpack(const void* packets, const unsigned* epoch, int slot0, int nslots, int64_t slot_packets, int64_t n,
+                     void* out, int64_t out_stride, int dtype, long long limit_cycles, int* status, cudaStream_t stream);
 // per-(token,expert) GEMV of the small-batch MoE entry point
 int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* topk_ids, int type, int out_dtype,
                     int64_t tokens, int64_t top_k, int64_t N, int64_t K, int64_t n_experts, int* status,
                     cudaStream_t stream);
 
 // Tensor-core (tcgen05) dequant-GEMM.  B operand = fp16/bf16 matrix [rows][ldb] (K-major).
+// Tensor-parallel output of the tensor-core GEMM: this rank's [M][N] result is column block
+// [col_off, col_off + N) of a gathered [M][ld] matrix that every rank holds; the kernel stores its
+// tiles into ALL ranks' copies (y_peer[r], plain 16-byte stores over NVLink, this rank included),
+// and the last CTA to finish increments epoch[slot] and then flag_peer[r][slot] on every rank.
+struct MmqTp {
+  int world, slot;
+  int64_t col_off, ld;
+  unsigned* epoch;
+  void* y_peer[8];
+  unsigned* flag_peer[8];
+};
 struct MmqArgs {
   const void* w;            // packed weights (expert 0 for MoE)
   const void* b;            // activation matrix, K-major, element type b_dtype (DT_F16 / DT_BF16)
@@ -82,8 +103,10 @@ struct MmqArgs {
   const int32_t* expert_ids;
   const int32_t* n_post_pad;
   int64_t n_sorted, expert_stride_bytes, top_k, rows_out;
+  int64_t n_experts;        // experts in w (0: unknown, ids are only limited to [0, 255] as in the reference)
   int moe_block;
   int* status;
+  const MmqTp* tp;          // null: plain output y
   void* part;               // optional fp32 scratch for split-K partial tiles (16-byte aligned), part_bytes long
   int64_t part_bytes;
 };
@@ -93,5 +116,9 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream);
 int mmq_moe_block_size();
 
 int64_t q8_soa_bytes(int64_t M, int64_t K);
+
+// Device address of the library's one status word on the current device (the word that
+// gguf_b200_last_status reads and clears); null if the runtime refuses the lookup.
+int* status_word_ptr();
 
 }  // namespace gguf_b200

@@ -148,13 +148,42 @@ struct MmqParams {
   const int32_t* n_post_pad;
   int64_t expert_stride_bytes, rows_out;
   int* status;
-  int debug;   // tuning aid (bit mask): 1 no decode, 2 no A store, 4 no MMA, 8 no B load
+  int n_experts;          // MoE: expert ids outside [0, n_experts) are skipped
   int raw_tma;            // 1: raw weight chunks arrive by 2-D TMA boxes (wmap), 0: by cp.async pieces
   int raw_stages;         // depth of the raw ring
   int64_t w_row0;         // first row of this matrix in wmap (MoE: added to expert * N)
   int y_tma;              // 1: the output tile leaves through shared memory and one TMA store (ymap)
   int ksplit, sps;        // K slices (grid.z) and main stages per slice; > 1: fp32 partial tiles go to ymap slice z
+  // tensor-parallel output (tp_world > 0, dense only): see MmqTp
+  int tp_world, tp_slot;
+  int64_t tp_col_off, tp_ld;
+  unsigned* tp_epoch;
+  void* tp_y[8];
+  unsigned* tp_flag[8];
 };
+
+// CTAs of the tensor-parallel launch in flight per call slot that have stored their tiles
+__device__ unsigned g_mmq_tp_done[64];
+
+// End of a tensor-parallel launch, called by every thread of a CTA after its stores to the peers:
+// CTA barrier, thread 0 fences system-wide and counts the CTA off; the last CTA of the grid
+// increments this rank's launch counter and raises the slot's flag on every rank.  The flags only
+// grow (one increment per rank and launch), so replays of a captured graph need no reset.
+__device__ __forceinline__ void tp_finish(unsigned* epoch, unsigned* const* flag, int world, int slot, unsigned total_ctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    unsigned* done = &g_mmq_tp_done[slot & 63];
+    const unsigned prev = atomicAdd(done, 1u);
+    if (prev == total_ctas - 1) {
+      *done = 0;
+      __threadfence_system();
+      epoch[slot] += 1;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) atomicAdd_system(flag[r] + slot, 1u);
+    }
+  }
+}
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST, bool TWO>
 __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
@@ -194,6 +223,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
   uint64_t* empty_a = bars + 16;              // [8]
   uint64_t* accum = bars + 32;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 33);
+  volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);   // set by any thread whose wait ran out
   uint64_t* raw_full = bars + 34;             // [MMQ_MAX_RAW]
   uint64_t* raw_empty = bars + 34 + MMQ_MAX_RAW;
   uint64_t* s_grid = bars + 48;
@@ -206,7 +236,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
   const uint8_t* wbase = p.w;
   if (MOE) {
     const int e = p.expert_ids[blockIdx.y];
-    if (e < 0 || e > 255) return;                    // same guard as the reference (moe.cuh:33)
+    if (e < 0 || e >= p.n_experts) return;           // the reference guards [0, 255] (moe.cuh:33); here also the real expert count
     if (t0 >= (int64_t)p.n_post_pad[0]) return;      // nothing routed to this block
     wbase += (int64_t)e * p.expert_stride_bytes;
   }
@@ -219,6 +249,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
       mbar_init(&empty_a[s], 1);
     }
     mbar_init(accum, 1);
+    *gave_up = 0;
     for (int s = 0; s < MMQ_MAX_RAW; ++s) {
       mbar_init(&raw_full[s], 1);
       mbar_init(&raw_empty[s], MMQ_PRODUCER_WARPS);
@@ -284,12 +315,10 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
     auto publish = [&](const uint32_t (&v)[32], int i) -> bool {   // wait for the slot, store the row, signal the MMA warp
       if (!wait_or_note(&empty_a[s], ph ^ 1u, 2, i)) return false;
       uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
-      if (!(p.debug & 2)) {
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc)
-          *reinterpret_cast<uint4*>(dst + ((cc ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
-        fence_proxy_async();
-      }
+      for (int cc = 0; cc < 8; ++cc)
+        *reinterpret_cast<uint4*>(dst + ((cc ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
+      fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
       s += NG;
@@ -316,12 +345,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
             const int i = c * 4 + SC;
             if (i < nmain && ok) {
               uint32_t v[32];
-              if (!(p.debug & 1)) {
-                Stage64<TYPE, ab_t>::template decode<SC>(chunk, v);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = 0;
-              }
+              Stage64<TYPE, ab_t>::template decode<SC>(chunk, v);
               ok = publish(v, i);
             }
           };
@@ -337,7 +361,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
             for (int h = 0; h < 2; ++h) {
               const int u = 2 * (i + i_begin) + h;
               uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
-              if (live && u < nunits && !(p.debug & 1)) {
+              if (live && u < nunits) {
                 constexpr int RW = Decoder<TYPE, ab_t>::RW;
                 uint32_t raw[RW];
                 Decoder<TYPE, ab_t>::load(srow, u, raw);
@@ -411,7 +435,22 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
       }
       // every producer thread arrives here, also after a time-out, so the barrier cannot hang
       asm volatile("bar.sync 2, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");
-      if (threadIdx.x == 0 && ok) {
+      if (p.tp_world > 0 && p.ksplit == 1) {
+        // tensor-parallel: the staged tile ([token][128 rows], 16-byte pieces) goes straight into
+        // every rank's gathered matrix, column block tp_col_off, with plain vector stores
+        constexpr int PIECES = MMQ_ROWS * (int)sizeof(out_t) / 16;      // per token
+        const int tokens_here = (int)min((int64_t)TN, p.M - t0);
+        const int rows_here = (int)min((int64_t)MMQ_ROWS, p.N - n0);    // (N is a multiple of 8 here)
+        const uint4* src = reinterpret_cast<const uint4*>(smem);
+        for (int rk = 0; rk < p.tp_world; ++rk) {
+          out_t* dst = static_cast<out_t*>(p.tp_y[rk]);
+          for (int e = threadIdx.x; e < tokens_here * PIECES; e += MMQ_PRODUCER_WARPS * 32) {
+            const int t = e / PIECES, pc = e - t * PIECES;
+            if (pc * (16 / (int)sizeof(out_t)) < rows_here)
+              *reinterpret_cast<uint4*>(dst + (t0 + t) * p.tp_ld + p.tp_col_off + n0 + pc * (16 / (int)sizeof(out_t))) = src[t * PIECES + pc];
+          }
+        }
+      } else if (threadIdx.x == 0 && ok) {
         asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&ymap), "r"(smem_u32(so)),
                      "r"((int)n0), "r"((int)t0), "r"((int)blockIdx.z)
                      : "memory");
@@ -450,12 +489,8 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
           if (++se == SA) { se = 0; phe ^= 1u; }
         }
         const int64_t col = i < nmain ? (int64_t)(i + i_begin) * MMQ_BK : p.kpad + (int64_t)(i - nmain) * MMQ_BK;
-        if (p.debug & 8) {
-          mbar_arrive(&full_a[sa]);
-        } else {
-          mbar_expect_tx(&full_a[sa], (uint32_t)B_STAGE);
-          tma_load_2d(sB + (size_t)sb * B_STAGE, &bmap, (int)col, (int)t0, &full_a[sa]);
-        }
+        mbar_expect_tx(&full_a[sa], (uint32_t)B_STAGE);
+        tma_load_2d(sB + (size_t)sb * B_STAGE, &bmap, (int)col, (int)t0, &full_a[sa]);
         if (++sa == SA) sa = 0;
         if (++sb == SB) sb = 0;
       }
@@ -489,7 +524,6 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
         tc_fence_after();
         const uint64_t ad = ad0 + (uint64_t)(sa * (MMQ_A_STAGE >> 4)), bd = bd0 + (uint64_t)(sb * (B_STAGE >> 4));
         if (elect_one()) {
-          if (!(p.debug & 4))
 #pragma unroll
           for (int kk = 0; kk < MMQ_BK / 16; ++kk)  // 16 values = 32 bytes = +2 in the descriptor's 16-byte units
             umma_f16(tmem_base, ad + 2 * kk, bd + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
@@ -499,14 +533,31 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
         if (++sa == SA) { sa = 0; pha ^= 1u; }
         if (++sb == SB) sb = 0;
       }
-      if (ok && elect_one()) umma_commit(accum);
+      // committed in every case: `accum` then completes once every tcgen05.mma this warp issued
+      // has finished, which is what the exit path below waits for after a time-out
+      if (elect_one()) umma_commit(accum);
       __syncwarp();
     }
   }
-  if (!ok && lane == 0) atomicExch(p.status, E_TIMEOUT);
+  if (!ok) {
+    if (lane == 0) atomicExch(p.status, E_TIMEOUT);
+    *gave_up = 1;
+  }
   tc_fence_before();
   __syncthreads();
+  if (*gave_up) {
+    // A bounded wait ran out somewhere in this CTA (the result is invalid and the status word says
+    // so).  Before the tensor memory is released and the CTA retires, everything it started must
+    // have finished: the MMA warp's last commit covers the tensor pipe (bounded wait on `accum`),
+    // and the bulk copies still in flight depend on nothing and land within microseconds, so a
+    // pause far longer than their latency covers them.  Nothing here can wait for ever.
+    if (warp == MMQ_PRODUCER_WARPS + 1) mbar_wait_bounded(accum, 0);
+    drain_pause();
+    tc_fence_before();
+    __syncthreads();
+  }
   if (warp == MMQ_PRODUCER_WARPS) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (!MOE && p.tp_world > 0 && p.ksplit == 1) tp_finish(p.tp_epoch, p.tp_flag, p.tp_world, p.tp_slot, gridDim.x * gridDim.y);
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -558,12 +609,12 @@ int mmq_perm(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_byt
   return 0;
 }
 
-// K slices for a problem of `tiles` output tiles and `nmain` 64-value stages per row: as many as
-// keep every slice at least 16 stages long and the grid within one wave of 148 SMs.
+// K slices for a problem of `tiles` output tiles and `nmain` 64-value stages per row: as many (up
+// to 16) as keep every slice at least 16 stages long and the grid within one wave of 148 SMs.
 static int mmq_pick_split(int tiles, int nmain) {
   static const char* env = getenv("GGUF_B200_MMQ_SPLIT");
   if (env && env[0] == '0') return 1;
-  for (int s = 4; s >= 2; --s)
+  for (int s = 16; s >= 2; --s)
     if ((int64_t)tiles * s <= 148 && nmain / s >= 16) return s;
   return 1;
 }
@@ -591,13 +642,47 @@ __global__ void __launch_bounds__(256) add_partials_kernel(const float4* __restr
   }
 }
 
+// The same sum, stored into every rank's gathered [M][ld] matrix at column col_off (8 outputs =
+// one 16-byte store per rank for 16-bit outputs), followed by the tensor-parallel completion.
+template <typename out_t>
+__global__ void __launch_bounds__(256) add_partials_tp_kernel(const float4* __restrict__ part, int64_t M, int64_t N, int slices,
+                                                              MmqParams p) {
+  const int64_t n8 = N / 8, total = M * n8, n4 = M * N / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / n8, c = (i - m * n8) * 8;
+    float v[8];
+    const int64_t b = (m * N + c) / 4;
+    float4 s0 = part[b], s1 = part[b + 1];
+    for (int z = 1; z < slices; ++z) {
+      const float4 a0 = part[(int64_t)z * n4 + b], a1 = part[(int64_t)z * n4 + b + 1];
+      s0.x += a0.x; s0.y += a0.y; s0.z += a0.z; s0.w += a0.w;
+      s1.x += a1.x; s1.y += a1.y; s1.z += a1.z; s1.w += a1.w;
+    }
+    v[0] = s0.x; v[1] = s0.y; v[2] = s0.z; v[3] = s0.w; v[4] = s1.x; v[5] = s1.y; v[6] = s1.z; v[7] = s1.w;
+    if (sizeof(out_t) == 4) {
+      for (int rk = 0; rk < p.tp_world; ++rk) {
+        float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.tp_y[rk]) + m * p.tp_ld + p.tp_col_off + c);
+        d[0] = s0;
+        d[1] = s1;
+      }
+    } else {
+      out_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = from_float<out_t>(v[j]);
+      for (int rk = 0; rk < p.tp_world; ++rk)
+        *reinterpret_cast<uint4*>(static_cast<out_t*>(p.tp_y[rk]) + m * p.tp_ld + p.tp_col_off + c) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+  tp_finish(p.tp_epoch, p.tp_flag, p.tp_world, p.tp_slot, gridDim.x);
+}
+
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST, bool TWO>
 static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap& map, int64_t b_rows, bool raw_tma, cudaStream_t stream) {
   EncodeTiledFn enc = encode_fn();
   MmqParams pp = p;
   CUtensorMap wmap = map;   // placeholder when unused
   if (raw_tma) {
-    const int64_t map_rows = MOE ? a.N * 256 : a.N;   // expert ids are limited to [0, 255]; boxes only touch experts that are routed to
+    const int64_t map_rows = MOE ? a.N * pp.n_experts : a.N;   // expert ids are limited to [0, n_experts): a box never leaves the caller's buffer
     const cuuint32_t estr[2] = {1, 1};
     const cuuint64_t wd[2] = {(cuuint64_t)(pp.row_bytes / 4), (cuuint64_t)map_rows};
     const cuuint64_t ws[1] = {(cuuint64_t)pp.row_bytes};
@@ -634,6 +719,9 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
       pp.ksplit = (pp.nmain + pp.sps - 1) / pp.sps;
     }
     const bool part = pp.ksplit > 1;
+    if (a.tp && !part) {
+      pp.y_tma = 1;   // tensor-parallel, unsplit: the staged tile is stored to the peers by the CTA itself, no tensor map
+    } else {
     const size_t es = part ? 4 : sizeof(out_t);
     const cuuint32_t estr[3] = {1, 1, 1};
     const cuuint64_t yd[3] = {(cuuint64_t)a.N, (cuuint64_t)a.M, (cuuint64_t)pp.ksplit};
@@ -644,11 +732,15 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
     if (enc(&ymap, ydt, 3, part ? a.part : a.y, yd, ys, yb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
       pp.y_tma = 1;
+    } else if (a.tp) {
+      return E_CUDA;
     } else {
       pp.ksplit = 1;
       pp.sps = pp.nmain;
     }
+    }
   }
+  if (a.tp && !pp.y_tma) return E_BAD_SHAPE;
   auto kern = mmq_kernel<TYPE, ab_t, out_t, TN, MOE, FAST, TWO>;
   static size_t configured[64] = {0};
   int dev = 0;
@@ -660,7 +752,12 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
   dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), (unsigned)pp.ksplit);
   kern<<<grid, mmq_threads(TYPE, FAST, TWO), smem, stream>>>(map, wmap, ymap, pp);
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
-  if (pp.ksplit > 1) {
+  if (pp.ksplit > 1 && a.tp) {
+    const int64_t n8 = a.M * a.N / 8;
+    const int blocks = (int)((n8 + 255) / 256 > 148 * 4 ? 148 * 4 : (n8 + 255) / 256);
+    add_partials_tp_kernel<out_t><<<blocks, 256, 0, stream>>>(static_cast<const float4*>(a.part), a.M, a.N, pp.ksplit, pp);
+    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  } else if (pp.ksplit > 1) {
     const int64_t n4 = a.M * a.N / 4;
     const int blocks = (int)((n4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n4 + 255) / 256);
     add_partials_kernel<out_t><<<blocks, 256, 0, stream>>>(static_cast<const float4*>(a.part), static_cast<out_t*>(a.y), n4, pp.ksplit);
@@ -741,8 +838,21 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
   p.expert_stride_bytes = a.expert_stride_bytes;
   p.rows_out = a.rows_out;
   p.status = a.status;
-  static const char* dbg = getenv("GGUF_B200_MMQ_DEBUG");
-  p.debug = dbg ? atoi(dbg) : 0;
+  if (a.tp) {
+    // the tile leaves through shared memory, in 16-byte pieces: rows and column offsets must allow it
+    if (a.sorted_ids || a.tp->world < 1 || a.tp->world > 8 || a.N % 8 != 0 || a.tp->col_off % 8 != 0 || a.tp->ld % 8 != 0) return E_BAD_SHAPE;
+    p.tp_world = a.tp->world;
+    p.tp_slot = a.tp->slot;
+    p.tp_col_off = a.tp->col_off;
+    p.tp_ld = a.tp->ld;
+    p.tp_epoch = a.tp->epoch;
+    for (int r = 0; r < a.tp->world; ++r) {
+      if (!a.tp->y_peer[r] || !a.tp->flag_peer[r] || (reinterpret_cast<uintptr_t>(a.tp->y_peer[r]) & 15)) return E_BAD_POINTER;
+      p.tp_y[r] = a.tp->y_peer[r];
+      p.tp_flag[r] = a.tp->flag_peer[r];
+    }
+  }
+  p.n_experts = a.n_experts > 0 ? (int)(a.n_experts < 256 ? a.n_experts : 256) : 256;
   const bool bf = a.b_dtype == DT_BF16;
   switch (a.type) {
     case T_Q4_0: return bf ? E_BAD_DTYPE : launch_out<T_Q4_0, __half>(a, p, stream);

@@ -27,15 +27,16 @@ constexpr int64_t kMaxVectors = 8;
 constexpr int64_t kMaxK = 32768;
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
-static __device__ int g_noalloc_status;
 
 struct DevicePtrs {
   void* scratch = nullptr;
   int* status = nullptr;
 };
 
-// Set-up, once per device, with that device current: resolve the device addresses of the two
-// file-scope symbols.  Returns false if the runtime refuses.
+// Set-up, once per device, with that device current: resolve the device address of the
+// file-scope scratch array, and take the library's one status word (the word that
+// gguf_b200_last_status reads), so that a bounded wait that expires in these kernels is reported
+// exactly as for every other entry point.  Returns false if the runtime refuses.
 bool device_ptrs(DevicePtrs& out) {
   static DevicePtrs cache[64];
   int dev = 0;
@@ -43,10 +44,10 @@ bool device_ptrs(DevicePtrs& out) {
   DevicePtrs& c = cache[dev];
   if (!c.scratch) {
     void* s = nullptr;
-    void* st = nullptr;
     if (cudaGetSymbolAddress(&s, g_noalloc_scratch) != cudaSuccess || !s) return false;
-    if (cudaGetSymbolAddress(&st, g_noalloc_status) != cudaSuccess || !st) return false;
-    c.status = static_cast<int*>(st);
+    int* st = status_word_ptr();
+    if (!st) return false;
+    c.status = st;
     c.scratch = s;
   }
   out = c;

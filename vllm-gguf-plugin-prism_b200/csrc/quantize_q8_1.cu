@@ -60,27 +60,13 @@ template <typename in_t, int MODE>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restrict__ x, uint8_t* __restrict__ out,
                                                             int64_t M, int64_t K, int64_t kpad, int sum_mode,
                                                             int64_t ldb, int corr_mode, const int32_t* __restrict__ gather_ids,
-                                                            int64_t gather_div, int64_t gather_limit, Q8Wait wt) {
+                                                            int64_t gather_div, int64_t gather_limit, Q8Tp tp) {
   pdl_trigger();  // the consumer kernel may start its weight prefetch now; it waits for this grid before reading
   pdl_wait();     // the activations (and the scratch we overwrite) belong to earlier kernels
-  if (wt.flag) {
-    // tensor-parallel consumer: the activations derive from a vector that all ranks' GEMV kernels
-    // wrote into this rank's memory; wait (bounded) until every rank has raised its flag for it
-    if (threadIdx.x == 0) {
-      const unsigned want = *wt.epoch * (unsigned)wt.world;
-      const long long t0 = clock64();
-      for (;;) {
-        unsigned v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wt.flag) : "memory");
-        if ((int)(v - want) >= 0) break;
-        if (clock64() - t0 > 2000000000ll) {   // about a second: a rank is missing
-          atomicExch(wt.status, E_TIMEOUT);
-          break;
-        }
-      }
-    }
-    __syncthreads();
-  }
+  // tensor-parallel decode: this launch's number for the GEMV behind it, and the tag of the
+  // gathered vector (written by all ranks' GEMV kernels into this rank's memory) that is added to x
+  if (MODE == Q8_MODE_SOA && tp.bump && blockIdx.x == 0 && threadIdx.x == 0) *tp.bump += 1u;
+  const unsigned add_tag = (MODE == Q8_MODE_SOA && tp.add) ? *tp.add_epoch : 0u;
   const int lane = threadIdx.x & 31;
   const int64_t nbr = kpad / 32;                                   // blocks per row
   const int64_t total = M * nbr;
@@ -97,7 +83,12 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
       have = id >= 0 && id < gather_limit;
       src = have ? id / gather_div : 0;
     }
-    const float xi = (have && k < K) ? to_float<in_t>(x[src * K + k]) : 0.0f;
+    float xi = (x && have && k < K) ? to_float<in_t>(x[src * K + k]) : 0.0f;
+    if (MODE == Q8_MODE_SOA && tp.add && k < K) {   // (one vector: row == 0)
+      float a;
+      if (!packet_read<in_t>(tp.add, k, add_tag, tp.limit_cycles, a)) atomicExch(tp.status, E_TIMEOUT);
+      xi = to_float<in_t>(from_float<in_t>(xi + tp.add_scale * a));   // x' is a vector of the activation type
+    }
     const Q8Lane r = quantize_lane(xi);
     const __half hd = __float2half(r.d), hs = __float2half(r.sum);
     if (MODE == Q8_MODE_REF) {
@@ -244,7 +235,7 @@ __global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restr
 
 template <int MODE>
 static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int sum_mode, int64_t ldb,
-                       int corr_mode, const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream, Q8Wait wt = Q8Wait{}) {
+                       int corr_mode, const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream, Q8Tp wt = Q8Tp{}) {
   if (M <= 0 || K <= 0) return M < 0 || K < 0 ? E_BAD_SHAPE : E_OK;
   const int64_t kpad = round_up(K, 512);
   const int64_t total = M * (kpad / 32);
@@ -292,7 +283,7 @@ static int launch_f16x8(const void* x, int x_dtype, void* out, int64_t M, int64_
 
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream, int perm, const Q8Wait* wait) {
+                         cudaStream_t stream, int perm, const Q8Tp* wait) {
   if (mode == Q8_MODE_F16) {
     // rows of x and of the output start on 16-byte boundaries when K and ldb are multiples of 8
     const bool aligned = K % 8 == 0 && ldb % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
@@ -301,7 +292,7 @@ int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64
   }
   switch (mode) {
     case Q8_MODE_REF: return launch_mode<Q8_MODE_REF>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);
-    case Q8_MODE_SOA: return launch_mode<Q8_MODE_SOA>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream, wait ? *wait : Q8Wait{});
+    case Q8_MODE_SOA: return launch_mode<Q8_MODE_SOA>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream, wait ? *wait : Q8Tp{});
     case Q8_MODE_F16:
       return launch_mode<Q8_MODE_F16>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, gather_ids, gather_div, gather_limit, stream);
   }

@@ -138,6 +138,7 @@ Tensor ggml_moe_a8(Tensor X, Tensor W, Tensor sorted_token_ids, Tensor expert_id
                             static_cast<const int32_t*>(sorted_token_ids.data_ptr()),
                             static_cast<const int32_t*>(expert_ids.data_ptr()),
                             static_cast<const int32_t*>(num_tokens_post_padded.data_ptr()), n_sorted, W.stride(0),
+                            W.size(0) < 256 ? W.size(0) : 256,   // ids beyond 255 are skipped, as in the reference (moe.cuh:33)
                             (int)type, code, tokens, top_k, row, K, current_stream(dev)),
            "ggml_moe_a8");
   return Y;

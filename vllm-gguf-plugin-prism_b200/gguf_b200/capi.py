@@ -16,6 +16,7 @@ _lib = None
 
 F32, F16, BF16 = 0, 1, 2
 OP_GEMV, OP_MMQ, OP_MOE, OP_MOE_VEC, OP_DEQUANT_MATMUL = range(5)
+_F = ctypes.c_float
 _DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 # name -> (restype, argtypes); mirrors include/gguf_b200.h one to one
@@ -34,11 +35,14 @@ SIGNATURES = {
     "gguf_b200_gemv_prepared": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_dequant_matmul": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
-    "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
+    "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_moe_a8_vec": (_I, [_P, _P, _P, _P, _L, _P, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_vec_a8_noalloc": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
-    "gguf_b200_mul_mat_vec_a8_tp": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
+    "gguf_b200_mul_mat_vec_a8_tp": (_I, [_P, _P, _P, _P, _I, _I, _F, _L, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
+    "gguf_b200_tp_unpack": (_I, [_P, _P, _I, _I, _L, _L, _P, _L, _I, _P]),
+    "gguf_b200_matmul_tp": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _L, _I, _I, _L, _L, _L, _I, _I, _P]),
     "gguf_b200_tp_wait": (_I, [_P, _P, _I, _I, _P]),
+    "gguf_b200_set_wait_limit_cycles": (None, [_L]),
     "gguf_b200_noalloc_scratch_bytes": (_L, []),
     "gguf_b200_moe_block_size": (_I, [_I]),
     "gguf_b200_last_status": (_I, []),
@@ -143,7 +147,7 @@ def moe_a8(X, W, sorted_ids, expert_ids, n_post_pad, qtype, N, top_k, tokens):
     nbytes = lib().gguf_b200_workspace_bytes(OP_MOE, qtype, n_sorted, N, K)
     ws = _ws(X, nbytes)
     _check(lib().gguf_b200_moe_a8(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), nbytes, sorted_ids.data_ptr(),
-                                  expert_ids.data_ptr(), n_post_pad.data_ptr(), n_sorted, W.stride(0), qtype,
+                                  expert_ids.data_ptr(), n_post_pad.data_ptr(), n_sorted, W.stride(0), W.shape[0], qtype,
                                   _DT[X.dtype], tokens, top_k, N, K, _stream(X)), "moe_a8")
     return Y
 
@@ -169,27 +173,62 @@ def mul_mat_vec_a8_noalloc(W, X, qtype, N):
     return Y
 
 
-def mul_mat_vec_a8_tp(W_local, X, y_ptrs, flag_ptrs, epochs_local, slot, qtype, rank, wait_slot=-1):
-    """Rank `rank`'s rows of the GEMV, written into every rank's output vector (y_ptrs: device
-    addresses of the full vectors, one per rank); then epochs_local[slot] += 1 and
-    flag_ptrs[r][slot] += 1 on every rank.  wait_slot >= 0: the quantizer first waits for that
-    slot's gather (X derives from it)."""
-    world = len(y_ptrs)
-    K = X.shape[1]
+def _ptr_array(ptrs):
+    arr = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr, ctypes.cast(arr, ctypes.c_void_p)
+
+
+def mul_mat_vec_a8_tp(W_local, X, packet_ptrs, epochs_local, slot, slot_packets, qtype, rank, add_slot=-1,
+                      add_scale=0.0, dtype=None):
+    """Rank `rank`'s rows of a decode GEMV, sent as tagged packets into every rank's packet arena
+    (packet_ptrs: device addresses of the arenas, one per rank, mapped into this process).
+    Activations x' = X + add_scale * gathered[add_slot] (X may be None when add_slot >= 0)."""
+    world = len(packet_ptrs)
     n_local = W_local.shape[0]
+    K = k_of(W_local, qtype)
+    dt = X.dtype if X is not None else dtype
     nbytes = lib().gguf_b200_workspace_bytes(OP_GEMV, qtype, 1, n_local, K)
+    ws = _ws(W_local, nbytes)
+    keep, pa = _ptr_array(packet_ptrs)
+    _check(lib().gguf_b200_mul_mat_vec_a8_tp(W_local.data_ptr(), X.data_ptr() if X is not None else None, pa,
+                                             epochs_local.data_ptr(), int(slot), int(add_slot), float(add_scale),
+                                             int(slot_packets), ws.data_ptr(), nbytes, qtype, _DT[dt], n_local, K,
+                                             int(rank), world, _stream(W_local)), "mul_mat_vec_a8_tp")
+
+
+def tp_unpack(packets_local: torch.Tensor, epochs_local: torch.Tensor, slot0: int, nslots: int, slot_packets: int, n: int,
+              dtype=torch.float16, out=None) -> torch.Tensor:
+    """Plain [nslots, n] tensor of the gathered vectors of slots slot0 .. slot0+nslots-1."""
+    if out is None:
+        out = torch.empty((nslots, n), dtype=dtype, device=packets_local.device)
+    _check(lib().gguf_b200_tp_unpack(packets_local.data_ptr(), epochs_local.data_ptr(), int(slot0), int(nslots),
+                                     int(slot_packets), int(n), out.data_ptr(), out.stride(0), _DT[out.dtype],
+                                     _stream(packets_local)), "tp_unpack")
+    return out
+
+
+def matmul_tp(op, W_local, X, y_ptrs, flag_ptrs, epochs_local, slot, qtype, rank):
+    """Rank `rank`'s column block of a prefill GEMM (op = OP_MMQ or OP_DEQUANT_MATMUL), stored into
+    every rank's gathered [M, world * N_local] output (y_ptrs); raises flag_ptrs[r][slot] on all ranks."""
+    world = len(y_ptrs)
+    M, K = X.shape
+    n_local = W_local.shape[0]
+    nbytes = lib().gguf_b200_workspace_bytes(op, qtype, M, n_local, K)
     ws = _ws(X, nbytes)
-    ya = (ctypes.c_void_p * world)(*[int(p) for p in y_ptrs])
-    fa = (ctypes.c_void_p * world)(*[int(p) for p in flag_ptrs])
-    _check(lib().gguf_b200_mul_mat_vec_a8_tp(W_local.data_ptr(), X.data_ptr(), ctypes.cast(ya, ctypes.c_void_p),
-                                             ctypes.cast(fa, ctypes.c_void_p), epochs_local.data_ptr(), int(slot),
-                                             int(wait_slot), ws.data_ptr(), nbytes, qtype, _DT[X.dtype], n_local, K,
-                                             int(rank), world, _stream(X)), "mul_mat_vec_a8_tp")
+    k1, ya = _ptr_array(y_ptrs)
+    k2, fa = _ptr_array(flag_ptrs)
+    _check(lib().gguf_b200_matmul_tp(int(op), W_local.data_ptr(), X.data_ptr(), ya, fa, epochs_local.data_ptr(), int(slot),
+                                     ws.data_ptr(), nbytes, qtype, _DT[X.dtype], M, n_local, K, int(rank), world,
+                                     _stream(X)), "matmul_tp")
 
 
 def tp_wait(flags_local: torch.Tensor, epochs_local: torch.Tensor, slot: int, world: int):
     _check(lib().gguf_b200_tp_wait(flags_local.data_ptr(), epochs_local.data_ptr(), int(slot), int(world),
                                    _stream(flags_local)), "tp_wait")
+
+
+def set_wait_limit_cycles(cycles: int) -> None:
+    lib().gguf_b200_set_wait_limit_cycles(int(cycles))
 
 
 def last_status() -> int:

@@ -11,9 +11,10 @@ kernel and the slices are all-gathered along the output dimension over ``torch.d
 Rows are independent, so the sharded result equals the single-GPU result bit for bit.
 
 For decode (one activation vector) :class:`FusedGatherGemv` removes the separate collective: the
-GEMV kernel stores its slice straight into every rank's output vector over NVLink (peer-mapped
-symmetric memory) and raises a per-call flag; a one-thread kernel on each rank waits for the
-flags of all ranks.  No NCCL call sits on that path.
+GEMV kernel sends every output element, as one tagged packet, straight into every rank's memory
+over NVLink (peer-mapped symmetric memory); the next GEMV's quantizer reads the packets.  For
+prefill :class:`FusedGatherMatmul` does the same with the tensor-core kernel's output tiles and a
+per-call flag.  No NCCL call sits on either path.
 """
 from __future__ import annotations
 
@@ -73,21 +74,65 @@ class ColumnParallelGGUFLinear:
         return gather_columns(y, self.group) if self.world > 1 else y
 
 
+def _symmetric_arena(nbytes: int, device, group):
+    """A zeroed uint8 buffer of `nbytes` that every rank of `group` maps; returns (tensor, [base pointers])."""
+    import torch.distributed._symmetric_memory as symm_mem
+
+    arena = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+    arena.zero_()
+    handle = symm_mem.rendezvous(arena, group)
+    ptrs = [int(p) for p in handle.buffer_ptrs]
+    torch.cuda.synchronize(device)
+    dist.barrier(group)  # every rank's buffer is zero before anyone writes into it
+    return arena, handle, ptrs
+
+
 class FusedGatherGemv:
     """Decode GEMVs of one tensor-parallel group whose outputs land in every rank's memory.
 
-    ``slots`` output vectors of ``n_total`` elements live in one symmetric-memory arena that all
-    ranks map; ``__call__(slot, w_local, x, qtype)`` runs this rank's rows of the product and
-    returns the full ``[1, n_total]`` vector of that slot once all ranks' slices have arrived
-    (stream-ordered: the wait is a kernel on the current stream, or rides in the next call's quantizer).  All ranks must make the same
-    sequence of calls.  Needs CUDA peer access between the ranks' GPUs.
+    Each of ``slots`` call slots holds one gathered vector of up to ``n_total`` elements as tagged
+    packets (see ``gguf_b200_mul_mat_vec_a8_tp``) in a symmetric-memory arena that all ranks map.
+    ``__call__(slot, w_local, x, qtype, add_slot, add_scale)`` runs this rank's rows of the product
+    and sends them to all ranks; the activations may include the vector gathered in another slot
+    (``x + add_scale * gathered[add_slot]``), which the call's own quantizer waits for -- a chain of
+    dependent GEMVs then contains no collective and no wait kernel.  ``gathered(slot)`` returns plain
+    vectors for any other consumer.  All ranks must make the same sequence of calls; needs CUDA
+    peer access between the ranks' GPUs.
     """
 
-    FLAG_BYTES = 4096  # 1024 uint32 flags at the head of the arena
-
     def __init__(self, n_total: int, slots: int, dtype: torch.dtype, device: torch.device, group=None):
-        import torch.distributed._symmetric_memory as symm_mem
+        from . import capi
 
+        self.capi = capi
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.n_total, self.slots, self.dtype = int(n_total), int(slots), dtype
+        self.packet_bytes = 8 if dtype == torch.float32 else 4
+        self.slot_packets = (self.n_total + 63) // 64 * 64
+        self.arena, self.handle, self.base_ptrs = _symmetric_arena(self.slots * self.slot_packets * self.packet_bytes,
+                                                                   device, self.group)
+        self.epochs = torch.zeros(self.slots, dtype=torch.int32, device=device)
+
+    def __call__(self, slot: int, w_local: torch.Tensor, x: torch.Tensor | None, qtype: int, add_slot: int = -1,
+                 add_scale: float = 0.0) -> None:
+        self.capi.mul_mat_vec_a8_tp(w_local, x, self.base_ptrs, self.epochs, slot, self.slot_packets, qtype, self.rank,
+                                    add_slot, add_scale, dtype=self.dtype)
+
+    def gathered(self, slot0: int, nslots: int = 1, n: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Plain ``[nslots, n]`` tensor of the vectors gathered in slots slot0.. (waits for all ranks' packets)."""
+        return self.capi.tp_unpack(self.arena, self.epochs, slot0, nslots, self.slot_packets,
+                                   self.n_total if n is None else n, self.dtype, out=out)
+
+
+class FusedGatherMatmul:
+    """Prefill GEMMs of one tensor-parallel group: every rank's tensor-core kernel stores its
+    column block of the ``[m, n_total]`` result into all ranks' output matrices (symmetric memory)
+    and raises a per-call flag; ``wait`` queues the one-thread kernel that waits for all ranks."""
+
+    FLAG_BYTES = 4096
+
+    def __init__(self, m: int, n_total: int, slots: int, dtype: torch.dtype, device: torch.device, group=None):
         from . import capi
 
         self.capi = capi
@@ -96,34 +141,29 @@ class FusedGatherGemv:
         self.world = dist.get_world_size(self.group)
         if slots > 1024:
             raise ValueError("at most 1024 call slots")
-        self.n_total, self.slots, self.dtype = int(n_total), int(slots), dtype
+        self.m, self.n_total, self.slots, self.dtype = int(m), int(n_total), int(slots), dtype
         esz = torch.empty((), dtype=dtype).element_size()
-        self.row_bytes = (self.n_total * esz + 255) // 256 * 256
-        nbytes = self.FLAG_BYTES + self.slots * self.row_bytes
-        self.arena = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        self.arena.zero_()
-        self.handle = symm_mem.rendezvous(self.arena, self.group)
-        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.slot_bytes = (self.m * self.n_total * esz + 255) // 256 * 256
+        self.arena, self.handle, self.base_ptrs = _symmetric_arena(self.FLAG_BYTES + self.slots * self.slot_bytes, device,
+                                                                   self.group)
         self.flags = self.arena[: self.FLAG_BYTES].view(torch.int32)
         self.epochs = torch.zeros(1024, dtype=torch.int32, device=device)
-        torch.cuda.synchronize(device)
-        dist.barrier(self.group)  # every rank's flags are zero before anyone raises one
 
-    def out(self, slot: int) -> torch.Tensor:
-        o = self.FLAG_BYTES + slot * self.row_bytes
-        return self.arena[o: o + self.row_bytes].view(self.dtype)[: self.n_total].view(1, self.n_total)
+    def out(self, slot: int, m: int | None = None, n_total: int | None = None) -> torch.Tensor:
+        m = self.m if m is None else m
+        n_total = self.n_total if n_total is None else n_total
+        o = self.FLAG_BYTES + slot * self.slot_bytes
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        return self.arena[o: o + m * n_total * esz].view(self.dtype).view(m, n_total)
 
-    def __call__(self, slot: int, w_local: torch.Tensor, x: torch.Tensor, qtype: int, wait_slot: int = -1,
-                 wait: bool = True) -> torch.Tensor:
-        """``wait_slot``: slot whose gathered vector ``x`` was computed from (the quantizer waits for
-        it, no separate kernel).  ``wait=False`` leaves the gather of ``slot`` to a later call's
-        ``wait_slot`` or to :meth:`wait`."""
-        off = self.FLAG_BYTES + slot * self.row_bytes
-        self.capi.mul_mat_vec_a8_tp(w_local, x, [b + off for b in self.base_ptrs], self.base_ptrs, self.epochs, slot, qtype,
-                                    self.rank, wait_slot)
+    def __call__(self, slot: int, op: int, w_local: torch.Tensor, x: torch.Tensor, qtype: int, wait: bool = True) -> torch.Tensor:
+        n_total = w_local.shape[0] * self.world
+        off = self.FLAG_BYTES + slot * self.slot_bytes
+        self.capi.matmul_tp(op, w_local, x, [b + off for b in self.base_ptrs], self.base_ptrs, self.epochs, slot, qtype,
+                            self.rank)
         if wait:
             self.wait(slot)
-        return self.out(slot)
+        return self.out(slot, x.shape[0], n_total)
 
     def wait(self, slot: int) -> None:
         self.capi.tp_wait(self.flags, self.epochs, slot, self.world)
