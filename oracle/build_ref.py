@@ -24,7 +24,13 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-REF = Path(os.environ.get("GGUF_REFERENCE_ROOT", "/root/reference"))
+
+def _ref_root():
+    sys.path.insert(0, str(HERE.parent))
+    from oracle import reference_root
+
+    return reference_root()
+
 
 
 def _torch_paths():
@@ -36,9 +42,10 @@ def _torch_paths():
 
 def build(force: bool = False) -> Path | None:
     so = OUT / "_C_gguf_ref.so"
-    csrc = REF / "vllm_gguf_plugin" / "csrc"
-    if not csrc.exists():
+    ref = _ref_root()
+    if ref is None:
         return so if so.exists() else None
+    csrc = ref / "vllm_gguf_plugin" / "csrc"
     srcs = [csrc / "torch_bindings.cpp", csrc / "gguf" / "gguf_kernel.cu", HERE / "ref_harness.cu"]
     hdrs = list((csrc / "gguf").glob("*")) + [Path(__file__)]
     if so.exists() and not force:

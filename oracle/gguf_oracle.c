@@ -33,7 +33,8 @@
 #define QK 32
 #define QK_K 256
 
-enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_XS = 23 };
+enum { T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14,
+       T_IQ2_XXS = 16, T_IQ4_NL = 20, T_IQ4_XS = 23 };
 enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 
 /* ------------------------------------------------------------------ */
@@ -123,6 +124,9 @@ static uint16_t hfms(uint16_t a, uint16_t b, uint16_t c) { /* a*b - c with a sin
   return s2h(v);
 }
 static uint16_t i2h(int v) { return s2h((i128)v << 48); } /* __int2half_rn */
+static uint16_t hneg(uint16_t a) { return (uint16_t)(a ^ 0x8000); }
+static uint16_t hadd(uint16_t a, uint16_t b) { return hsub(a, hneg(b)); }
+static uint16_t hfma(uint16_t a, uint16_t b, uint16_t c) { return hfms(a, b, hneg(c)); } /* a*b + c, one rounding */
 
 static uint16_t f2h(float f) { /* __float2half_rn */
   uint32_t u;
@@ -192,10 +196,23 @@ int oracle_type_size(int type) {
     case T_Q6_K: return 210;
     case T_IQ2_XXS: return 66;
     case T_IQ4_XS: return 136;
+    /* dequantize only (no matmul restatement for these yet) */
+    case T_Q4_1: return 20;
+    case T_Q5_0: return 22;
+    case T_Q5_1: return 24;
+    case T_Q2_K: return 84;
+    case T_Q3_K: return 110;
+    case T_Q5_K: return 176;
+    case T_IQ4_NL: return 18;
   }
   return 0;
 }
-int oracle_block_size(int type) { return (type == T_Q4_0 || type == T_Q8_0) ? QK : (oracle_type_size(type) ? QK_K : 0); }
+int oracle_block_size(int type) {
+  switch (type) {
+    case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL: return QK;
+  }
+  return oracle_type_size(type) ? QK_K : 0;
+}
 
 /* 6-bit (scale, min) pair j of a Q4_K super-block: get_scale_min_k4, dequantize.cuh:156-163 */
 static void scale_min_k4(int j, const uint8_t* q, int* sc, int* m) {
@@ -304,6 +321,98 @@ int oracle_dequantize(const uint8_t* w, int type, void* out, int out_dt, int64_t
               store_f(out, out_dt, o + 32 * ib + 8 * il + j, v);
             }
           }
+        }
+      } break;
+      case T_Q4_1: { /* dequantize_q4_1, dequantize.cuh:17-31: v = q*d + m (contract: one fused multiply-add) */
+        uint16_t d = rd16(blk), m = rd16(blk + 2);
+        for (int j = 0; j < 16; ++j) {
+          int q = blk[4 + j];
+          store_h(out, out_dt, o + j, q4k_contract ? hfma(i2h(q & 0xF), d, m) : hadd(hmul(i2h(q & 0xF), d), m));
+          store_h(out, out_dt, o + j + 16, q4k_contract ? hfma(i2h(q >> 4), d, m) : hadd(hmul(i2h(q >> 4), d), m));
+        }
+      } break;
+      case T_Q5_0:   /* dequantize_q5_0, dequantize.cuh:33-50: (q - 16) * d */
+      case T_Q5_1: { /* dequantize_q5_1, dequantize.cuh:52-69: q * d + m */
+        const int one = type == T_Q5_1;
+        uint16_t d = rd16(blk), m = one ? rd16(blk + 2) : 0;
+        const uint8_t* qhp = blk + (one ? 4 : 2);
+        const uint8_t* qs = blk + (one ? 8 : 6);
+        uint32_t qh = (uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24);
+        for (int j = 0; j < 16; ++j) {
+          int x0 = (qs[j] & 0xF) | (((qh >> j) << 4) & 0x10);
+          int x1 = (qs[j] >> 4) | ((qh >> (j + 12)) & 0x10);
+          uint16_t v0, v1;
+          if (one) {
+            v0 = q4k_contract ? hfma(i2h(x0), d, m) : hadd(hmul(i2h(x0), d), m);
+            v1 = q4k_contract ? hfma(i2h(x1), d, m) : hadd(hmul(i2h(x1), d), m);
+          } else {
+            v0 = hmul(hsub(i2h(x0), i2h(16)), d);
+            v1 = hmul(hsub(i2h(x1), i2h(16)), d);
+          }
+          store_h(out, out_dt, o + j, v0);
+          store_h(out, out_dt, o + j + 16, v1);
+        }
+      } break;
+      case T_Q2_K: { /* dequantize_block_q2_K, dequantize.cuh:101-120: dall*(sc&15)*q - dmin*(sc>>4) */
+        const uint8_t *scales = blk, *qs = blk + 16;
+        uint16_t dall = rd16(blk + 80), dmin = rd16(blk + 82);
+        for (int n = 0; n < 2; ++n)
+          for (int l = 0; l < 32; ++l) {
+            int is = 8 * n + l / 16;
+            int q = qs[32 * n + l];
+            for (int k = 0; k < 4; ++k) {
+              int sc = scales[is + 2 * k];
+              uint16_t a = i2h((sc & 0xF) * ((q >> (2 * k)) & 3)), mm = hmul(dmin, i2h(sc >> 4));
+              /* contraction: the subtraction fuses with the FIRST product (a*dall - mm in one rounding) */
+              uint16_t v = q4k_contract ? hfms(dall, a, mm) : hsub(hmul(dall, a), mm);
+              store_h(out, out_dt, o + 128 * n + l + 32 * k, v);
+            }
+          }
+      } break;
+      case T_Q3_K: { /* dequantize_block_q3_K, dequantize.cuh:122-154 */
+        const uint8_t *hm = blk, *qs = blk + 32, *sc = blk + 96;
+        uint16_t d_all = rd16(blk + 108);
+        for (int n = 0; n < 2; ++n)
+          for (int j = 0; j < 4; ++j)
+            for (int is0 = 0; is0 < 2; ++is0) {
+              int is = 8 * n + 2 * j + is0, us;
+              if (is < 4) us = (sc[is] & 0xF) | (((sc[is + 8] >> 0) & 3) << 4);
+              else if (is < 8) us = (sc[is] & 0xF) | (((sc[is + 4] >> 2) & 3) << 4);
+              else if (is < 12) us = (sc[is - 8] >> 4) | (((sc[is] >> 4) & 3) << 4);
+              else us = (sc[is - 8] >> 4) | (((sc[is - 4] >> 6) & 3) << 4);
+              uint16_t dl = hmul(d_all, i2h((int8_t)us - 32));
+              int m = 1 << (4 * n + j);
+              for (int l = 16 * is0; l < 16 * is0 + 16; ++l) {
+                int v = (int8_t)((qs[32 * n + l] >> (2 * j)) & 3) - ((hm[l] & m) ? 0 : 4);
+                store_h(out, out_dt, o + 128 * n + 32 * j + l, hmul(dl, i2h(v)));
+              }
+            }
+      } break;
+      case T_Q5_K: { /* dequantize_block_q5_K, dequantize.cuh:198-230 */
+        uint16_t dall = rd16(blk), dmin = rd16(blk + 2);
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        for (int il = 0; il < 4; ++il) {
+          int sc, m;
+          scale_min_k4(2 * il, scales, &sc, &m);
+          uint16_t d1 = hmul(dall, i2h(sc)), m1 = hmul(dmin, i2h(m));
+          scale_min_k4(2 * il + 1, scales, &sc, &m);
+          uint16_t d2 = hmul(dall, i2h(sc)), m2 = hmul(dmin, i2h(m));
+          for (int l = 0; l < 32; ++l) {
+            int lo = (qs[32 * il + l] & 0xF) + ((qh[l] & (1 << (2 * il))) ? 16 : 0);
+            int hi = (qs[32 * il + l] >> 4) + ((qh[l] & (2 << (2 * il))) ? 16 : 0);
+            store_h(out, out_dt, o + 64 * il + l, q4k_contract ? hfms(d1, i2h(lo), m1) : hsub(hmul(d1, i2h(lo)), m1));
+            store_h(out, out_dt, o + 64 * il + 32 + l, q4k_contract ? hfms(d2, i2h(hi), m2) : hsub(hmul(d2, i2h(hi)), m2));
+          }
+        }
+      } break;
+      case T_IQ4_NL: { /* dequantize_block_iq4_nl, dequantize.cuh:400-418 (fp32 math) */
+        float df = h2f(rd16(blk));
+        for (int j = 0; j < 16; ++j) {
+          int q = blk[2 + j];
+          volatile float lo = df * (float)gguf_b200_kvalues_iq4nl[q & 0xf];
+          volatile float hi = df * (float)gguf_b200_kvalues_iq4nl[q >> 4];
+          store_f(out, out_dt, o + j, lo);
+          store_f(out, out_dt, o + j + 16, hi);
         }
       } break;
       case T_IQ4_XS: { /* dequantize_block_iq4_xs, dequantize.cuh:420-435 (fp32 math) */

@@ -50,8 +50,11 @@ def gguf_py_fixture():
     print("wrote golden_gguf_py.npz")
 
 
-def routing_fixture(ref_root=Path(os.environ.get("GGUF_REFERENCE_ROOT", "/root/reference"))):
-    if not (ref_root / "vllm_gguf_plugin").exists():
+def routing_fixture(ref_root=None):
+    from oracle import reference_root
+
+    ref_root = ref_root or reference_root()
+    if ref_root is None:
         print("reference checkout absent: golden_routing.json not regenerated")
         return
     import torch

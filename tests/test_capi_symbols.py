@@ -33,7 +33,8 @@ def test_geometry_and_error_codes(native_libs):
     sizes = {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210), 16: (256, 66), 23: (256, 136)}
     for t, (bs, ts) in sizes.items():
         assert lib.gguf_b200_block_size(t) == bs and lib.gguf_b200_type_size(t) == ts
-    assert lib.gguf_b200_type_size(3) == 0
+    assert lib.gguf_b200_type_size(3) == 20 and lib.gguf_b200_block_size(13) == 256     # dequantize-only types
+    assert lib.gguf_b200_type_size(9) == 0 and lib.gguf_b200_block_size(9) == 0
     assert lib.gguf_b200_q8_1_row_bytes(1024) == 1024 // 32 * 36
     assert lib.gguf_b200_q8_1_row_bytes(800) == 1024 // 32 * 36
     assert lib.gguf_b200_moe_block_size(2) == 64 and lib.gguf_b200_moe_block_size(16) == 0

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import MMQ_TYPES, REL_L2_TOL, TYPES, RefCuda, bits, np_act, rel_l2
+from helpers import DEQUANT_ONLY_TYPES, MMQ_TYPES, REL_L2_TOL, TYPES, RefCuda, bits, np_act, rel_l2
 
 from gguf_b200 import capi, synth
 from oracle import cpu
@@ -76,6 +76,39 @@ def test_dequantize_bit_exact(ref, name, dtype):
     if ref.available:
         r = ref.ops.ggml_dequantize(w, t, N, K, dtype)
         assert torch.equal(bits(got), bits(r)), "differs from the reference kernel"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("name", DEQUANT_ONLY_TYPES)
+def test_dequantize_more_types_bit_exact(ref, name, dtype):
+    """Block types that so far only the standalone dequantize serves."""
+    t = DEQUANT_ONLY_TYPES[name]
+    N, K = 40, 2048
+    wn, w = dev_w(t, N, K, seed=t)
+    got = capi.dequantize(w, t, N, K, dtype)
+    torch.cuda.synchronize()
+    dn = str(dtype).split(".")[1]
+    want = cpu.dequantize(wn, t, N * K, dn)
+    want_t = torch.from_numpy(want.view(np.int32) if dn == "float32" else want.view(np.int16)).reshape(N, K)
+    assert torch.equal(bits(got).cpu(), want_t), "differs from the CPU oracle"
+    if ref.available:
+        r = ref.ops.ggml_dequantize(w, t, N, K, dtype)
+        assert torch.equal(bits(got), bits(r)), "differs from the reference kernel"
+
+
+def test_dequantize_full_matrices_bit_exact_on_device(ref):
+    """One full benchmark matrix per type, compared on the device with the reference kernel."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    for name, (N, K) in {"Q4_K": (14336, 4096), "Q6_K": (37888, 3584), "IQ4_XS": (37888, 3584), "IQ2_XXS": (28672, 8192),
+                         "Q8_0": (3072, 1024), "Q4_0": (2048, 2048)}.items():
+        t = TYPES[name]
+        w = torch.from_numpy(synth.make_weight(t, N, K, seed=7)).to(DEV)
+        got = capi.dequantize(w, t, N, K, torch.float16)
+        want = ref.ops.ggml_dequantize(w, t, N, K, torch.float16)
+        assert torch.equal(bits(got), bits(want)), name
+        del w, got, want
+        torch.cuda.empty_cache()
 
 
 def test_dequantize_ragged_counts(ref):
@@ -361,7 +394,7 @@ def test_tp_gemv_packets_one_gpu(name, dtype):
     arena gives the unsharded GEMV bit for bit.  A second call whose activations are
     x + s * (vector gathered by the first) reads the packets in its own quantizer."""
     t = TYPES[name]
-    N, K, world = 1024, 2048, 2
+    N, K, world = 2048, 1024, 2
     wn, w = dev_w(t, N, K, seed=5)
     x = dev_x(1, K, seed=5, dtype=dtype)
     want = capi.mul_mat_vec_a8(w, x, t, N)

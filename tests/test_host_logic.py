@@ -103,3 +103,85 @@ def test_linear_method_mixed_type_shards_call_per_shard(recorded_ops):
     calls.clear()
     y = m.apply(layer, torch.zeros(9, 256, dtype=torch.float16))
     assert calls == ["ggml_mul_mat_a8", "ggml_mul_mat_a8"] and tuple(y.shape) == (9, 16)
+
+
+def _strict_set_weight_attrs(weight, attrs):
+    """vLLM's set_weight_attrs: refuses to overwrite an attribute that is already there."""
+    for k, v in (attrs or {}).items():
+        assert not hasattr(weight, k), f"Overwriting existing tensor attribute: {k}"
+        setattr(weight, k, v)
+
+
+def test_create_weights_accepts_vllm_weight_loader_extra(recorded_ops, monkeypatch):
+    """vLLM's LinearBase / FusedMoE always pass `weight_loader` among the extras and its
+    set_weight_attrs asserts on overwrite: both create_weights must pop it first."""
+    _, linear = recorded_ops
+    from vllm_gguf_plugin.quantization import fused_moe
+
+    monkeypatch.setattr(linear, "set_weight_attrs", _strict_set_weight_attrs)
+    monkeypatch.setattr(fused_moe, "set_weight_attrs", _strict_set_weight_attrs)
+    theirs = lambda *a, **k: None
+    layer = torch.nn.Module()
+    linear.GGUFLinearMethod(None).create_weights(layer, 256, [16], 256, 16, torch.float16, weight_loader=theirs)
+    assert layer.weight.fallback_weight_loader is theirs and layer.weight.weight_loader is not theirs
+    moe = torch.nn.Module()
+    fused_moe.GGUFMoEMethod(None).create_weights(moe, 4, 256, 128, torch.float16, weight_loader=theirs)
+    assert moe.w13_weight.base_weight_loader is theirs and callable(moe.w2_weight.weight_loader)
+
+
+@pytest.mark.parametrize("rank", [0, 1])
+def test_linear_loader_slices_for_tensor_parallel_ranks(recorded_ops, monkeypatch, rank):
+    """Column-parallel layers keep rows [r*N/g, ...) (reference params.py:227-236), row-parallel
+    layers keep whole blocks [r*bytes/g, ...) of every row (params.py:259-264)."""
+    _, linear = recorded_ops
+    monkeypatch.setattr(linear, "tensor_parallel_rank_and_size", lambda: (rank, 2))
+    full = torch.arange(16 * 288, dtype=torch.int64).remainder(251).to(torch.uint8).reshape(16, 288)   # 2 Q4_K blocks per row
+    m = linear.GGUFLinearMethod(None)
+    col = torch.nn.Module()
+    m.create_weights(col, 512, [8], 512, 16, torch.float16)          # 8 of 16 output rows per rank
+    col.weight.weight_loader(col.weight, full)
+    col.weight_type.weight_loader(col.weight_type, torch.tensor(12))
+    m.process_weights_after_loading(col)
+    assert torch.equal(col.weight.data, full[rank * 8:(rank + 1) * 8])
+    row = torch.nn.Module()
+    m.create_weights(row, 256, [16], 512, 16, torch.float16)         # 256 of 512 input values per rank
+    row.weight.weight_loader(row.weight, full)
+    m.process_weights_after_loading(row)
+    assert torch.equal(row.weight.data, full[:, rank * 144:(rank + 1) * 144])
+    merged = torch.nn.Module()
+    m.create_weights(merged, 512, [4, 4], 512, 16, torch.float16)    # gate / up, each 8 rows in the file
+    for sid in (0, 1):
+        merged.weight.weight_loader(merged.weight, full[sid * 8:(sid + 1) * 8], sid)
+        merged.weight_type.weight_loader(merged.weight_type, torch.tensor(12), sid)
+    m.process_weights_after_loading(merged)
+    want = torch.cat([full[rank * 4:rank * 4 + 4], full[8 + rank * 4:8 + rank * 4 + 4]])
+    assert torch.equal(merged.weight.data, want)
+
+
+@pytest.mark.parametrize("size", [1, 2])
+def test_moe_loader_honours_expert_and_shard_ids(recorded_ops, monkeypatch, size):
+    _, linear = recorded_ops
+    from vllm_gguf_plugin.quantization import fused_moe
+
+    rank = size - 1
+    monkeypatch.setattr(linear, "tensor_parallel_rank_and_size", lambda: (rank, size))
+    E, I, H = 3, 8, 64                          # Q4_0: 18 bytes per 32 values -> rows of 36 (w13) / 18*I/32.. bytes
+    w1 = torch.randint(0, 255, (E, I, 36), dtype=torch.uint8)
+    w3 = torch.randint(0, 255, (E, I, 36), dtype=torch.uint8)
+    w2 = torch.randint(0, 255, (E, H, 72), dtype=torch.uint8)
+    layer = torch.nn.Module()
+    meth = fused_moe.GGUFMoEMethod(None)
+    meth.create_weights(layer, E, H, I // size, torch.float16, weight_loader=lambda *a, **k: None)
+    # stacked tensors for w1 / w3, one expert at a time for w2
+    layer.w13_weight.weight_loader(layer.w13_weight, w1, "experts.gate", shard_id="w1", expert_id=0)
+    layer.w13_weight.weight_loader(layer.w13_weight, w3, "experts.up", shard_id="w3", expert_id=0)
+    for e in range(E):
+        assert layer.w2_weight.weight_loader(layer.w2_weight, w2[e], "experts.down", shard_id="w2", expert_id=e, return_success=True)
+    n = I // size
+    assert tuple(layer.w13_weight.shape) == (E, 2 * n, 36)
+    assert torch.equal(layer.w13_weight.data[:, :n], w1[:, rank * n:(rank + 1) * n])
+    assert torch.equal(layer.w13_weight.data[:, n:], w3[:, rank * n:(rank + 1) * n])
+    b = 72 // size
+    assert torch.equal(layer.w2_weight.data, w2[:, :, rank * b:(rank + 1) * b])
+    layer.w13_weight_type.weight_loader(layer.w13_weight_type, torch.tensor(2), "x", shard_id="w1", expert_id=0)
+    assert layer.w13_weight_type.weight_type == 2

@@ -112,9 +112,11 @@ def test_moe_oracle_equals_per_slot_matmul():
 
 
 def test_iq_tables_match_reference_header_when_present():
-    hdr = Path(os.environ.get("GGUF_REFERENCE_ROOT", "/root/reference")) / "vllm_gguf_plugin/csrc/gguf/ggml-common.h"
-    if not hdr.exists():
+    from oracle import reference_root
+
+    if reference_root() is None:
         pytest.skip("reference checkout absent")
+    hdr = reference_root() / "vllm_gguf_plugin/csrc/gguf/ggml-common.h"
     import sys
 
     sys.path.insert(0, str(ROOT / "include"))

@@ -85,10 +85,15 @@ def _worker(rank, world, port, out_dir):
         torch.cuda.synchronize()
         dist.barrier()
         (Path(out_dir) / f"ok{rank}").write_text("ok")
-    finally:
-        torch.cuda.synchronize()
-        dist.barrier()
         dist.destroy_process_group()
+    except BaseException:
+        # leave at once, idle (every wait of the kernels is bounded), without a collective that
+        # the other ranks may never join
+        import traceback
+
+        traceback.print_exc()
+        torch.cuda.synchronize()
+        os._exit(1)
 
 
 def test_tensor_parallel_on_real_peers(native_libs, tmp_path):

@@ -73,8 +73,8 @@ const char* gguf_b200_error_string(int code) {
   return "unknown error";
 }
 
-int gguf_b200_type_size(int type) { return type_size(type); }
-int gguf_b200_block_size(int type) { return block_size(type); }
+int gguf_b200_type_size(int type) { return dequant_type_size(type); }
+int gguf_b200_block_size(int type) { return dequant_block_size(type); }
 int64_t gguf_b200_q8_1_row_bytes(int64_t K) { return round_up(K, 512) / 32 * 36; }
 void gguf_b200_set_q4k_contract(int fused) { g_q4k_contract = fused ? 1 : 0; }
 int gguf_b200_moe_block_size(int type) { return is_mmq_type(type) ? mmq_moe_block_size() : 0; }
@@ -102,9 +102,9 @@ int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int6
 }
 
 int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream) {
-  if (!type_size(type)) return E_BAD_TYPE;
+  if (!dequant_type_size(type)) return E_BAD_TYPE;
   if (!dtype_ok(out_dtype)) return E_BAD_DTYPE;
-  if (n_elems < 0 || n_elems % block_size(type) != 0) return E_BAD_SHAPE;
+  if (n_elems < 0 || n_elems % dequant_block_size(type) != 0) return E_BAD_SHAPE;
   if (n_elems == 0) return E_OK;
   if (!W || !out || !aligned16(out) || (reinterpret_cast<uintptr_t>(W) & 15)) return E_BAD_POINTER;
   return launch_dequantize(W, type, out, out_dtype, n_elems, g_q4k_contract, static_cast<cudaStream_t>(stream));

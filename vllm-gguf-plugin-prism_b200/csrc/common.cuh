@@ -23,6 +23,15 @@
 namespace gguf_b200 {
 
 enum : int { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_XS = 23 };
+// further block types, so far served by the standalone dequantize only:
+//   Q4_1    20 : half d | half m | u8 qs[16]                      value = q*d + m
+//   Q5_0    22 : half d | u8 qh[4] | u8 qs[16]                    5th bit of value j in bit j (j+16: bit j+16... see dequantize.cu)
+//   Q5_1    24 : half d | half m | u8 qh[4] | u8 qs[16]
+//   Q2_K    84 : u8 scales[16] | u8 qs[64] | half d | half dmin
+//   Q3_K   110 : u8 hmask[32] | u8 qs[64] | u8 scales[12] | half d
+//   Q5_K   176 : half d | half dmin | u8 scales[12] | u8 qh[32] | u8 qs[128]
+//   IQ4_NL  18 : half d | u8 qs[16]                               4-bit indices into the IQ4 level table
+enum : int { T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q2_K = 10, T_Q3_K = 11, T_Q5_K = 13, T_IQ4_NL = 20 };
 enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 
 // error codes returned through the C-ABI (0 = success)
@@ -45,6 +54,13 @@ template <> struct BlockTraits<T_Q4_K>    { static constexpr int QK = 256, TS = 
 template <> struct BlockTraits<T_Q6_K>    { static constexpr int QK = 256, TS = 210; };
 template <> struct BlockTraits<T_IQ2_XXS> { static constexpr int QK = 256, TS = 66;  };
 template <> struct BlockTraits<T_IQ4_XS>  { static constexpr int QK = 256, TS = 136; };
+template <> struct BlockTraits<T_Q4_1>    { static constexpr int QK = 32,  TS = 20;  };
+template <> struct BlockTraits<T_Q5_0>    { static constexpr int QK = 32,  TS = 22;  };
+template <> struct BlockTraits<T_Q5_1>    { static constexpr int QK = 32,  TS = 24;  };
+template <> struct BlockTraits<T_Q2_K>    { static constexpr int QK = 256, TS = 84;  };
+template <> struct BlockTraits<T_Q3_K>    { static constexpr int QK = 256, TS = 110; };
+template <> struct BlockTraits<T_Q5_K>    { static constexpr int QK = 256, TS = 176; };
+template <> struct BlockTraits<T_IQ4_NL>  { static constexpr int QK = 32,  TS = 18;  };
 
 __host__ __device__ inline int type_size(int t) {
   switch (t) {
@@ -59,6 +75,22 @@ __host__ __device__ inline int type_size(int t) {
 }
 __host__ __device__ inline int block_size(int t) {
   return (t == T_Q4_0 || t == T_Q8_0) ? 32 : (type_size(t) ? 256 : 0);
+}
+// the same for every type the standalone dequantize knows (a superset of the matmul types)
+__host__ __device__ inline int dequant_type_size(int t) {
+  switch (t) {
+    case T_Q4_1: return 20;
+    case T_Q5_0: return 22;
+    case T_Q5_1: return 24;
+    case T_Q2_K: return 84;
+    case T_Q3_K: return 110;
+    case T_Q5_K: return 176;
+    case T_IQ4_NL: return 18;
+  }
+  return type_size(t);
+}
+__host__ __device__ inline int dequant_block_size(int t) {
+  return (t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1 || t == T_IQ4_NL) ? 32 : (type_size(t) ? block_size(t) : (dequant_type_size(t) ? 256 : 0));
 }
 __host__ __device__ inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 
@@ -138,11 +170,48 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
       : "memory");
 }
 
+// Loads from shared memory through 32-bit shared-window addresses.  (A pointer that went through
+// an integer cast loses its address space and the compiler falls back to generic 64-bit loads and
+// address arithmetic; these helpers keep everything in the shared window.)  volatile: the loads
+// stay behind the mbarrier wait that made the data visible.
+__device__ __forceinline__ uint32_t lds32(uint32_t saddr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t saddr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128s(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+  return v;
+}
+__device__ __forceinline__ float lds_half_f32(uint32_t saddr) {   // one fp16 value, widened
+  unsigned short h;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(saddr));
+  return __half2float(__ushort_as_half(h));
+}
+template <int N> __device__ __forceinline__ void lds_words_unaligned(uint32_t a, uint32_t (&w)[N]) {
+  const uint32_t al = a & ~3u, sh = (a & 3u) * 8u;
+  uint32_t r[N + 1];
+#pragma unroll
+  for (int i = 0; i <= N; ++i) r[i] = lds32(al + 4u * i);
+#pragma unroll
+  for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(r[i], r[i + 1], sh);
+}
+// N consecutive 32-bit words starting at a shared address that is only 2-byte aligned: the N + 1
+// aligned words that cover them, realigned with funnel shifts.
+template <int N> __device__ __forceinline__ void lds_words_unaligned(const uint8_t* p, uint32_t (&w)[N]) {
+  lds_words_unaligned<N>(smem_u32(p), w);
+}
 // 32-bit word from shared memory at an address that is only 2-byte aligned.
 __device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t* p) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
-  return __funnelshift_r(w[0], w[1], (uint32_t)(a & 3) * 8u);
+  uint32_t w[1];
+  lds_words_unaligned<1>(p, w);
+  return w[0];
 }
 __device__ __forceinline__ float lds_half_as_float(const uint8_t* p) {
   return __half2float(*reinterpret_cast<const __half*>(p));

@@ -1,6 +1,8 @@
 // Standalone dequantize: packed GGUF blocks -> dense fp16/bf16/fp32, bit-identical to the
 // reference's ggml_dequantize (vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:87-102 and the
-// per-type kernels of dequantize.cuh:3-15, 69-99, 165-196, 232-256, 258-275, 420-435).
+// per-type kernels of dequantize.cuh:3-15, 69-99, 165-196, 232-256, 258-275, 420-435; further
+// types: Q4_1 :17-31, Q5_0 :33-50, Q5_1 :52-69, Q2_K :101-120, Q3_K :122-154, Q5_K :198-230,
+// IQ4_NL :400-418).
 //
 // The reference spends one 32/64-thread CTA per super-block with 1-2 byte loads and strided
 // 2-byte stores, and zero-fills the output first.  Here the op is treated as what it is -- an
@@ -86,6 +88,12 @@ template <bool CONTRACT> __device__ __forceinline__ __half q4k_value(__half d1, 
   if (CONTRACT) return __hfma(d1, q, __hneg(m1));
   return __hsub_rn(__hmul_rn(d1, q), m1);
 }
+// q*d + m of Q4_1 / Q5_1 (__hadd2(__hmul2(v, d), m), dequantize.cuh:28-29, 66-67): the same question
+template <bool CONTRACT> __device__ __forceinline__ __half mul_add_value(__half q, __half d, __half m) {
+  if (CONTRACT) return __hfma(q, d, m);
+  return __hadd_rn(__hmul_rn(q, d), m);
+}
+__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) { return ldg_u16(p) | (ldg_u16(p + 2) << 16); }
 
 template <int TYPE, typename out_t, bool Q4K_CONTRACT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ w, out_t* __restrict__ y,
@@ -93,7 +101,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
   __shared__ uint64_t s_grid[TYPE == T_IQ2_XXS ? 256 : 1];
   __shared__ uint8_t s_signs[TYPE == T_IQ2_XXS ? 128 : 1];
   __shared__ int8_t s_kv[16];
-  if (TYPE == T_IQ4_XS) {
+  if (TYPE == T_IQ4_XS || TYPE == T_IQ4_NL) {
     if (threadIdx.x < 16) s_kv[threadIdx.x] = d_kvalues_iq4nl[threadIdx.x];
     __syncthreads();
   }
@@ -175,6 +183,96 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
       for (int j = 0; j < 8; ++j)
         f[j] = d * (float)((uint32_t)(grid >> (8 * j)) & 0xffu) * ((signs >> j) & 1 ? -1.f : 1.f);
       store_from_float(y + o, f);
+    } else if (TYPE == T_Q4_1) {  // dequantize_q4_1: q*d + m
+      const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
+      const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(blk));
+      const __half d = __ushort_as_half((unsigned short)(dm & 0xffff)), m = __ushort_as_half((unsigned short)(dm >> 16));
+      const int sh = (lane & 2) ? 4 : 0;   // (20-byte blocks: 4-byte aligned)
+      const uint32_t qa = __ldg(reinterpret_cast<const uint32_t*>(blk + 4 + 8 * (lane & 1))), qb = __ldg(reinterpret_cast<const uint32_t*>(blk + 8 + 8 * (lane & 1)));
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        h[j] = mul_add_value<Q4K_CONTRACT>(__int2half_rn((int)((((j < 4 ? qa : qb) >> (8 * (j & 3))) >> sh) & 0xF)), d, m);
+      store_from_half(y + o, h);
+    } else if (TYPE == T_Q5_0 || TYPE == T_Q5_1) {  // dequantize_q5_0: (q - 16)*d ; dequantize_q5_1: q*d + m
+      constexpr int HDR = TYPE == T_Q5_1 ? 4 : 2;
+      const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
+      const __half d = __ushort_as_half((unsigned short)ldg_u16(blk));
+      const __half m = TYPE == T_Q5_1 ? __ushort_as_half((unsigned short)ldg_u16(blk + 2)) : __half();
+      const uint32_t qh = ldg_u32_a2(blk + HDR);
+      const int t = lane & 3, j0 = 8 * (t & 1);               // values 8t..8t+7: bytes qs[j0..j0+7], low (t < 2) or high nibbles
+      const uint2 q = ldg_8_a2(blk + HDR + 4 + j0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int b = byte_of(q, j), jj = j0 + j;
+        const int x = t < 2 ? ((b & 0xF) | (int)(((qh >> jj) << 4) & 0x10)) : ((b >> 4) | (int)((qh >> (jj + 12)) & 0x10));
+        if (TYPE == T_Q5_1) h[j] = mul_add_value<Q4K_CONTRACT>(__int2half_rn(x), d, m);
+        else h[j] = hmul_rn(__hsub_rn(__int2half_rn(x), __int2half_rn(16)), d);
+      }
+      store_from_half(y + o, h);
+    } else if (TYPE == T_IQ4_NL) {  // dequantize_block_iq4_nl (fp32)
+      const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
+      const float d = __half2float(__ushort_as_half((unsigned short)ldg_u16(blk)));
+      const uint2 q = ldg_8_a2(blk + 2 + 8 * (lane & 1));
+      const int sh = (lane & 2) ? 4 : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = d * (float)s_kv[(byte_of(q, j) >> sh) & 0xF];
+      store_from_float(y + o, f);
+    } else if (TYPE == T_Q2_K) {  // dequantize_block_q2_K
+      const uint8_t* blk = w + c * TS;                         // 84-byte blocks: 4-byte aligned
+      const int v = 8 * lane, n = v >> 7, k = (v & 127) >> 5, l0 = v & 31;
+      const int sc = __ldg(blk + 8 * n + (l0 >> 4) + 2 * k);
+      const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(blk + 80));
+      const __half dall = __ushort_as_half((unsigned short)(dm & 0xffff)), dmin = __ushort_as_half((unsigned short)(dm >> 16));
+      const __half mm = hmul_rn(dmin, __int2half_rn(sc >> 4));
+      const uint32_t qa = __ldg(reinterpret_cast<const uint32_t*>(blk + 16 + 32 * n + l0)), qb = __ldg(reinterpret_cast<const uint32_t*>(blk + 20 + 32 * n + l0));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int q2 = (((j < 4 ? qa : qb) >> (8 * (j & 3))) >> (2 * k)) & 3;
+        h[j] = q4k_value<Q4K_CONTRACT>(dall, __int2half_rn((sc & 0xF) * q2), mm);
+      }
+      store_from_half(y + o, h);
+    } else if (TYPE == T_Q3_K) {  // dequantize_block_q3_K
+      const uint8_t* blk = w + c * TS;                         // 110-byte blocks: 2-byte aligned
+      const int v = 8 * lane, n = v >> 7, jq = (v & 127) >> 5, l0 = v & 31, is = 8 * n + 2 * jq + (l0 >> 4);
+      const uint8_t* scp = blk + 96;
+      int us;
+      if (is < 4) us = (__ldg(scp + is) & 0xF) | (((__ldg(scp + is + 8) >> 0) & 3) << 4);
+      else if (is < 8) us = (__ldg(scp + is) & 0xF) | (((__ldg(scp + is + 4) >> 2) & 3) << 4);
+      else if (is < 12) us = (__ldg(scp + is - 8) >> 4) | (((__ldg(scp + is) >> 4) & 3) << 4);
+      else us = (__ldg(scp + is - 8) >> 4) | (((__ldg(scp + is - 4) >> 6) & 3) << 4);
+      const __half dl = hmul_rn(__ushort_as_half((unsigned short)ldg_u16(blk + 108)), __int2half_rn((int)(int8_t)us - 32));
+      const uint2 q = ldg_8_a2(blk + 32 + 32 * n + l0), hm = ldg_8_a2(blk + l0);
+      const int mbit = 1 << (4 * n + jq);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int x = (int)((byte_of(q, j) >> (2 * jq)) & 3) - ((byte_of(hm, j) & mbit) ? 0 : 4);
+        h[j] = hmul_rn(dl, __int2half_rn(x));
+      }
+      store_from_half(y + o, h);
+    } else if (TYPE == T_Q5_K) {  // dequantize_block_q5_K
+      const uint8_t* blk = w + c * TS;                         // 176-byte blocks: 16-byte aligned
+      const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(blk));
+      const __half dall = __ushort_as_half((unsigned short)(dm & 0xffff)), dmin = __ushort_as_half((unsigned short)(dm >> 16));
+      const int il = lane >> 3, off = (lane & 7) * 8, hi = off >= 32, l0 = off & 31, is = 2 * il + hi;
+      const uint8_t* sc8 = blk + 4;
+      int sc, m;
+      if (is < 4) {
+        sc = __ldg(sc8 + is) & 63;
+        m = __ldg(sc8 + is + 4) & 63;
+      } else {
+        sc = (__ldg(sc8 + is + 4) & 0xF) | ((__ldg(sc8 + is - 4) >> 6) << 4);
+        m = (__ldg(sc8 + is + 4) >> 4) | ((__ldg(sc8 + is) >> 6) << 4);
+      }
+      const __half d1 = hmul_rn(dall, __int2half_rn(sc)), m1 = hmul_rn(dmin, __int2half_rn(m));
+      const uint2 q = __ldg(reinterpret_cast<const uint2*>(blk + 48 + 32 * il + l0));
+      const uint2 qh = __ldg(reinterpret_cast<const uint2*>(blk + 16 + l0));
+      const int hbit = 1 << (2 * il + hi);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int x = (int)((byte_of(q, j) >> (4 * hi)) & 0xF) + ((byte_of(qh, j) & hbit) ? 16 : 0);
+        h[j] = q4k_value<Q4K_CONTRACT>(d1, __int2half_rn(x), m1);
+      }
+      store_from_half(y + o, h);
     } else {  // T_IQ4_XS: dequantize_block_iq4_xs (fp32)
       const uint8_t* blk = w + c * TS;
       const int ib = lane >> 2, off = (lane & 3) * 8, hi = off >= 16;
@@ -196,7 +294,8 @@ static int launch_t(const void* w, void* out, int64_t n, int q4k_contract, cudaS
   const int64_t cap = 148 * 32;  // four rounds of the 8 resident CTAs per SM measured best (148*8: -5 %, one CTA per 8 chunks: -25 %)
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
-  if (TYPE == T_Q4_K && q4k_contract)
+  constexpr bool fusible = TYPE == T_Q4_K || TYPE == T_Q5_K || TYPE == T_Q2_K || TYPE == T_Q4_1 || TYPE == T_Q5_1;
+  if (fusible && q4k_contract)
     dequantize_kernel<TYPE, out_t, true><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n);
   else
     dequantize_kernel<TYPE, out_t, false><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n);
@@ -223,6 +322,13 @@ int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t
     case T_Q6_K: return launch_d<T_Q6_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
     case T_IQ2_XXS: return launch_d<T_IQ2_XXS>(w, out, out_dtype, n_elems, q4k_contract, stream);
     case T_IQ4_XS: return launch_d<T_IQ4_XS>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q4_1: return launch_d<T_Q4_1>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q5_0: return launch_d<T_Q5_0>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q5_1: return launch_d<T_Q5_1>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q2_K: return launch_d<T_Q2_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q3_K: return launch_d<T_Q3_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q5_K: return launch_d<T_Q5_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_IQ4_NL: return launch_d<T_IQ4_NL>(w, out, out_dtype, n_elems, q4k_contract, stream);
   }
   return E_BAD_TYPE;
 }

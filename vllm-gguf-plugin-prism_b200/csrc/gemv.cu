@@ -68,16 +68,7 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
   return d;
 }
 // n consecutive 32-bit words from a 2-byte aligned shared address
-template <int N> __device__ __forceinline__ void lds_words_a2(const uint8_t* p, uint32_t (&w)[N]) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const uint32_t* al = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
-  const uint32_t sh = (uint32_t)(a & 3) * 8u;
-  uint32_t r[N + 1];
-#pragma unroll
-  for (int i = 0; i <= N; ++i) r[i] = al[i];
-#pragma unroll
-  for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(r[i], r[i + 1], sh);
-}
+template <int N> __device__ __forceinline__ void lds_words_a2(const uint8_t* p, uint32_t (&w)[N]) { lds_words_unaligned<N>(p, w); }
 
 struct Tables {
   const uint2* grid;    // IQ2_XXS: 256 x 8 magnitudes
@@ -208,16 +199,10 @@ template <int MT> struct Unit<T_Q6_K, MT> {   // unit u: half ip = u>>1, column 
 };
 
 template <int MT> struct Unit<T_IQ4_XS, MT> {   // unit ib = 32 values
-  static __device__ __forceinline__ uint32_t lut(uint32_t idx, const Tables& t) {
-    // idx: four 4-bit indices, one per byte.  Two byte-permutes pick from the low / high half of
-    // the 16-entry table by the low 3 bits, a byte mask built from bit 3 merges them.
-    const uint32_t s = idx & 0x07070707u;
-    const uint32_t pk = s | (s >> 4);                       // byte0 = n0|n1<<4, byte2 = n2|n3<<4
-    const uint32_t sel = __byte_perm(pk, 0, 0x0020);        // low 16 bits: the four selector nibbles
-    const uint32_t lo = __byte_perm(t.kv[0], t.kv[1], sel);
-    const uint32_t hi = __byte_perm(t.kv[2], t.kv[3], sel);
-    const uint32_t mk = ((idx & 0x08080808u) >> 3) * 0xFFu;
-    return (hi & mk) | (lo & ~mk);
+  // Levels of four 4-bit indices (low 16 bits of q3, bit 3 of each cleared; sel = which table half):
+  // two byte-permutes pick from levels 0-7 and 8-15 by the low three bits, a third merges them.
+  static __device__ __forceinline__ uint32_t lut4(uint32_t q3, uint32_t sel, const Tables& t) {
+    return __byte_perm(__byte_perm(t.kv[0], t.kv[1], q3), __byte_perm(t.kv[2], t.kv[3], q3), sel);
   }
   static __device__ __forceinline__ void run(const uint8_t* blk, int ib, int g0, const XView& x, const Tables& t, int mc, float (&acc)[MT]) {
     const uint2 hdr = *reinterpret_cast<const uint2*>(blk);  // d | scales_h | scales_l[4]
@@ -229,8 +214,12 @@ template <int MT> struct Unit<T_IQ4_XS, MT> {   // unit ib = 32 values
     uint32_t w[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      w[i] = lut(q[i] & 0x0F0F0F0Fu, t);
-      w[4 + i] = lut((q[i] >> 4) & 0x0F0F0F0Fu, t);
+      // the packed word is its own selector: nibbles (b0 lo, b0 hi, b1 lo, b1 hi | b2 ..) = values (4i, 16+4i, 4i+1, 17+4i | ..)
+      const uint32_t q3 = q[i] & 0x77777777u;
+      const uint32_t sel = ((q[i] & 0x88888888u) >> 1) | 0x32103210u;
+      const uint32_t a = lut4(q3, sel, t), b = lut4(q3 >> 16, sel >> 16, t);
+      w[i] = __byte_perm(a, b, 0x6420);       // values 4i..4i+3
+      w[4 + i] = __byte_perm(a, b, 0x7531);   // values 16+4i..
     }
     const int g = g0 + ib;
     const float dl = d * (float)ls;

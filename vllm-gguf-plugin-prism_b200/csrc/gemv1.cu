@@ -29,20 +29,12 @@ __device__ __forceinline__ int dp4a_us1(uint32_t a, uint32_t b, int c) {
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-template <int N> __device__ __forceinline__ void lds_a2(const uint8_t* p, uint32_t (&w)[N]) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const uint32_t* al = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
-  const uint32_t sh = (uint32_t)(a & 3) * 8u;
-  uint32_t r[N + 1];
-#pragma unroll
-  for (int i = 0; i <= N; ++i) r[i] = al[i];
-#pragma unroll
-  for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(r[i], r[i + 1], sh);
-}
+// `blk` below is the 32-bit shared-window address of a weight block (all loads stay in that window)
+template <int N> __device__ __forceinline__ void lds_a2(uint32_t a, uint32_t (&w)[N]) { lds_words_unaligned<N>(a, w); }
 
 struct Tab1 {
-  const uint2* grid;
-  const uint2* smask;
+  uint32_t grid;    // shared-window addresses of this lane's copies of the IQ2_XXS code books
+  uint32_t smask;
   uint32_t kv[4];
 };
 
@@ -59,8 +51,8 @@ template <> struct G1<T_Q8_0> {
     const float2 d = __ldg(ds + u);
     xd[0] = d.x; xd[1] = d.y;
   }
-  static __device__ __forceinline__ float unit(const uint8_t* blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const float d = lds_half_as_float(blk);
+  static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = lds_half_f32(blk);
     uint32_t w[8];
     lds_a2<8>(blk + 2, w);
     int s0 = 0, s1 = 0;
@@ -79,8 +71,8 @@ template <> struct G1<T_Q4_0> {
   static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
-  static __device__ __forceinline__ float unit(const uint8_t* blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const float d = lds_half_as_float(blk);
+  static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = lds_half_f32(blk);
     uint32_t q[4];
     lds_a2<4>(blk + 2, q);
     int lo = 0, hi = 0;  // hi = 16 * (high-nibble dot): nibbles stay in place
@@ -106,8 +98,8 @@ template <> struct G1<T_Q4_K> {
     const float4 d = __ldg(reinterpret_cast<const float4*>(ds + 2 * u));
     xd[0] = d.x; xd[1] = d.y; xd[2] = d.z; xd[3] = d.w;  // d8_0, d8_0*sum0, d8_1, d8_1*sum1
   }
-  static __device__ __forceinline__ float unit(const uint8_t* blk, int p, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+  static __device__ __forceinline__ float unit(uint32_t blk, int p, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const uint4 hdr = lds128s(blk);
     const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
     const float d = __low2float(dm), dmin = __high2float(dm);
     const int sh = 16 * (p & 1);
@@ -117,8 +109,7 @@ template <> struct G1<T_Q4_K> {
     const uint32_t mn2 = low ? (b & 0x3F3Fu) : (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u));
     const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
     const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
-    const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + 32 * p);
-    const uint4 qa = qp[0], qb = qp[1];
+    const uint4 qa = lds128s(blk + 16 + 32 * p), qb = lds128s(blk + 32 + 32 * p);
     const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
 #pragma unroll
@@ -158,14 +149,17 @@ template <> struct G1<T_Q6_K> {
     xd[0] = __ldg(ds + ga).x;
     xd[1] = __ldg(ds + gb).x;
   }
-  static __device__ __forceinline__ float unit(const uint8_t* blk, int u4, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+  static __device__ __forceinline__ float unit(uint32_t blk, int u4, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
     const int ip = u4 >> 1, h = u4 & 1;
     uint32_t ql[8], qh[8];
     lds_a2<8>(blk + 64 * ip + 32 * h, ql);
     lds_a2<8>(blk + 128 + 32 * ip, qh);
-    const int8_t* scp = reinterpret_cast<const int8_t*>(blk + 192 + 8 * ip + 2 * h);
-    const int sa0 = scp[0], sa1 = scp[1], sb0 = scp[4], sb1 = scp[5];
-    const float d = lds_half_as_float(blk + 208);
+    // the scale pairs sit at even offsets of a 2-byte aligned block: two 16-bit loads
+    unsigned short sca, scb;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sca) : "r"(blk + 192 + 8 * ip + 2 * h));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(scb) : "r"(blk + 196 + 8 * ip + 2 * h));
+    const int sa0 = (int)(int8_t)(sca & 0xFF), sa1 = (int)(int8_t)(sca >> 8), sb0 = (int)(int8_t)(scb & 0xFF), sb1 = (int)(int8_t)(scb >> 8);
+    const float d = lds_half_f32(blk + 208);
     const int s2 = 2 * h;
     int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
 #pragma unroll
@@ -190,32 +184,40 @@ template <> struct G1<T_Q6_K> {
 };
 
 // ---- IQ4_XS: unit ib = 32 values -------------------------------------------------------------
+// The 16 levels live in four registers.  One byte-permute picks four bytes out of eight by four
+// 3-bit selectors, so a 4-bit index takes two permutes (levels 0-7, levels 8-15) and a third that
+// chooses between them by bit 3 -- and the packed weight word itself serves as the selector: its
+// nibbles are (value b, value 16+b) for each byte b.  The level bytes therefore come out in the
+// order (v, v+16, v+1, v+17); instead of sorting them back, the lane's activations are shuffled
+// into that order once, when they are loaded.
 template <> struct G1<T_IQ4_XS> {
   static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
   static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
-    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+    uint32_t n[8];
+    G1<T_Q8_0>::load_x(qs, ds, u, b, n, xd);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {   // n[i] = values 4i..4i+3, n[4+i] = values 16+4i..
+      x[2 * i] = __byte_perm(n[i], n[4 + i], 0x5140);       // (4i, 16+4i, 4i+1, 16+4i+1)
+      x[2 * i + 1] = __byte_perm(n[i], n[4 + i], 0x7362);   // (4i+2, 16+4i+2, 4i+3, 16+4i+3)
+    }
   }
-  static __device__ __forceinline__ uint32_t lut(uint32_t idx, const Tab1& t) {
-    const uint32_t s = idx & 0x07070707u;
-    const uint32_t pk = s | (s >> 4);
-    const uint32_t sel = __byte_perm(pk, 0, 0x0020);
-    const uint32_t lo = __byte_perm(t.kv[0], t.kv[1], sel);
-    const uint32_t hi = __byte_perm(t.kv[2], t.kv[3], sel);
-    const uint32_t mk = ((idx & 0x08080808u) >> 3) * 0xFFu;
-    return (hi & mk) | (lo & ~mk);
+  // levels of the four 4-bit indices in the low 16 bits of q3 (bit 3 of each cleared) / sel (which half)
+  static __device__ __forceinline__ uint32_t lut4(uint32_t q3, uint32_t sel, const Tab1& t) {
+    return __byte_perm(__byte_perm(t.kv[0], t.kv[1], q3), __byte_perm(t.kv[2], t.kv[3], q3), sel);
   }
-  static __device__ __forceinline__ float unit(const uint8_t* blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
-    const uint2 hdr = *reinterpret_cast<const uint2*>(blk);
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
+    const uint2 hdr = lds64(blk);
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
     const int ls = (int)(((hdr.y >> (4 * ib)) & 0xF) | ((((hdr.x >> 16) >> (2 * ib)) & 3) << 4)) - 32;
-    const uint2* qp = reinterpret_cast<const uint2*>(blk + 8 + 16 * ib);
-    const uint2 qa = qp[0], qb = qp[1];
+    const uint2 qa = lds64(blk + 8 + 16 * ib), qb = lds64(blk + 16 + 16 * ib);
     const uint32_t q[4] = {qa.x, qa.y, qb.x, qb.y};
     int s0 = 0, s1 = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      s0 = __dp4a((int)lut(q[i] & 0x0F0F0F0Fu, t), (int)x[i], s0);
-      s1 = __dp4a((int)lut((q[i] >> 4) & 0x0F0F0F0Fu, t), (int)x[4 + i], s1);
+      const uint32_t q3 = q[i] & 0x77777777u;                                  // selectors within a half of the table
+      const uint32_t sel = ((q[i] & 0x88888888u) >> 1) | 0x32103210u;          // nibble j: j (low half) or j + 4 (high half)
+      s0 = __dp4a((int)lut4(q3, sel, t), (int)x[2 * i], s0);
+      s1 = __dp4a((int)lut4(q3 >> 16, sel >> 16, t), (int)x[2 * i + 1], s1);
     }
     return d * (float)ls * xd[0] * (float)(s0 + s1);
   }
@@ -227,16 +229,16 @@ template <> struct G1<T_IQ2_XXS> {
   static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
-  static __device__ __forceinline__ float unit(const uint8_t* blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
-    const float d = lds_half_as_float(blk);
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
+    const float d = lds_half_f32(blk);
     uint32_t q[2];
     lds_a2<2>(blk + 2 + 8 * ib, q);
     const uint32_t aux = q[1];
     int sp = 0, sn = 0;
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
-      const uint2 gr = t.grid[((q[0] >> (8 * il)) & 0xFF) * G1_TAB_COPIES];     // this lane's copy of the entry
-      const uint2 sm = t.smask[((aux >> (7 * il)) & 127) * G1_TAB_COPIES];
+      const uint2 gr = lds64(t.grid + ((q[0] >> (8 * il)) & 0xFF) * (8 * G1_TAB_COPIES));     // this lane's copy of the entry
+      const uint2 sm = lds64(t.smask + ((aux >> (7 * il)) & 127) * (8 * G1_TAB_COPIES));
       sp = dp4a_us1(gr.x, x[2 * il], sp);
       sp = dp4a_us1(gr.y, x[2 * il + 1], sp);
       sn = dp4a_us1(gr.x & sm.x, x[2 * il], sn);
@@ -275,6 +277,7 @@ struct G1Params {
   int rows_per_item;     // <= G1_R
   int slot_bytes;        // distance between the rows of an item inside a stage
   int stages, stage_bytes;
+  int partial_bytes;     // shared memory for the staged results (0 when every warp stores its own)
   int contig;            // 1: contiguous row ranges per lane, 0: round-robin row groups
   int* status;
   // MoE decode (topk_ids != null, one vector): blockIdx.y is an output row s of y; it uses the
@@ -340,8 +343,8 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
 
   uint8_t* cur = smem;
   Tab1 tb;
-  tb.grid = nullptr;
-  tb.smask = nullptr;
+  tb.grid = 0;
+  tb.smask = 0;
   if (TYPE == T_IQ2_XXS) {
     // Both code books are stored G1_TAB_COPIES times, copy c in the 8-byte column c of every
     // 128-byte line: lane l reads copy l % 16, and since a 64-bit shared load is served one
@@ -351,30 +354,16 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     uint2* g = reinterpret_cast<uint2*>(cur);
     uint2* sm = g + 256 * G1_TAB_COPIES;
     cur += (256 + 128) * 8 * G1_TAB_COPIES;
-    for (int i = threadIdx.x; i < 256 * G1_TAB_COPIES; i += blockDim.x) {
-      const uint64_t v = d_iq2xxs_grid[i / G1_TAB_COPIES];
-      g[i] = make_uint2((uint32_t)v, (uint32_t)(v >> 32));
-    }
-    for (int i = threadIdx.x; i < 128 * G1_TAB_COPIES; i += blockDim.x) {
-      const uint32_t s = d_ksigns_iq2xs[i / G1_TAB_COPIES];
-      uint32_t lo = 0, hi = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        lo |= ((s >> j) & 1u) ? (0xFFu << (8 * j)) : 0u;
-        hi |= ((s >> (4 + j)) & 1u) ? (0xFFu << (8 * j)) : 0u;
-      }
-      sm[i] = make_uint2(lo, hi);
-    }
-    tb.grid = g + (lane & (G1_TAB_COPIES - 1));
-    tb.smask = sm + (lane & (G1_TAB_COPIES - 1));
+    tb.grid = smem_u32(g + (lane & (G1_TAB_COPIES - 1)));
+    tb.smask = smem_u32(sm + (lane & (G1_TAB_COPIES - 1)));
   }
   if (TYPE == T_IQ4_XS) {
     const uint32_t* kv = reinterpret_cast<const uint32_t*>(d_kvalues_iq4nl);
 #pragma unroll
     for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
   }
-  float* partial = reinterpret_cast<float*>(cur);  // [rl][G1_BATCH][G1_R][MV][ks]
-  cur += (size_t)G1_BATCH * 8 * G1_R * MV * sizeof(float);
+  float* partial = reinterpret_cast<float*>(cur);  // [rl][G1_BATCH][G1_R][MV][ks], present only when results are staged
+  cur += p.partial_bytes;
   uint8_t* ring = cur + (size_t)warp * p.stages * p.stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cur + (size_t)G1_WARPS * p.stages * p.stage_bytes) + warp * p.stages;
   if (lane == 0)
@@ -464,18 +453,38 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     }
   };
 
-  int p_it = 0, p_st = 0;
-  for (int s = 0; s < p.stages - 1; ++s) {
+  // Every stage of the ring is filled before anything else happens: with the ring as deep as the
+  // warp's whole share (small matrices) ALL of this kernel's weight bytes are requested up front,
+  // while the previous kernel of the stream is still draining and before the activations exist.
+  int p_it = 0;
+  for (int s = 0; s < p.stages; ++s) {
     if (p_it < my_iters) {
       int64_t r0;
       int cnt;
       item(rl_i, p_it, r0, cnt);
-      issue(r0, cnt, p_st);
+      issue(r0, cnt, s);
       ++p_it;
-      if (++p_st == p.stages) p_st = 0;
     }
   }
 
+  if (TYPE == T_IQ2_XXS) {   // fill the code-book copies while the first weight copies are in flight
+    uint2* tab_g = reinterpret_cast<uint2*>(smem);
+    uint2* tab_s = tab_g + 256 * G1_TAB_COPIES;
+    for (int i = threadIdx.x; i < 256 * G1_TAB_COPIES; i += blockDim.x) {
+      const uint64_t v = d_iq2xxs_grid[i / G1_TAB_COPIES];
+      tab_g[i] = make_uint2((uint32_t)v, (uint32_t)(v >> 32));
+    }
+    for (int i = threadIdx.x; i < 128 * G1_TAB_COPIES; i += blockDim.x) {
+      const uint32_t s = d_ksigns_iq2xs[i / G1_TAB_COPIES];
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= ((s >> j) & 1u) ? (0xFFu << (8 * j)) : 0u;
+        hi |= ((s >> (4 + j)) & 1u) ? (0xFFu << (8 * j)) : 0u;
+      }
+      tab_s[i] = make_uint2(lo, hi);
+    }
+  }
   // The weight copies above touch nothing another kernel writes; everything below does.
   pdl_wait();
   const unsigned tag = p.world > 0 ? (sizeof(out_t) == 2 ? (p.epoch[p.slot] & 0xFFFFu) : p.epoch[p.slot]) : 0u;
@@ -511,14 +520,6 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   for (int i = 0; i < iters; ++i) {
     const bool mine = i < my_iters && !dead;
     if (mine) {
-      if (p_it < my_iters) {
-        int64_t r0;
-        int cnt;
-        item(rl_i, p_it, r0, cnt);
-        issue(r0, cnt, p_st);
-        ++p_it;
-        if (++p_st == p.stages) p_st = 0;
-      }
       if (!mbar_wait_bounded(&bars[c_st], c_phase)) {
         if (lane == 0) atomicExch(p.status, E_TIMEOUT);
         dead = true;
@@ -529,6 +530,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       int cnt;
       item(rl_i, i, c_row, cnt);
       uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
+      const uint32_t stage_s = smem_u32(stage);
       const int64_t beg0 = c_row * row_bytes + (int64_t)sb0 * TS;
       const int64_t last_end = (c_row + cnt - 1) * row_bytes + (int64_t)sb0 * TS + slice_bytes;
       if (last_end > w_safe) {  // tail bytes the bulk copy must not touch: fetched with plain loads
@@ -544,8 +546,8 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
 #pragma unroll
         for (int m = 0; m < MV; ++m) acc[m][rr] = 0.f;
         if (rr < cnt) {
-          const uint8_t* data = contiguous ? stage + (beg0 & 15) + (size_t)rr * row_bytes
-                                           : stage + (size_t)rr * p.slot_bytes + ((beg0 + rr * row_bytes) & 15);
+          const uint32_t data = stage_s + (contiguous ? (uint32_t)(beg0 & 15) + (uint32_t)rr * (uint32_t)row_bytes
+                                                      : (uint32_t)rr * (uint32_t)p.slot_bytes + (uint32_t)((beg0 + rr * row_bytes) & 15));
 #pragma unroll
           for (int j = 0; j < UMAX; ++j)
             if (lane + 32 * j < units) {
@@ -567,7 +569,14 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
           }
         }
       }
-      __syncwarp();
+      __syncwarp();   // every lane is done with the stage: refill it with the warp's next item
+      if (p_it < my_iters) {
+        int64_t r0;
+        int cnt2;
+        item(rl_i, p_it, r0, cnt2);
+        issue(r0, cnt2, c_st);
+        ++p_it;
+      }
       if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
     }
     if (staged && ((i % G1_BATCH) == G1_BATCH - 1 || i == iters - 1)) {
@@ -608,7 +617,7 @@ template <int TYPE, typename out_t, int MV>
 static int launch_g1(G1Params p, cudaStream_t stream) {
   using T = G1<TYPE>;
   constexpr int TS = BlockTraits<TYPE>::TS;
-  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 2);
+  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 16);
   static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
   static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
   static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 6000);
@@ -630,12 +639,32 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   while (R > 1 && (int64_t)R * (ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16)) > item_cap) --R;
   p.rows_per_item = R;
   p.slot_bytes = ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16);
-  p.stages = stages_env < 2 ? 2 : stages_env;
   p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
   const size_t tables = TYPE == T_IQ2_XXS ? (size_t)(256 + 128) * 8 * G1_TAB_COPIES : 0;
-  const size_t smem = tables + (size_t)G1_BATCH * 8 * G1_R * MV * 4 + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
-  if (smem > 227 * 1024) return 1;
+  p.partial_bytes = (ks > 1 || p.world > 0) ? G1_BATCH * 8 * G1_R * MV * 4 : 0;
+  const size_t fixed = tables + (size_t)p.partial_bytes + (size_t)G1_WARPS * 8 * 16;   // + barriers (at most 16 stages)
   auto kern = gemv1_kernel<TYPE, out_t, MV>;
+  // Grid first (it decides how many items a warp gets), then the ring depth: as many stages as a
+  // warp has items, within what leaves room for two CTAs per SM; GGUF_B200_GEMV1_STAGES caps it.
+  const size_t budget2 = (size_t)113 * 1024;
+  int per_sm = ctas_env < 1 ? 1 : (ctas_env > 2 ? 2 : ctas_env);
+  if (fixed + (size_t)G1_WARPS * 2 * p.stage_bytes > budget2) per_sm = 1;
+  int64_t grid = 148 * per_sm;
+  const int64_t groups = (p.n + R - 1) / R;
+  const int64_t need = (groups + p.rl - 1) / p.rl;
+  if (grid > need) grid = need;
+  if (grid < 1) grid = 1;
+  const int64_t rows_per_lane = (p.n + grid * p.rl - 1) / (grid * p.rl);
+  int want = (int)((rows_per_lane + R - 1) / R);
+  const int cap = stages_env < 2 ? 16 : (stages_env > 16 ? 16 : stages_env);
+  if (want > cap) want = cap;
+  if (want < 2) want = 2;
+  const size_t room = (per_sm == 2 ? budget2 : (size_t)226 * 1024) - fixed;
+  int fit = (int)(room / ((size_t)G1_WARPS * p.stage_bytes));
+  if (fit < 2) return 1;   // not even a double buffer: the general kernel takes the shape
+  p.stages = want < fit ? want : fit;
+  const size_t smem = tables + (size_t)p.partial_bytes + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
+  if (smem > 227 * 1024) return 1;
   static size_t configured[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -643,14 +672,6 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
     configured[dev & 63] = smem;
   }
-  int per_sm = (int)((227 * 1024) / (smem + 1024));
-  if (per_sm > ctas_env) per_sm = ctas_env;
-  if (per_sm < 1) per_sm = 1;
-  int64_t grid = 148 * per_sm;
-  const int64_t groups = (p.n + R - 1) / R;
-  const int64_t need = (groups + p.rl - 1) / p.rl;
-  if (grid > need) grid = need;
-  if (grid < 1) grid = 1;
   unsigned gy = 1;
   if (p.topk_ids) {   // MoE decode: the CTAs are shared out over the (token, expert) pairs
     gy = (unsigned)p.moe_slots;

@@ -12,12 +12,17 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K, IQ2_XXS, IQ4_XS = 2, 8, 12, 14, 16, 23
+Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL = 3, 6, 7, 10, 11, 13, 20
 #             type: (values per block, bytes per block)
 QUANT_SIZES = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ2_XXS: (256, 66),
-               IQ4_XS: (256, 136)}
-NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ2_XXS: "IQ2_XXS", IQ4_XS: "IQ4_XS"}
+               IQ4_XS: (256, 136),
+               Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q2_K: (256, 84), Q3_K: (256, 110), Q5_K: (256, 176),
+               IQ4_NL: (32, 18)}
+NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ2_XXS: "IQ2_XXS", IQ4_XS: "IQ4_XS",
+         Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q2_K: "Q2_K", Q3_K: "Q3_K", Q5_K: "Q5_K", IQ4_NL: "IQ4_NL"}
 # where the fp16 scale(s) sit inside a block, and the |N(0,1)| multiplier the configs name
-_D_OFFSETS = {Q4_0: (0,), Q8_0: (0,), Q4_K: (0, 2), Q6_K: (208,), IQ2_XXS: (0,), IQ4_XS: (0,)}
+_D_OFFSETS = {Q4_0: (0,), Q8_0: (0,), Q4_K: (0, 2), Q6_K: (208,), IQ2_XXS: (0,), IQ4_XS: (0,),
+              Q4_1: (0, 2), Q5_0: (0,), Q5_1: (0, 2), Q2_K: (80, 82), Q3_K: (108,), Q5_K: (0, 2), IQ4_NL: (0,)}
 _D_SCALE = {Q4_0: 0.01, Q8_0: 0.002, Q4_K: 0.01, Q6_K: 0.01, IQ2_XXS: 0.01, IQ4_XS: 0.01}
 
 
@@ -33,7 +38,7 @@ def make_weight(qtype: int, n: int, k: int, seed: int = 0, d_scale: float | None
     rng = np.random.default_rng(seed)
     nb = n * (k // bs)
     blocks = rng.integers(0, 256, size=(nb, ts), dtype=np.uint8)
-    scale = _D_SCALE[qtype] if d_scale is None else d_scale
+    scale = _D_SCALE.get(qtype, 0.01) if d_scale is None else d_scale
     for off in _D_OFFSETS[qtype]:
         d = (np.abs(rng.standard_normal(nb)) * scale).astype(np.float16)
         blocks[:, off:off + 2] = d.view(np.uint8).reshape(nb, 2)

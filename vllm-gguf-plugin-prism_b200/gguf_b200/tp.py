@@ -74,8 +74,20 @@ class ColumnParallelGGUFLinear:
         return gather_columns(y, self.group) if self.world > 1 else y
 
 
+def _group_info(group):
+    """(group, rank, world); without an initialised process group: a group of one."""
+    if not dist.is_initialized():
+        return None, 0, 1
+    group = group if group is not None else dist.group.WORLD
+    return group, dist.get_rank(group), dist.get_world_size(group)
+
+
 def _symmetric_arena(nbytes: int, device, group):
-    """A zeroed uint8 buffer of `nbytes` that every rank of `group` maps; returns (tensor, [base pointers])."""
+    """A zeroed uint8 buffer of `nbytes` that every rank of `group` maps; returns (tensor, handle,
+    [base pointers]).  A group of one gets ordinary device memory."""
+    if group is None or dist.get_world_size(group) == 1:
+        arena = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        return arena, None, [arena.data_ptr()]
     import torch.distributed._symmetric_memory as symm_mem
 
     arena = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
@@ -104,9 +116,7 @@ class FusedGatherGemv:
         from . import capi
 
         self.capi = capi
-        self.group = group if group is not None else dist.group.WORLD
-        self.rank = dist.get_rank(self.group)
-        self.world = dist.get_world_size(self.group)
+        self.group, self.rank, self.world = _group_info(group)
         self.n_total, self.slots, self.dtype = int(n_total), int(slots), dtype
         self.packet_bytes = 8 if dtype == torch.float32 else 4
         self.slot_packets = (self.n_total + 63) // 64 * 64
@@ -136,9 +146,7 @@ class FusedGatherMatmul:
         from . import capi
 
         self.capi = capi
-        self.group = group if group is not None else dist.group.WORLD
-        self.rank = dist.get_rank(self.group)
-        self.world = dist.get_world_size(self.group)
+        self.group, self.rank, self.world = _group_info(group)
         if slots > 1024:
             raise ValueError("at most 1024 call slots")
         self.m, self.n_total, self.slots, self.dtype = int(m), int(n_total), int(slots), dtype

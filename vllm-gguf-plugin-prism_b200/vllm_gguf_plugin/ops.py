@@ -67,6 +67,12 @@ QUANT_SIZES = {
     GGML_TYPE_IQ4_XS: (256, 136),
 }
 _CUDA_GEMV_QUANT_TYPES = frozenset(QUANT_SIZES)
+# ggml_dequantize alone also serves these
+DEQUANT_ONLY_SIZES = {
+    GGML_TYPE_Q4_1: (32, 20), GGML_TYPE_Q5_0: (32, 22), GGML_TYPE_Q5_1: (32, 24), GGML_TYPE_Q2_K: (256, 84),
+    GGML_TYPE_Q3_K: (256, 110), GGML_TYPE_Q5_K: (256, 176), GGML_TYPE_IQ4_NL: (32, 18),
+}
+_CUDA_DEQUANT_TYPES = _CUDA_GEMV_QUANT_TYPES | frozenset(DEQUANT_ONLY_SIZES)
 _CUDA_GEMM_QUANT_TYPES = frozenset({GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_Q6_K})
 _DEQUANT_MATMUL_TYPES = frozenset({GGML_TYPE_IQ2_XXS, GGML_TYPE_IQ4_XS})
 
@@ -119,7 +125,7 @@ def _ggml_moe_a8_vec_fake(X, W, topk_ids, top_k, quant_type, row, tokens):
 
 
 def ggml_dequantize(W: torch.Tensor, quant_type: int, m: int, n: int, dtype: torch.dtype | None) -> torch.Tensor:
-    _require(quant_type, _CUDA_GEMV_QUANT_TYPES, "ggml_dequantize")
+    _require(quant_type, _CUDA_DEQUANT_TYPES, "ggml_dequantize")
     return torch.ops._C_gguf.ggml_dequantize(W, quant_type, m, n, dtype)
 
 

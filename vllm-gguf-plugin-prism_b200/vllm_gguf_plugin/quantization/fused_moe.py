@@ -153,22 +153,51 @@ class GGUFMoEMethod(FusedMoEMethodBase):
                        intermediate_size_per_partition: int, params_dtype: torch.dtype, **extra_weight_attrs):
         """Registers w13_weight [E, 2I, bytes] / w2_weight [E, H, bytes] as raw GGUF bytes (sized on
         load: the byte width depends on the quant type) and their type parameters."""
+        # vLLM's FusedMoE passes its own loader among the extras; its set_weight_attrs refuses to
+        # overwrite an attribute, so it is taken out first (reference: fused_moe.py:182)
+        base_loader = extra_weight_attrs.pop("weight_loader", None)
         for name in ("w13_weight", "w2_weight"):
             w = torch.nn.Parameter(torch.empty(0, dtype=torch.uint8), requires_grad=False)
-            set_weight_attrs(w, {"is_gguf_weight": True, "weight_loader": self._load_weight})
+            w.num_experts = num_experts
+            set_weight_attrs(w, {"is_gguf_weight": True, "weight_loader": self._load_weight, "base_weight_loader": base_loader})
             set_weight_attrs(w, extra_weight_attrs)
             layer.register_parameter(name, w)
             t = _TypeParam()
             set_weight_attrs(t, {"is_gguf_weight_type": True, "weight_loader": self._load_type})
+            set_weight_attrs(t, extra_weight_attrs)
             layer.register_parameter(name + "_type", t)
 
     @staticmethod
-    def _load_weight(param, loaded_weight, *args, **kwargs):
-        param.data = loaded_weight.to(torch.uint8).contiguous()
+    def _load_weight(param, loaded_weight, weight_name=None, shard_id=None, expert_id=None, return_success=False):
+        """vLLM's MoE loader call (param, loaded_weight, weight_name, shard_id, expert_id).  GGUF stores
+        the experts of one projection stacked ([E, rows, bytes]) or one expert at a time ([rows,
+        bytes] with expert_id).  shard_id "w1" / "w3" are the gate / up halves of w13 (rows [0, I)
+        and [I, 2I) of every expert), "w2" the down projection.  Tensor parallelism slices w1/w3 by
+        rows and w2 by whole blocks of every row (reference: params.py:158-208)."""
+        from .linear import tensor_parallel_rank_and_size
+
+        w = loaded_weight.to(torch.uint8)
+        rank, size = tensor_parallel_rank_and_size()
+        if size > 1:
+            dim = w.dim() - (1 if shard_id == "w2" else 2)      # bytes for w2, rows for w1 / w3
+            n = w.shape[dim] // size
+            if n > 0:
+                w = w.narrow(dim, rank * n, n)
+        rows, width = w.shape[-2], w.shape[-1]
+        halves = 2 if shard_id in ("w1", "w3") else 1
+        if param.data.numel() == 0:
+            param.data = torch.zeros((param.num_experts, rows * halves, width), dtype=torch.uint8, device=w.device)
+        r0 = rows if shard_id == "w3" else 0
+        if w.dim() == 3:
+            param.data[:, r0:r0 + rows].copy_(w)
+        else:
+            param.data[int(expert_id), r0:r0 + rows].copy_(w)
+        return True if return_success else None
 
     @staticmethod
     def _load_type(param, loaded_weight, *args, **kwargs):
         param.weight_type = int(loaded_weight.item()) if isinstance(loaded_weight, torch.Tensor) else int(loaded_weight)
+        return True if kwargs.get("return_success") else None
 
     def get_fused_moe_quant_config(self, layer: torch.nn.Module):
         return None

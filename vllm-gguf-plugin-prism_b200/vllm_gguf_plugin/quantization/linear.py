@@ -40,6 +40,18 @@ except Exception:  # pragma: no cover - exercised on boxes without vLLM
             setattr(weight, k, v)
 
 
+def tensor_parallel_rank_and_size() -> tuple[int, int]:
+    """(rank, size) of vLLM's tensor-parallel group, (0, 1) when vLLM or the group is absent.
+    The weight loaders slice by it as the reference's parameter classes do
+    (quantization/params.py:227-265)."""
+    try:
+        from vllm.distributed import get_tensor_model_parallel_rank, get_tensor_model_parallel_world_size
+
+        return get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
+    except Exception:
+        return 0, 1
+
+
 def _fused_mul_mat_gguf(x: torch.Tensor, weight: torch.Tensor, weight_type: int) -> torch.Tensor:
     # thresholds as in the reference (linear.py:38-41)
     if weight_type in IMATRIX_QUANT_TYPES:
@@ -113,35 +125,58 @@ class GGUFLinearMethod(LinearMethodBase):
         """Registers ``weight`` (raw GGUF bytes, sized when the first shard arrives because
         the byte width depends on the tensor's quant type) and ``weight_type``."""
         self.params_dtype = params_dtype
+        # vLLM's layers pass their own `weight_loader` among the extras, and its set_weight_attrs
+        # refuses to overwrite an attribute: take it out first, as the reference does
+        # (linear.py:104).  It is kept as `fallback_weight_loader`; the loaders below are the ones
+        # that understand raw GGUF bytes whose width is only known when the tensor arrives.
+        fallback = extra_weight_attrs.pop("weight_loader", None)
         weight = torch.nn.Parameter(torch.empty(0, dtype=torch.uint8), requires_grad=False)
         weight.shard_id = []
         weight.shard_offset_map = {}
         weight.output_partition_sizes = list(output_partition_sizes)
         weight.input_size_per_partition = input_size_per_partition
+        # how the layer is sharded over the tensor-parallel group: by output rows (column-parallel:
+        # the per-partition output is smaller than the full one) or by input columns (row-parallel)
+        weight.tp_shard_rows = sum(output_partition_sizes) < output_size
+        weight.tp_shard_cols = input_size_per_partition < input_size
         set_weight_attrs(weight, {"input_dim": 1, "output_dim": 0, "is_gguf_weight": True,
-                                  "weight_loader": self._load_weight})
+                                  "weight_loader": self._load_weight, "fallback_weight_loader": fallback})
         set_weight_attrs(weight, extra_weight_attrs)
         layer.register_parameter("weight", weight)
         wtype = GGUFWeightType()
         set_weight_attrs(wtype, {"is_gguf_weight_type": True, "ignore_warning": True,
                                  "weight_loader": self._load_weight_type})
+        set_weight_attrs(wtype, extra_weight_attrs)
         layer.register_parameter("weight_type", wtype)
 
     @staticmethod
     def _load_weight_type(param, loaded_weight, loaded_shard_id=None):
         t = int(loaded_weight.item()) if isinstance(loaded_weight, torch.Tensor) else int(loaded_weight)
-        if loaded_shard_id is None:
-            param.weight_type = t
-        else:
-            param.shard_weight_type[loaded_shard_id] = t
-            param.weight_type = param.weight_type or t
+        ids = loaded_shard_id if isinstance(loaded_shard_id, tuple) else (loaded_shard_id,)
+        for sid in ids:
+            if sid is None:
+                param.weight_type = t
+            else:
+                param.shard_weight_type[sid] = t
+                param.weight_type = param.weight_type or t
 
     @staticmethod
     def _load_weight(param, loaded_weight, loaded_shard_id=None):
-        """Stores one tensor (or one shard of a merged layer) of raw block bytes."""
+        """Stores one tensor (or one shard of a merged layer) of raw block bytes, narrowed to this
+        tensor-parallel rank: rows for a column-parallel layer (params.py:227-236), whole blocks of
+        every row for a row-parallel one (params.py:259-264)."""
         if not hasattr(param, "_shards"):
             param._shards = {}
-        param._shards[loaded_shard_id] = loaded_weight.to(torch.uint8)
+        w = loaded_weight.to(torch.uint8)
+        rank, size = tensor_parallel_rank_and_size()
+        if size > 1 and w.dim() == 2:
+            if getattr(param, "tp_shard_rows", False) and w.shape[0] // size > 0:
+                n = w.shape[0] // size
+                w = w.narrow(0, rank * n, n)
+            if getattr(param, "tp_shard_cols", False) and w.shape[1] // size > 0:
+                b = w.shape[1] // size
+                w = w.narrow(1, rank * b, b)
+        param._shards[loaded_shard_id] = w.contiguous()
         if loaded_shard_id is not None and loaded_shard_id not in param.shard_id:
             param.shard_id.append(loaded_shard_id)
 
