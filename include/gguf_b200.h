@@ -8,7 +8,8 @@
  * never allocates, never synchronises.  Work is enqueued on `stream` (a cudaStream_t passed
  * as void*).  Scratch memory is provided by the caller (gguf_b200_workspace_bytes).
  *
- * Types: GGML ids 2 (Q4_0), 8 (Q8_0), 12 (Q4_K), 14 (Q6_K), 16 (IQ2_XXS), 23 (IQ4_XS).
+ * Types: GGML ids 2 (Q4_0), 3 (Q4_1), 6 (Q5_0), 7 (Q5_1), 8 (Q8_0), 12 (Q4_K), 13 (Q5_K), 14 (Q6_K),
+ * 16 (IQ2_XXS), 20 (IQ4_NL), 23 (IQ4_XS); the standalone dequantize also takes 10 (Q2_K), 11 (Q3_K).
  * Weights W are raw GGUF blocks, row-major `uint8 [N][K/QK*type_size]`, base 16-byte aligned.
  * Activations X are `[M][K]` contiguous in `dtype`; outputs Y are `[M][N]` in the same dtype.
  */
@@ -57,9 +58,19 @@ int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int6
 
 /* Standalone dequantize, bit-exact with the reference.
  * Replaces: ggml_dequantize, gguf_kernel.cu:87-102 (+ dequantize.cuh:527-571 dispatch).
+ * Types: all matmul types plus Q2_K (10) and Q3_K (11).
  * Writes n_elems = m*n values (a multiple of the block size); every output element is
  * written, so the caller need not zero-fill. */
 int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream);
+
+/* Embedding look-up: out[r][0..K) = dequantize(weight row row_ids[r]) for r < n_rows, bit-exact with
+ * gguf_b200_dequantize of the selected rows.
+ * Replaces: index_select of the rows followed by ggml_dequantize in the embedding caller
+ * (quantization/vocal_embeds.py:88-96) -- one kernel, no copy of the selected rows.
+ * row_ids: int64 on the device; an id outside [0, weight_rows) gives a row of zeros.  K a multiple
+ * of 256.  All block types of gguf_b200_dequantize. */
+int gguf_b200_dequantize_rows(const void* W, int type, const int64_t* row_ids, int64_t n_rows, int64_t K,
+                              int64_t weight_rows, void* out, int out_dtype, void* stream);
 
 /* Scratch bytes an op wants for the given sizes (rows = M, or tokens for the MoE ops).  For the
  * dense GEMM ops this includes room for fp32 partial tiles when the problem is split over K
@@ -84,13 +95,13 @@ int gguf_b200_gemv_prepared(const void* W, const void* workspace, void* Y, int t
                             int64_t M, int64_t N, int64_t K, void* stream);
 
 /* Prefill GEMM on tensor cores (same q8_1-quantized activations).
- * Replaces: ggml_mul_mat_a8, gguf_kernel.cu:220-290 (+ mmq.cuh).  Types 2, 8, 12, 14. */
+ * Replaces: ggml_mul_mat_a8, gguf_kernel.cu:220-290 (+ mmq.cuh).  Types 2, 3, 6, 7, 8, 12, 13, 14. */
 int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
                          int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
 
 /* Fused dequantize + dense GEMM with unquantized activations: Y = X . dequant(W)^T.
  * Replaces the two-step route the reference takes for IQ types at larger batches
- * (quantization/linear.py:50-54: ggml_dequantize then x @ W.T).  dtype f16 or bf16. */
+ * (quantization/linear.py:50-54: ggml_dequantize then x @ W.T).  dtype f16 or bf16.  Types 16, 20, 23. */
 int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
                              int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
 
@@ -108,6 +119,24 @@ int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* workspace, int
                      const int32_t* num_tokens_post_padded, int64_t n_sorted, int64_t expert_stride_bytes,
                      int64_t n_experts, int type, int dtype, int64_t tokens, int64_t top_k, int64_t N, int64_t K,
                      void* stream);
+
+/* The whole MoE step of one layer in one call: expert alignment, gate/up expert GEMM, activation,
+ * down expert GEMM, routing weights and the sum over the top_k experts.
+ * Replaces: the tiled branch of _fused_moe_gguf, quantization/fused_moe.py:56-95 (moe_align_block_size,
+ * ggml_moe_a8, apply_moe_activation, ggml_moe_a8, mul_ by the routing weights, moe_sum: six library
+ * ops there).  Here the activation runs inside the second GEMM's activation quantizer and the routing
+ * weights inside its epilogue; the alignment and the final sum are small kernels of this library.
+ *   X [tokens][H]; W13 [E][2I][H/QK*ts] (gate rows, then up rows, of every expert); W2 [E][H][I/QK*ts];
+ *   topk_ids int32 [tokens*top_k] and topk_weights float [tokens*top_k] on the device; Y [tokens][H].
+ *   act: 1 = silu, 2 = gelu (erf form).  Types 2, 3, 6, 7, 8, 12, 13, 14; n_experts <= 256; I % 8 == 0.
+ *   A slot whose expert id is outside [0, n_experts) contributes nothing (expert-parallel masking).
+ * Workspace: gguf_b200_fused_moe_workspace_bytes (slot lists, both intermediate matrices, activations). */
+int64_t gguf_b200_fused_moe_workspace_bytes(int type13, int type2, int dtype, int64_t tokens, int64_t top_k,
+                                            int64_t n_experts, int64_t H, int64_t I);
+int gguf_b200_fused_moe(const void* X, const void* W13, const void* W2, void* Y, const int32_t* topk_ids,
+                        const float* topk_weights, void* workspace, int64_t workspace_bytes, int type13, int type2,
+                        int dtype, int act, int64_t tokens, int64_t top_k, int64_t n_experts, int64_t H, int64_t I,
+                        void* stream);
 
 /* Small-batch MoE: one GEMV per (token, expert) pair.
  * Replaces: ggml_moe_a8_vec, gguf_kernel.cu:395-530 (+ moe_vec.cuh:3-53).

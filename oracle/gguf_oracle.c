@@ -196,11 +196,10 @@ int oracle_type_size(int type) {
     case T_Q6_K: return 210;
     case T_IQ2_XXS: return 66;
     case T_IQ4_XS: return 136;
-    /* dequantize only (no matmul restatement for these yet) */
     case T_Q4_1: return 20;
     case T_Q5_0: return 22;
     case T_Q5_1: return 24;
-    case T_Q2_K: return 84;
+    case T_Q2_K: return 84;  /* (Q2_K, Q3_K: dequantize only) */
     case T_Q3_K: return 110;
     case T_Q5_K: return 176;
     case T_IQ4_NL: return 18;
@@ -541,6 +540,35 @@ static void unpack_codes(const uint8_t* blk, int type, int8_t* w) {
           w[32 * ib + j + 16] = gguf_b200_kvalues_iq4nl[q >> 4];
         }
       break;
+    case T_Q4_1:
+      for (int j = 0; j < 16; ++j) {
+        w[j] = blk[4 + j] & 0xF;
+        w[j + 16] = blk[4 + j] >> 4;
+      }
+      break;
+    case T_Q5_0:
+    case T_Q5_1: { /* 4 low bits from qs, fifth bit j of qh for value j (vecdotq.cuh:108-122) */
+      const uint8_t* qhp = blk + (type == T_Q5_1 ? 4 : 2);
+      const uint8_t* qs = blk + (type == T_Q5_1 ? 8 : 6);
+      uint32_t qh = (uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24);
+      for (int j = 0; j < 16; ++j) {
+        w[j] = (int8_t)((qs[j] & 0xF) | (((qh >> j) & 1) << 4));
+        w[j + 16] = (int8_t)((qs[j] >> 4) | (((qh >> (j + 16)) & 1) << 4));
+      }
+    } break;
+    case T_IQ4_NL:
+      for (int j = 0; j < 16; ++j) {
+        w[j] = gguf_b200_kvalues_iq4nl[blk[2 + j] & 0xf];
+        w[j + 16] = gguf_b200_kvalues_iq4nl[blk[2 + j] >> 4];
+      }
+      break;
+    case T_Q5_K:
+      for (int il = 0; il < 4; ++il)
+        for (int l = 0; l < 32; ++l) {
+          w[64 * il + l] = (int8_t)((blk[48 + 32 * il + l] & 0xF) | (((blk[16 + l] >> (2 * il)) & 1) << 4));
+          w[64 * il + 32 + l] = (int8_t)((blk[48 + 32 * il + l] >> 4) | (((blk[16 + l] >> (2 * il + 1)) & 1) << 4));
+        }
+      break;
   }
 }
 
@@ -607,6 +635,44 @@ static double block_dot(const uint8_t* blk, int type, const uint8_t* y, int mmq)
         const uint8_t* yb = y + 36 * g;
         acc += d * iq4xs_ls(blk, g) * h2f(rd16(yb)) * idot(w + 32 * g, (const int8_t*)yb + 4, 32);
       }
+    } break;
+    case T_Q4_1:   /* sumi * h(d4*d8) + h(m4*s8): both products in half (__hmul2), vecdotq.cuh:72-96 */
+    case T_Q5_1: { /* the same with 5-bit codes, vecdotq.cuh:134-163 */
+      uint16_t d = rd16(blk), m = rd16(blk + 2);
+      acc = (double)idot(w, (const int8_t*)y + 4, 32) * h2f(hmul(d, rd16(y))) + h2f(hmul(m, rd16(y + 2)));
+    } break;
+    case T_Q5_0: { /* d5 * (sumi*d8 - 16*s8), vecdotq.cuh:101-129.  The tiled kernel folds the -16 into
+                      the codes and drops the s8 term (load_tiles_q5_0 + vec_dot_q8_0_q8_1_impl). */
+      double d5 = h2f(rd16(blk)), d8 = h2f(rd16(y)), s8 = h2f(rd16(y + 2));
+      if (mmq) {
+        int sumi = 0;
+        for (int j = 0; j < 32; ++j) sumi += (w[j] - 16) * ((const int8_t*)y + 4)[j];
+        acc = d5 * d8 * sumi;
+      } else {
+        acc = d5 * (idot(w, (const int8_t*)y + 4, 32) * d8 - 16.0 * s8);
+      }
+    } break;
+    case T_IQ4_NL: /* d * d8 * (sumi1 + sumi2), vecdotq.cuh:1766-1789 */
+      acc = (double)h2f(rd16(blk)) * h2f(rd16(y)) * idot(w, (const int8_t*)y + 4, 32);
+      break;
+    case T_Q5_K: { /* vecdotq.cuh:386-413 (GEMV) / :415-445 (tiled), as Q4_K with 5-bit codes */
+      double d = h2f(rd16(blk)), dmin = h2f(rd16(blk + 2)), sd = 0, sm = 0;
+      for (int g = 0; g < nsub; ++g) {
+        int sc, m;
+        scale_min_k4(g, blk + 4, &sc, &m);
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        double d8 = h2f(rd16(yb)), s8 = h2f(rd16(yb + 2));
+        sd += d8 * (double)(idot(w + 32 * g, q8, 32) * sc);
+        if (mmq) {
+          sm += s8 * m;
+        } else {
+          int sq = 0;
+          for (int j = 0; j < 32; ++j) sq += q8[j];
+          sm += d8 * (double)(sq * m);
+        }
+      }
+      acc = d * sd - dmin * sm;
     } break;
   }
   return acc;

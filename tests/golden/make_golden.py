@@ -28,8 +28,12 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT / "vllm-gguf-plugin-prism_b200"))
+sys.path.insert(0, str(ROOT))
 
-TYPES = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14, "IQ2_XXS": 16, "IQ4_XS": 23}
+TYPES = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14, "IQ2_XXS": 16, "IQ4_XS": 23,
+         "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q5_K": 13, "IQ4_NL": 20}
+# dequantize fixtures only (no fused matmul for these in this library)
+DEQUANT_ONLY = {"Q2_K": 10, "Q3_K": 11}
 
 
 def gguf_py_fixture():
@@ -37,7 +41,7 @@ def gguf_py_fixture():
     from gguf_b200 import synth
 
     out = {}
-    for name, t in TYPES.items():
+    for name, t in {**TYPES, **DEQUANT_ONLY}.items():
         n, k = 6, 512
         w = synth.make_weight(t, n, k, seed=40 + t)
         wd = gguf.dequantize(w, gguf.GGMLQuantizationType(t)).astype(np.float32)

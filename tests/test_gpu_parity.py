@@ -81,7 +81,7 @@ def test_dequantize_bit_exact(ref, name, dtype):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("name", DEQUANT_ONLY_TYPES)
 def test_dequantize_more_types_bit_exact(ref, name, dtype):
-    """Block types that so far only the standalone dequantize serves."""
+    """Block types that only the standalone dequantize serves."""
     t = DEQUANT_ONLY_TYPES[name]
     N, K = 40, 2048
     wn, w = dev_w(t, N, K, seed=t)
@@ -109,6 +109,29 @@ def test_dequantize_full_matrices_bit_exact_on_device(ref):
         assert torch.equal(bits(got), bits(want)), name
         del w, got, want
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "IQ2_XXS", "Q5_K", "Q3_K", "IQ4_NL"])
+def test_embedding_row_gather_equals_index_select_then_dequantize(ref, name):
+    """The embedding caller: rows picked inside the dequantize kernel, bit for bit what the
+    reference's two steps (index_select, ggml_dequantize) give; an id outside the table gives zeros."""
+    from vllm_gguf_plugin.quantization import vocal_embeds
+
+    t = {**TYPES, **DEQUANT_ONLY_TYPES}[name]
+    V, H = 300, 1024
+    wn, w = dev_w(t, V, H, seed=3)
+    ids = torch.tensor([[5, 299, 0], [17, 17, 123]], device=DEV)
+    for dtype in (torch.float16, torch.bfloat16, torch.float32):
+        got = vocal_embeds._apply_gguf_embedding(ids, w, t, H, dtype)
+        assert got.shape == (2, 3, H) and got.dtype == dtype
+        quant = torch.index_select(w, 0, ids.flatten())
+        want = capi.dequantize(quant, t, ids.numel(), H, dtype)
+        assert torch.equal(bits(got.view(-1, H)), bits(want))
+        if ref.available:
+            r = ref.ops.ggml_dequantize(quant, t, H, ids.numel(), dtype)
+            assert torch.equal(bits(got.view(-1, H)), bits(r.view(-1, H)))
+    bad = capi.dequantize_rows(w, torch.tensor([1, V + 5, -1], device=DEV), t)
+    assert torch.equal(bad[0], capi.dequantize(w[1:2].clone(), t, 1, H)[0]) and float(bad[1:].abs().sum()) == 0.0
 
 
 def test_dequantize_ragged_counts(ref):
@@ -256,7 +279,7 @@ def test_mmq_other_dtypes(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ4_XS"])
+@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ4_XS", "IQ4_NL"])
 def test_dequant_matmul_parity(ref, name, dtype):
     """IQ types above the GEMV threshold: the reference dequantizes and calls a dense matmul."""
     t = TYPES[name]
@@ -354,7 +377,7 @@ def test_ops_api_equals_capi_and_dispatcher_end_to_end():
         want = capi.mul_mat_a8(w, x64, t, 256) if name in MMQ_TYPES else capi.dequant_matmul(w, x64, t, 256)
         assert torch.equal(y, want)
     with pytest.raises(NotImplementedError):
-        ops.ggml_mul_mat_vec_a8(w, x1, 3, 256)
+        ops.ggml_mul_mat_vec_a8(w, x1, 10, 256)
     with pytest.raises(RuntimeError):
         ops.ggml_mul_mat_vec_a8(w[:, :-1].contiguous(), x1, 23, 256)      # not a whole number of blocks
 
@@ -381,6 +404,92 @@ def test_fused_moe_dispatcher_matches_dense_experts():
             want[tok] += float(tw[tok, j]) * (h @ d2[e].T)
     # activations are q8_1-quantized twice on the kernel path: the reference's own tolerance class
     assert rel_l2(out.float().cpu(), want.cpu()) < 3e-2
+
+
+def _reference_moe_sequence(ref, x, w13, w2, tw, ids, t13, t2):
+    """The reference's tiled MoE branch (quantization/fused_moe.py:56-95) restated with the
+    reference's own kernels: block-4 alignment, ggml_moe_a8, silu-and-mul in the activation type
+    (silu rounded, then multiplied), ggml_moe_a8, routing weights, sum over top_k."""
+    T, top_k = ids.shape
+    E, N2, _ = w13.shape
+    H = w2.shape[1]
+    s4, e4, n4 = [torch.from_numpy(a).to(DEV) for a in synth.moe_align_block_size(ids.cpu().numpy(), 4, E)]
+    out = ref.ops.ggml_moe_a8(x, w13, s4, e4, n4, t13, N2, top_k, T)
+    g, u = out[:, :N2 // 2].float(), out[:, N2 // 2:]
+    act = (g / (1.0 + torch.exp(-g))).to(out.dtype) * u
+    out = ref.ops.ggml_moe_a8(act.contiguous(), w2, s4, e4, n4, t2, H, 1, T * top_k)
+    out = (out.view(T, top_k, H).float() * tw.view(T, top_k, 1).float()).to(x.dtype)
+    return out.float().sum(dim=1).to(x.dtype)
+
+
+@pytest.mark.parametrize("case", [("Q4_0", 2, 2, 8, 512, 256, 96, 2), ("Q4_K", 12, 14, 6, 1024, 512, 70, 3), ("Q8_0", 8, 8, 4, 256, 256, 130, 1),
+                                  ("Q5_K", 13, 6, 5, 512, 256, 80, 2)])
+def test_fused_moe_step_matches_reference_sequence(ref, case):
+    """gguf_b200_fused_moe (alignment + GEMM + activation-in-quantizer + GEMM with routing weights in
+    the epilogue + sum) against the reference's sequence of separate ops on its own kernels."""
+    name, t13, t2, E, H, I, T, top_k = case
+    w13 = torch.from_numpy(np.stack([synth.make_weight(t13, 2 * I, H, seed=e) for e in range(E)])).to(DEV)
+    w2 = torch.from_numpy(np.stack([synth.make_weight(t2, H, I, seed=100 + e) for e in range(E)])).to(DEV)
+    x = dev_x(T, H, seed=3)
+    twn, idn = synth.make_routing(T, E, top_k, 3)
+    tw, ids = torch.from_numpy(twn).to(DEV), torch.from_numpy(idn).to(DEV)
+    got = capi.fused_moe(x, w13, w2, ids, tw, t13, t2)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0 and bool(torch.isfinite(got).all())
+    # the same library, op by op (separate alignment, activation, weighting and sum)
+    blk = capi.lib().gguf_b200_moe_block_size(t13)
+    s, e, n = [torch.from_numpy(a).to(DEV) for a in synth.moe_align_block_size(idn, blk, E)]
+    o1 = capi.moe_a8(x, w13, s, e, n, t13, 2 * I, top_k, T)
+    a1 = (torch.nn.functional.silu(o1[:, :I].float()).half() * o1[:, I:]).contiguous()
+    o2 = capi.moe_a8(a1, w2, s, e, n, t2, H, 1, T * top_k)
+    stepwise = (o2.view(T, top_k, H).float() * tw.view(T, top_k, 1)).half().float().sum(1).half()
+    assert rel_l2(got.float().cpu(), stepwise.float().cpu()) <= 5e-4
+    if ref.available:
+        want = _reference_moe_sequence(ref, x, w13, w2, tw, ids, t13, t2)
+        assert rel_l2(got.float().cpu(), want.float().cpu()) <= REL_L2_TOL
+    # a slot routed to "no expert" (id -1, as expert-parallel masking does) contributes nothing
+    ids2 = ids.clone()
+    ids2[0, 0] = -1
+    got2 = capi.fused_moe(x, w13, w2, ids2, tw, t13, t2)
+    tw2 = tw.clone()
+    tw2[0, 0] = 0.0
+    want2 = capi.fused_moe(x, w13, w2, ids, tw2, t13, t2)
+    assert rel_l2(got2.float().cpu(), want2.float().cpu()) <= 1e-3
+    assert torch.equal(got2[1:], want2[1:])
+
+
+def test_fused_moe_dispatcher_uses_the_fused_step(ref):
+    """_fused_moe_gguf above 64 tokens = the fused call; gelu as well; bf16 activations."""
+    from vllm_gguf_plugin.quantization import fused_moe
+
+    t, E, H, I, T, top_k = 2, 8, 512, 256, 96, 2
+    w13 = torch.from_numpy(np.stack([synth.make_weight(t, 2 * I, H, seed=e) for e in range(E)])).to(DEV)
+    w2 = torch.from_numpy(np.stack([synth.make_weight(t, H, I, seed=100 + e) for e in range(E)])).to(DEV)
+    twn, idn = synth.make_routing(T, E, top_k, 3)
+    tw, ids = torch.from_numpy(twn).to(DEV), torch.from_numpy(idn).to(DEV).int()
+    for dtype in (torch.float16, torch.bfloat16):
+        x = dev_x(T, H, seed=3, dtype=dtype)
+        for act, code in (("silu", capi.ACT_SILU), ("gelu", capi.ACT_GELU)):
+            out = fused_moe._fused_moe_gguf(x, w13, w2, tw, ids, t, t, act)
+            assert torch.equal(out, capi.fused_moe(x, w13, w2, ids, tw, t, t, code))
+            assert out.dtype == dtype and bool(torch.isfinite(out).all())
+
+
+def test_fused_moe_full_size_matches_reference_sequence(ref):
+    """The MoE benchmark configuration end to end: 64 experts, top-8, hidden 2048, intermediate 1024, Q4_0, 256 tokens."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    t, E, top_k, H, I, T = 2, 64, 8, 2048, 1024, 256
+    w13 = torch.from_numpy(np.stack([synth.make_weight(t, 2 * I, H, seed=100 + e) for e in range(E)])).to(DEV)
+    w2 = torch.from_numpy(np.stack([synth.make_weight(t, H, I, seed=300 + e) for e in range(E)])).to(DEV)
+    x = torch.from_numpy(synth.make_activation(T, H, seed=1)).to(DEV)
+    twn, idn = synth.make_routing(T, E, top_k, 0)
+    tw, ids = torch.from_numpy(twn).to(DEV), torch.from_numpy(idn).to(DEV)
+    got = capi.fused_moe(x, w13, w2, ids, tw, t, t)
+    want = _reference_moe_sequence(ref, x, w13, w2, tw, ids, t, t)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(got.float().cpu(), want.float().cpu()) <= REL_L2_TOL
 
 
 # ---------------------------------------------------------------- fused gather (tensor parallel) --
@@ -578,3 +687,67 @@ def test_moe_full_size_close_to_reference(ref):
     torch.cuda.synchronize()
     assert capi.last_status() == 0
     assert rel_l2(yv.float().cpu(), rv.float().cpu()) <= REL_L2_TOL
+
+
+FULL_GEMV = [("Q6_K", 37888, 3584), ("Q6_K", 3584, 18944), ("IQ4_XS", 37888, 3584), ("IQ4_XS", 3584, 18944),
+             ("IQ2_XXS", 28672, 8192), ("IQ2_XXS", 8192, 28672), ("Q4_K", 4096, 14336), ("Q8_0", 3072, 1024)]
+
+
+@pytest.mark.parametrize("case", FULL_GEMV)
+def test_gemv_full_size_configs_close_to_reference(ref, case):
+    """Decode GEMV at the full size of every benchmark configuration, against the reference's kernel."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    name, N, K = case
+    t = TYPES[name]
+    w = torch.from_numpy(synth.make_weight(t, N, K, seed=11)).to(DEV)
+    x = dev_x(1, K, seed=11)
+    y = capi.mul_mat_vec_a8(w, x, t, N)
+    r = ref.ops.ggml_mul_mat_vec_a8(w, x, t, N)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(y.float().cpu(), r.float().cpu()) <= 1e-4
+
+
+FULL_GEMM = [("Q6_K", 37888, 3584, 256), ("Q6_K", 3584, 18944, 256), ("IQ4_XS", 37888, 3584, 256), ("IQ4_XS", 3584, 18944, 256),
+             ("IQ2_XXS", 28672, 8192, 128), ("IQ2_XXS", 8192, 28672, 128)]
+
+
+@pytest.mark.parametrize("case", FULL_GEMM)
+def test_gemm_full_size_configs_close_to_reference(ref, case):
+    """Prefill at the full size of the Qwen2.5-7B and 70B-class configurations: q8_1 tensor-core GEMM
+    against the reference's tiled kernel (Q6_K), fused dequantize-GEMM against the reference's
+    dequantize followed by a dense product (IQ types)."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    name, N, K, M = case
+    t = TYPES[name]
+    w = torch.from_numpy(synth.make_weight(t, N, K, seed=13)).to(DEV)
+    x = dev_x(M, K, seed=13)
+    if name in MMQ_TYPES:
+        y = capi.mul_mat_a8(w, x, t, N)
+        r = ref.ops.ggml_mul_mat_a8(w, x, t, N)
+    else:
+        y = capi.dequant_matmul(w, x, t, N)
+        r = x @ ref.ops.ggml_dequantize(w, t, N, K, torch.float16).T
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+
+
+def test_moe_down_projection_full_size_close_to_reference(ref):
+    """The second expert GEMM of the MoE configuration: 2048 routed rows of 1024 values, top_k = 1, w2 [64, 2048, 576 bytes]."""
+    if not ref.available:
+        pytest.skip("reference kernels not built")
+    t, E, top_k, hid, inter, T = 2, 64, 8, 2048, 1024, 256
+    w2 = torch.from_numpy(np.stack([synth.make_weight(t, hid, inter, seed=200 + e) for e in range(E)])).to(DEV)
+    x2 = torch.from_numpy(synth.make_activation(T * top_k, inter, seed=2)).to(DEV)
+    _, ids = synth.make_routing(T, E, top_k, 0)
+    blk = capi.lib().gguf_b200_moe_block_size(t)
+    s, e, n = [torch.from_numpy(a).to(DEV) for a in synth.moe_align_block_size(ids, blk, E)]
+    s4, e4, n4 = [torch.from_numpy(a).to(DEV) for a in synth.moe_align_block_size(ids, 4, E)]
+    y = capi.moe_a8(x2, w2, s, e, n, t, hid, 1, T * top_k)
+    r = ref.ops.ggml_moe_a8(x2, w2, s4, e4, n4, t, hid, 1, T * top_k)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL

@@ -36,7 +36,7 @@ def recorded_ops(monkeypatch, native_libs):
 
 def test_dispatcher_routes_like_the_reference(recorded_ops):
     calls, linear = recorded_ops
-    assert len(ROUTING) == 288
+    assert len(ROUTING) == 528
     for case in ROUTING:
         t, rows, m = case["type"], case["rows"], case["m"]
         bs, ts = synth.QUANT_SIZES[t]

@@ -6,7 +6,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from helpers import REL_L2_TOL, ROOT, TYPES, rel_l2
+from helpers import DEQUANT_ONLY_TYPES, REL_L2_TOL, ROOT, TYPES, rel_l2
 
 from gguf_b200 import synth
 from oracle import cpu
@@ -14,13 +14,13 @@ from oracle import cpu
 GOLD = np.load(Path(__file__).parent / "golden" / "golden_gguf_py.npz")
 
 
-@pytest.mark.parametrize("name", TYPES)
+@pytest.mark.parametrize("name", list(TYPES) + list(DEQUANT_ONLY_TYPES))
 def test_dequantize_matches_gguf_py_fixture(name):
-    t = TYPES[name]
+    t = {**TYPES, **DEQUANT_ONLY_TYPES}[name]
     w, want = GOLD[f"w_{name}"], GOLD[f"dq_{name}"]
     n = want.size
     got32 = cpu.as_float(cpu.dequantize(w, t, n, "float32"), "float32").reshape(want.shape)
-    if name in ("IQ2_XXS", "IQ4_XS"):
+    if name in ("IQ2_XXS", "IQ4_XS", "IQ4_NL"):
         # fp32 decoders: the reference kernel and gguf-py do the same fp32 multiplies
         assert np.array_equal(got32, want)
     else:

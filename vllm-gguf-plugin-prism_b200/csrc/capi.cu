@@ -32,13 +32,22 @@ int* status_word_ptr() {
 
 static int* status_ptr() { return status_word_ptr(); }
 
-int mmq_corr_mode(int type) { return type == T_Q4_0 ? CORR_Q4_0 : (type == T_Q4_K ? CORR_MIN : CORR_NONE); }
+int mmq_corr_mode(int type) {
+  switch (type) {
+    case T_Q4_0: return CORR_Q4_0;
+    case T_Q4_K: case T_Q5_K: return CORR_MIN;
+    case T_Q4_1: case T_Q5_1: return CORR_PLUS;
+  }
+  return CORR_NONE;
+}
 int64_t mmq_ldb(int type, int64_t K) {
   const int64_t kpad = round_up(K, 512);
   return mmq_corr_mode(type) == CORR_NONE ? kpad : kpad + round_up(kpad / 32, 64);
 }
 
-static bool is_mmq_type(int t) { return t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K; }
+static bool is_mmq_type(int t) {
+  return t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K || t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1 || t == T_Q5_K;
+}
 static bool dtype_ok(int d) { return d == DT_F32 || d == DT_F16 || d == DT_BF16; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -61,7 +70,7 @@ const char* gguf_b200_version(void) { return "gguf_b200 0.1 (sm_100a)"; }
 const char* gguf_b200_error_string(int code) {
   switch (code) {
     case E_OK: return "ok";
-    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q8_0=8, Q4_K=12, Q6_K=14, IQ2_XXS=16, IQ4_XS=23)";
+    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q4_1=3, Q5_0=6, Q5_1=7, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14, IQ2_XXS=16, IQ4_NL=20, IQ4_XS=23; dequantize also Q2_K=10, Q3_K=11)";
     case E_BAD_DTYPE: return "unsupported dtype (expected f32=0, f16=1, bf16=2)";
     case E_BAD_SHAPE: return "bad shape (negative size, or K not a multiple of the block size)";
     case E_BAD_POINTER: return "null or misaligned pointer (16-byte alignment required)";
@@ -110,6 +119,16 @@ int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int6
   return launch_dequantize(W, type, out, out_dtype, n_elems, g_q4k_contract, static_cast<cudaStream_t>(stream));
 }
 
+int gguf_b200_dequantize_rows(const void* W, int type, const int64_t* row_ids, int64_t n_rows, int64_t K,
+                              int64_t weight_rows, void* out, int out_dtype, void* stream) {
+  if (!dequant_type_size(type)) return E_BAD_TYPE;
+  if (!dtype_ok(out_dtype)) return E_BAD_DTYPE;
+  if (n_rows < 0 || weight_rows < 0 || K <= 0 || K % 256 != 0) return E_BAD_SHAPE;
+  if (n_rows == 0) return E_OK;
+  if (!W || !out || !row_ids || !aligned16(out) || !aligned16(W) || (reinterpret_cast<uintptr_t>(row_ids) & 7)) return E_BAD_POINTER;
+  return launch_dequantize(W, type, out, out_dtype, n_rows * K, g_q4k_contract, static_cast<cudaStream_t>(stream), row_ids, K, weight_rows);
+}
+
 // Up to this many tokens the op is bound by reading the weights once, which the GEMV kernel does
 // best; it then runs with the tiled kernels' formulas (Q4_K min term from the stored fp16 sum).
 // Measured cross-over on 14336x4096: the types with whole-stage tensor-core decoders win from 5
@@ -143,7 +162,7 @@ int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, in
   if (!st) return E_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // the Q4_K GEMV takes its min term from the quantized codes (sum_mode 1), all others from the fp16 sum
-  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s);
+  rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s);
   if (rc) return rc;
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
 }
@@ -181,7 +200,7 @@ int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* packe
     qt.add_epoch = epochs_local + add_slot;
     qt.add_scale = add_scale;
   }
-  rc = launch_quantize_q8_1(X, dtype, ws, 1, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s, 0, &qt);
+  rc = launch_quantize_q8_1(X, dtype, ws, 1, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s, 0, &qt);
   if (rc) return rc;
   rc = launch_gemv1(W, ws, nullptr, type, dtype, N_local, K, st, s, &tp);
   return rc == 1 ? E_TOO_LARGE : rc;   // rows too long for the single-vector kernel
@@ -207,7 +226,7 @@ int gguf_b200_matmul_tp(int op, const void* W, const void* X, void* const* y_pee
   int rc = check_common(W, X, y_peers[rank], type, dtype, M, N_local, K);
   if (rc || M == 0 || N_local == 0) return rc;
   if (op == GGUF_B200_OP_DEQUANT_MATMUL) {
-    if (type != T_IQ2_XXS && type != T_IQ4_XS) return E_BAD_TYPE;
+    if (type != T_IQ2_XXS && type != T_IQ4_XS && type != T_IQ4_NL) return E_BAD_TYPE;
     if (dtype != DT_F16 && dtype != DT_BF16) return E_BAD_DTYPE;
     if (K % 64 != 0) return E_BAD_SHAPE;
   } else if (!is_mmq_type(type)) {
@@ -275,7 +294,7 @@ int gguf_b200_gemv_prepare(const void* X, int dtype, void* ws, int64_t ws_bytes,
   if (M == 0) return E_OK;
   if (!X || !ws || !aligned16(ws) || !aligned16(X)) return E_BAD_POINTER;
   if (ws_bytes < q8_soa_bytes(M, K)) return E_WORKSPACE;
-  return launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0,
+  return launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0,
                               static_cast<cudaStream_t>(stream));
 }
 
@@ -300,7 +319,10 @@ int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* ws, int64_
   if (!st) return E_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (M <= mmq_gemv_max_tokens(type)) {
-    rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, 0, 0, CORR_NONE, nullptr, 1, 0, s);
+    // GEMV kernels with the tiled kernels' formulas: min / offset terms from the stored fp16 sum of the
+    // inputs -- except Q5_0, whose tiled kernel folds the -16 into the codes (no sum term at all:
+    // load_tiles_q5_0 + vec_dot_q8_0_q8_1_impl, vecdotq.cuh:676-749), i.e. 16 * d8 * sum(q8)
+    rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, type == T_Q5_0 ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s);
     if (rc) return rc;
     return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
   }
@@ -328,7 +350,7 @@ int gguf_b200_dequant_matmul(const void* W, const void* X, void* Y, void* ws, in
                              int64_t M, int64_t N, int64_t K, void* stream) {
   int rc = check_common(W, X, Y, type, dtype, M, N, K);
   if (rc || M == 0 || N == 0) return rc;
-  if (type != T_IQ2_XXS && type != T_IQ4_XS) return E_BAD_TYPE;
+  if (type != T_IQ2_XXS && type != T_IQ4_XS && type != T_IQ4_NL) return E_BAD_TYPE;
   if (dtype != DT_F16 && dtype != DT_BF16) return E_BAD_DTYPE;
   if (K % 64 != 0) return E_BAD_SHAPE;
   int* st = status_ptr();
@@ -393,6 +415,104 @@ int gguf_b200_moe_a8(const void* X, const void* W, void* Y, void* ws, int64_t ws
   return launch_mmq(a, s);
 }
 
+namespace {
+struct FusedMoeLayout {
+  int64_t n_sorted, o_counts, o_sorted, o_experts, o_npp, o_y1, o_y2, o_xb, total;
+};
+FusedMoeLayout fused_moe_layout(int type13, int type2, int dtype, int64_t tokens, int64_t top_k, int64_t E, int64_t H, int64_t I) {
+  FusedMoeLayout L{};
+  const int blk = mmq_moe_block_size();
+  const int64_t slots = tokens * top_k, esz = dtype == DT_F32 ? 4 : 2;
+  L.n_sorted = moe_align_sorted_len(slots, (int)E, blk);
+  int64_t o = 0;
+  auto take = [&](int64_t bytes) { const int64_t at = o; o += round_up(bytes, 256); return at; };
+  L.o_counts = take(2 * E * 4);
+  L.o_sorted = take(L.n_sorted * 4);
+  L.o_experts = take(L.n_sorted / blk * 4);
+  L.o_npp = take(4);
+  L.o_y1 = take(slots * 2 * I * esz);
+  L.o_y2 = take(slots * H * esz);
+  const int64_t xb1 = L.n_sorted * mmq_ldb(type13, H) * 2, xb2 = L.n_sorted * mmq_ldb(type2, I) * 2;
+  L.o_xb = take(xb1 > xb2 ? xb1 : xb2);
+  L.total = o;
+  return L;
+}
+}  // namespace
+
+int64_t gguf_b200_fused_moe_workspace_bytes(int type13, int type2, int dtype, int64_t tokens, int64_t top_k, int64_t n_experts,
+                                            int64_t H, int64_t I) {
+  if (!is_mmq_type(type13) || !is_mmq_type(type2) || tokens < 0 || top_k <= 0 || n_experts <= 0 || n_experts > 256 || H <= 0 || I <= 0) return 0;
+  return fused_moe_layout(type13, type2, dtype, tokens, top_k, n_experts, H, I).total;
+}
+
+int gguf_b200_fused_moe(const void* X, const void* W13, const void* W2, void* Y, const int32_t* topk_ids,
+                        const float* topk_weights, void* ws, int64_t ws_bytes, int type13, int type2, int dtype, int act,
+                        int64_t tokens, int64_t top_k, int64_t n_experts, int64_t H, int64_t I, void* stream) {
+  int rc = check_common(W13, X, Y, type13, dtype, tokens, 2 * I, H);
+  if (rc) return rc;
+  rc = check_common(W2, X, Y, type2, dtype, tokens, H, I);
+  if (rc) return rc;
+  if (!is_mmq_type(type13) || !is_mmq_type(type2)) return E_BAD_TYPE;
+  if (top_k <= 0 || n_experts <= 0 || (act != 1 && act != 2) || I % 8 != 0) return E_BAD_SHAPE;
+  if (n_experts > 256) return E_TOO_LARGE;
+  if (tokens == 0) return E_OK;
+  if (!topk_ids || !topk_weights || !ws || !aligned16(ws)) return E_BAD_POINTER;
+  const FusedMoeLayout L = fused_moe_layout(type13, type2, dtype, tokens, top_k, n_experts, H, I);
+  if (ws_bytes < L.total) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(ws);
+  int32_t* sorted = reinterpret_cast<int32_t*>(base + L.o_sorted);
+  int32_t* experts = reinterpret_cast<int32_t*>(base + L.o_experts);
+  int32_t* npp = reinterpret_cast<int32_t*>(base + L.o_npp);
+  void* y1 = base + L.o_y1;
+  void* y2 = base + L.o_y2;
+  void* xb = base + L.o_xb;
+  const int64_t slots = tokens * top_k;
+  const int blk = mmq_moe_block_size();
+  // 1. expert-sorted, block-padded slot lists
+  rc = launch_moe_align(topk_ids, slots, (int)n_experts, blk, reinterpret_cast<int32_t*>(base + L.o_counts), sorted, experts, npp, s);
+  if (rc) return rc;
+  // 2. gate/up projection of every routed slot.  Rows of y1 / y2 that belong to slots without a valid
+  //    expert are never written and never read (the final sum skips them), so nothing is zero-filled.
+  const int64_t rb13 = H / block_size(type13) * type_size(type13), rb2 = I / block_size(type2) * type_size(type2);
+  auto gemm = [&](const void* x, int64_t x_rows_div, const void* w, int type, int64_t N, int64_t K, int64_t row_bytes, void* y,
+                  const float* scale, int act_mode, int64_t x_ld) -> int {
+    const int64_t ldb = mmq_ldb(type, K);
+    const int64_t estride = N * row_bytes;
+    const int perm = mmq_perm(type, N, K, true, estride);
+    int r = launch_quantize_q8_1(x, dtype, xb, L.n_sorted, K, Q8_MODE_F16, 0, ldb, mmq_corr_mode(type), sorted, x_rows_div, slots, s,
+                                 perm, nullptr, act_mode, x_ld);
+    if (r) return r;
+    MmqArgs a{};
+    a.perm = perm;
+    a.w = w; a.b = xb; a.y = y;
+    a.type = type; a.out_dtype = dtype; a.b_dtype = DT_F16;
+    a.M = L.n_sorted; a.N = N; a.K = K; a.ldb = ldb;
+    a.corr_mode = mmq_corr_mode(type);
+    a.sorted_ids = sorted;
+    a.expert_ids = experts;
+    a.n_post_pad = npp;
+    a.n_sorted = L.n_sorted;
+    a.expert_stride_bytes = estride;
+    a.top_k = x_rows_div;
+    a.rows_out = slots;
+    a.n_experts = n_experts;
+    a.moe_block = blk;
+    a.row_scale = scale;
+    a.status = st;
+    return launch_mmq(a, s);
+  };
+  rc = gemm(X, top_k, W13, type13, 2 * I, H, rb13, y1, nullptr, 0, 0);
+  if (rc) return rc;
+  // 3. down projection: its activation quantizer applies act(gate) * up on the fly, its epilogue the routing weights
+  rc = gemm(y1, 1, W2, type2, H, I, rb2, y2, topk_weights, act, 2 * I);
+  if (rc) return rc;
+  // 4. sum over the top_k slots of every token
+  return launch_moe_sum(y2, Y, topk_ids, (int)n_experts, tokens, top_k, H, dtype, s);
+}
+
 int gguf_b200_moe_a8_vec(const void* X, const void* W, void* Y, void* ws, int64_t ws_bytes, const int32_t* topk_ids,
                          int64_t n_experts, int type, int dtype, int64_t tokens, int64_t top_k, int64_t N, int64_t K,
                          void* stream) {
@@ -404,7 +524,7 @@ int gguf_b200_moe_a8_vec(const void* X, const void* W, void* Y, void* ws, int64_
   int* st = status_ptr();
   if (!st) return E_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  rc = launch_quantize_q8_1(X, dtype, ws, tokens, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s);
+  rc = launch_quantize_q8_1(X, dtype, ws, tokens, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s);
   if (rc) return rc;
   return launch_moe_gemv(W, ws, Y, topk_ids, type, dtype, tokens, top_k, N, K, n_experts, st, s);
 }

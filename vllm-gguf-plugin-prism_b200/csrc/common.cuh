@@ -23,7 +23,7 @@
 namespace gguf_b200 {
 
 enum : int { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_XS = 23 };
-// further block types, so far served by the standalone dequantize only:
+// further block types (Q2_K and Q3_K: standalone dequantize only):
 //   Q4_1    20 : half d | half m | u8 qs[16]                      value = q*d + m
 //   Q5_0    22 : half d | u8 qh[4] | u8 qs[16]                    5th bit of value j in bit j (j+16: bit j+16... see dequantize.cu)
 //   Q5_1    24 : half d | half m | u8 qh[4] | u8 qs[16]
@@ -62,6 +62,7 @@ template <> struct BlockTraits<T_Q3_K>    { static constexpr int QK = 256, TS = 
 template <> struct BlockTraits<T_Q5_K>    { static constexpr int QK = 256, TS = 176; };
 template <> struct BlockTraits<T_IQ4_NL>  { static constexpr int QK = 32,  TS = 18;  };
 
+// block geometry of the types the matmul entry points take
 __host__ __device__ inline int type_size(int t) {
   switch (t) {
     case T_Q4_0: return 18;
@@ -70,28 +71,29 @@ __host__ __device__ inline int type_size(int t) {
     case T_Q6_K: return 210;
     case T_IQ2_XXS: return 66;
     case T_IQ4_XS: return 136;
+    case T_Q4_1: return 20;
+    case T_Q5_0: return 22;
+    case T_Q5_1: return 24;
+    case T_Q5_K: return 176;
+    case T_IQ4_NL: return 18;
   }
   return 0;
 }
 __host__ __device__ inline int block_size(int t) {
-  return (t == T_Q4_0 || t == T_Q8_0) ? 32 : (type_size(t) ? 256 : 0);
+  switch (t) {
+    case T_Q4_0: case T_Q8_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_IQ4_NL: return 32;
+  }
+  return type_size(t) ? 256 : 0;
 }
 // the same for every type the standalone dequantize knows (a superset of the matmul types)
 __host__ __device__ inline int dequant_type_size(int t) {
   switch (t) {
-    case T_Q4_1: return 20;
-    case T_Q5_0: return 22;
-    case T_Q5_1: return 24;
     case T_Q2_K: return 84;
     case T_Q3_K: return 110;
-    case T_Q5_K: return 176;
-    case T_IQ4_NL: return 18;
   }
   return type_size(t);
 }
-__host__ __device__ inline int dequant_block_size(int t) {
-  return (t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1 || t == T_IQ4_NL) ? 32 : (type_size(t) ? block_size(t) : (dequant_type_size(t) ? 256 : 0));
-}
+__host__ __device__ inline int dequant_block_size(int t) { return type_size(t) ? block_size(t) : (dequant_type_size(t) ? 256 : 0); }
 __host__ __device__ inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 
 // ---- typed stores -----------------------------------------------------------------

@@ -95,9 +95,17 @@ template <bool CONTRACT> __device__ __forceinline__ __half mul_add_value(__half 
 }
 __device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) { return ldg_u16(p) | (ldg_u16(p + 2) << 16); }
 
+// Row gather (embedding look-up: the reference selects the rows with index_select and then
+// dequantizes the copy, quantization/vocal_embeds.py:88-96): output row r = weight row ids[r].
+struct RowGather {
+  const int64_t* ids = nullptr;   // null: plain dequantize of consecutive blocks
+  int64_t row_bytes = 0, weight_rows = 0;
+  int chunks_per_row = 0;         // K / 256
+};
+
 template <int TYPE, typename out_t, bool Q4K_CONTRACT>
-__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ w, out_t* __restrict__ y,
-                                                         int64_t n_elems) {
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ w_all, out_t* __restrict__ y,
+                                                         int64_t n_elems, RowGather rg) {
   __shared__ uint64_t s_grid[TYPE == T_IQ2_XXS ? 256 : 1];
   __shared__ uint8_t s_signs[TYPE == T_IQ2_XXS ? 128 : 1];
   __shared__ int8_t s_kv[16];
@@ -114,11 +122,25 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
   const int lane = threadIdx.x & 31;
   const int64_t chunks = (n_elems + 255) / 256;  // 256 outputs per warp step
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  for (int64_t c = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += warps) {
-    const int64_t o = c * 256 + lane * 8;
+  for (int64_t cg = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); cg < chunks; cg += warps) {
+    const int64_t o = cg * 256 + lane * 8;
     if (o >= n_elems) continue;
     __half h[8];
     float f[8];
+    // chunk c of the block stream that starts at w (gather: the chunk's own weight row)
+    const uint8_t* w = w_all;
+    int64_t c = cg;
+    if (rg.ids) {
+      const int64_t r = cg / rg.chunks_per_row, id = rg.ids[r];
+      c = cg - r * rg.chunks_per_row;
+      if (id < 0 || id >= rg.weight_rows) {   // no such row: zeros (index_select would have refused)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { h[j] = __float2half_rn(0.f); f[j] = 0.f; }
+        Store8<out_t>::st(y + o, h, f, false);
+        continue;
+      }
+      w = w_all + id * rg.row_bytes;
+    }
     if (TYPE == T_Q4_0) {  // dequantize_q4_0: (q - 8) exactly, then one half multiply by d
       const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
       const __half d = __ushort_as_half((unsigned short)ldg_u16(blk));
@@ -288,7 +310,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
 }
 
 template <int TYPE, typename out_t>
-static int launch_t(const void* w, void* out, int64_t n, int q4k_contract, cudaStream_t s) {
+static int launch_t(const void* w, void* out, int64_t n, int q4k_contract, cudaStream_t s, const RowGather& rg) {
   const int64_t chunks = (n + 255) / 256;
   int64_t ctas = (chunks + 7) / 8;
   const int64_t cap = 148 * 32;  // four rounds of the 8 resident CTAs per SM measured best (148*8: -5 %, one CTA per 8 chunks: -25 %)
@@ -296,39 +318,46 @@ static int launch_t(const void* w, void* out, int64_t n, int q4k_contract, cudaS
   if (ctas < 1) ctas = 1;
   constexpr bool fusible = TYPE == T_Q4_K || TYPE == T_Q5_K || TYPE == T_Q2_K || TYPE == T_Q4_1 || TYPE == T_Q5_1;
   if (fusible && q4k_contract)
-    dequantize_kernel<TYPE, out_t, true><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n);
+    dequantize_kernel<TYPE, out_t, true><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n, rg);
   else
-    dequantize_kernel<TYPE, out_t, false><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n);
+    dequantize_kernel<TYPE, out_t, false><<<(int)ctas, 256, 0, s>>>((const uint8_t*)w, (out_t*)out, n, rg);
   return cudaGetLastError() == cudaSuccess ? E_OK : E_CUDA;
 }
 
 template <int TYPE>
-static int launch_d(const void* w, void* out, int dt, int64_t n, int c, cudaStream_t s) {
+static int launch_d(const void* w, void* out, int dt, int64_t n, int c, cudaStream_t s, const RowGather& rg) {
   switch (dt) {
-    case DT_F32: return launch_t<TYPE, float>(w, out, n, c, s);
-    case DT_F16: return launch_t<TYPE, __half>(w, out, n, c, s);
-    case DT_BF16: return launch_t<TYPE, __nv_bfloat16>(w, out, n, c, s);
+    case DT_F32: return launch_t<TYPE, float>(w, out, n, c, s, rg);
+    case DT_F16: return launch_t<TYPE, __half>(w, out, n, c, s, rg);
+    case DT_BF16: return launch_t<TYPE, __nv_bfloat16>(w, out, n, c, s, rg);
   }
   return E_BAD_DTYPE;
 }
 
 int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t n_elems, int q4k_contract,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const int64_t* row_ids, int64_t K, int64_t weight_rows) {
   if (n_elems == 0) return E_OK;
+  RowGather rg;
+  if (row_ids) {
+    rg.ids = row_ids;
+    rg.row_bytes = K / dequant_block_size(type) * dequant_type_size(type);
+    rg.weight_rows = weight_rows;
+    rg.chunks_per_row = (int)(K / 256);
+  }
   switch (type) {
-    case T_Q4_0: return launch_d<T_Q4_0>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q8_0: return launch_d<T_Q8_0>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q4_K: return launch_d<T_Q4_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q6_K: return launch_d<T_Q6_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_IQ2_XXS: return launch_d<T_IQ2_XXS>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_IQ4_XS: return launch_d<T_IQ4_XS>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q4_1: return launch_d<T_Q4_1>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q5_0: return launch_d<T_Q5_0>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q5_1: return launch_d<T_Q5_1>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q2_K: return launch_d<T_Q2_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q3_K: return launch_d<T_Q3_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_Q5_K: return launch_d<T_Q5_K>(w, out, out_dtype, n_elems, q4k_contract, stream);
-    case T_IQ4_NL: return launch_d<T_IQ4_NL>(w, out, out_dtype, n_elems, q4k_contract, stream);
+    case T_Q4_0: return launch_d<T_Q4_0>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q8_0: return launch_d<T_Q8_0>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q4_K: return launch_d<T_Q4_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q6_K: return launch_d<T_Q6_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ2_XXS: return launch_d<T_IQ2_XXS>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ4_XS: return launch_d<T_IQ4_XS>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q4_1: return launch_d<T_Q4_1>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q5_0: return launch_d<T_Q5_0>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q5_1: return launch_d<T_Q5_1>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q2_K: return launch_d<T_Q2_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q3_K: return launch_d<T_Q3_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_Q5_K: return launch_d<T_Q5_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ4_NL: return launch_d<T_IQ4_NL>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
   }
   return E_BAD_TYPE;
 }

@@ -24,6 +24,7 @@ constexpr int G1_WARPS = 8;
 constexpr int G1_BATCH = 32;   // row iterations between two flushes of the slice partials
 constexpr int G1_TAB_COPIES = 16;   // bank-conflict-free copies of the IQ2_XXS code books (see the kernel)
 
+__device__ __forceinline__ __half2 u32_as_half2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 __device__ __forceinline__ int dp4a_us1(uint32_t a, uint32_t b, int c) {
   int d;
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -104,9 +105,11 @@ template <> struct G1<T_Q4_K> {
     const float d = __low2float(dm), dmin = __high2float(dm);
     const int sh = 16 * (p & 1);
     const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, c = hdr.w >> sh;
-    const bool low = p < 2;  // get_scale_min_k4, both cases computed, no branch
-    const uint32_t sc2 = low ? (a & 0x3F3Fu) : ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u));
-    const uint32_t mn2 = low ? (b & 0x3F3Fu) : (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u));
+    // get_scale_min_k4: both cases computed and merged with a mask (lanes of a warp differ in p:
+    // a branch here would run both sides one after the other)
+    const uint32_t lowm = p < 2 ? 0xFFFFFFFFu : 0u;
+    const uint32_t sc2 = ((a & 0x3F3Fu) & lowm) | (((c & 0x0F0Fu) | ((a >> 2) & 0x3030u)) & ~lowm);
+    const uint32_t mn2 = ((b & 0x3F3Fu) & lowm) | ((((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) & ~lowm);
     const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
     const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
     const uint4 qa = lds128s(blk + 16 + 32 * p), qb = lds128s(blk + 32 + 32 * p);
@@ -248,6 +251,144 @@ template <> struct G1<T_IQ2_XXS> {
   }
 };
 
+// ---- Q4_1: value = q*d + m; the min term uses the fp16 sum of the inputs (vecdotq.cuh:72-96) -----
+// Both products of the reference (d*d8 and m*s8) are formed in half precision (__hmul2) before
+// they are widened; the same is done here.
+__device__ __forceinline__ float hmul_f32(float a, float b) {   // a, b hold fp16 values: their product rounded to fp16
+  return __half2float(__hmul(__float2half_rn(a), __float2half_rn(b)));
+}
+template <> struct G1<T_Q4_1> {
+  static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const __half2 dm = u32_as_half2(lds32(blk));            // 20-byte blocks: 4-byte aligned
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t q = lds32(blk + 4 + 4 * i);
+      lo = dp4a_us1(q & 0x0F0F0F0Fu, x[i], lo);
+      hi = dp4a_us1(q & 0xF0F0F0F0u, x[4 + i], hi);
+    }
+    return (float)(lo + (hi >> 4)) * hmul_f32(__low2float(dm), xd[0]) + hmul_f32(__high2float(dm), xd[1]);
+  }
+};
+
+// fifth bits of four values (bits 0..3 of x) moved to bit 4 of the four bytes of a word: the
+// multiplier puts bit k at 8k + 4 and all sixteen partial products fall on different bit positions
+__device__ __forceinline__ uint32_t spread_bit4(uint32_t x) { return ((x & 0xFu) * 0x02040810u) & 0x10101010u; }
+
+// ---- Q5_0: value = (q - 16)*d, q = 4 low bits | fifth bit from qh (vecdotq.cuh:101-129) ------------
+template <> struct G1<T_Q5_0> {
+  static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = lds_half_f32(blk);
+    uint32_t w[5];
+    lds_a2<5>(blk + 2, w);                                    // qh, then 16 bytes of nibbles (2-byte aligned)
+    const uint32_t qh = w[0];
+    int s0 = 0, s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s0 = dp4a_us1((w[1 + i] & 0x0F0F0F0Fu) | spread_bit4(qh >> (4 * i)), x[i], s0);
+      s1 = dp4a_us1(((w[1 + i] >> 4) & 0x0F0F0F0Fu) | spread_bit4(qh >> (16 + 4 * i)), x[4 + i], s1);
+    }
+    return d * ((float)(s0 + s1) * xd[0] - 16.0f * xd[1]);
+  }
+};
+
+// ---- Q5_1: value = q*d + m (vecdotq.cuh:134-163) -------------------------------------------------
+template <> struct G1<T_Q5_1> {
+  static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const uint2 hdr = lds64(blk);                             // 24-byte blocks: 8-byte aligned
+    const __half2 dm = u32_as_half2(hdr.x);
+    const uint32_t qh = hdr.y;
+    const uint2 qa = lds64(blk + 8), qb = lds64(blk + 16);
+    const uint32_t w[4] = {qa.x, qa.y, qb.x, qb.y};
+    int s0 = 0, s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s0 = dp4a_us1((w[i] & 0x0F0F0F0Fu) | spread_bit4(qh >> (4 * i)), x[i], s0);
+      s1 = dp4a_us1(((w[i] >> 4) & 0x0F0F0F0Fu) | spread_bit4(qh >> (16 + 4 * i)), x[4 + i], s1);
+    }
+    return (float)(s0 + s1) * hmul_f32(__low2float(dm), xd[0]) + hmul_f32(__high2float(dm), xd[1]);
+  }
+};
+
+// ---- IQ4_NL: 32 values, levels from the IQ4 table (vecdotq.cuh:1766-1789); see G1<T_IQ4_XS> -------
+template <> struct G1<T_IQ4_NL> {
+  static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_IQ4_XS>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
+    const float d = lds_half_f32(blk);
+    uint32_t q[4];
+    lds_a2<4>(blk + 2, q);
+    int s0 = 0, s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t q3 = q[i] & 0x77777777u;
+      const uint32_t sel = ((q[i] & 0x88888888u) >> 1) | 0x32103210u;
+      s0 = __dp4a((int)G1<T_IQ4_XS>::lut4(q3, sel, t), (int)x[2 * i], s0);
+      s1 = __dp4a((int)G1<T_IQ4_XS>::lut4(q3 >> 16, sel >> 16, t), (int)x[2 * i + 1], s1);
+    }
+    return d * xd[0] * (float)(s0 + s1);
+  }
+};
+
+// ---- Q5_K: like Q4_K with a fifth bit from qh; unit p = 64 values (sub-blocks 2p, 2p+1) ------------
+// (vecdotq.cuh:386-413, 1279-1323; the min term uses d8 * sum(q8), as for Q4_K)
+template <> struct G1<T_Q5_K> {
+  static constexpr int UPB = 4, XW = 16, XD = 4, UMAX = 2;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q4_K>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int p, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const uint4 hdr = lds128s(blk);
+    const __half2 dm = u32_as_half2(hdr.x);
+    const float d = __low2float(dm), dmin = __high2float(dm);
+    const int sh = 16 * (p & 1);
+    const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, c = hdr.w >> sh;
+    // get_scale_min_k4: both cases computed and merged with a mask (lanes of a warp differ in p:
+    // a branch here would run both sides one after the other)
+    const uint32_t lowm = p < 2 ? 0xFFFFFFFFu : 0u;
+    const uint32_t sc2 = ((a & 0x3F3Fu) & lowm) | (((c & 0x0F0Fu) | ((a >> 2) & 0x3030u)) & ~lowm);
+    const uint32_t mn2 = ((b & 0x3F3Fu) & lowm) | ((((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) & ~lowm);
+    const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
+    const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
+    const uint4 ha = lds128s(blk + 16), hb = lds128s(blk + 32);                 // qh[0..31]: bit 2p / 2p+1 of byte l
+    const uint4 qa = lds128s(blk + 48 + 32 * p), qb = lds128s(blk + 64 + 32 * p);
+    const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+    int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const uint32_t hh = h[2 * i + e] >> (2 * p);
+        const uint32_t lo = (q[2 * i + e] & 0x0F0F0F0Fu) | ((hh << 4) & 0x10101010u);
+        const uint32_t hi = ((q[2 * i + e] >> 4) & 0x0F0F0F0Fu) | ((hh << 3) & 0x10101010u);
+        if (e == 0) {
+          a0 = dp4a_us1(lo, x[2 * i], a0);
+          b0 = dp4a_us1(hi, x[8 + 2 * i], b0);
+        } else {
+          a1 = dp4a_us1(lo, x[2 * i + 1], a1);
+          b1 = dp4a_us1(hi, x[8 + 2 * i + 1], b1);
+        }
+      }
+    }
+    return d * (xd[0] * (float)((a0 + a1) * sc0) + xd[2] * (float)((b0 + b1) * sc1)) - dmin * (xd[1] * m0 + xd[3] * m1);
+  }
+};
+
 // ---- kernel ---------------------------------------------------------------------------------
 //
 // Work item of a warp = a group of up to G1_R consecutive rows (x its K-slice).  With one slice
@@ -285,6 +426,7 @@ struct G1Params {
   // vector s / top_k of the xq_vecs quantized ones
   const int32_t* topk_ids;
   int top_k, n_experts, xq_vecs, moe_slots;
+  int vec0;              // dense: first of the MV vectors this launch handles, out of the xq_vecs in the scratch
   int64_t expert_bytes;
   // Tensor-parallel output (world > 0): every result is sent to ALL ranks (this one included) as
   // a packet {value, tag} written with one store into ll_peer[r][y_off + row]; tag = epoch[slot],
@@ -299,7 +441,7 @@ struct G1Params {
 template <typename out_t>
 __device__ __forceinline__ void store_result(const G1Params& p, int64_t row, float v, int m, unsigned tag) {
   if (p.world == 0) {
-    if (p.topk_ids) m = (int)blockIdx.y;   // MoE decode: one output row of y per (token, expert) pair
+    m = p.topk_ids ? (int)blockIdx.y : m + p.vec0;   // MoE decode: one output row of y per (token, expert) pair
     static_cast<out_t*>(p.y)[(int64_t)m * p.n + row] = from_float<out_t>(v);
     return;
   }
@@ -333,7 +475,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kpad = (int)round_up(p.k, 512);
   const uint8_t* wb = p.w;      // this CTA's weight matrix
-  int vec0 = 0;                 // its first activation vector
+  int vec0 = p.vec0;            // its first activation vector
   if (p.topk_ids) {
     const int e = p.topk_ids[blockIdx.y];
     if (e < 0 || e >= p.n_experts) return;   // not a valid expert: the row is left as it is
@@ -357,7 +499,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     tb.grid = smem_u32(g + (lane & (G1_TAB_COPIES - 1)));
     tb.smask = smem_u32(sm + (lane & (G1_TAB_COPIES - 1)));
   }
-  if (TYPE == T_IQ4_XS) {
+  if (TYPE == T_IQ4_XS || TYPE == T_IQ4_NL) {
     const uint32_t* kv = reinterpret_cast<const uint32_t*>(d_kvalues_iq4nl);
 #pragma unroll
     for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
@@ -382,6 +524,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   const uint32_t slice_bytes = (uint32_t)nblk * TS;
   const bool contiguous = p.ks == 1;
   const bool staged = p.ks > 1 || p.world > 0;   // results meet in shared memory before they are stored
+  const bool full_units = __all_sync(0xffffffffu, units == 32 * UMAX);   // every lane of the warp has UMAX units
 
   // ---- which rows: lane_first(l) = first row of row lane l of this CTA, lane_count(l) its rows
   // (contiguous), or first group / number of passes (round-robin) -------------------------------
@@ -542,18 +685,46 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       }
       float acc[MV][G1_R];
 #pragma unroll
-      for (int rr = 0; rr < G1_R; ++rr) {
+      for (int rr = 0; rr < G1_R; ++rr)
 #pragma unroll
         for (int m = 0; m < MV; ++m) acc[m][rr] = 0.f;
-        if (rr < cnt) {
-          const uint32_t data = stage_s + (contiguous ? (uint32_t)(beg0 & 15) + (uint32_t)rr * (uint32_t)row_bytes
-                                                      : (uint32_t)rr * (uint32_t)p.slot_bytes + (uint32_t)((beg0 + rr * row_bytes) & 15));
+      auto row_data = [&](int rr) -> uint32_t {
+        return stage_s + (contiguous ? (uint32_t)(beg0 & 15) + (uint32_t)rr * (uint32_t)row_bytes
+                                     : (uint32_t)rr * (uint32_t)p.slot_bytes + (uint32_t)((beg0 + rr * row_bytes) & 15));
+      };
+      // the common items (whole rows, every lane with all its units): straight-line code, so that
+      // the loads and dot-product chains of all cnt * UMAX units can overlap
+      if (full_units && cnt == 2) {
+        const uint32_t d0 = row_data(0), d1 = row_data(1);
 #pragma unroll
-          for (int j = 0; j < UMAX; ++j)
-            if (lane + 32 * j < units) {
+        for (int j = 0; j < UMAX; ++j)
 #pragma unroll
-              for (int m = 0; m < MV; ++m) acc[m][rr] += T::unit(data + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-            }
+          for (int m = 0; m < MV; ++m) {
+            acc[m][0] += T::unit(d0 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+            acc[m][1] += T::unit(d1 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+          }
+      } else if (full_units && cnt == 3) {
+        const uint32_t d0 = row_data(0), d1 = row_data(1), d2 = row_data(2);
+#pragma unroll
+        for (int j = 0; j < UMAX; ++j)
+#pragma unroll
+          for (int m = 0; m < MV; ++m) {
+            acc[m][0] += T::unit(d0 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+            acc[m][1] += T::unit(d1 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+            acc[m][2] += T::unit(d2 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+          }
+      } else {
+#pragma unroll
+        for (int rr = 0; rr < G1_R; ++rr) {
+          if (rr < cnt) {
+            const uint32_t data = row_data(rr);
+#pragma unroll
+            for (int j = 0; j < UMAX; ++j)
+              if (lane + 32 * j < units) {
+#pragma unroll
+                for (int m = 0; m < MV; ++m) acc[m][rr] += T::unit(data + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+              }
+          }
         }
       }
 #pragma unroll
@@ -617,7 +788,11 @@ template <int TYPE, typename out_t, int MV>
 static int launch_g1(G1Params p, cudaStream_t stream) {
   using T = G1<TYPE>;
   constexpr int TS = BlockTraits<TYPE>::TS;
-  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 16);
+  // Two stages per warp measured best on every shape: with three or more (up to the warp's whole
+  // share) all of a small matrix is requested at once, the memory system serves the requests
+  // interleaved, and every warp's FIRST item arrives late (14336x4096 Q4_K: 9.7 us with 2 stages,
+  // 11.1 with 3, 12.9 with 6).
+  static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 2);
   static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
   static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
   static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 6000);
@@ -663,15 +838,35 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   int fit = (int)(room / ((size_t)G1_WARPS * p.stage_bytes));
   if (fit < 2) return 1;   // not even a double buffer: the general kernel takes the shape
   p.stages = want < fit ? want : fit;
-  const size_t smem = tables + (size_t)p.partial_bytes + (size_t)G1_WARPS * p.stages * p.stage_bytes + (size_t)G1_WARPS * p.stages * 8;
-  if (smem > 227 * 1024) return 1;
-  static size_t configured[64] = {0};
+  auto smem_of = [&](int stages) { return tables + (size_t)p.partial_bytes + (size_t)G1_WARPS * stages * p.stage_bytes + (size_t)G1_WARPS * stages * 8; };
   int dev = 0;
   cudaGetDevice(&dev);
-  if (smem > configured[dev & 63]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return E_CUDA;
-    configured[dev & 63] = smem;
+  static bool carveout_set[64] = {false};
+  if (!carveout_set[dev & 63]) {   // two CTAs of up to 113 KB need (almost) the whole SM as shared memory
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) return E_CUDA;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return E_CUDA;
+    carveout_set[dev & 63] = true;
   }
+  // the deeper ring must not cost the second CTA of an SM: ask the runtime, once per size
+  static int checked_stages[64][17];   // [device][wanted stages] -> stages that keep per_sm CTAs resident (0 = not asked yet), for the last stage size seen
+  static int checked_bytes[64][17];
+  if (per_sm == 2 && p.stages > 2) {
+    int& memo = checked_stages[dev & 63][p.stages];
+    int& memo_b = checked_bytes[dev & 63][p.stages];
+    if (memo == 0 || memo_b != p.stage_bytes + p.partial_bytes + (int)tables) {
+      int st = p.stages, nb = 0;
+      while (st > 2) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, G1_WARPS * 32, smem_of(st)) != cudaSuccess) return E_CUDA;
+        if (nb >= 2) break;
+        --st;
+      }
+      memo = st;
+      memo_b = p.stage_bytes + p.partial_bytes + (int)tables;
+    }
+    p.stages = memo;
+  }
+  const size_t smem = smem_of(p.stages);
+  if (smem > 227 * 1024) return 1;
   unsigned gy = 1;
   if (p.topk_ids) {   // MoE decode: the CTAs are shared out over the (token, expert) pairs
     gy = (unsigned)p.moe_slots;
@@ -701,10 +896,11 @@ static int launch_g1_out(const G1Params& p, int out_dtype, int mv, cudaStream_t 
 
 // Returns E_OK, a negative error, or 1 when the shape is outside this kernel's reach.
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp, int vectors, const GemvMoe* moe) {
+                 cudaStream_t stream, const GemvTp* tp, int vectors, const GemvMoe* moe, int vec0, int total_vecs) {
   G1Params p{};
   if (vectors != 1 && (vectors != 2 || tp || moe)) return 1;
-  p.xq_vecs = vectors;
+  p.xq_vecs = total_vecs > 0 ? total_vecs : vectors;
+  p.vec0 = vec0;
   if (moe) {
     if (tp) return 1;
     const int64_t eb = N * (K / block_size(type)) * type_size(type);
@@ -739,6 +935,11 @@ int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_d
     case T_Q6_K: return launch_g1_out<T_Q6_K>(p, out_dtype, vectors, stream);
     case T_IQ2_XXS: return launch_g1_out<T_IQ2_XXS>(p, out_dtype, vectors, stream);
     case T_IQ4_XS: return launch_g1_out<T_IQ4_XS>(p, out_dtype, vectors, stream);
+    case T_Q4_1: return launch_g1_out<T_Q4_1>(p, out_dtype, vectors, stream);
+    case T_Q5_0: return launch_g1_out<T_Q5_0>(p, out_dtype, vectors, stream);
+    case T_Q5_1: return launch_g1_out<T_Q5_1>(p, out_dtype, vectors, stream);
+    case T_Q5_K: return launch_g1_out<T_Q5_K>(p, out_dtype, vectors, stream);
+    case T_IQ4_NL: return launch_g1_out<T_IQ4_NL>(p, out_dtype, vectors, stream);
   }
   return E_BAD_TYPE;
 }

@@ -10,7 +10,7 @@ namespace gguf_b200 {
 // output layouts of the q8_1 quantizer (quantize_q8_1.cu)
 enum : int { Q8_MODE_REF = 0, Q8_MODE_SOA = 1, Q8_MODE_F16 = 2 };
 // correction column appended to the fp16 activation matrix of the tensor-core kernels
-enum : int { CORR_NONE = 0, CORR_Q4_0 = 1, CORR_MIN = 2 };
+enum : int { CORR_NONE = 0, CORR_Q4_0 = 1, CORR_MIN = 2, CORR_PLUS = 3 };   // B-side column: 8*(d8*sum(q8) - s8), -s8, +s8
 
 // Tensor-parallel input of the SoA quantizer (one vector).  A gathered vector lives on every rank
 // as "packets": one 32-bit word {16-bit value, 16-bit tag} per element for f16/bf16 outputs, one
@@ -31,15 +31,17 @@ struct Q8Tp {
 // input row gather_ids[r] / gather_div; ids outside [0, gather_limit) give a zero row.
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream, int perm = 0, const Q8Tp* tp = nullptr);
+                         cudaStream_t stream, int perm = 0, const Q8Tp* tp = nullptr, int act = 0, int64_t x_ld = 0);
+// act (F16 mode): 0 = none; 1 = silu, 2 = gelu: the input rows are [gate | up] of x_ld = 2K values and act(gate) * up is quantized
 // leading dimension (elements) of the fp16 activation matrix of the tensor-core kernels
 int64_t mmq_ldb(int type, int64_t K);
 int mmq_corr_mode(int type);
 // value order the tensor-core kernel will expect in the fp16 activation matrix for this problem
 int mmq_perm(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_bytes);
 
+// row_ids != null: row gather -- out row r (K values, K a multiple of 256) = weight row row_ids[r] of weight_rows
 int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t n_elems, int q4k_contract,
-                      cudaStream_t stream);
+                      cudaStream_t stream, const int64_t* row_ids = nullptr, int64_t K = 0, int64_t weight_rows = 0);
 
 // Fused dequant-GEMV over SoA q8_1 activations (see quantize_q8_1.cu for the layout).
 // Y[m, n] for m in [0, M); rows of W are N x (K/QK*TS) bytes, contiguous, 16-byte aligned base.
@@ -62,7 +64,10 @@ struct GemvMoe {
   int64_t tokens, top_k, n_experts, slots;
 };
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1, const GemvMoe* moe = nullptr);
+                 cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1, const GemvMoe* moe = nullptr,
+                 int vec0 = 0, int total_vecs = 0);   // vec0 / total_vecs: the `vectors` handled are vec0.. of total_vecs in the scratch
+// 1 when the q8_1 scratch of this type's GEMV must hold d * sum(q) instead of the fp16 sum of the inputs
+inline int gemv_sum_mode(int type) { return (type == 12 || type == 13) ? 1 : 0; }   // Q4_K, Q5_K
 // Packets of `nslots` gathered vectors (slot_packets apart) -> plain vectors out[s][0..n) (out_stride
 // elements apart); every packet is polled until its tag equals epoch[slot0 + s] (bounded).
 // one thread waits (bounded) until flag[slot] has reached world * epoch[slot]
@@ -105,6 +110,7 @@ struct MmqArgs {
   int64_t n_sorted, expert_stride_bytes, top_k, rows_out;
   int64_t n_experts;        // experts in w (0: unknown, ids are only limited to [0, 255] as in the reference)
   int moe_block;
+  const float* row_scale;   // MoE: output row r is multiplied by row_scale[r] (routing weights); null: no scaling
   int* status;
   const MmqTp* tp;          // null: plain output y
   void* part;               // optional fp32 scratch for split-K partial tiles (16-byte aligned), part_bytes long
@@ -116,6 +122,13 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream);
 int mmq_moe_block_size();
 
 int64_t q8_soa_bytes(int64_t M, int64_t K);
+
+// fused MoE step (moe_fused.cu)
+int64_t moe_align_sorted_len(int64_t slots, int n_experts, int block);
+int launch_moe_align(const int32_t* topk_ids, int64_t slots, int n_experts, int block, int32_t* scratch, int32_t* sorted_ids,
+                     int32_t* expert_ids, int32_t* n_post_pad, cudaStream_t stream);
+int launch_moe_sum(const void* y, void* out, const int32_t* topk_ids, int n_experts, int64_t tokens, int64_t top_k, int64_t h,
+                   int dtype, cudaStream_t stream);
 
 // Device address of the library's one status word on the current device (the word that
 // gguf_b200_last_status reads and clears); null if the runtime refuses the lookup.

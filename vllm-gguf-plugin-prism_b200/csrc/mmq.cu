@@ -66,6 +66,8 @@ __host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, in
   return (two || (mmq_groups(type, fast, two) <= 3 && tn > 128)) ? 3 : 4;
 }
 constexpr int MMQ_MAX_RAW = 6;
+// shared memory between the operand rings and the raw ring: barriers, then the decoder's tables
+__host__ __device__ constexpr int mmq_aux_bytes(int type) { return type == T_IQ2_XXS ? 8192 : 4096; }
 constexpr int MMQ_A_STAGE = MMQ_ROWS * MMQ_BK * 2;  // 16 KB
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
@@ -149,7 +151,8 @@ struct MmqParams {
   int64_t expert_stride_bytes, rows_out;
   int* status;
   int n_experts;          // MoE: expert ids outside [0, n_experts) are skipped
-  int raw_tma;            // 1: raw weight chunks arrive by 2-D TMA boxes (wmap), 0: by cp.async pieces
+  const float* row_scale; // MoE: routing weight of every output row (null: none)
+  int raw_tma;            // 1: raw weight chunks arrive as 2-D TMA boxes (wmap), 0: as one 1-D bulk copy per row and chunk
   int raw_stages;         // depth of the raw ring
   int64_t w_row0;         // first row of this matrix in wmap (MoE: added to expert * N)
   int y_tma;              // 1: the output tile leaves through shared memory and one TMA store (ymap)
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
   constexpr int NG = mmq_groups(TYPE, FAST, TWO);
   static_assert(NG <= SA, "a producer group may not lap the A ring");
   constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
-  // raw ring geometry: dense TMA boxes or padded cp.async slots
+  // raw ring geometry: dense TMA boxes, or padded slots that each take one row's bulk copy
   const bool tma = FAST || p.raw_tma;
   const int kc = tma ? TmaGeom<TYPE>::KC_T : RawGeom<TYPE>::KC;
   const int rbc = kc / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;
@@ -214,7 +217,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
   uint8_t* sA = smem;
   uint8_t* sB = smem + SA * MMQ_A_STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB + SB * B_STAGE);
-  uint8_t* sRaw = sB + SB * B_STAGE + 4096;   // barriers and codebooks take the 4 KB in between
+  uint8_t* sRaw = sB + SB * B_STAGE + mmq_aux_bytes(TYPE);   // barriers and decoder tables sit in between
   // One "full" and one "empty" barrier per A slot serve both operands of a stage, so the MMA
   // thread polls and commits once per stage: full[i % SA] collects the warps of the group that
   // decoded stage i plus the B loader's expect-tx arrival and bytes; empty[i % SA] is the
@@ -226,9 +229,9 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
   volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);   // set by any thread whose wait ran out
   uint64_t* raw_full = bars + 34;             // [MMQ_MAX_RAW]
   uint64_t* raw_empty = bars + 34 + MMQ_MAX_RAW;
-  uint64_t* s_grid = bars + 48;
-  uint8_t* s_signs = reinterpret_cast<uint8_t*>(s_grid + 256);
-  int8_t* s_kv = reinterpret_cast<int8_t*>(s_signs + 128);
+  int8_t* s_kv = reinterpret_cast<int8_t*>(bars + 48);                 // 16 bytes
+  uint4* s_sgn = reinterpret_cast<uint4*>(bars + 64);                   // IQ2_XXS: 128 x 16 bytes at offset 512
+  uint2* s_sel = reinterpret_cast<uint2*>(s_sgn + 128);                 // IQ2_XXS: 256 x 8 bytes
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n0 = (int64_t)blockIdx.x * MMQ_ROWS;
@@ -257,10 +260,10 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
     fence_barrier_init();
   }
   if (TYPE == T_IQ2_XXS) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_grid[i] = d_iq2xxs_grid[i];
-    for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = d_ksigns_iq2xs[i];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_sel[i] = iq2xxs_pair_selectors(d_iq2xxs_grid[i]);
+    for (int i = threadIdx.x; i < 128; i += blockDim.x) s_sgn[i] = iq2xxs_pair_signs(d_ksigns_iq2xs[i]);
   }
-  if (TYPE == T_IQ4_XS && threadIdx.x < 16) s_kv[threadIdx.x] = d_kvalues_iq4nl[threadIdx.x];
+  if ((TYPE == T_IQ4_XS || TYPE == T_IQ4_NL) && threadIdx.x < 16) s_kv[threadIdx.x] = d_kvalues_iq4nl[threadIdx.x];
   if (warp == MMQ_PRODUCER_WARPS) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
@@ -280,35 +283,9 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
     const int64_t n = n0 + r;
     const bool live = n < p.N;
     const uint8_t* row = wbase + (live ? n : 0) * p.row_bytes;
-    DecodeCtx cx{s_grid, s_signs, s_kv};
+    DecodeCtx cx{s_sel, s_sgn, s_kv};
     const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
     const int nunits = (int)((p.K + 31) / 32);   // 32-value units of a row that exist
-    const int64_t tile_end = (int64_t)p.N * p.row_bytes;   // bytes of this weight matrix (expert)
-    // cp.async staging (shapes the TMA boxes cannot serve): warp w copies rows w, w+8, ... of the
-    // tile, one coalesced 16-byte piece per lane and row, one chunk ahead of the decode.
-    auto issue_chunk = [&](int c) {
-      uint8_t* slot0 = sRaw + (size_t)(c % 2) * RAW_STAGE;
-      for (int rr = warp; rr < MMQ_ROWS; rr += MMQ_PRODUCER_WARPS) {
-        const int64_t nn = n0 + rr;
-        if (nn >= p.N) break;
-        const int64_t beg = nn * p.row_bytes + (int64_t)(c + c_begin) * rbc;
-        int64_t end = beg + rbc;
-        const int64_t row_end = (nn + 1) * p.row_bytes;
-        if (end > row_end) end = row_end;
-        const int64_t a0 = beg & ~int64_t(15);
-        const int64_t off = a0 + 16 * (int64_t)lane;
-        if (off < end) {
-          uint8_t* dst = slot0 + (size_t)rr * slot + 16 * lane;
-          if (off + 16 <= tile_end) {
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(wbase + off) : "memory");
-          } else {  // last bytes of the buffer: never read past its end
-            for (int64_t o = off; o < tile_end; o += 2)
-              *reinterpret_cast<uint16_t*>(dst + (o - off)) = *reinterpret_cast<const uint16_t*>(wbase + o);
-          }
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
     int s = g;                 // A slot of this group's next stage and its phase
     uint32_t ph = 0;
     while (s >= SA) { s -= SA; ph ^= 1u; }
@@ -329,15 +306,8 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
     uint32_t rph = 0;
     auto run = [&](auto G) {
       constexpr int GI = decltype(G)::value;
-      if (!tma) issue_chunk(0);
-      for (int c = 0; c < nchunks; ++c) {   // runs to the end even after a time-out: the cp.async path meets at a barrier
-        if (tma) {
-          if (ok && !wait_or_note(&raw_full[rs], rph, 1, c)) ok = false;
-        } else {
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
-          asm volatile("bar.sync 1, %0;" ::"n"(MMQ_PRODUCER_WARPS * 32) : "memory");   // chunk c landed for everyone; chunk c-1 fully decoded
-          if (c + 1 < nchunks) issue_chunk(c + 1);
-        }
+      for (int c = 0; c < nchunks; ++c) {
+        if (ok && !wait_or_note(&raw_full[rs], rph, 1, c)) ok = false;
         if constexpr (FAST) {
           const uint8_t* chunk = sRaw + (size_t)rs * RAW_STAGE + (size_t)r * TmaGeom<TYPE>::RBC_T;
           auto stage = [&](auto SCc) {
@@ -354,7 +324,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
         } else {
           // row pointer such that (pointer + byte offset in the row) lands in this thread's slot of chunk c
           const int64_t beg = n * p.row_bytes + (int64_t)(c + c_begin) * rbc;
-          const uint8_t* srow = sRaw + (size_t)(tma ? rs : (c & 1)) * RAW_STAGE + (size_t)r * slot + (tma ? 0 : (beg & 15)) - (int64_t)(c + c_begin) * rbc;
+          const uint8_t* srow = sRaw + (size_t)rs * RAW_STAGE + (size_t)r * slot + (tma ? 0 : (beg & 15)) - (int64_t)(c + c_begin) * rbc;
           for (int i = c * SPC + GI; i < (c + 1) * SPC && i < nmain && ok; i += NG) {
             uint32_t v[32];
 #pragma unroll
@@ -374,11 +344,10 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
             ok = publish(v, i);
           }
         }
-        if (tma) {   // this warp is done reading the raw chunk: hand the slot back to the loader
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&raw_empty[rs]);
-          if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
-        }
+        // this warp is done reading the raw chunk: hand the slot back to the loader
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
       }
       // correction columns (Q4_0 / Q4_K): a few stages at the end, straight from global memory
       int i0 = nmain;
@@ -472,7 +441,12 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
           } else {
             orow = t < p.M ? t : p.rows_out;
           }
-          if (live && orow < p.rows_out) y[orow * p.N + n] = from_float<out_t>(__uint_as_float(acc[j]));
+          if (live && orow < p.rows_out) {
+            out_t o = from_float<out_t>(__uint_as_float(acc[j]));
+            // routing weight applied as the reference applies it: to the stored value, rounded again
+            if (MOE && p.row_scale) o = from_float<out_t>(to_float<out_t>(o) * p.row_scale[orow]);
+            y[orow * p.N + n] = o;
+          }
         }
       }
     }
@@ -496,16 +470,65 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
       }
     }
   } else if (warp == MMQ_PRODUCER_WARPS + 2) {
-    // ---------------- raw-weight loader: one 2-D TMA box (chunk bytes x 128 rows) per chunk ----------------
-    if (lane == 0 && tma) {
-      int64_t wrow = p.w_row0 + n0;
-      if (MOE) wrow += (int64_t)p.expert_ids[blockIdx.y] * p.N;
+    // ---------------- raw-weight loader ----------------
+    if (tma) {
+      // one 2-D TMA box (chunk bytes x 128 rows) per chunk
+      if (lane == 0) {
+        int64_t wrow = p.w_row0 + n0;
+        if (MOE) wrow += (int64_t)p.expert_ids[blockIdx.y] * p.N;
+        int st = 0;
+        uint32_t sph = 0;
+        for (int c = 0; c < nchunks; ++c) {
+          if (!wait_or_note(&raw_empty[st], sph ^ 1u, 5, c)) { ok = false; break; }
+          mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
+          tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, (c + c_begin) * (rbc / 4), (int)wrow, &raw_full[st]);
+          if (++st == p.raw_stages) { st = 0; sph ^= 1u; }
+        }
+      }
+    } else {
+      // Rows that no tensor map can describe (row bytes not a multiple of 16, or chunk starts that are
+      // only 2-byte aligned): one 1-D bulk copy per row and chunk, from the row's chunk address rounded
+      // down to 16 bytes into the row's padded slot, so the decoders index from the remainder.  Lane l
+      // issues the copies of rows l, l + 32, l + 64, l + 96; all of them complete on the chunk's barrier.
+      // Nothing is read past the weight buffer: its last (< 16) bytes are fetched with plain loads.
+      const int64_t tile_end = (int64_t)p.N * p.row_bytes;   // bytes of this weight matrix (expert)
+      const int64_t safe_end = tile_end & ~int64_t(15);
       int st = 0;
       uint32_t sph = 0;
       for (int c = 0; c < nchunks; ++c) {
-        if (!wait_or_note(&raw_empty[st], sph ^ 1u, 5, c)) { ok = false; break; }
-        mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
-        tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, (c + c_begin) * (rbc / 4), (int)wrow, &raw_full[st]);
+        const bool got = wait_or_note(&raw_empty[st], sph ^ 1u, 5, c);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        uint8_t* stage = sRaw + (size_t)st * RAW_STAGE;
+        int64_t a0[4], a1[4];
+        uint32_t total = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int rr = lane + 32 * q;
+          const int64_t nn = n0 + rr;
+          a0[q] = a1[q] = 0;
+          if (nn < p.N) {
+            const int64_t beg = nn * p.row_bytes + (int64_t)(c + c_begin) * rbc;
+            int64_t end = beg + rbc;
+            const int64_t row_end = (nn + 1) * p.row_bytes;
+            if (end > row_end) end = row_end;
+            if (end > beg) {
+              a0[q] = beg & ~int64_t(15);
+              a1[q] = (end + 15) & ~int64_t(15);
+              if (a1[q] > safe_end) {   // the buffer's ragged tail: plain loads, visible through the barrier below
+                for (int64_t o = safe_end > a0[q] ? safe_end : a0[q]; o < end; ++o) stage[(size_t)rr * slot + (o - a0[q])] = wbase[o];
+                a1[q] = safe_end;
+              }
+              if (a1[q] > a0[q]) total += (uint32_t)(a1[q] - a0[q]);
+              else a1[q] = a0[q];
+            }
+          }
+        }
+        if (total) asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&raw_full[st])), "r"(total) : "memory");
+        __syncwarp();   // every lane's byte count is registered before any copy can complete and before the arrival
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (a1[q] > a0[q]) bulk_g2s(stage + (size_t)(lane + 32 * q) * slot, wbase + a0[q], (uint32_t)(a1[q] - a0[q]), &raw_full[st]);
+        if (lane == 0) mbar_arrive(&raw_full[st]);
         if (++st == p.raw_stages) { st = 0; sph ^= 1u; }
       }
     }
@@ -691,10 +714,10 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return E_CUDA;
   }
-  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TWO, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TWO, TN) * TN * MMQ_BK * 2 + 4096;
+  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TWO, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TWO, TN) * TN * MMQ_BK * 2 + mmq_aux_bytes(TYPE);
   const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
   const size_t budget = (TWO ? 113 : 226) * 1024;   // two CTAs share the SM's 228 KB (1 KB each is reserved)
-  int rs = raw_tma ? (int)((budget - ab_bytes) / raw_stage) : 2;
+  int rs = (int)((budget - ab_bytes) / raw_stage);
   if (rs > MMQ_MAX_RAW) rs = MMQ_MAX_RAW;
   if (rs < 2) rs = 2;
   pp.raw_tma = raw_tma ? 1 : 0;
@@ -804,7 +827,7 @@ static int launch_shape(const MmqArgs& a, const MmqParams& p, cudaStream_t s) {
     case 128: return launch_tn<TYPE, ab_t, out_t, 128, false>(a, p, a.M, s);
     default: {
       const int rc = launch_tn<TYPE, ab_t, out_t, 256, false>(a, p, a.M, s);
-      // (padded cp.async staging of the widest rows does not fit beside three 256-token stages)
+      // (two padded raw chunks of the widest rows do not fit beside three 256-token stages)
       return rc == E_TOO_LARGE ? launch_tn<TYPE, ab_t, out_t, 128, false>(a, p, a.M, s) : rc;
     }
   }
@@ -838,6 +861,7 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
   p.expert_stride_bytes = a.expert_stride_bytes;
   p.rows_out = a.rows_out;
   p.status = a.status;
+  p.row_scale = a.row_scale;
   if (a.tp) {
     // the tile leaves through shared memory, in 16-byte pieces: rows and column offsets must allow it
     if (a.sorted_ids || a.tp->world < 1 || a.tp->world > 8 || a.N % 8 != 0 || a.tp->col_off % 8 != 0 || a.tp->ld % 8 != 0) return E_BAD_SHAPE;
@@ -859,6 +883,10 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
     case T_Q8_0: return bf ? E_BAD_DTYPE : launch_out<T_Q8_0, __half>(a, p, stream);
     case T_Q4_K: return bf ? E_BAD_DTYPE : launch_out<T_Q4_K, __half>(a, p, stream);
     case T_Q6_K: return bf ? E_BAD_DTYPE : launch_out<T_Q6_K, __half>(a, p, stream);
+    case T_Q4_1: return bf ? E_BAD_DTYPE : launch_out<T_Q4_1, __half>(a, p, stream);
+    case T_Q5_0: return bf ? E_BAD_DTYPE : launch_out<T_Q5_0, __half>(a, p, stream);
+    case T_Q5_1: return bf ? E_BAD_DTYPE : launch_out<T_Q5_1, __half>(a, p, stream);
+    case T_Q5_K: return bf ? E_BAD_DTYPE : launch_out<T_Q5_K, __half>(a, p, stream);
     // the dequantize-then-matmul route computes and returns in the activations' own 16-bit type
     case T_IQ2_XXS:
       if (a.out_dtype != a.b_dtype) return E_BAD_DTYPE;
@@ -866,6 +894,9 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
     case T_IQ4_XS:
       if (a.out_dtype != a.b_dtype) return E_BAD_DTYPE;
       return bf ? launch_shape<T_IQ4_XS, __nv_bfloat16, __nv_bfloat16>(a, p, stream) : launch_shape<T_IQ4_XS, __half, __half>(a, p, stream);
+    case T_IQ4_NL:
+      if (a.out_dtype != a.b_dtype) return E_BAD_DTYPE;
+      return bf ? launch_shape<T_IQ4_NL, __nv_bfloat16, __nv_bfloat16>(a, p, stream) : launch_shape<T_IQ4_NL, __half, __half>(a, p, stream);
   }
   return E_BAD_TYPE;
 }

@@ -50,10 +50,32 @@ __device__ __forceinline__ uint32_t word_at(const uint32_t* r, int i, uint32_t s
 __device__ __forceinline__ uint32_t shift_of(const uint8_t* p) { return (uint32_t)(reinterpret_cast<uintptr_t>(p) & 3) * 8u; }
 
 struct DecodeCtx {
-  const uint64_t* grid;   // IQ2_XXS tables in shared memory
-  const uint8_t* signs;
+  const uint2* sel;       // IQ2_XXS: per grid entry, the byte-permute selectors of its four value pairs (see Decoder<T_IQ2_XXS>)
+  const uint4* sgn;       // IQ2_XXS: per 7-bit sign index, the sign-bit masks of the four value pairs
   const int8_t* kv;       // IQ4_XS levels in shared memory
 };
+// Shared-memory tables of the IQ2_XXS decoder, built once per CTA from the format's grid and
+// sign tables.  A grid entry holds eight magnitudes, each one of {8, 25, 43}; with the three
+// products d*8, d*25, d*43 of a 32-value group rounded to 16 bits and parked in two registers,
+// every PAIR of decoded values is one byte-permute whose 16-bit selector depends only on the grid
+// entry -- those selectors are what the table holds -- and the signs are one XOR per pair.
+__device__ __forceinline__ uint2 iq2xxs_pair_selectors(uint64_t grid_entry) {
+  uint32_t s[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t m = (uint32_t)(grid_entry >> (8 * j)) & 0xFFu;
+    const uint32_t c = (m > 8u ? 1u : 0u) + (m > 25u ? 1u : 0u);   // which of the three magnitudes
+    const uint32_t nib = (2u * c) | ((2u * c + 1u) << 4);           // its two bytes in the register pair
+    s[j >> 2] |= nib << (8 * (j & 3));
+  }
+  return make_uint2(s[0], s[1]);
+}
+__device__ __forceinline__ uint4 iq2xxs_pair_signs(uint32_t sign_bits) {
+  uint32_t m[4];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) m[p] = (((sign_bits >> (2 * p)) & 1u) << 15) | (((sign_bits >> (2 * p + 1)) & 1u) << 31);
+  return make_uint4(m[0], m[1], m[2], m[3]);
+}
 
 template <int TYPE, typename ab_t> struct Decoder;
 
@@ -197,6 +219,150 @@ template <typename ab_t> struct Decoder<T_Q4_K, ab_t> {
   }
 };
 
+// ---- Q4_1: A = half(q * d); the min term m * s8 is a correction column (B side: +s8) -----------------
+template <typename ab_t> struct Decoder<T_Q4_1, ab_t> {
+  static constexpr int RW = 5;   // 20 bytes, 4-byte aligned
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint32_t* b = reinterpret_cast<const uint32_t*>(row + (int64_t)u * 20);
+#pragma unroll
+    for (int i = 0; i < 5; ++i) raw[i] = b[i];
+  }
+  static __device__ __forceinline__ void decode(const uint8_t*, int, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const uint32_t du = raw[0] & 0xFFFFu;
+    const __half2 d2 = u32_as_h2(du | (du << 16)), off = __floats2half2_rn(1024.f, 1024.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // half-word i of the nibble bytes holds qs[2i], qs[2i+1]
+      const uint32_t wv = raw[1 + (i >> 1)];
+      const uint32_t t = (i & 1) ? (wv >> 16) : (wv & 0xFFFFu);
+      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(t & 0xF, (t >> 8) & 0xF), off), d2));
+      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((t >> 4) & 0xF, (t >> 12) & 0xF), off), d2));
+    }
+  }
+  // correction columns [32c, 32c+32): A'[n, g] = m of block g
+  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t g = 32 * (int64_t)c + 2 * i;
+      const uint32_t a = g * 32 < K ? ldg16(row + g * 20 + 2) : 0u;
+      const uint32_t b = (g + 1) * 32 < K ? ldg16(row + (g + 1) * 20 + 2) : 0u;
+      out[i] = a | (b << 16);
+    }
+  }
+};
+
+// fifth bits: bit j of qh belongs to value j
+__device__ __forceinline__ uint32_t q5_code(uint32_t nib, uint32_t qh, int j) { return nib | (((qh >> j) & 1u) << 4); }
+
+// ---- Q5_0: value = half((q - 16) * d), 22-byte blocks (2-byte aligned): d | qh[4] | qs[16] ------------
+template <typename ab_t> struct Decoder<T_Q5_0, ab_t> {
+  static constexpr int RW = 8;   // 22 bytes at 2-byte alignment: <= 6 words (+ shifts)
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    ldg_cover<7>(row + (int64_t)u * 22, 22, raw);
+    raw[7] = 0;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const uint32_t sh = shift_of(row + (int64_t)u * 22);
+    const uint32_t w0 = word_at(raw, 0, sh), w1 = word_at(raw, 1, sh);
+    const uint32_t du = w0 & 0xFFFFu, qh = (w0 >> 16) | (w1 << 16);
+    const __half2 d2 = u32_as_h2(du | (du << 16)), off = __floats2half2_rn(1040.f, 1040.f);   // 1024 + 16
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // half-word 3+i of the block holds qs[2i], qs[2i+1]
+      const int h = 3 + i;
+      const uint32_t wv = word_at(raw, h >> 1, sh);
+      const uint32_t t = (h & 1) ? (wv >> 16) : (wv & 0xFFFFu);
+      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code(t & 0xF, qh, 2 * i), q5_code((t >> 8) & 0xF, qh, 2 * i + 1)), off), d2));
+      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code((t >> 4) & 0xF, qh, 16 + 2 * i), q5_code((t >> 12) & 0xF, qh, 17 + 2 * i)), off), d2));
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+// ---- Q5_1: A = half(q * d), 24-byte blocks (8-byte aligned): d | m | qh[4] | qs[16]; correction column m ----
+template <typename ab_t> struct Decoder<T_Q5_1, ab_t> {
+  static constexpr int RW = 6;
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint2* b = reinterpret_cast<const uint2*>(row + (int64_t)u * 24);
+    const uint2 a0 = b[0], a1 = b[1], a2 = b[2];
+    raw[0] = a0.x; raw[1] = a0.y; raw[2] = a1.x; raw[3] = a1.y; raw[4] = a2.x; raw[5] = a2.y;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t*, int, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const uint32_t du = raw[0] & 0xFFFFu, qh = raw[1];
+    const __half2 d2 = u32_as_h2(du | (du << 16)), off = __floats2half2_rn(1024.f, 1024.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t wv = raw[2 + (i >> 1)];
+      const uint32_t t = (i & 1) ? (wv >> 16) : (wv & 0xFFFFu);
+      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code(t & 0xF, qh, 2 * i), q5_code((t >> 8) & 0xF, qh, 2 * i + 1)), off), d2));
+      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code((t >> 4) & 0xF, qh, 16 + 2 * i), q5_code((t >> 12) & 0xF, qh, 17 + 2 * i)), off), d2));
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t g = 32 * (int64_t)c + 2 * i;
+      const uint32_t a = g * 32 < K ? ldg16(row + g * 24 + 2) : 0u;
+      const uint32_t b = (g + 1) * 32 < K ? ldg16(row + (g + 1) * 24 + 2) : 0u;
+      out[i] = a | (b << 16);
+    }
+  }
+};
+
+// ---- Q5_K: A = half(d1 * q), d1 = half(d * sc), q = 4 bits of qs | fifth bit of qh; -dmin*m is a correction column ----
+// 176-byte blocks (16-byte aligned): d | dmin | scales[12] | qh[32] | qs[128].  unit u: sub-block j = u&7:
+// nibble (j&1) of qs[32*(j>>1) + l], bit j of qh[l], l = 0..31.
+template <typename ab_t> struct Decoder<T_Q5_K, ab_t> {
+  static constexpr int RW = 20;  // header (16) + 32 bytes of nibbles + 32 bytes of high bits
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 176;
+    const uint4 h = *reinterpret_cast<const uint4*>(blk);
+    const uint4* qp = reinterpret_cast<const uint4*>(blk + 48 + 32 * ((u >> 1) & 3));
+    const uint4* hp = reinterpret_cast<const uint4*>(blk + 16);
+    const uint4 a = qp[0], b = qp[1], c = hp[0], e = hp[1];
+    raw[0] = h.x; raw[1] = h.y; raw[2] = h.z; raw[3] = h.w;
+    raw[4] = a.x; raw[5] = a.y; raw[6] = a.z; raw[7] = a.w; raw[8] = b.x; raw[9] = b.y; raw[10] = b.z; raw[11] = b.w;
+    raw[12] = c.x; raw[13] = c.y; raw[14] = c.z; raw[15] = c.w; raw[16] = e.x; raw[17] = e.y; raw[18] = e.z; raw[19] = e.w;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t*, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const int j = u & 7, sh = 4 * (j & 1);
+    const __half dall = __ushort_as_half((unsigned short)(raw[0] & 0xffff));
+    int sc, m;
+    q4k_scale_min(raw[1], raw[2], raw[3], j, sc, m);
+    (void)m;
+    const __half2 dv = __half2half2(__hmul_rn(dall, __int2half_rn(sc)));
+    const __half2 off = __floats2half2_rn(1024.f, 1024.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // word i: bytes 4i..4i+3 -> values 4i..4i+3 of this sub-block
+      const uint32_t w = raw[4 + i] >> sh, hb = (raw[12 + i] >> j) & 0x01010101u;
+      const uint32_t c0 = (w & 0xF) | ((hb & 1u) << 4), c1 = ((w >> 8) & 0xF) | (((hb >> 8) & 1u) << 4);
+      const uint32_t c2 = ((w >> 16) & 0xF) | (((hb >> 16) & 1u) << 4), c3 = ((w >> 24) & 0xF) | (((hb >> 24) & 1u) << 4);
+      out[2 * i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(c0, c1), off), dv));
+      out[2 * i + 1] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(c2, c3), off), dv));
+    }
+  }
+  // correction columns [32c, 32c+32): A'[n, g] = half(dmin * m_g)  (pairs with -s8 on the B side)
+  static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int sb = 0; sb < 4; ++sb) {
+      const int64_t sbi = 4 * (int64_t)c + sb;
+      if (sbi * 256 >= K) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[4 * sb + i] = 0;
+        continue;
+      }
+      const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(row + sbi * 176));
+      const __half dmin = __ushort_as_half((unsigned short)(hdr.x >> 16));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int sc, ma, mb;
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * i, sc, ma);
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * i + 1, sc, mb);
+        out[4 * sb + i] = (uint32_t)__half_as_ushort(__hmul_rn(dmin, __int2half_rn(ma))) |
+                          ((uint32_t)__half_as_ushort(__hmul_rn(dmin, __int2half_rn(mb))) << 16);
+      }
+    }
+  }
+};
+
 // ---- Q6_K: value = half(d * half(sc * (code - 32))) ------------------------------------------
 // unit u: super-block u>>3, group g = u&7: ip = g>>2 (128-value half), q = g&3:
 //   low 4 bits = nibble (q>>1) of ql[64ip + 32(q&1) + l], high 2 bits = bits 2q.. of qh[32ip + l], l = 0..31,
@@ -266,7 +432,31 @@ template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
 };
 
+// ---- IQ4_NL: fp32 d*level rounded once to ab_t; unit = one 18-byte block (2-byte aligned) ----------
+template <typename ab_t> struct Decoder<T_IQ4_NL, ab_t> {
+  static constexpr int RW = 7;
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    ldg_cover<RW - 1>(row + (int64_t)u * 18, 18, raw);
+    raw[RW - 1] = 0;
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx& cx, uint32_t (&out)[16]) {
+    const uint32_t sh = shift_of(row + (int64_t)u * 18);
+    const float d = __half2float(__ushort_as_half((unsigned short)(word_at(raw, 0, sh) & 0xFFFFu)));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // stream half-word 1+i holds qs[2i], qs[2i+1]
+      const int h = 1 + i;
+      const uint32_t wv = word_at(raw, h >> 1, sh);
+      const uint32_t t = (h & 1) ? (wv >> 16) : (wv & 0xFFFFu);
+      out[i] = pack2<ab_t>(d * (float)cx.kv[t & 0xF], d * (float)cx.kv[(t >> 8) & 0xF]);
+      out[8 + i] = pack2<ab_t>(d * (float)cx.kv[(t >> 4) & 0xF], d * (float)cx.kv[(t >> 12) & 0xF]);
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
 // ---- IQ2_XXS: fp32 d*(0.5+s)*0.25*grid*sign rounded once; unit = 32-value group ib = u&7 ----------
+// (value = +-round(d * magnitude): the product is formed in fp32 and rounded once, as in the
+// reference; multiplying by -1.f afterwards is exact, so flipping the sign bit is the same)
 template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
   static constexpr int RW = 5;   // [0] word holding d, [1..3] the group's 8 bytes (+ cover), [4] pad
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
@@ -281,16 +471,16 @@ template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
     const uint32_t sh = shift_of(blk + 2 + 8 * (u & 7));
     const uint32_t idx = word_at(raw + 1, 0, sh), aux = word_at(raw + 1, 1, sh);
     const float d = dh * (0.5f + (float)(aux >> 28)) * 0.25f;
+    // the three possible magnitudes of this group, each rounded once (the sign flips only the top bit)
+    const uint32_t r0 = pack2<ab_t>(d * 8.f, d * 25.f), r1 = pack2<ab_t>(d * 43.f, 0.f);
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
-      const uint64_t g = cx.grid[(idx >> (8 * il)) & 0xFF];
-      const uint32_t sg = cx.signs[(aux >> (7 * il)) & 127];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = d * (float)((uint32_t)(g >> (16 * j)) & 0xFF) * ((sg >> (2 * j)) & 1 ? -1.f : 1.f);
-        const float b = d * (float)((uint32_t)(g >> (16 * j + 8)) & 0xFF) * ((sg >> (2 * j + 1)) & 1 ? -1.f : 1.f);
-        out[4 * il + j] = pack2<ab_t>(a, b);
-      }
+      const uint2 sel = cx.sel[(idx >> (8 * il)) & 0xFF];
+      const uint4 sg = cx.sgn[(aux >> (7 * il)) & 127];
+      out[4 * il + 0] = __byte_perm(r0, r1, sel.x) ^ sg.x;
+      out[4 * il + 1] = __byte_perm(r0, r1, sel.x >> 16) ^ sg.y;
+      out[4 * il + 2] = __byte_perm(r0, r1, sel.y) ^ sg.z;
+      out[4 * il + 3] = __byte_perm(r0, r1, sel.y >> 16) ^ sg.w;
     }
   }
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}

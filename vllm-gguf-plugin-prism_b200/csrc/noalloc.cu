@@ -74,7 +74,7 @@ int gguf_b200_mul_mat_vec_a8_noalloc(const void* W, const void* X, void* Y, int 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The quantizer rewrites every byte of the scratch that the GEMV will read (codes up to the
   // padded K and one {d, sum} pair per 32), so nothing has to be cleared between calls.
-  int rc = launch_quantize_q8_1(X, dtype, dp.scratch, M, K, Q8_MODE_SOA, type == T_Q4_K ? 1 : 0, 0, CORR_NONE, nullptr, 1, 0, s);
+  int rc = launch_quantize_q8_1(X, dtype, dp.scratch, M, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s);
   if (rc) return rc;
   return launch_gemv(W, dp.scratch, Y, type, dtype, M, N, K, dp.status, s);
 }

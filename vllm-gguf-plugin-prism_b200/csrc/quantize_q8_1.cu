@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
           const float s8 = __half2float(hs);
           float c;
           if (corr_mode == CORR_Q4_0) c = 8.0f * (d8 * (float)qs - s8);  // weights stored as (q-8): add back 8*d*(d8*sum(q) - s8)
-          else c = -s8;                                                  // CORR_MIN: minus min * s8
+          else c = corr_mode == CORR_PLUS ? s8 : -s8;                    // CORR_PLUS: + m * s8;  CORR_MIN: minus min * s8
           xb[row * ldb + kpad + kb] = __float2half_rn(c);
         }
         // zero the tail of the correction area so that padded contraction columns contribute nothing
@@ -144,11 +144,22 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
 // ^2, lane ^1) and the last three are adds inside the thread, in the same order, so the fp32 sum
 // has the same bits.  perm = 1 stores every group of four values in the order (0,2,1,3) (see
 // Stage64 in mmq_decode.cuh).
+// act != 0 (fused MoE step): the input rows are [gate | up] of x_ld = 2K values and the value that
+// is quantized is act(gate) * up, formed as the reference's separate activation op forms it --
+// silu(g) = g / (1 + exp(-g)) (gelu: 0.5 g (1 + erf(g / sqrt 2))) rounded to the activation type,
+// then multiplied by up in that type (one more rounding) -- so the activated matrix never exists
+// in memory.  (This file is built with fast-math: exp() is the hardware approximation, which can
+// move the rounded silu by one unit in the last place in rare cases.)
+template <typename in_t> __device__ __forceinline__ float act_mul(int act, float g, float u) {
+  const float a = act == 1 ? g / (1.0f + expf(-g)) : 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
+  return to_float<in_t>(from_float<in_t>(to_float<in_t>(from_float<in_t>(a)) * u));
+}
+
 template <typename in_t>
 __global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restrict__ x, __half* __restrict__ xb, int64_t M, int64_t K,
                                                              int64_t kpad, int64_t ldb, int corr_mode, int perm,
                                                              const int32_t* __restrict__ gather_ids, int64_t gather_div,
-                                                             int64_t gather_limit) {
+                                                             int64_t gather_limit, int act, int64_t x_ld) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, t = lane & 3;
@@ -170,7 +181,19 @@ __global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restr
       src = have ? id / gather_div : 0;
     }
     float v[8];
-    if (have && k + 8 <= K) {
+    if (act) {
+      if (have && k + 8 <= K && sizeof(in_t) == 2 && K % 8 == 0 && x_ld % 8 == 0) {
+        const uint4 ga = *reinterpret_cast<const uint4*>(x + src * x_ld + k), ua = *reinterpret_cast<const uint4*>(x + src * x_ld + K + k);
+        const in_t* ge = reinterpret_cast<const in_t*>(&ga);
+        const in_t* ue = reinterpret_cast<const in_t*>(&ua);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = act_mul<in_t>(act, to_float<in_t>(ge[j]), to_float<in_t>(ue[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (have && k + j < K) ? act_mul<in_t>(act, to_float<in_t>(x[src * x_ld + k + j]), to_float<in_t>(x[src * x_ld + K + k + j])) : 0.0f;
+      }
+    } else if (have && k + 8 <= K) {
       if (sizeof(in_t) == 4) {
         const float4 a = *reinterpret_cast<const float4*>(x + src * K + k), c = *reinterpret_cast<const float4*>(x + src * K + k + 4);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
@@ -224,7 +247,7 @@ __global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restr
       qs += __shfl_xor_sync(0xffffffffu, qs, 1, 32);
       if (inb && t == 0) {
         const float s8 = __half2float(hs);
-        const float c = corr_mode == CORR_Q4_0 ? 8.0f * (d8 * (float)qs - s8) : -s8;   // see quantize_q8_1_kernel
+        const float c = corr_mode == CORR_Q4_0 ? 8.0f * (d8 * (float)qs - s8) : (corr_mode == CORR_PLUS ? s8 : -s8);   // see quantize_q8_1_kernel
         xb[row * ldb + kpad + kb] = __float2half_rn(c);
       }
       if (inb && kb == 0)
@@ -258,7 +281,7 @@ static int launch_mode(const void* x, int x_dtype, void* out, int64_t M, int64_t
 }
 
 static int launch_f16x8(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int64_t ldb, int corr_mode, int perm,
-                        const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream) {
+                        const int32_t* gid, int64_t gdiv, int64_t glim, cudaStream_t stream, int act, int64_t x_ld) {
   if (M <= 0 || K <= 0) return M < 0 || K < 0 ? E_BAD_SHAPE : E_OK;
   const int64_t kpad = round_up(K, 512);
   const int64_t total = M * (kpad / 32);
@@ -267,13 +290,13 @@ static int launch_f16x8(const void* x, int x_dtype, void* out, int64_t M, int64_
   __half* o = static_cast<__half*>(out);
   switch (x_dtype) {
     case DT_F32:
-      launch_pdl(quantize_f16x8_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim);
+      launch_pdl(quantize_f16x8_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim, act, x_ld);
       break;
     case DT_F16:
-      launch_pdl(quantize_f16x8_kernel<__half>, dim3(blocks), dim3(256), 0, stream, (const __half*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim);
+      launch_pdl(quantize_f16x8_kernel<__half>, dim3(blocks), dim3(256), 0, stream, (const __half*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim, act, x_ld);
       break;
     case DT_BF16:
-      launch_pdl(quantize_f16x8_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim);
+      launch_pdl(quantize_f16x8_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, o, M, K, kpad, ldb, corr_mode, perm, gid, gdiv, glim, act, x_ld);
       break;
     default:
       return E_BAD_DTYPE;
@@ -283,12 +306,14 @@ static int launch_f16x8(const void* x, int x_dtype, void* out, int64_t M, int64_
 
 int launch_quantize_q8_1(const void* x, int x_dtype, void* out, int64_t M, int64_t K, int mode, int sum_mode,
                          int64_t ldb, int corr_mode, const int32_t* gather_ids, int64_t gather_div, int64_t gather_limit,
-                         cudaStream_t stream, int perm, const Q8Tp* wait) {
+                         cudaStream_t stream, int perm, const Q8Tp* wait, int act, int64_t x_ld) {
   if (mode == Q8_MODE_F16) {
     // rows of x and of the output start on 16-byte boundaries when K and ldb are multiples of 8
     const bool aligned = K % 8 == 0 && ldb % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-    if (aligned) return launch_f16x8(x, x_dtype, out, M, K, ldb, corr_mode, perm, gather_ids, gather_div, gather_limit, stream);
-    if (perm) return E_BAD_POINTER;
+    if (aligned) return launch_f16x8(x, x_dtype, out, M, K, ldb, corr_mode, perm, gather_ids, gather_div, gather_limit, stream, act, x_ld);
+    if (perm || act) return E_BAD_POINTER;
+  } else if (act) {
+    return E_BAD_SHAPE;
   }
   switch (mode) {
     case Q8_MODE_REF: return launch_mode<Q8_MODE_REF>(x, x_dtype, out, M, K, sum_mode, ldb, corr_mode, nullptr, 1, 0, stream);

@@ -76,6 +76,25 @@ Tensor ggml_dequantize(Tensor W, int64_t type, int64_t m, int64_t n, std::option
   return out;
 }
 
+// Embedding look-up: rows `ids` of the packed weight, dequantized (replaces index_select +
+// ggml_dequantize of the reference's embedding caller, quantization/vocal_embeds.py:88-96).
+Tensor dequantize_rows(Tensor W, Tensor ids, int64_t type, std::optional<ScalarType> dtype) {
+  const int32_t dev = W.get_device_index();
+  const DeviceGuard guard(dev);
+  const int64_t K = check_weight(W, type, "dequantize_rows");
+  STD_TORCH_CHECK(W.dim() == 2, "dequantize_rows: W must be [rows, bytes]");
+  STD_TORCH_CHECK(ids.scalar_type() == ScalarType::Long && ids.is_contiguous() && ids.dim() == 1,
+                  "dequantize_rows: ids must be a contiguous 1-D int64 tensor");
+  STD_TORCH_CHECK(K % 256 == 0, "dequantize_rows: the row length must be a multiple of 256");
+  const ScalarType dt = dtype.value_or(ScalarType::Half);
+  const int code = dtype_code(dt, "dequantize_rows");
+  Tensor out = torch::stable::new_empty(W, {ids.size(0), K}, dt);
+  check_rc(gguf_b200_dequantize_rows(W.data_ptr(), (int)type, static_cast<const int64_t*>(ids.data_ptr()), ids.size(0), K,
+                                     W.size(0), out.data_ptr(), code, current_stream(dev)),
+           "dequantize_rows");
+  return out;
+}
+
 static Tensor matmul_common(const Tensor& W, const Tensor& X, int64_t type, int64_t row, int op, const char* name) {
   const int32_t dev = X.get_device_index();
   const DeviceGuard guard(dev);
@@ -165,6 +184,32 @@ Tensor ggml_moe_a8_vec(Tensor X, Tensor W, Tensor topk_ids, int64_t top_k, int64
   return Y;
 }
 
+// The tiled MoE step in one call (see gguf_b200_fused_moe).  act: 1 silu, 2 gelu.
+Tensor fused_moe(Tensor X, Tensor W13, Tensor W2, Tensor topk_weights, Tensor topk_ids, int64_t type13, int64_t type2, int64_t act) {
+  const int32_t dev = X.get_device_index();
+  const DeviceGuard guard(dev);
+  const int64_t H = check_weight(W13, type13, "fused_moe");
+  const int64_t I = check_weight(W2, type2, "fused_moe");
+  STD_TORCH_CHECK(W13.dim() == 3 && W2.dim() == 3 && W13.size(0) == W2.size(0), "fused_moe: W13 / W2 must be [experts, rows, bytes]");
+  STD_TORCH_CHECK(W13.size(1) == 2 * I && W2.size(1) == H, "fused_moe: W13 must be [E, 2I, .] and W2 [E, H, .]");
+  STD_TORCH_CHECK(X.dim() == 2 && X.is_contiguous() && X.size(1) == H, "fused_moe: X must be contiguous [tokens, H]");
+  STD_TORCH_CHECK(topk_ids.scalar_type() == ScalarType::Int && topk_ids.is_contiguous() && topk_ids.dim() == 2 && topk_ids.size(0) == X.size(0),
+                  "fused_moe: topk_ids must be contiguous int32 [tokens, top_k]");
+  STD_TORCH_CHECK(topk_weights.scalar_type() == ScalarType::Float && topk_weights.is_contiguous() && topk_weights.numel() == topk_ids.numel(),
+                  "fused_moe: topk_weights must be contiguous float32 [tokens, top_k]");
+  const int code = dtype_code(X.scalar_type(), "fused_moe");
+  const int64_t tokens = X.size(0), top_k = topk_ids.size(1), E = W13.size(0);
+  Tensor Y = torch::stable::new_empty(X, {tokens, H}, X.scalar_type());
+  const int64_t ws_bytes = gguf_b200_fused_moe_workspace_bytes((int)type13, (int)type2, code, tokens, top_k, E, H, I);
+  STD_TORCH_CHECK(ws_bytes > 0 || tokens == 0, "fused_moe: unsupported types or sizes");
+  Tensor ws = scratch(X, ws_bytes);
+  check_rc(gguf_b200_fused_moe(X.data_ptr(), W13.data_ptr(), W2.data_ptr(), Y.data_ptr(), static_cast<const int32_t*>(topk_ids.data_ptr()),
+                               static_cast<const float*>(topk_weights.data_ptr()), ws.data_ptr(), ws_bytes, (int)type13, (int)type2, code,
+                               (int)act, tokens, top_k, E, H, I, current_stream(dev)),
+           "fused_moe");
+  return Y;
+}
+
 int64_t ggml_moe_get_block_size(int64_t type) { return gguf_b200_moe_block_size((int)type); }
 
 STABLE_TORCH_LIBRARY(_C_gguf, ops) {
@@ -177,6 +222,8 @@ STABLE_TORCH_LIBRARY(_C_gguf, ops) {
   ops.def("ggml_moe_a8_vec(Tensor X, Tensor W, Tensor topk_ids, int top_k, int type, SymInt row, SymInt tokens) -> Tensor");
   ops.def("ggml_moe_get_block_size(int type) -> int");
   ops.def("dequant_matmul(Tensor W, Tensor X, int type, SymInt row) -> Tensor");
+  ops.def("dequantize_rows(Tensor W, Tensor ids, int type, ScalarType? dtype) -> Tensor");
+  ops.def("fused_moe(Tensor X, Tensor W13, Tensor W2, Tensor topk_weights, Tensor topk_ids, int type13, int type2, int act) -> Tensor");
 }
 
 STABLE_TORCH_LIBRARY_IMPL(_C_gguf, CUDA, ops) {
@@ -186,6 +233,8 @@ STABLE_TORCH_LIBRARY_IMPL(_C_gguf, CUDA, ops) {
   ops.impl("ggml_moe_a8", TORCH_BOX(&ggml_moe_a8));
   ops.impl("ggml_moe_a8_vec", TORCH_BOX(&ggml_moe_a8_vec));
   ops.impl("dequant_matmul", TORCH_BOX(&dequant_matmul));
+  ops.impl("dequantize_rows", TORCH_BOX(&dequantize_rows));
+  ops.impl("fused_moe", TORCH_BOX(&fused_moe));
 }
 
 STABLE_TORCH_LIBRARY_IMPL(_C_gguf, CompositeExplicitAutograd, ops) {

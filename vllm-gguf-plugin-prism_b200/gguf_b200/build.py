@@ -24,7 +24,7 @@ OUT = PKG / "vllm_gguf_plugin"
 OBJ = PKG / "build"
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-CU_FILES = ["capi.cu", "quantize_q8_1.cu", "dequantize.cu", "gemv.cu", "gemv1.cu", "mmq.cu", "noalloc.cu", "tp.cu"]
+CU_FILES = ["capi.cu", "quantize_q8_1.cu", "dequantize.cu", "gemv.cu", "gemv1.cu", "mmq.cu", "noalloc.cu", "tp.cu", "moe_fused.cu"]
 FAST_MATH = {"quantize_q8_1.cu"}
 
 

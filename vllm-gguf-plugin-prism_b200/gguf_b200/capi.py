@@ -29,6 +29,7 @@ SIGNATURES = {
     "gguf_b200_q8_1_row_bytes": (_L, [_L]),
     "gguf_b200_quantize_q8_1": (_I, [_P, _I, _P, _L, _L, _P]),
     "gguf_b200_dequantize": (_I, [_P, _I, _P, _I, _L, _P]),
+    "gguf_b200_dequantize_rows": (_I, [_P, _I, _P, _L, _L, _L, _P, _I, _P]),
     "gguf_b200_workspace_bytes": (_L, [_I, _I, _L, _L, _L]),
     "gguf_b200_mul_mat_vec_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_gemv_prepare": (_I, [_P, _I, _P, _L, _I, _L, _L, _P]),
@@ -36,6 +37,8 @@ SIGNATURES = {
     "gguf_b200_mul_mat_a8": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_dequant_matmul": (_I, [_P, _P, _P, _P, _L, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_moe_a8": (_I, [_P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _L, _I, _I, _L, _L, _L, _L, _P]),
+    "gguf_b200_fused_moe_workspace_bytes": (_L, [_I, _I, _I, _L, _L, _L, _L, _L]),
+    "gguf_b200_fused_moe": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _L, _L, _L, _L, _L, _P]),
     "gguf_b200_moe_a8_vec": (_I, [_P, _P, _P, _P, _L, _P, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_vec_a8_noalloc": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_vec_a8_tp": (_I, [_P, _P, _P, _P, _I, _I, _F, _L, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
@@ -101,6 +104,16 @@ def dequantize(W: torch.Tensor, qtype: int, m: int, n: int, dtype=torch.float16)
     return out
 
 
+def dequantize_rows(W: torch.Tensor, row_ids: torch.Tensor, qtype: int, dtype=torch.float16) -> torch.Tensor:
+    """[len(row_ids), K] = dequantized rows row_ids of the packed [rows, bytes] weight (embedding look-up)."""
+    K = k_of(W, qtype)
+    ids = row_ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((ids.numel(), K), dtype=dtype, device=W.device)
+    _check(lib().gguf_b200_dequantize_rows(W.data_ptr(), qtype, ids.data_ptr(), ids.numel(), K, W.shape[0], out.data_ptr(),
+                                           _DT[dtype], _stream(W)), "dequantize_rows")
+    return out
+
+
 def _matmul(fn_name: str, op: int, W: torch.Tensor, X: torch.Tensor, qtype: int, N: int) -> torch.Tensor:
     M, K = X.shape
     Y = torch.empty((M, N), dtype=X.dtype, device=X.device)
@@ -149,6 +162,27 @@ def moe_a8(X, W, sorted_ids, expert_ids, n_post_pad, qtype, N, top_k, tokens):
     _check(lib().gguf_b200_moe_a8(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), nbytes, sorted_ids.data_ptr(),
                                   expert_ids.data_ptr(), n_post_pad.data_ptr(), n_sorted, W.stride(0), W.shape[0], qtype,
                                   _DT[X.dtype], tokens, top_k, N, K, _stream(X)), "moe_a8")
+    return Y
+
+
+ACT_SILU, ACT_GELU = 1, 2
+
+
+def fused_moe(X, W13, W2, topk_ids, topk_weights, qtype13, qtype2, act=ACT_SILU):
+    """The tiled MoE step in one call: X [T, H], W13 [E, 2I, bytes], W2 [E, H, bytes], topk_ids int32 [T, k],
+    topk_weights float32 [T, k] -> [T, H]."""
+    T, H = X.shape
+    E, I2 = W13.shape[0], W13.shape[1]
+    top_k = topk_ids.shape[1]
+    I = I2 // 2
+    Y = torch.empty((T, H), dtype=X.dtype, device=X.device)
+    nbytes = lib().gguf_b200_fused_moe_workspace_bytes(qtype13, qtype2, _DT[X.dtype], T, top_k, E, H, I)
+    ws = _ws(X, nbytes)
+    ids = topk_ids.to(torch.int32).contiguous()
+    tw = topk_weights.to(torch.float32).contiguous()
+    _check(lib().gguf_b200_fused_moe(X.data_ptr(), W13.data_ptr(), W2.data_ptr(), Y.data_ptr(), ids.data_ptr(), tw.data_ptr(),
+                                     ws.data_ptr(), nbytes, qtype13, qtype2, _DT[X.dtype], int(act), T, top_k, E, H, I,
+                                     _stream(X)), "fused_moe")
     return Y
 
 

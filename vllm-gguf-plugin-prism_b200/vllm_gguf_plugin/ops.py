@@ -8,11 +8,15 @@ same names, argument order and meaning -- on top of the ``_C_gguf`` torch librar
 Differences from the reference, all deliberate:
 * no Triton backend and no CPU fallback: if the extension is missing, import fails loudly;
   ``VLLM_GGUF_USE_CUDA`` is accepted for compatibility but selects nothing;
-* supported block types are Q4_0, Q8_0, Q4_K, Q6_K, IQ2_XXS, IQ4_XS; any other type raises
+* supported block types are Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ2_XXS, IQ4_NL, IQ4_XS
+  (plus Q2_K and Q3_K for ggml_dequantize alone); any other type raises
   ``NotImplementedError`` (the reference silently returns zeros for an unknown type in its
   matmul switch, gguf_kernel.cu:236-289);
 * ``ggml_moe_get_block_size`` returns this library's token-block size (64, tensor-core tile)
   instead of 4; callers already feed it to ``moe_align_block_size`` (fused_moe.py:64-68);
+* ``ggml_dequantize_rows`` is new: the embedding look-up (index_select of rows + ggml_dequantize,
+  quantization/vocal_embeds.py:88-96) as one kernel;
+* ``ggml_fused_moe`` is new: the whole tiled MoE step of a layer in one call;
 * ``ggml_dequant_matmul`` is new: the fused form of "ggml_dequantize then x @ W.T" that the
   reference uses for IQ types above the GEMV batch threshold (quantization/linear.py:50-54).
 """
@@ -60,21 +64,24 @@ _CUDA_ENABLED = True
 # (values per block, bytes per block) -- gguf.GGML_QUANT_SIZES for the supported types
 QUANT_SIZES = {
     GGML_TYPE_Q4_0: (32, 18),
+    GGML_TYPE_Q4_1: (32, 20),
+    GGML_TYPE_Q5_0: (32, 22),
+    GGML_TYPE_Q5_1: (32, 24),
     GGML_TYPE_Q8_0: (32, 34),
     GGML_TYPE_Q4_K: (256, 144),
+    GGML_TYPE_Q5_K: (256, 176),
     GGML_TYPE_Q6_K: (256, 210),
     GGML_TYPE_IQ2_XXS: (256, 66),
+    GGML_TYPE_IQ4_NL: (32, 18),
     GGML_TYPE_IQ4_XS: (256, 136),
 }
 _CUDA_GEMV_QUANT_TYPES = frozenset(QUANT_SIZES)
 # ggml_dequantize alone also serves these
-DEQUANT_ONLY_SIZES = {
-    GGML_TYPE_Q4_1: (32, 20), GGML_TYPE_Q5_0: (32, 22), GGML_TYPE_Q5_1: (32, 24), GGML_TYPE_Q2_K: (256, 84),
-    GGML_TYPE_Q3_K: (256, 110), GGML_TYPE_Q5_K: (256, 176), GGML_TYPE_IQ4_NL: (32, 18),
-}
+DEQUANT_ONLY_SIZES = {GGML_TYPE_Q2_K: (256, 84), GGML_TYPE_Q3_K: (256, 110)}
 _CUDA_DEQUANT_TYPES = _CUDA_GEMV_QUANT_TYPES | frozenset(DEQUANT_ONLY_SIZES)
-_CUDA_GEMM_QUANT_TYPES = frozenset({GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_Q6_K})
-_DEQUANT_MATMUL_TYPES = frozenset({GGML_TYPE_IQ2_XXS, GGML_TYPE_IQ4_XS})
+_CUDA_GEMM_QUANT_TYPES = frozenset({GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q5_0, GGML_TYPE_Q5_1, GGML_TYPE_Q8_0,
+                                    GGML_TYPE_Q4_K, GGML_TYPE_Q5_K, GGML_TYPE_Q6_K})
+_DEQUANT_MATMUL_TYPES = frozenset({GGML_TYPE_IQ2_XXS, GGML_TYPE_IQ4_NL, GGML_TYPE_IQ4_XS})
 
 
 def _require(quant_type: int, allowed, op: str) -> None:
@@ -111,6 +118,17 @@ def _dequant_matmul_fake(W, X, quant_type, row):
     return torch.empty((X.size(0), row), dtype=X.dtype, device=W.device)
 
 
+@register_fake("_C_gguf::dequantize_rows")
+def _dequantize_rows_fake(W, ids, quant_type, dtype=None):
+    block, size = (QUANT_SIZES | DEQUANT_ONLY_SIZES)[int(quant_type)]
+    return torch.empty((ids.shape[0], W.shape[1] // size * block), dtype=dtype or torch.float16, device=W.device)
+
+
+@register_fake("_C_gguf::fused_moe")
+def _fused_moe_fake(X, W13, W2, topk_weights, topk_ids, type13, type2, act):
+    return torch.empty_like(X)
+
+
 @register_fake("_C_gguf::ggml_moe_a8")
 def _ggml_moe_a8_fake(X, W, sorted_token_ids, expert_ids, num_tokens_post_padded, quant_type, row, top_k, tokens):
     return torch.empty((X.size(0) * top_k, row), dtype=X.dtype, device=W.device)
@@ -145,6 +163,13 @@ def ggml_dequant_matmul(W: torch.Tensor, X: torch.Tensor, quant_type: int, row: 
     return torch.ops._C_gguf.dequant_matmul(W, X, quant_type, row)
 
 
+def ggml_dequantize_rows(W: torch.Tensor, ids: torch.Tensor, quant_type: int, dtype: torch.dtype | None) -> torch.Tensor:
+    """Rows ``ids`` (1-D int64) of the packed ``[rows, bytes]`` weight, dequantized to ``[len(ids), K]``:
+    the embedding look-up in one kernel (the reference does index_select, then ggml_dequantize)."""
+    _require(quant_type, _CUDA_DEQUANT_TYPES, "ggml_dequantize_rows")
+    return torch.ops._C_gguf.dequantize_rows(W, ids, quant_type, dtype)
+
+
 def ggml_moe_a8(
     X: torch.Tensor,
     W: torch.Tensor,
@@ -160,6 +185,21 @@ def ggml_moe_a8(
     return torch.ops._C_gguf.ggml_moe_a8(
         X, W, sorted_token_ids, expert_ids, num_tokens_post_padded, quant_type, row, top_k, tokens
     )
+
+
+MOE_ACTIVATIONS = {"silu": 1, "gelu": 2}
+
+
+def ggml_fused_moe(X: torch.Tensor, W13: torch.Tensor, W2: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                   quant_type: int, quant_type2: int, activation: str) -> torch.Tensor:
+    """The tiled MoE step of one layer in one call: alignment, gate/up expert GEMM, activation, down
+    expert GEMM, routing weights and the top-k sum (the reference runs six ops for it,
+    quantization/fused_moe.py:56-95).  X [T, H] -> [T, H]."""
+    _require(quant_type, _CUDA_GEMM_QUANT_TYPES, "ggml_fused_moe")
+    _require(quant_type2, _CUDA_GEMM_QUANT_TYPES, "ggml_fused_moe")
+    return torch.ops._C_gguf.fused_moe(X, W13, W2, topk_weights.to(torch.float32).contiguous(),
+                                       topk_ids.to(torch.int32).contiguous(), quant_type, quant_type2,
+                                       MOE_ACTIVATIONS[activation])
 
 
 def ggml_moe_a8_vec(

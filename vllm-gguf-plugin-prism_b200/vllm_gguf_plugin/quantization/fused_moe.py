@@ -10,6 +10,8 @@ expert GEMMs can be exercised on a box without vLLM.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -101,6 +103,11 @@ def _fused_moe_gguf(
     E, N, _ = w1.shape
     top_k = topk_ids.shape[1]
     if weight_type2 in MMQ_QUANT_TYPES and weight_type in MMQ_QUANT_TYPES and x.shape[0] > 64:
+        if (activation in ops.MOE_ACTIVATIONS and E <= 256 and w2.shape[0] == E and (N // 2) % 8 == 0
+                and os.environ.get("VLLM_GGUF_FUSED_MOE", "1") == "1"):
+            # one call: alignment, both expert GEMMs, activation, routing weights and top-k sum
+            return ops.ggml_fused_moe(x, w1, w2, topk_weights, topk_ids, weight_type, weight_type2, activation)
+        # the reference's sequence of separate ops (fused_moe.py:64-95)
         block_size = ops.ggml_moe_get_block_size(weight_type)
         sorted_token_ids, expert_ids, num_tokens_post_padded = _align(topk_ids, block_size, E)
         out = ops.ggml_moe_a8(x, w1, sorted_token_ids, expert_ids, num_tokens_post_padded, weight_type, N, top_k,

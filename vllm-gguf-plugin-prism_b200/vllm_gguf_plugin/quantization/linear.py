@@ -62,7 +62,14 @@ def _fused_mul_mat_gguf(x: torch.Tensor, weight: torch.Tensor, weight_type: int)
         return torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
     if weight_type in UNQUANTIZED_TYPES:
         return x @ weight.T
-    if x.shape[0] <= mmvq_safe and weight_type in MMVQ_QUANT_TYPES:
+    if int(weight_type) in ops.DEQUANT_ONLY_SIZES:
+        # Q2_K / Q3_K have a dequantize kernel here but no fused matmul yet: dequantize, then a dense
+        # product.  (The reference quantizes the activations to q8_1 on its route for these types, so
+        # this differs from it by that quantization noise, about 5e-3 relative.)
+        block_size, type_size = quant_sizes(weight_type)
+        shape = (weight.shape[0], weight.shape[1] // type_size * block_size)
+        y = x @ ops.ggml_dequantize(weight, weight_type, *shape, x.dtype).T
+    elif x.shape[0] <= mmvq_safe and weight_type in MMVQ_QUANT_TYPES:
         y = ops.ggml_mul_mat_vec_a8(weight, x, weight_type, weight.shape[0])
     elif weight_type in MMQ_QUANT_TYPES:
         y = ops.ggml_mul_mat_a8(weight, x, weight_type, weight.shape[0])

@@ -22,8 +22,10 @@ MMVQ_QUANT_TYPES = STANDARD_QUANT_TYPES | KQUANT_TYPES | IMATRIX_QUANT_TYPES
 MMQ_QUANT_TYPES = STANDARD_QUANT_TYPES | KQUANT_TYPES
 
 # block geometry of the types this build has kernels for: type -> (values, bytes) per block
-SUPPORTED_QUANT_SIZES = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
-                         IQ2_XXS: (256, 66), IQ4_XS: (256, 136)}
+SUPPORTED_QUANT_SIZES = {Q4_0: (32, 18), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q8_0: (32, 34),
+                         Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210),
+                         IQ2_XXS: (256, 66), IQ4_NL: (32, 18), IQ4_XS: (256, 136),
+                         Q2_K: (256, 84), Q3_K: (256, 110)}   # (Q2_K, Q3_K: dequantize route only)
 
 
 def quant_sizes(weight_type: int) -> tuple[int, int]:
