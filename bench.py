@@ -304,12 +304,12 @@ def moe_case(dev="cuda"):
     w2 = torch.from_numpy(np.stack([synth.make_weight(t, hid, inter, seed=200 + e) for e in range(e_cnt)])).to(dev)
     x1 = torch.from_numpy(synth.make_activation(tokens, hid, seed=1)).to(dev)
     x2 = torch.from_numpy(synth.make_activation(tokens * top_k, inter, seed=2)).to(dev)
-    _, ids = synth.make_routing(tokens, e_cnt, top_k, 0)
+    tw, ids = synth.make_routing(tokens, e_cnt, top_k, 0)
     blk = capi.lib().gguf_b200_moe_block_size(t)
     ours = [torch.from_numpy(a).to(dev) for a in synth.moe_align_block_size(ids, blk, e_cnt)]
     ref4 = [torch.from_numpy(a).to(dev) for a in synth.moe_align_block_size(ids, 4, e_cnt)]   # the reference's own block size
     return dict(t=t, e_cnt=e_cnt, top_k=top_k, hid=hid, inter=inter, tokens=tokens, w13=w13, w2=w2, x1=x1, x2=x2, ids=ids,
-                ours=ours, ref4=ref4)
+                ours=ours, ref4=ref4, ids_dev=torch.from_numpy(ids).to(dev), tw_dev=torch.from_numpy(tw).to(dev))
 
 
 def moe_times(c, ref):
@@ -325,11 +325,26 @@ def moe_times(c, ref):
              weight_GBs_gate_up=c["w13"].numel() / t1 / 1e9, weight_GBs_down=c["w2"].numel() / t2 / 1e9,
              frac_of_measured_hbm_gate_up=c["w13"].numel() / t1 / 1e9 / hbm, frac_of_measured_hbm_down=c["w2"].numel() / t2 / 1e9 / hbm,
              tflops_gate_up=ops1 / t1 / 1e12, tflops_down=ops2 / t2 / 1e12, bound="hbm (32 rows per expert)", status=capi.last_status())
+    # the whole step of a layer (alignment, both GEMMs, activation, routing weights, top-k sum) in one call
+    tf_ = graph_time([lambda: capi.fused_moe(c["x1"], c["w13"], c["w2"], c["ids_dev"], c["tw_dev"], t, t)] * 4)
+    r.update(us_fused_step=tf_ * 1e6, weight_GBs_fused_step=(c["w13"].numel() + c["w2"].numel()) / tf_ / 1e9,
+             frac_of_measured_hbm_fused_step=(c["w13"].numel() + c["w2"].numel()) / tf_ / 1e9 / hbm)
     if ref is not None:
+        import torch
+
         s4, e4, n4 = c["ref4"]
         r1 = graph_time([lambda: ref.ggml_moe_a8(c["x1"], c["w13"], s4, e4, n4, t, 2 * inter, top_k, tokens)] * 2, reps=3)
         r2 = graph_time([lambda: ref.ggml_moe_a8(c["x2"], c["w2"], s4, e4, n4, t, hid, 1, tokens * top_k)] * 2, reps=3)
         r.update(us_reference_gate_up=r1 * 1e6, us_reference_down=r2 * 1e6, speedup_gate_up=r1 / t1, speedup_down=r2 / t2)
+
+        def ref_step():   # the reference's sequence with its own kernels (alignment precomputed, activation / weighting / sum in torch)
+            o = ref.ggml_moe_a8(c["x1"], c["w13"], s4, e4, n4, t, 2 * inter, top_k, tokens)
+            a = (torch.nn.functional.silu(o[:, :inter]) * o[:, inter:]).contiguous()
+            o = ref.ggml_moe_a8(a, c["w2"], s4, e4, n4, t, hid, 1, tokens * top_k)
+            return (o.view(tokens, top_k, hid) * c["tw_dev"].view(tokens, top_k, 1).to(o.dtype)).sum(1)
+
+        rs = graph_time([ref_step] * 2, reps=3)
+        r.update(us_reference_step=rs * 1e6, speedup_step=rs / tf_)
     return r
 
 

@@ -161,7 +161,10 @@ int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, in
   int* st = status_ptr();
   if (!st) return E_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // the Q4_K GEMV takes its min term from the quantized codes (sum_mode 1), all others from the fp16 sum
+  // one or two vectors: ONE launch, the GEMV kernel quantizes the activations itself (same codes)
+  rc = launch_gemv_fused(W, X, Y, type, dtype, M, N, K, gemv_sum_mode(type), st, s);
+  if (rc <= 0) return rc;
+  // the Q4_K / Q5_K GEMV takes its min term from the quantized codes (sum_mode 1), all others from the fp16 sum
   rc = launch_quantize_q8_1(X, dtype, ws, M, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s);
   if (rc) return rc;
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);

@@ -646,6 +646,19 @@ int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dt
   return launch_any(p, type, out_dtype, M, false, stream);
 }
 
+int launch_gemv_fused(const void* w, const void* x, void* y, int type, int dtype, int64_t M, int64_t N, int64_t K, int sum_mode,
+                      int* status, cudaStream_t stream) {
+  // Every CTA quantizes the whole vector for itself, so the saving (one kernel less in the chain
+  // before the first dot product) shrinks as K grows and the extra arithmetic grows with it.
+  // Measured on B200, per call: K = 1024..4096 one vector 0.5-0.7 us faster (3072x1024 Q8_0 4.5 -> 3.8,
+  // 14336x4096 Q4_K 10.7 -> 10.0); K = 8192 even; K = 14336 1.9 us and K = 18944 4.5 us SLOWER, two
+  // vectors of K = 4096 1.5 us slower.  Hence: one vector, K up to this bound.
+  static const int use = gemv_tune_int("GGUF_B200_GEMV_FUSED_QUANT", 1);
+  static const int kmax = gemv_tune_int("GGUF_B200_GEMV_FUSED_QUANT_KMAX", 4096);
+  if (!use || M != 1 || K > kmax) return 1;
+  return launch_gemv1(w, nullptr, y, type, dtype, N, K, status, stream, nullptr, (int)M, nullptr, 0, 0, x, sum_mode);
+}
+
 int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* topk_ids, int type, int out_dtype,
                     int64_t tokens, int64_t top_k, int64_t N, int64_t K, int64_t n_experts, int* status,
                     cudaStream_t stream) {

@@ -14,8 +14,11 @@
 //    per-warp ring of stages, mbarrier completion, 16-byte rounded starts for the 2-byte aligned
 //    formats, bounded waits.
 //  * The unit loop is unrolled at compile time and integer dots run on independent dp4a chains.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "q8_1_lane.cuh"
 #include "tables.cuh"
 
 namespace gguf_b200 {
@@ -30,8 +33,48 @@ __device__ __forceinline__ int dp4a_us1(uint32_t a, uint32_t b, int c) {
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-// `blk` below is the 32-bit shared-window address of a weight block (all loads stay in that window)
-template <int N> __device__ __forceinline__ void lds_a2(uint32_t a, uint32_t (&w)[N]) { lds_words_unaligned<N>(a, w); }
+// `blk` below is the 32-bit shared-window address of a weight block (all loads stay in that window).
+// The loads of the decoders are asm statements WITHOUT `volatile`: to the compiler they are pure
+// functions of the address, so the two dot products of a two-vector kernel share one set of loads
+// and one header decode, and loads of different units may be moved next to each other.  What keeps
+// them behind the arrival of the data is a data dependency: every address derives from
+// fresh_stage(), a volatile statement placed after the barrier wait.
+__device__ __forceinline__ uint32_t fresh_stage(uint32_t a) {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(a) : "memory");
+  return r;
+}
+__device__ __forceinline__ uint32_t pl32(uint32_t a) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 pl64(uint32_t a) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 pl128(uint32_t a) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t pl16(uint32_t a) {
+  unsigned short h;
+  asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(a));
+  return h;
+}
+__device__ __forceinline__ float plh(uint32_t a) { return __half2float(__ushort_as_half((unsigned short)pl16(a))); }
+// N consecutive words from an address that is only 2-byte aligned: the N + 1 aligned words that
+// cover them, realigned with funnel shifts
+template <int N> __device__ __forceinline__ void lds_a2(uint32_t a, uint32_t (&w)[N]) {
+  const uint32_t al = a & ~3u, sh = (a & 3u) * 8u;
+  uint32_t r[N + 1];
+#pragma unroll
+  for (int i = 0; i <= N; ++i) r[i] = pl32(al + 4u * i);
+#pragma unroll
+  for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(r[i], r[i + 1], sh);
+}
 
 struct Tab1 {
   uint32_t grid;    // shared-window addresses of this lane's copies of the IQ2_XXS code books
@@ -47,13 +90,13 @@ template <> struct G1<T_Q8_0> {
   static constexpr int UPB = 1, XW = 8, XD = 2, UMAX = 4;
   static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int, uint32_t (&x)[XW], float (&xd)[XD]) {
     const uint4* p = reinterpret_cast<const uint4*>(qs + (size_t)u * 32);
-    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    const uint4 a = p[0], b = p[1];   // plain loads: the quantized activations may be in shared memory
     x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-    const float2 d = __ldg(ds + u);
+    const float2 d = ds[u];
     xd[0] = d.x; xd[1] = d.y;
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const float d = lds_half_f32(blk);
+    const float d = plh(blk);
     uint32_t w[8];
     lds_a2<8>(blk + 2, w);
     int s0 = 0, s1 = 0;
@@ -73,7 +116,7 @@ template <> struct G1<T_Q4_0> {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const float d = lds_half_f32(blk);
+    const float d = plh(blk);
     uint32_t q[4];
     lds_a2<4>(blk + 2, q);
     int lo = 0, hi = 0;  // hi = 16 * (high-nibble dot): nibbles stay in place
@@ -93,14 +136,14 @@ template <> struct G1<T_Q4_K> {
     const uint4* p = reinterpret_cast<const uint4*>(qs + (size_t)u * 64);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 a = __ldg(p + i);
+      const uint4 a = p[i];
       x[4 * i] = a.x; x[4 * i + 1] = a.y; x[4 * i + 2] = a.z; x[4 * i + 3] = a.w;
     }
-    const float4 d = __ldg(reinterpret_cast<const float4*>(ds + 2 * u));
+    const float4 d = *reinterpret_cast<const float4*>(ds + 2 * u);
     xd[0] = d.x; xd[1] = d.y; xd[2] = d.z; xd[3] = d.w;  // d8_0, d8_0*sum0, d8_1, d8_1*sum1
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int p, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const uint4 hdr = lds128s(blk);
+    const uint4 hdr = pl128(blk);
     const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
     const float d = __low2float(dm), dmin = __high2float(dm);
     const int sh = 16 * (p & 1);
@@ -112,7 +155,7 @@ template <> struct G1<T_Q4_K> {
     const uint32_t mn2 = ((b & 0x3F3Fu) & lowm) | ((((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) & ~lowm);
     const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
     const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
-    const uint4 qa = lds128s(blk + 16 + 32 * p), qb = lds128s(blk + 32 + 32 * p);
+    const uint4 qa = pl128(blk + 16 + 32 * p), qb = pl128(blk + 32 + 32 * p);
     const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
 #pragma unroll
@@ -136,7 +179,7 @@ template <> struct G1<T_Q6_K> {
     const int ga = 8 * b + 4 * ip + h, gb = ga + 2;
     const uint4* pa = reinterpret_cast<const uint4*>(qs + (size_t)ga * 32);
     const uint4* pb = reinterpret_cast<const uint4*>(qs + (size_t)gb * 32);
-    const uint4 a0 = __ldg(pa), a1 = __ldg(pa + 1), b0 = __ldg(pb), b1 = __ldg(pb + 1);
+    const uint4 a0 = pa[0], a1 = pa[1], b0 = pb[0], b1 = pb[1];
     x[0] = a0.x; x[1] = a0.y; x[2] = a0.z; x[3] = a0.w; x[4] = a1.x; x[5] = a1.y; x[6] = a1.z; x[7] = a1.w;
     x[8] = b0.x; x[9] = b0.y; x[10] = b0.z; x[11] = b0.w; x[12] = b1.x; x[13] = b1.y; x[14] = b1.z; x[15] = b1.w;
     int s[4] = {0, 0, 0, 0};
@@ -149,8 +192,8 @@ template <> struct G1<T_Q6_K> {
     }
     x[16] = ((uint32_t)s[0] & 0xFFFFu) | ((uint32_t)s[1] << 16);
     x[17] = ((uint32_t)s[2] & 0xFFFFu) | ((uint32_t)s[3] << 16);
-    xd[0] = __ldg(ds + ga).x;
-    xd[1] = __ldg(ds + gb).x;
+    xd[0] = ds[ga].x;
+    xd[1] = ds[gb].x;
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int u4, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
     const int ip = u4 >> 1, h = u4 & 1;
@@ -158,11 +201,9 @@ template <> struct G1<T_Q6_K> {
     lds_a2<8>(blk + 64 * ip + 32 * h, ql);
     lds_a2<8>(blk + 128 + 32 * ip, qh);
     // the scale pairs sit at even offsets of a 2-byte aligned block: two 16-bit loads
-    unsigned short sca, scb;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sca) : "r"(blk + 192 + 8 * ip + 2 * h));
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(scb) : "r"(blk + 196 + 8 * ip + 2 * h));
+    const uint32_t sca = pl16(blk + 192 + 8 * ip + 2 * h), scb = pl16(blk + 196 + 8 * ip + 2 * h);
     const int sa0 = (int)(int8_t)(sca & 0xFF), sa1 = (int)(int8_t)(sca >> 8), sb0 = (int)(int8_t)(scb & 0xFF), sb1 = (int)(int8_t)(scb >> 8);
-    const float d = lds_half_f32(blk + 208);
+    const float d = plh(blk + 208);
     const int s2 = 2 * h;
     int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
 #pragma unroll
@@ -209,10 +250,10 @@ template <> struct G1<T_IQ4_XS> {
     return __byte_perm(__byte_perm(t.kv[0], t.kv[1], q3), __byte_perm(t.kv[2], t.kv[3], q3), sel);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
-    const uint2 hdr = lds64(blk);
+    const uint2 hdr = pl64(blk);
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
     const int ls = (int)(((hdr.y >> (4 * ib)) & 0xF) | ((((hdr.x >> 16) >> (2 * ib)) & 3) << 4)) - 32;
-    const uint2 qa = lds64(blk + 8 + 16 * ib), qb = lds64(blk + 16 + 16 * ib);
+    const uint2 qa = pl64(blk + 8 + 16 * ib), qb = pl64(blk + 16 + 16 * ib);
     const uint32_t q[4] = {qa.x, qa.y, qb.x, qb.y};
     int s0 = 0, s1 = 0;
 #pragma unroll
@@ -233,15 +274,15 @@ template <> struct G1<T_IQ2_XXS> {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
-    const float d = lds_half_f32(blk);
+    const float d = plh(blk);
     uint32_t q[2];
     lds_a2<2>(blk + 2 + 8 * ib, q);
     const uint32_t aux = q[1];
     int sp = 0, sn = 0;
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
-      const uint2 gr = lds64(t.grid + ((q[0] >> (8 * il)) & 0xFF) * (8 * G1_TAB_COPIES));     // this lane's copy of the entry
-      const uint2 sm = lds64(t.smask + ((aux >> (7 * il)) & 127) * (8 * G1_TAB_COPIES));
+      const uint2 gr = pl64(t.grid + ((q[0] >> (8 * il)) & 0xFF) * (8 * G1_TAB_COPIES));     // this lane's copy of the entry
+      const uint2 sm = pl64(t.smask + ((aux >> (7 * il)) & 127) * (8 * G1_TAB_COPIES));
       sp = dp4a_us1(gr.x, x[2 * il], sp);
       sp = dp4a_us1(gr.y, x[2 * il + 1], sp);
       sn = dp4a_us1(gr.x & sm.x, x[2 * il], sn);
@@ -263,11 +304,11 @@ template <> struct G1<T_Q4_1> {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const __half2 dm = u32_as_half2(lds32(blk));            // 20-byte blocks: 4-byte aligned
+    const __half2 dm = u32_as_half2(pl32(blk));            // 20-byte blocks: 4-byte aligned
     int lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t q = lds32(blk + 4 + 4 * i);
+      const uint32_t q = pl32(blk + 4 + 4 * i);
       lo = dp4a_us1(q & 0x0F0F0F0Fu, x[i], lo);
       hi = dp4a_us1(q & 0xF0F0F0F0u, x[4 + i], hi);
     }
@@ -286,7 +327,7 @@ template <> struct G1<T_Q5_0> {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const float d = lds_half_f32(blk);
+    const float d = plh(blk);
     uint32_t w[5];
     lds_a2<5>(blk + 2, w);                                    // qh, then 16 bytes of nibbles (2-byte aligned)
     const uint32_t qh = w[0];
@@ -307,10 +348,10 @@ template <> struct G1<T_Q5_1> {
     G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const uint2 hdr = lds64(blk);                             // 24-byte blocks: 8-byte aligned
+    const uint2 hdr = pl64(blk);                             // 24-byte blocks: 8-byte aligned
     const __half2 dm = u32_as_half2(hdr.x);
     const uint32_t qh = hdr.y;
-    const uint2 qa = lds64(blk + 8), qb = lds64(blk + 16);
+    const uint2 qa = pl64(blk + 8), qb = pl64(blk + 16);
     const uint32_t w[4] = {qa.x, qa.y, qb.x, qb.y};
     int s0 = 0, s1 = 0;
 #pragma unroll
@@ -329,7 +370,7 @@ template <> struct G1<T_IQ4_NL> {
     G1<T_IQ4_XS>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1& t) {
-    const float d = lds_half_f32(blk);
+    const float d = plh(blk);
     uint32_t q[4];
     lds_a2<4>(blk + 2, q);
     int s0 = 0, s1 = 0;
@@ -352,7 +393,7 @@ template <> struct G1<T_Q5_K> {
     G1<T_Q4_K>::load_x(qs, ds, u, b, x, xd);
   }
   static __device__ __forceinline__ float unit(uint32_t blk, int p, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
-    const uint4 hdr = lds128s(blk);
+    const uint4 hdr = pl128(blk);
     const __half2 dm = u32_as_half2(hdr.x);
     const float d = __low2float(dm), dmin = __high2float(dm);
     const int sh = 16 * (p & 1);
@@ -364,8 +405,8 @@ template <> struct G1<T_Q5_K> {
     const uint32_t mn2 = ((b & 0x3F3Fu) & lowm) | ((((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) & ~lowm);
     const int sc0 = sc2 & 0xFF, sc1 = (sc2 >> 8) & 0xFF;
     const float m0 = (float)(mn2 & 0xFF), m1 = (float)((mn2 >> 8) & 0xFF);
-    const uint4 ha = lds128s(blk + 16), hb = lds128s(blk + 32);                 // qh[0..31]: bit 2p / 2p+1 of byte l
-    const uint4 qa = lds128s(blk + 48 + 32 * p), qb = lds128s(blk + 64 + 32 * p);
+    const uint4 ha = pl128(blk + 16), hb = pl128(blk + 32);                 // qh[0..31]: bit 2p / 2p+1 of byte l
+    const uint4 qa = pl128(blk + 48 + 32 * p), qb = pl128(blk + 64 + 32 * p);
     const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
     int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
@@ -419,7 +460,16 @@ struct G1Params {
   int slot_bytes;        // distance between the rows of an item inside a stage
   int stages, stage_bytes;
   int partial_bytes;     // shared memory for the staged results (0 when every warp stores its own)
+  // Activations not yet quantized (x_raw != null): xq is unused; every CTA quantizes the MV vectors it
+  // needs (K values each, element type = the output type) to q8_1 in its own shared memory right after
+  // the programmatic wait -- bit-identical to the standalone quantizer -- so a decode GEMV is ONE launch.
+  const void* x_raw;
+  int x_sum_mode;        // 1: the {d, sum} pair holds d * sum(q) instead of the fp16 sum of the inputs
+  int x_bytes;           // shared memory for the quantized activations (0 with x_alias)
+  int x_alias;           // 1: they sit in the LAST stage of warp 0's ring, which is filled only after every warp has
+                         //    its activations in registers (the first stages - 1 are on their way before)
   int contig;            // 1: contiguous row ranges per lane, 0: round-robin row groups
+  int first_rows;        // contiguous: rows of a lane's first item (<= rows_per_item)
   int* status;
   // MoE decode (topk_ids != null, one vector): blockIdx.y is an output row s of y; it uses the
   // weights of expert topk_ids[s] (experts back to back, expert_bytes apart) and the activation
@@ -504,8 +554,11 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
 #pragma unroll
     for (int i = 0; i < 4; ++i) tb.kv[i] = kv[i];
   }
+  uint8_t* s_x = cur;                               // quantized activations (when this kernel quantizes them itself)
+  cur += p.x_bytes;
   float* partial = reinterpret_cast<float*>(cur);  // [rl][G1_BATCH][G1_R][MV][ks], present only when results are staged
   cur += p.partial_bytes;
+  if (p.x_alias) s_x = cur + (size_t)(p.stages - 1) * p.stage_bytes;
   uint8_t* ring = cur + (size_t)warp * p.stages * p.stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cur + (size_t)G1_WARPS * p.stages * p.stage_bytes) + warp * p.stages;
   if (lane == 0)
@@ -524,7 +577,6 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   const uint32_t slice_bytes = (uint32_t)nblk * TS;
   const bool contiguous = p.ks == 1;
   const bool staged = p.ks > 1 || p.world > 0;   // results meet in shared memory before they are stored
-  const bool full_units = __all_sync(0xffffffffu, units == 32 * UMAX);   // every lane of the warp has UMAX units
 
   // ---- which rows: lane_first(l) = first row of row lane l of this CTA, lane_count(l) its rows
   // (contiguous), or first group / number of passes (round-robin) -------------------------------
@@ -540,11 +592,16 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     return (int)(q_rows + (wl < r_rows ? 1 : 0));
   };
   // first row and row count of item i of row lane l
+  // (contiguous: the FIRST item of a lane holds only p.first_rows rows -- it is on its way before
+  //  the activations exist and the sooner it lands the sooner the lane starts to work)
+  const int F = p.first_rows;
   auto item = [&](int l, int i, int64_t& row, int& cnt) {
     if (p.contig) {
-      const int left = lane_rows(l) - i * R;
-      row = lane_row0(l) + (int64_t)i * R;
-      cnt = left < R ? (left > 0 ? left : 0) : R;
+      const int done = i == 0 ? 0 : F + (i - 1) * R;
+      const int left = lane_rows(l) - done;
+      const int want = i == 0 ? F : R;
+      row = lane_row0(l) + done;
+      cnt = left < want ? (left > 0 ? left : 0) : want;
     } else {
       const int64_t g = ((int64_t)i * gridDim.x + blockIdx.x) * p.rl + l;
       row = g * R;
@@ -553,7 +610,10 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     }
   };
   auto lane_iters = [&](int l) -> int {
-    if (p.contig) return (lane_rows(l) + R - 1) / R;
+    if (p.contig) {
+      const int n_l = lane_rows(l);
+      return n_l <= F ? (n_l > 0 ? 1 : 0) : 1 + (n_l - F + R - 1) / R;
+    }
     const int64_t f = (int64_t)blockIdx.x * p.rl + l;
     return f < groups ? (int)((groups - f + lanes - 1) / lanes) : 0;
   };
@@ -596,17 +656,20 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     }
   };
 
-  // Every stage of the ring is filled before anything else happens: with the ring as deep as the
-  // warp's whole share (small matrices) ALL of this kernel's weight bytes are requested up front,
-  // while the previous kernel of the stream is still draining and before the activations exist.
-  int p_it = 0;
-  for (int s = 0; s < p.stages; ++s) {
+  // All stages but one are filled before anything else happens, while the previous kernel of the
+  // stream is still draining and before the activations exist; the last one follows when the
+  // activations are in registers.  (Filling every stage at once was slower: the memory system
+  // serves what is outstanding interleaved, so every warp's FIRST item arrived later and the first
+  // dot products with it -- 14336x4096 Q4_K 8.6 us against 8.0 us.)
+  int p_it = 0, p_st = 0;
+  for (int s = 0; s < p.stages - 1; ++s) {
     if (p_it < my_iters) {
       int64_t r0;
       int cnt;
       item(rl_i, p_it, r0, cnt);
-      issue(r0, cnt, s);
+      issue(r0, cnt, p_st);
       ++p_it;
+      if (++p_st == p.stages) p_st = 0;
     }
   }
 
@@ -635,10 +698,79 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   uint32_t xq[MV][UMAX][T::XW];
   float xd[MV][UMAX][T::XD];
   int uoff[UMAX], usub[UMAX];
+  const uint8_t* xq_base = p.xq;   // SoA q8_1: int8 codes [vectors][kpad], then float2 {d, sum} [vectors][kpad / 32]
+  int xq_vecs = p.xq_vecs, xq_v0 = vec0;
+  if (p.x_raw) {
+    // Quantize this CTA's MV vectors into shared memory, eight values per thread (four lanes own a
+    // block of 32).  The reference's butterfly adds element i to element i^16, then i^8, i^4, i^2,
+    // i^1; with lane t of a quad holding elements 8t..8t+7 the first two levels are shuffles across
+    // the quad and the last three are adds inside the thread, in the same order, so the fp32 sum (and
+    // with it every bit of the result) is that of the standalone quantizer.
+    const out_t* xr = static_cast<const out_t*>(p.x_raw) + (size_t)vec0 * p.k;
+    const int per_vec = kpad / 8, t = lane & 3;
+    float2* s_ds = reinterpret_cast<float2*>(s_x + (size_t)MV * kpad);
+    const bool vec_ok = (p.k % 8 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+    for (int i0 = threadIdx.x; i0 < MV * per_vec; i0 += G1_WARPS * 32) {   // (a multiple of 64 items: whole warps)
+      const int v = i0 / per_vec, idx = i0 - v * per_vec, k = idx * 8;
+      const out_t* src = xr + (size_t)v * p.k + k;
+      float val[8];
+      if (vec_ok && k + 8 <= p.k) {
+        if (sizeof(out_t) == 4) {
+          const float4 a = *reinterpret_cast<const float4*>(src), c = *reinterpret_cast<const float4*>(src + 4);
+          val[0] = a.x; val[1] = a.y; val[2] = a.z; val[3] = a.w; val[4] = c.x; val[5] = c.y; val[6] = c.z; val[7] = c.w;
+        } else {
+          const uint4 a = *reinterpret_cast<const uint4*>(src);
+          const out_t* e = reinterpret_cast<const out_t*>(&a);
 #pragma unroll
-  for (int m = 0; m < MV; ++m) {   // SoA scratch: int8 codes [MV][kpad], then float2 {d, sum} [MV][kpad / 32]
-    const uint8_t* qs = p.xq + (size_t)(vec0 + m) * kpad;
-    const float2* ds = reinterpret_cast<const float2*>(p.xq + (size_t)p.xq_vecs * kpad) + (size_t)(vec0 + m) * (kpad / 32);
+          for (int j = 0; j < 8; ++j) val[j] = to_float<out_t>(e[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) val[j] = k + j < p.k ? to_float<out_t>(src[j]) : 0.0f;
+      }
+      float amax = 0.f, sm[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        amax = fmaxf(amax, fabsf(val[j]));
+        sm[j] = val[j] + __shfl_xor_sync(0xffffffffu, val[j], 2, 32);          // i ^ 16
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sm[j] += __shfl_xor_sync(0xffffffffu, sm[j], 1, 32);   // i ^ 8
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2, 32));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1, 32));
+      float s4[4], s2[2];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s4[j] = sm[j] + sm[j + 4];               // i ^ 4
+#pragma unroll
+      for (int j = 0; j < 2; ++j) s2[j] = s4[j] + s4[j + 2];               // i ^ 2
+      const float sum = s2[0] + s2[1];                                      // i ^ 1
+      const float d = amax / 127;
+      uint32_t w0 = 0, w1 = 0;
+      int qsum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int8_t qq = amax == 0.0f ? 0 : roundf(val[j] / d);
+        qsum += qq;
+        if (j < 4) w0 |= ((uint32_t)qq & 0xFFu) << (8 * j);
+        else w1 |= ((uint32_t)qq & 0xFFu) << (8 * (j - 4));
+      }
+      *reinterpret_cast<uint2*>(s_x + (size_t)v * kpad + k) = make_uint2(w0, w1);
+      qsum += __shfl_xor_sync(0xffffffffu, qsum, 2, 32);
+      qsum += __shfl_xor_sync(0xffffffffu, qsum, 1, 32);
+      if (t == 0) {
+        const float d8 = __half2float(__float2half(d));
+        s_ds[(size_t)v * (kpad / 32) + (k >> 5)] = make_float2(d8, p.x_sum_mode ? d8 * (float)qsum : __half2float(__float2half(sum)));
+      }
+    }
+    __syncthreads();
+    xq_base = s_x;
+    xq_vecs = MV;
+    xq_v0 = 0;
+  }
+#pragma unroll
+  for (int m = 0; m < MV; ++m) {
+    const uint8_t* qs = xq_base + (size_t)(xq_v0 + m) * kpad;
+    const float2* ds = reinterpret_cast<const float2*>(xq_base + (size_t)xq_vecs * kpad) + (size_t)(xq_v0 + m) * (kpad / 32);
 #pragma unroll
     for (int j = 0; j < UMAX; ++j) {
       const int u = lane + 32 * j;
@@ -647,6 +779,10 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       if (u < units) {
         T::load_x(qs, ds, sb0 * UPB + u, 0, xq[m][j], xd[m][j]);
       } else {
+        // no such unit in this slice: zero activations against the slice's first block, so that the
+        // loop below needs no test per unit (it adds d * 0 of a block the row contains anyway)
+        uoff[j] = 0;
+        usub[j] = 0;
 #pragma unroll
         for (int i = 0; i < T::XW; ++i) xq[m][j][i] = 0;
 #pragma unroll
@@ -655,6 +791,10 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     }
   }
   if (TYPE == T_IQ2_XXS) __syncthreads();  // tables staged
+  if (p.x_alias) {   // every warp has read its activations: the stage they sat in may now take weights
+    __syncthreads();
+    fence_proxy_async();
+  }
   pdl_trigger();  // activations are in registers: the next kernel may be scheduled behind this one
 
   int c_st = 0;
@@ -663,6 +803,14 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   for (int i = 0; i < iters; ++i) {
     const bool mine = i < my_iters && !dead;
     if (mine) {
+      if (p_it < my_iters) {   // the stage freed by the previous pass takes the next item
+        int64_t r0;
+        int cnt2;
+        item(rl_i, p_it, r0, cnt2);
+        issue(r0, cnt2, p_st);
+        ++p_it;
+        if (++p_st == p.stages) p_st = 0;
+      }
       if (!mbar_wait_bounded(&bars[c_st], c_phase)) {
         if (lane == 0) atomicExch(p.status, E_TIMEOUT);
         dead = true;
@@ -673,7 +821,6 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       int cnt;
       item(rl_i, i, c_row, cnt);
       uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
-      const uint32_t stage_s = smem_u32(stage);
       const int64_t beg0 = c_row * row_bytes + (int64_t)sb0 * TS;
       const int64_t last_end = (c_row + cnt - 1) * row_bytes + (int64_t)sb0 * TS + slice_bytes;
       if (last_end > w_safe) {  // tail bytes the bulk copy must not touch: fetched with plain loads
@@ -683,6 +830,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         for (int64_t o = w_safe + lane; o < last_end; o += 32) base[o - abeg] = wb[o];
         __syncwarp();
       }
+      const uint32_t stage_s = fresh_stage(smem_u32(stage));   // after the wait and the tail bytes: see pl32
       float acc[MV][G1_R];
 #pragma unroll
       for (int rr = 0; rr < G1_R; ++rr)
@@ -692,40 +840,26 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         return stage_s + (contiguous ? (uint32_t)(beg0 & 15) + (uint32_t)rr * (uint32_t)row_bytes
                                      : (uint32_t)rr * (uint32_t)p.slot_bytes + (uint32_t)((beg0 + rr * row_bytes) & 15));
       };
-      // the common items (whole rows, every lane with all its units): straight-line code, so that
-      // the loads and dot-product chains of all cnt * UMAX units can overlap
-      if (full_units && cnt == 2) {
-        const uint32_t d0 = row_data(0), d1 = row_data(1);
+      // straight-line code for every row count, so that the loads and the dot-product chains of all
+      // cnt * UMAX units can overlap
+      auto rows = [&](auto cnt_c) {
+        constexpr int C = decltype(cnt_c)::value;
+        uint32_t d[C];
+#pragma unroll
+        for (int rr = 0; rr < C; ++rr) d[rr] = row_data(rr);
+        // (the vectors innermost: their two dot products share one set of loads and one header decode)
 #pragma unroll
         for (int j = 0; j < UMAX; ++j)
 #pragma unroll
-          for (int m = 0; m < MV; ++m) {
-            acc[m][0] += T::unit(d0 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-            acc[m][1] += T::unit(d1 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-          }
-      } else if (full_units && cnt == 3) {
-        const uint32_t d0 = row_data(0), d1 = row_data(1), d2 = row_data(2);
+          for (int rr = 0; rr < C; ++rr)
 #pragma unroll
-        for (int j = 0; j < UMAX; ++j)
-#pragma unroll
-          for (int m = 0; m < MV; ++m) {
-            acc[m][0] += T::unit(d0 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-            acc[m][1] += T::unit(d1 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-            acc[m][2] += T::unit(d2 + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-          }
-      } else {
-#pragma unroll
-        for (int rr = 0; rr < G1_R; ++rr) {
-          if (rr < cnt) {
-            const uint32_t data = row_data(rr);
-#pragma unroll
-            for (int j = 0; j < UMAX; ++j)
-              if (lane + 32 * j < units) {
-#pragma unroll
-                for (int m = 0; m < MV; ++m) acc[m][rr] += T::unit(data + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
-              }
-          }
-        }
+            for (int m = 0; m < MV; ++m) acc[m][rr] += T::unit(d[rr] + uoff[j], usub[j], xq[m][j], xd[m][j], tb);
+      };
+      switch (cnt) {
+        case 1: rows(std::integral_constant<int, 1>{}); break;
+        case 2: rows(std::integral_constant<int, 2>{}); break;
+        case 3: rows(std::integral_constant<int, 3>{}); break;
+        default: rows(std::integral_constant<int, 4>{}); break;
       }
 #pragma unroll
       for (int rr = 0; rr < G1_R; ++rr) {
@@ -740,14 +874,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
           }
         }
       }
-      __syncwarp();   // every lane is done with the stage: refill it with the warp's next item
-      if (p_it < my_iters) {
-        int64_t r0;
-        int cnt2;
-        item(rl_i, p_it, r0, cnt2);
-        issue(r0, cnt2, c_st);
-        ++p_it;
-      }
+      __syncwarp();   // every lane is done with the stage: the next pass may refill it
       if (++c_st == p.stages) { c_st = 0; c_phase ^= 1u; }
     }
     if (staged && ((i % G1_BATCH) == G1_BATCH - 1 || i == iters - 1)) {
@@ -795,7 +922,7 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   static const int stages_env = g1_env("GGUF_B200_GEMV1_STAGES", 2);
   static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
   static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
-  static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 6000);
+  static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 7168);
   static const int contig_env = g1_env("GGUF_B200_GEMV1_CONTIG", 1);
   p.contig = (contig_env || p.world > 0) ? 1 : 0;
   const int cap_blocks = 32 * (T::UMAX / MV) / T::UPB;  // blocks whose units fit one lane-register set
@@ -809,21 +936,34 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   p.slice_r = p.bpr % ks;
   const int slice_bytes = (p.slice_q + (p.slice_r ? 1 : 0)) * TS;   // the longest slice
   int R = rows_env < 1 ? 1 : (rows_env > G1_R ? G1_R : rows_env);
-  // (the 16 copies of the IQ2_XXS code books take 48 KB: smaller items keep two CTAs on an SM)
-  const int item_cap = TYPE == T_IQ2_XXS && item_env > 3900 ? 3900 : item_env;
-  while (R > 1 && (int64_t)R * (ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16)) > item_cap) --R;
-  p.rows_per_item = R;
-  p.slot_bytes = ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16);
-  p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
+  // An item is as large as two stages per warp allow with two CTAs on an SM (16 stages in 113 KB less
+  // the tables, the staged results and the barriers: 6.9 KB, 3.9 KB with the 48 KB of IQ2_XXS code-book
+  // copies).  Larger items mean fewer barrier round trips per warp: 57344x4096 Q4_K 25.1 -> 21.8 us,
+  // 14336x4096 8.3 -> 7.8 us with three rows instead of two.
   const size_t tables = TYPE == T_IQ2_XXS ? (size_t)(256 + 128) * 8 * G1_TAB_COPIES : 0;
   p.partial_bytes = (ks > 1 || p.world > 0) ? G1_BATCH * 8 * G1_R * MV * 4 : 0;
-  const size_t fixed = tables + (size_t)p.partial_bytes + (size_t)G1_WARPS * 8 * 16;   // + barriers (at most 16 stages)
+  const int room2 = (int)(((size_t)113 * 1024 - tables - (size_t)p.partial_bytes - (size_t)G1_WARPS * 8 * 16) / (2 * G1_WARPS)) - 48;
+  const int item_cap = item_env < room2 ? item_env : room2;
+  while (R > 1 && (int64_t)R * (ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16)) > item_cap) --R;
+  p.rows_per_item = R;
+  static const int first_env = g1_env("GGUF_B200_GEMV1_FIRST_ROWS", 0);
+  p.first_rows = first_env > 0 && first_env < R ? first_env : R;
+  p.slot_bytes = ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16);
+  p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
+  const int kpad = (int)round_up(p.k, 512);
+  p.x_bytes = p.x_raw ? (int)round_up((int64_t)MV * (kpad + kpad / 4), 128) : 0;
+  p.x_alias = (p.x_raw && p.x_bytes <= p.stage_bytes) ? 1 : 0;
+  if (p.x_alias) p.x_bytes = 0;
+  const size_t fixed = tables + (size_t)p.x_bytes + (size_t)p.partial_bytes + (size_t)G1_WARPS * 8 * 16;   // + barriers (at most 16 stages)
   auto kern = gemv1_kernel<TYPE, out_t, MV>;
   // Grid first (it decides how many items a warp gets), then the ring depth: as many stages as a
   // warp has items, within what leaves room for two CTAs per SM; GGUF_B200_GEMV1_STAGES caps it.
   const size_t budget2 = (size_t)113 * 1024;
   int per_sm = ctas_env < 1 ? 1 : (ctas_env > 2 ? 2 : ctas_env);
-  if (fixed + (size_t)G1_WARPS * 2 * p.stage_bytes > budget2) per_sm = 1;
+  if (fixed + (size_t)G1_WARPS * 2 * p.stage_bytes > budget2) {
+    if (p.x_raw) return 1;   // quantizing in the kernel would cost the second CTA of every SM: the caller quantizes separately
+    per_sm = 1;
+  }
   int64_t grid = 148 * per_sm;
   const int64_t groups = (p.n + R - 1) / R;
   const int64_t need = (groups + p.rl - 1) / p.rl;
@@ -838,7 +978,7 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   int fit = (int)(room / ((size_t)G1_WARPS * p.stage_bytes));
   if (fit < 2) return 1;   // not even a double buffer: the general kernel takes the shape
   p.stages = want < fit ? want : fit;
-  auto smem_of = [&](int stages) { return tables + (size_t)p.partial_bytes + (size_t)G1_WARPS * stages * p.stage_bytes + (size_t)G1_WARPS * stages * 8; };
+  auto smem_of = [&](int stages) { return tables + (size_t)p.x_bytes + (size_t)p.partial_bytes + (size_t)G1_WARPS * stages * p.stage_bytes + (size_t)G1_WARPS * stages * 8; };
   int dev = 0;
   cudaGetDevice(&dev);
   static bool carveout_set[64] = {false};
@@ -853,7 +993,7 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   if (per_sm == 2 && p.stages > 2) {
     int& memo = checked_stages[dev & 63][p.stages];
     int& memo_b = checked_bytes[dev & 63][p.stages];
-    if (memo == 0 || memo_b != p.stage_bytes + p.partial_bytes + (int)tables) {
+    if (memo == 0 || memo_b != p.stage_bytes + p.partial_bytes + p.x_bytes + (int)tables) {
       int st = p.stages, nb = 0;
       while (st > 2) {
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, G1_WARPS * 32, smem_of(st)) != cudaSuccess) return E_CUDA;
@@ -861,7 +1001,7 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
         --st;
       }
       memo = st;
-      memo_b = p.stage_bytes + p.partial_bytes + (int)tables;
+      memo_b = p.stage_bytes + p.partial_bytes + p.x_bytes + (int)tables;
     }
     p.stages = memo;
   }
@@ -896,8 +1036,11 @@ static int launch_g1_out(const G1Params& p, int out_dtype, int mv, cudaStream_t 
 
 // Returns E_OK, a negative error, or 1 when the shape is outside this kernel's reach.
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
-                 cudaStream_t stream, const GemvTp* tp, int vectors, const GemvMoe* moe, int vec0, int total_vecs) {
+                 cudaStream_t stream, const GemvTp* tp, int vectors, const GemvMoe* moe, int vec0, int total_vecs,
+                 const void* x_raw, int x_sum_mode) {
   G1Params p{};
+  p.x_raw = x_raw;
+  p.x_sum_mode = x_sum_mode;
   if (vectors != 1 && (vectors != 2 || tp || moe)) return 1;
   p.xq_vecs = total_vecs > 0 ? total_vecs : vectors;
   p.vec0 = vec0;

@@ -47,6 +47,10 @@ int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t
 // Y[m, n] for m in [0, M); rows of W are N x (K/QK*TS) bytes, contiguous, 16-byte aligned base.
 int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t M, int64_t N, int64_t K,
                 int* status, cudaStream_t stream);
+// The whole decode op for M <= 2 vectors in ONE launch (activations quantized inside the GEMV kernel);
+// returns 1 when the shape needs the two-kernel route.
+int launch_gemv_fused(const void* w, const void* x, void* y, int type, int dtype, int64_t M, int64_t N, int64_t K, int sum_mode,
+                      int* status, cudaStream_t stream);
 // One- and two-vector specialisation (gemv1.cu): activations in registers.  Returns 1 when the
 // shape is outside its reach (the caller then uses the general kernel).
 // Tensor-parallel output of the single-vector kernel: every result is sent to all `world` ranks
@@ -65,7 +69,10 @@ struct GemvMoe {
 };
 int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_dtype, int64_t N, int64_t K, int* status,
                  cudaStream_t stream, const GemvTp* tp = nullptr, int vectors = 1, const GemvMoe* moe = nullptr,
-                 int vec0 = 0, int total_vecs = 0);   // vec0 / total_vecs: the `vectors` handled are vec0.. of total_vecs in the scratch
+                 int vec0 = 0, int total_vecs = 0,    // vec0 / total_vecs: the `vectors` handled are vec0.. of total_vecs in the scratch
+                 const void* x_raw = nullptr, int x_sum_mode = 0);
+// x_raw != null (element type = out_dtype): the activations [vectors or tokens][K] are NOT quantized yet and xq_soa is
+// ignored -- every CTA quantizes what it needs in shared memory (one launch per GEMV); returns 1 if that does not fit.
 // 1 when the q8_1 scratch of this type's GEMV must hold d * sum(q) instead of the fp16 sum of the inputs
 inline int gemv_sum_mode(int type) { return (type == 12 || type == 13) ? 1 : 0; }   // Q4_K, Q5_K
 // Packets of `nslots` gathered vectors (slot_packets apart) -> plain vectors out[s][0..n) (out_stride

@@ -4,10 +4,11 @@ Outputs, next to the Python package they serve (git-ignored, shipped with the tr
   vllm_gguf_plugin/libgguf_b200.so   the C-ABI kernel library (include/gguf_b200.h)
   vllm_gguf_plugin/_C_gguf.abi3.so   torch stable-ABI library `_C_gguf` calling the C-ABI
 
-Only quantize_q8_1.cu is compiled with --use_fast_math: its two fp32 divisions must be the
-same approximate instructions the reference emits (the reference builds everything with that
-flag, setup.py:34-42).  The other files contain no expression the flag would change in a way
-that matters, and stay with IEEE defaults.
+quantize_q8_1.cu and gemv1.cu (the decode GEMV that quantizes its activations itself) are
+compiled with --use_fast_math: the two fp32 divisions of the q8_1 quantization must be the same
+approximate instructions the reference emits (the reference builds everything with that flag,
+setup.py:34-42).  The other files contain no expression the flag would change in a way that
+matters, and stay with IEEE defaults.
 """
 from __future__ import annotations
 
@@ -25,7 +26,7 @@ OBJ = PKG / "build"
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CU_FILES = ["capi.cu", "quantize_q8_1.cu", "dequantize.cu", "gemv.cu", "gemv1.cu", "mmq.cu", "noalloc.cu", "tp.cu", "moe_fused.cu"]
-FAST_MATH = {"quantize_q8_1.cu"}
+FAST_MATH = {"quantize_q8_1.cu", "gemv1.cu"}
 
 
 def _stale(target: Path, deps) -> bool:
