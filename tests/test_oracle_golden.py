@@ -120,7 +120,7 @@ def test_iq_tables_match_reference_header_when_present():
     import sys
 
     sys.path.insert(0, str(ROOT / "include"))
-    from gen_iq_tables import render, tables
+    from gen_iq_tables import more_tables, render, tables
 
     src = hdr.read_text()
 
@@ -130,4 +130,8 @@ def test_iq_tables_match_reference_header_when_present():
 
     grid, ksigns, kvalues = tables()
     assert arr("iq2xxs_grid") == grid and arr("ksigns_iq2xs") == ksigns and arr("kvalues_iq4nl") == kvalues
+    iq2xs, iq2s, iq3xxs, iq3s, iq1s = more_tables()
+    assert arr("iq2xs_grid") == iq2xs and arr("iq2s_grid") == iq2s
+    assert arr("iq3xxs_grid") == iq3xxs and arr("iq3xs_grid") == iq3s   # (the IQ3_S code book is called iq3xs_grid there)
+    assert arr("iq1s_grid_gpu") == iq1s
     assert (ROOT / "include" / "gguf_b200_iq_tables.h").read_text() == render()

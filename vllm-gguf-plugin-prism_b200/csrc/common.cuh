@@ -131,6 +131,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the thread may stay parked for up to `ns` nanoseconds (it is
+// resumed as soon as the phase completes), instead of the much shorter default after which a
+// waiting warp comes back to poll again -- polls that take issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // non-blocking probe of a phase (try_wait may park the thread; this never does)
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -153,7 +167,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   do {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity, 8000u)) return true;
   } while (clock64() - t0 < limit_cycles);
   return false;
 }

@@ -438,11 +438,12 @@ template <> struct G1<T_Q5_K> {
 // amortises the per-item costs (copy issue, barrier wait, address arithmetic) over G1_R rows.
 //
 // Rows are shared out over the grid's "row lanes" (a row lane = the ks warps of a CTA that work
-// on the same rows; rl lanes per CTA) in one of two ways:
-//   contiguous   lane w owns rows [w*q + min(w, r), ...) with q = N / lanes, r = N % lanes: every
-//                lane gets q or q+1 rows, so no lane runs a whole extra pass, a lane streams one
-//                contiguous byte range, and the rows of a CTA are one contiguous range;
-//   round-robin  row groups are dealt to the lanes in turn (group = pass * lanes + lane).
+// on the same rows; rl lanes per CTA): lane w owns the contiguous rows [w*q + min(w, r), ...) with
+// q = N / lanes, r = N % lanes -- every lane gets q or q+1 rows, so no lane runs a whole extra
+// pass, a lane streams one contiguous byte range, and the rows of a CTA are one contiguous range.
+// (Dealing row groups to the lanes in turn measured the same with one slice and 4 % slower with
+// K-slices; giving a lane a smaller FIRST item, to start its arithmetic sooner, was slower on every
+// shape -- one more barrier round trip per warp costs more than the earlier start gains.)
 
 constexpr int G1_R = 4;
 constexpr int G1_MAX_WORLD = 8;
@@ -468,8 +469,9 @@ struct G1Params {
   int x_bytes;           // shared memory for the quantized activations (0 with x_alias)
   int x_alias;           // 1: they sit in the LAST stage of warp 0's ring, which is filled only after every warp has
                          //    its activations in registers (the first stages - 1 are on their way before)
-  int contig;            // 1: contiguous row ranges per lane, 0: round-robin row groups
-  int first_rows;        // contiguous: rows of a lane's first item (<= rows_per_item)
+  int ks_shift;          // log2(ks)
+  int q_rows, r_rows;    // N / lanes and N % lanes for lanes = grid.x * rl
+  unsigned inv_r;        // ceil(2^32 / rows_per_item): x / rows_per_item = umulhi(x, inv_r)  (unused when it is 1)
   int* status;
   // MoE decode (topk_ids != null, one vector): blockIdx.y is an output row s of y; it uses the
   // weights of expert topk_ids[s] (experts back to back, expert_bytes apart) and the activation
@@ -566,8 +568,10 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   fence_barrier_init();
   __syncwarp();
 
+  // (everything below is 32-bit arithmetic on values the host prepared: a 64-bit division per warp
+  //  costs as much as half a row of dot products, and a warp only has six or seven rows)
   const bool active = warp < p.ks * p.rl;
-  const int ks_i = warp % p.ks, rl_i = warp / p.ks;
+  const int ks_i = warp & (p.ks - 1), rl_i = warp >> p.ks_shift;
   const int sb0 = ks_i * p.slice_q + min(ks_i, p.slice_r);
   const int nblk = active ? p.slice_q + (ks_i < p.slice_r ? 1 : 0) : 0;
   const int units = nblk * UPB;
@@ -578,54 +582,32 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   const bool contiguous = p.ks == 1;
   const bool staged = p.ks > 1 || p.world > 0;   // results meet in shared memory before they are stored
 
-  // ---- which rows: lane_first(l) = first row of row lane l of this CTA, lane_count(l) its rows
-  // (contiguous), or first group / number of passes (round-robin) -------------------------------
-  const int64_t lanes = (int64_t)gridDim.x * p.rl;
-  const int64_t q_rows = p.n / lanes, r_rows = p.n % lanes;
-  const int64_t groups = (p.n + R - 1) / R;
-  auto lane_row0 = [&](int l) -> int64_t {
-    const int64_t wl = (int64_t)blockIdx.x * p.rl + l;
-    return wl * q_rows + (wl < r_rows ? wl : r_rows);
+  // ---- which rows: row lane wl (= the ks warps of a CTA that work on the same rows) owns the
+  // contiguous range [wl * q + min(wl, r), ...) of q or q + 1 rows, q = N / lanes, r = N % lanes ----
+  auto lane_row0 = [&](int l) -> int {
+    const int wl = (int)blockIdx.x * p.rl + l;
+    return wl * p.q_rows + min(wl, p.r_rows);
   };
-  auto lane_rows = [&](int l) -> int {
-    const int64_t wl = (int64_t)blockIdx.x * p.rl + l;
-    return (int)(q_rows + (wl < r_rows ? 1 : 0));
-  };
+  auto lane_rows = [&](int l) -> int { return p.q_rows + (((int)blockIdx.x * p.rl + l) < p.r_rows ? 1 : 0); };
   // first row and row count of item i of row lane l
-  // (contiguous: the FIRST item of a lane holds only p.first_rows rows -- it is on its way before
-  //  the activations exist and the sooner it lands the sooner the lane starts to work)
-  const int F = p.first_rows;
-  auto item = [&](int l, int i, int64_t& row, int& cnt) {
-    if (p.contig) {
-      const int done = i == 0 ? 0 : F + (i - 1) * R;
-      const int left = lane_rows(l) - done;
-      const int want = i == 0 ? F : R;
-      row = lane_row0(l) + done;
-      cnt = left < want ? (left > 0 ? left : 0) : want;
-    } else {
-      const int64_t g = ((int64_t)i * gridDim.x + blockIdx.x) * p.rl + l;
-      row = g * R;
-      const int64_t left = p.n - row;
-      cnt = g < groups ? (int)(left < R ? left : R) : 0;
-    }
+  auto item = [&](int l, int i, int& row, int& cnt) {
+    const int done = i * R;
+    row = lane_row0(l) + done;
+    cnt = min(R, max(lane_rows(l) - done, 0));
   };
   auto lane_iters = [&](int l) -> int {
-    if (p.contig) {
-      const int n_l = lane_rows(l);
-      return n_l <= F ? (n_l > 0 ? 1 : 0) : 1 + (n_l - F + R - 1) / R;
-    }
-    const int64_t f = (int64_t)blockIdx.x * p.rl + l;
-    return f < groups ? (int)((groups - f + lanes - 1) / lanes) : 0;
+    const unsigned x = (unsigned)(lane_rows(l) + R - 1);
+    return (int)(R == 1 ? x : __umulhi(x, p.inv_r));   // x / R
   };
   const int iters = lane_iters(0);   // lane 0 of a CTA never has fewer passes than the others: uniform over the CTA
   const int my_iters = (active && nblk > 0) ? lane_iters(rl_i) : 0;
 
   // copy of the rows [r0, r0 + cnt) (this warp's slice of them) into stage st
-  auto issue = [&](int64_t r0, int cnt, int st) {
+  auto issue = [&](int r0, int cnt, int st) {
     uint8_t* dst = ring + (size_t)st * p.stage_bytes;
     if (contiguous) {
       if (lane == 0) {
-        const int64_t beg = r0 * row_bytes, end = beg + (int64_t)cnt * row_bytes;
+        const int64_t beg = (int64_t)r0 * row_bytes, end = beg + (int64_t)cnt * row_bytes;
         const int64_t abeg = beg & ~int64_t(15);
         int64_t aend = (end + 15) & ~int64_t(15);
         if (aend > w_safe) aend = w_safe;
@@ -639,7 +621,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       }
     } else {
       // one copy per row; lane j computes and issues row j's, lane 0 announces the byte total first
-      const int64_t beg = (r0 + lane) * row_bytes + (int64_t)sb0 * TS, end = beg + slice_bytes;
+      const int64_t beg = (int64_t)(r0 + lane) * row_bytes + (int64_t)sb0 * TS, end = beg + slice_bytes;
       const int64_t abeg = beg & ~int64_t(15);
       int64_t aend = (end + 15) & ~int64_t(15);
       if (aend > w_safe) aend = w_safe;
@@ -664,8 +646,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
   int p_it = 0, p_st = 0;
   for (int s = 0; s < p.stages - 1; ++s) {
     if (p_it < my_iters) {
-      int64_t r0;
-      int cnt;
+      int r0, cnt;
       item(rl_i, p_it, r0, cnt);
       issue(r0, cnt, p_st);
       ++p_it;
@@ -804,8 +785,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     const bool mine = i < my_iters && !dead;
     if (mine) {
       if (p_it < my_iters) {   // the stage freed by the previous pass takes the next item
-        int64_t r0;
-        int cnt2;
+        int r0, cnt2;
         item(rl_i, p_it, r0, cnt2);
         issue(r0, cnt2, p_st);
         ++p_it;
@@ -817,12 +797,11 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
       }
     }
     if (mine && !dead) {
-      int64_t c_row;
-      int cnt;
+      int c_row, cnt;
       item(rl_i, i, c_row, cnt);
       uint8_t* stage = ring + (size_t)c_st * p.stage_bytes;
-      const int64_t beg0 = c_row * row_bytes + (int64_t)sb0 * TS;
-      const int64_t last_end = (c_row + cnt - 1) * row_bytes + (int64_t)sb0 * TS + slice_bytes;
+      const int64_t beg0 = (int64_t)c_row * row_bytes + (int64_t)sb0 * TS;
+      const int64_t last_end = beg0 + (int64_t)(cnt - 1) * row_bytes + slice_bytes;
       if (last_end > w_safe) {  // tail bytes the bulk copy must not touch: fetched with plain loads
         const int64_t lbeg = contiguous ? beg0 : last_end - slice_bytes;
         const int64_t abeg = lbeg & ~int64_t(15);
@@ -889,8 +868,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         const int m = t / (per_lane * p.rl), t2 = t - m * per_lane * p.rl;
         const int gl = t2 / per_lane, t3 = t2 - gl * per_lane;
         const int ii = i0 + t3 / G1_R, rr = t3 % G1_R;
-        int64_t r0;
-        int c;
+        int r0, c;
         item(gl, ii, r0, c);
         if (rr < c) {
           float s = 0.f;
@@ -923,13 +901,12 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   static const int ctas_env = g1_env("GGUF_B200_GEMV1_CTAS", 2);
   static const int rows_env = g1_env("GGUF_B200_GEMV1_ROWS", G1_R);
   static const int item_env = g1_env("GGUF_B200_GEMV1_ITEM_BYTES", 7168);
-  static const int contig_env = g1_env("GGUF_B200_GEMV1_CONTIG", 1);
-  p.contig = (contig_env || p.world > 0) ? 1 : 0;
   const int cap_blocks = 32 * (T::UMAX / MV) / T::UPB;  // blocks whose units fit one lane-register set
   int ks = 1;
   while (ks < 8 && (p.bpr + ks - 1) / ks > cap_blocks) ks *= 2;
   if ((p.bpr + ks - 1) / ks > cap_blocks) return 1;  // row too long for this kernel: caller falls back
   p.ks = ks;
+  p.ks_shift = ks == 1 ? 0 : (ks == 2 ? 1 : (ks == 4 ? 2 : 3));
   p.rl = G1_WARPS / ks;
   // balanced split (bpr >= ks always holds: ks > 1 only when bpr exceeds cap_blocks >= 4)
   p.slice_q = p.bpr / ks;
@@ -946,8 +923,7 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
   const int item_cap = item_env < room2 ? item_env : room2;
   while (R > 1 && (int64_t)R * (ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16)) > item_cap) --R;
   p.rows_per_item = R;
-  static const int first_env = g1_env("GGUF_B200_GEMV1_FIRST_ROWS", 0);
-  p.first_rows = first_env > 0 && first_env < R ? first_env : R;
+  p.inv_r = R == 1 ? 0u : (unsigned)(((1ull << 32) + R - 1) / R);
   p.slot_bytes = ks == 1 ? slice_bytes : (int)round_up(slice_bytes + 32, 16);
   p.stage_bytes = ks == 1 ? (int)round_up((int64_t)R * slice_bytes + 32, 16) : R * p.slot_bytes;
   const int kpad = (int)round_up(p.k, 512);
@@ -1013,6 +989,9 @@ static int launch_g1(G1Params p, cudaStream_t stream) {
     const int64_t per_pair = (148 * per_sm + gy - 1) / gy;
     if (grid > per_pair) grid = per_pair;
   }
+  if (p.n > 0x7fffff00ll) return 1;   // rows are counted in 32 bits
+  p.q_rows = (int)(p.n / (grid * p.rl));
+  p.r_rows = (int)(p.n % (grid * p.rl));
   return launch_pdl(kern, dim3((unsigned)grid, gy), dim3(G1_WARPS * 32), smem, stream, p) == cudaSuccess ? E_OK : E_CUDA;
 }
 
