@@ -9,7 +9,8 @@
  * as void*).  Scratch memory is provided by the caller (gguf_b200_workspace_bytes).
  *
  * Types: GGML ids 2 (Q4_0), 3 (Q4_1), 6 (Q5_0), 7 (Q5_1), 8 (Q8_0), 12 (Q4_K), 13 (Q5_K), 14 (Q6_K),
- * 16 (IQ2_XXS), 20 (IQ4_NL), 23 (IQ4_XS); the standalone dequantize also takes 10 (Q2_K), 11 (Q3_K).
+ * 16 (IQ2_XXS), 20 (IQ4_NL), 23 (IQ4_XS); the standalone dequantize also takes 10 (Q2_K), 11 (Q3_K),
+ * 17 (IQ2_XS), 18 (IQ3_XXS), 19 (IQ1_S), 21 (IQ3_S), 22 (IQ2_S), 29 (IQ1_M).
  * Weights W are raw GGUF blocks, row-major `uint8 [N][K/QK*type_size]`, base 16-byte aligned.
  * Activations X are `[M][K]` contiguous in `dtype`; outputs Y are `[M][N]` in the same dtype.
  */
@@ -58,7 +59,8 @@ int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int6
 
 /* Standalone dequantize, bit-exact with the reference.
  * Replaces: ggml_dequantize, gguf_kernel.cu:87-102 (+ dequantize.cuh:527-571 dispatch).
- * Types: all matmul types plus Q2_K (10) and Q3_K (11).
+ * Types: all matmul types plus Q2_K, Q3_K, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M (every type of the
+ * reference's dispatch).
  * Writes n_elems = m*n values (a multiple of the block size); every output element is
  * written, so the caller need not zero-fill. */
 int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream);
@@ -186,11 +188,31 @@ int64_t gguf_b200_noalloc_scratch_bytes(void);
  * Activations: x'[k] = X[k] + add_scale * gathered[add_slot][k] rounded to `dtype` (add_slot < 0:
  * x' = X; X may be null when add_slot >= 0) -- the quantizer of this call polls the packets of
  * add_slot itself, so a chain of dependent decode GEMVs needs no collective or wait kernel at all.
- * Returns GGUF_B200_E_TOO_LARGE when the rows are too long for the single-vector kernel. */
+ * Returns GGUF_B200_E_TOO_LARGE when the rows are too long for the single-vector kernel.
+ * add_parts = 1 when add_slot holds a gathered vector; = world when it holds the fp32 partial
+ * vectors of a row-parallel call (below), whose sum is then what is added. */
 int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* packet_peers, uint32_t* epochs_local,
-                                int slot, int add_slot, float add_scale, int64_t slot_packets, void* ws,
+                                int slot, int add_slot, float add_scale, int add_parts, int64_t slot_packets, void* ws,
                                 int64_t ws_bytes, int type, int dtype, int64_t N_local, int64_t K, int rank, int world,
                                 void* stream);
+/* Row-parallel (K-sharded) decode with the all-reduce fused in.  Reference: the loader narrows dim 1
+ * of a row-parallel layer's weight to whole blocks (quantization/params.py:238-265) and the serving
+ * engine all-reduces the partial outputs with a separate NCCL collective.  Here rank `rank` holds
+ * W_local = uint8 [N][K_local/QK*type_size] (its K_local columns of every row) and X_local, its
+ * K_local elements of the activation vector; its GEMV sends the fp32 partial sums to ALL ranks as
+ * 8-byte packets {f32, tag32} (partial vector r at packet index r*N of the slot, counted in 8-byte
+ * packets from the slot's first byte; the slot has slot_packets packet units of 4 bytes for
+ * f16/bf16 arenas and 8 for f32 ones, so it needs world*N*8 bytes).  The reduced vector is the sum
+ * of the world partial vectors in rank order, rounded once to dtype -- identical bits on every
+ * rank -- formed by gguf_b200_tp_unpack_sum or by the activation quantizer of the next tensor-
+ * parallel call (add_parts = world).  x'[k] = X_local[k] + add_scale * v[rank*K_local + k] with v
+ * the vector in add_slot (gathered: add_parts = 1; reduced: add_parts = world), as above. */
+int gguf_b200_mul_mat_vec_a8_tp_rowpar(const void* W_local, const void* X_local, void* const* packet_peers,
+                                       uint32_t* epochs_local, int slot, int add_slot, float add_scale, int add_parts,
+                                       int64_t slot_packets, void* ws, int64_t ws_bytes, int type, int dtype, int64_t N,
+                                       int64_t K_local, int rank, int world, void* stream);
+int gguf_b200_tp_unpack_sum(const void* packets_local, const uint32_t* epochs_local, int slot, int64_t slot_packets,
+                            int64_t n, int parts, void* out, int dtype, void* stream);
 /* Packets -> plain vectors, for consumers that are not one of the calls above: out[s][0..n) =
  * values of slot slot0+s (s < nslots, out rows out_stride elements apart), each packet polled
  * until its tag equals epochs_local[slot0+s]. */

@@ -4,8 +4,9 @@
  * tests (and the CPU-baseline leg of the benchmark) can check the CUDA kernels.
  *
  * It restates, in plain C, the arithmetic of the reference plugin's CUDA kernels
- * (vllm_gguf_plugin/csrc/gguf/ of akmorley/vllm-gguf-plugin-prism) for six block types:
- *   Q4_0 (2), Q8_0 (8), Q4_K (12), Q6_K (14), IQ2_XXS (16), IQ4_XS (23).
+ * (vllm_gguf_plugin/csrc/gguf/ of akmorley/vllm-gguf-plugin-prism) for these block types:
+ *   Q4_0 (2), Q8_0 (8), Q4_K (12), Q6_K (14), IQ2_XXS (16), IQ4_XS (23), and later additions
+ *   (Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL; dequantize only: IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M).
  * Each function names the reference lines it follows.  Half-precision steps are
  * emulated exactly (one IEEE rounding per __hmul/__hsub/__int2half_rn), so the
  * dequantize outputs are bit patterns, not approximations.  Matmul entry points are
@@ -34,7 +35,8 @@
 #define QK_K 256
 
 enum { T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14,
-       T_IQ2_XXS = 16, T_IQ4_NL = 20, T_IQ4_XS = 23 };
+       T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ1_S = 19, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ4_XS = 23,
+       T_IQ1_M = 29 };
 enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 
 /* ------------------------------------------------------------------ */
@@ -203,6 +205,12 @@ int oracle_type_size(int type) {
     case T_Q3_K: return 110;
     case T_Q5_K: return 176;
     case T_IQ4_NL: return 18;
+    case T_IQ2_XS: return 74;  /* (the code-book types below: dequantize only) */
+    case T_IQ2_S: return 82;
+    case T_IQ3_XXS: return 98;
+    case T_IQ3_S: return 110;
+    case T_IQ1_S: return 50;
+    case T_IQ1_M: return 56;
   }
   return 0;
 }
@@ -321,6 +329,83 @@ int oracle_dequantize(const uint8_t* w, int type, void* out, int out_dt, int64_t
             }
           }
         }
+      } break;
+      case T_IQ2_XS: case T_IQ2_S: case T_IQ3_XXS: case T_IQ3_S: {
+        /* dequantize_block_iq2_xs / iq2_s / iq3_xxs / iq3_s, dequantize.cuh:277-353: per group of 8
+         * values (ib = sub-block of 32, il = group) y[j] = d * grid[j] * sign(j) in fp32, with
+         * d = half2float(x.d) * (0.5f + scale) * 0.25f (IQ2) or * 0.5f (IQ3). */
+        float df = h2f(rd16(blk));
+        for (int ib = 0; ib < 8; ++ib)
+          for (int il = 0; il < 4; ++il) {
+            uint64_t grid;
+            uint32_t signs, sc;
+            float mul;
+            if (type == T_IQ2_XS) {          /* half d | u16 qs[32] | u8 scales[8] */
+              uint32_t q = rd16(blk + 2 + 2 * (4 * ib + il));
+              grid = gguf_b200_iq2xs_grid[q & 511];
+              signs = gguf_b200_ksigns_iq2xs[q >> 9];
+              sc = (blk[66 + ib] >> (4 * (il / 2))) & 0xf;
+              mul = 0.25f;
+            } else if (type == T_IQ2_S) {    /* half d | u8 qs[64] (32 indices, 32 sign bytes) | u8 qh[8] | u8 scales[8] */
+              grid = gguf_b200_iq2s_grid[blk[2 + 4 * ib + il] | (((uint32_t)blk[66 + ib] << (8 - 2 * il)) & 0x300)];
+              signs = blk[2 + 32 + 4 * ib + il];
+              sc = (blk[74 + ib] >> (4 * (il / 2))) & 0xf;
+              mul = 0.25f;
+            } else if (type == T_IQ3_XXS) {  /* half d | u8 qs[64] | u32 scale+signs [8] */
+              const uint8_t* q3 = blk + 2 + 8 * ib;
+              const uint8_t* g = blk + 2 + 64 + 4 * ib;
+              uint32_t aux32 = (uint32_t)g[0] | ((uint32_t)g[1] << 8) | ((uint32_t)g[2] << 16) | ((uint32_t)g[3] << 24);
+              grid = (uint64_t)gguf_b200_iq3xxs_grid[q3[2 * il]] | ((uint64_t)gguf_b200_iq3xxs_grid[q3[2 * il + 1]] << 32);
+              signs = gguf_b200_ksigns_iq2xs[(aux32 >> (7 * il)) & 127];
+              sc = aux32 >> 28;
+              mul = 0.5f;
+            } else {                         /* half d | u8 qs[64] | u8 qh[8] | u8 signs[32] | u8 scales[4] */
+              const uint8_t* qs = blk + 2 + 8 * ib;
+              uint32_t qh = blk[66 + ib];
+              grid = (uint64_t)gguf_b200_iq3s_grid[qs[2 * il] | ((qh << (8 - 2 * il)) & 256)] |
+                     ((uint64_t)gguf_b200_iq3s_grid[qs[2 * il + 1] | ((qh << (7 - 2 * il)) & 256)] << 32);
+              signs = blk[74 + 4 * ib + il];
+              sc = (blk[106 + ib / 2] >> (4 * (ib % 2))) & 0xf;
+              mul = 0.5f;
+            }
+            volatile float d = df * (0.5f + (float)sc);
+            d = d * mul;
+            for (int j = 0; j < 8; ++j) {
+              volatile float v = d * (float)((grid >> (8 * j)) & 0xff);
+              v = v * ((signs >> j) & 1 ? -1.f : 1.f);
+              store_f(out, out_dt, o + 32 * ib + 8 * il + j, v);
+            }
+          }
+      } break;
+      case T_IQ1_S: case T_IQ1_M: {
+        /* dequantize_block_iq1_s / iq1_m, dequantize.cuh:355-399: y[j] = d * (q[j] + delta), q in {0,1,2}
+         * nibble-packed in the code book, delta = -1 - 1/8 or -1 + 1/8, d = scale * (2 * s3 + 1). */
+        for (int ib = 0; ib < 8; ++ib)
+          for (int il = 0; il < 4; ++il) {
+            volatile float d;
+            float delta;
+            uint32_t g;
+            if (type == T_IQ1_S) {           /* half d | u8 qs[32] | u16 qh[8] */
+              uint32_t qh = rd16(blk + 34 + 2 * ib);
+              delta = (qh & 0x8000) ? -1.f - 0.125f : -1.f + 0.125f;
+              d = h2f(rd16(blk)) * (float)(2 * ((qh >> 12) & 7) + 1);
+              g = gguf_b200_iq1s_grid[blk[2 + 4 * ib + il] | (((qh >> (3 * il)) & 7) << 8)];
+            } else {                         /* u8 qs[32] | u8 qh[16] | u16 scales[4] */
+              uint32_t sc0 = rd16(blk + 48), sc1 = rd16(blk + 50), sc2 = rd16(blk + 52), sc3 = rd16(blk + 54);
+              uint16_t s16 = (uint16_t)((sc0 >> 12) | ((sc1 >> 8) & 0x00f0) | ((sc2 >> 4) & 0x0f00) | (sc3 & 0xf000));
+              int ib16 = 2 * ib + il / 2;
+              uint32_t scw = rd16(blk + 48 + 2 * (ib16 / 4));
+              d = h2f(s16) * (float)(2 * ((scw >> (3 * (ib16 % 4))) & 7) + 1);
+              uint32_t qh = blk[32 + 2 * ib + il / 2];
+              delta = (qh & (0x08u << (4 * (il % 2)))) ? -1.f - 0.125f : -1.f + 0.125f;
+              g = gguf_b200_iq1s_grid[blk[4 * ib + il] | (((qh >> (4 * (il % 2))) & 7) << 8)];
+            }
+            for (int j = 0; j < 8; ++j) {
+              volatile float q = (float)((g >> (8 * (j & 3) + 4 * (j >> 2))) & 0xf) + delta;
+              volatile float v = d * q;
+              store_f(out, out_dt, o + 32 * ib + 8 * il + j, v);
+            }
+          }
       } break;
       case T_Q4_1: { /* dequantize_q4_1, dequantize.cuh:17-31: v = q*d + m (contract: one fused multiply-add) */
         uint16_t d = rd16(blk), m = rd16(blk + 2);

@@ -74,9 +74,10 @@ def test_tensor_parallel_entry_points_validate_arguments(native_libs):
     p = ctypes.c_void_p(4096)
     two = (ctypes.c_void_p * 2)(4096, 8192)
     ptrs = ctypes.cast(two, ctypes.c_void_p)
-    # decode: W, X, packet arenas, epochs, slot, add_slot, add_scale, slot_packets, ws, ws_bytes, type, dtype, N_local, K, rank, world, stream
+    # decode: W, X, packet arenas, epochs, slot, add_slot, add_scale, add_parts, slot_packets, ws, ws_bytes, type, dtype, N_local, K, rank, world, stream
     args = lambda **kw: [kw.get("W", p), kw.get("X", p), kw.get("y", ptrs), kw.get("e", p), kw.get("slot", 0), kw.get("add", -1), 0.0,
-                         kw.get("sp", 1024), p, 1 << 20, kw.get("type", 12), 1, 64, 256, kw.get("rank", 0), kw.get("world", 2), null]
+                         kw.get("parts", 1), kw.get("sp", 1024), p, 1 << 20, kw.get("type", 12), 1, 64, 256, kw.get("rank", 0),
+                         kw.get("world", 2), null]
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(y=null)) == -4
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(e=null)) == -4
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(X=null)) == -4          # no activations at all
@@ -86,6 +87,15 @@ def test_tensor_parallel_entry_points_validate_arguments(native_libs):
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(sp=100)) == -3          # slot too small for world * N_local
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(add=0)) == -3           # a call cannot consume its own slot
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(type=10)) == -1
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(add=1, parts=3)) == -3  # partial vectors come one per rank, or not at all
+    # row-parallel: same arguments, N and K_local in place of N_local and K; a slot holds world * N fp32 partials
+    assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(y=null)) == -4
+    assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(world=9)) == -3
+    assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(sp=200)) == -3   # 2 ranks x 64 rows x 8 bytes > 200 x 4
+    assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(type=11)) == -1
+    assert lib.gguf_b200_tp_unpack_sum(null, p, 0, 1024, 64, 2, p, 1, null) == -4
+    assert lib.gguf_b200_tp_unpack_sum(p, p, 0, 1024, 64, 9, p, 1, null) == -3
+    assert lib.gguf_b200_tp_unpack_sum(p, p, 0, 1024, 4096, 2, p, 1, null) == -3   # partials beyond the slot
     assert lib.gguf_b200_tp_unpack(null, p, 0, 1, 1024, 64, p, 64, 1, null) == -4
     assert lib.gguf_b200_tp_unpack(p, p, 0, 1, 1024, 2048, p, 2048, 1, null) == -3   # n beyond the slot
     assert lib.gguf_b200_tp_unpack(p, p, 0, 1, 1024, 64, p, 64, 9, null) == -2

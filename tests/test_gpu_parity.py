@@ -111,7 +111,7 @@ def test_dequantize_full_matrices_bit_exact_on_device(ref):
         torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "IQ2_XXS", "Q5_K", "Q3_K", "IQ4_NL"])
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "IQ2_XXS", "Q5_K", "Q3_K", "IQ4_NL", "IQ3_S", "IQ1_M"])
 def test_embedding_row_gather_equals_index_select_then_dequantize(ref, name):
     """The embedding caller: rows picked inside the dequantize kernel, bit for bit what the
     reference's two steps (index_select, ggml_dequantize) give; an id outside the table gives zeros."""
@@ -546,6 +546,64 @@ def test_tp_gemv_packets_one_gpu(name, dtype):
     # both slots at once
     both = capi.tp_unpack(arenas[0], epochs[0], 1, 2, slot_packets, N, dtype)
     assert torch.equal(both[0:1], want) and torch.equal(both[1:2], want2)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("name", ["Q4_K", "Q8_0", "Q6_K", "IQ2_XXS"])
+def test_tp_gemv_row_parallel_one_gpu(ref, name, dtype):
+    """K-sharded decode, two emulated ranks: each sends the fp32 partial sums over its half of K to
+    both arenas; their sum in rank order is the all-reduced vector -- the same bits on both ranks,
+    equal to 'partial GEMVs in fp32, added, rounded once', and close to the unsharded GEMV and to
+    the reference kernel.  A column-parallel call then consumes the reduced vector in its quantizer,
+    and a row-parallel call consumes a gathered one (the two pairings of a tensor-parallel MLP)."""
+    t = TYPES[name]
+    N, K, world = 1024, 4096, 2
+    wn, w = dev_w(t, N, K, seed=11)
+    x = dev_x(1, K, seed=11, dtype=dtype)
+    from gguf_b200 import tp as tpmod
+
+    wk = [tpmod.shard_cols(w, t, r, world) for r in range(world)]
+    xk = [x[:, r * K // world:(r + 1) * K // world].contiguous() for r in range(world)]
+    parts = [capi.mul_mat_vec_a8(wk[r], xk[r].float(), t, N) for r in range(world)]      # fp32 partial GEMVs
+    want = (parts[0] + parts[1]).to(dtype)
+    psz = 8 if dtype == torch.float32 else 4
+    slots, slot_packets = 4, world * N * 8 // psz
+    arenas = [torch.zeros(slots * slot_packets * psz, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    epochs = [torch.zeros(slots, dtype=torch.int32, device=DEV) for _ in range(world)]
+    ptrs = [a.data_ptr() for a in arenas]
+    for rep in range(2):
+        for r in range(world):
+            capi.mul_mat_vec_a8_tp_rowpar(wk[r], xk[r], ptrs, epochs[r], 0, slot_packets, t, r)
+        got = [capi.tp_unpack_sum(arenas[r], epochs[r], 0, slot_packets, N, world, dtype) for r in range(world)]
+        assert torch.equal(got[0], got[1])
+        assert torch.equal(got[0].view(1, N), want), "not the rank-ordered fp32 sum of the partial GEMVs"
+    full = capi.mul_mat_vec_a8(w, x, t, N)
+    assert rel_l2(got[0].float().cpu().view(1, N), full.float().cpu()) <= 1e-3   # (fp16 rounding of the result: 5e-4)
+    if ref.available and name != "IQ2_XXS" or ref.available and K <= 4096:
+        r_full = ref.ops.ggml_mul_mat_vec_a8(w, x, t, N)
+        assert rel_l2(got[0].float().cpu().view(1, N), r_full.float().cpu()) <= 1e-3
+    # column-parallel call on x2 = x[:N] + s * reduced(slot 0)  (rows of w2 split over the ranks)
+    s = 2.0 ** -10
+    _, w2 = dev_w(t, 512, N, seed=12)
+    x2 = (x[:, :N].float() + s * want.float()).to(dtype)
+    want2 = capi.mul_mat_vec_a8(w2, x2, t, 512)
+    for r in range(world):
+        capi.mul_mat_vec_a8_tp(w2[r * 256:(r + 1) * 256].contiguous(), x[:, :N].contiguous(), ptrs, epochs[r], 1, slot_packets, t, r,
+                               add_slot=0, add_scale=s, add_parts=world)
+    for r in range(world):
+        assert torch.equal(capi.tp_unpack(arenas[r], epochs[r], 1, 1, slot_packets, 512, dtype), want2)
+    # row-parallel call whose activations are this rank's slice of s * gathered(slot 1)  (no X at all)
+    _, w3 = dev_w(t, 256, 512, seed=13)
+    x3 = (s * want2.float()).to(dtype)
+    w3k = [tpmod.shard_cols(w3, t, r, world) for r in range(world)]
+    p3 = [capi.mul_mat_vec_a8(w3k[r], x3[:, r * 256:(r + 1) * 256].contiguous().float(), t, 256) for r in range(world)]
+    want3 = (p3[0] + p3[1]).to(dtype)
+    for r in range(world):
+        capi.mul_mat_vec_a8_tp_rowpar(w3k[r], None, ptrs, epochs[r], 2, slot_packets, t, r, add_slot=1, add_scale=s, dtype=dtype)
+    for r in range(world):
+        assert torch.equal(capi.tp_unpack_sum(arenas[r], epochs[r], 2, slot_packets, 256, world, dtype).view(1, 256), want3)
     torch.cuda.synchronize()
     assert capi.last_status() == 0
 

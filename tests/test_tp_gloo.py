@@ -40,6 +40,17 @@ def _worker(rank, world, port, qtype, n, k, m, out_dir):
         assert torch.equal(y, full), "sharded result must equal the unsharded one exactly"
         with pytest.raises(ValueError):
             tp.shard_rows(w[:n - 1], rank, world)
+        # row-parallel: whole blocks of every row per rank, this rank's K/g activations, all-reduce
+        if (k // synth.QUANT_SIZES[qtype][0]) % world == 0:
+            row = tp.RowParallelGGUFLinear(w, qtype, matmul=oracle_matmul)
+            bw = w.shape[1] // world
+            assert torch.equal(row.weight, w[:, rank * bw:(rank + 1) * bw])
+            y_row = row(x[:, rank * k // world:(rank + 1) * k // world].contiguous())
+            assert y_row.shape == (m, n)
+            err = float(torch.linalg.norm(y_row - full) / torch.linalg.norm(full))
+            assert err <= 1e-5, err   # (same products, summed in two halves)
+        with pytest.raises(ValueError):
+            tp.shard_cols(w[:, : synth.QUANT_SIZES[qtype][1]], qtype, rank, world)   # one block per row cannot be split in two
         (Path(out_dir) / f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

@@ -42,7 +42,7 @@ def _worker(rank, world, port, out_dir):
 
         # ---- decode: packets over NVLink, chained through the quantizer ------------------------
         n_up = 2048                                       # up: K=1024 -> N=2048 ; down: K=2048 -> N=1024
-        fused = tp.FusedGatherGemv(n_up, 6, torch.float16, dev)
+        fused = tp.FusedGatherGemv(n_up, 6, torch.float16, dev, reduce_n=1024)
         for name, t in (("Q4_K", 12), ("IQ2_XXS", 16), ("Q8_0", 8)):
             w_up, w_dn = weight(t, n_up, 1024, 1), weight(t, 1024, n_up, 2)
             x = act(1, 1024, 3)
@@ -63,6 +63,38 @@ def _worker(rank, world, port, out_dir):
                 assert torch.equal(got[1], y1), f"{name}: chained call 1 differs (rank {rank})"
                 assert torch.equal(got[2], y2), f"{name}: chained call 2 differs (rank {rank})"
                 dist.barrier()   # nobody rewrites slot 0 while a slower rank still unpacks it
+        # ---- row-parallel decode: K-shards, fp32 partial sums to every rank, summed in rank order ---
+        # (the pairing of a tensor-parallel MLP: up = column-parallel, down = row-parallel on this
+        #  rank's slice of the up result, ONE reduction per pair)
+        for name, t in (("Q4_K", 12), ("Q8_0", 8)):
+            w_up, w_dn = weight(t, n_up, 1024, 11), weight(t, 1024, n_up, 12)
+            x = act(1, 1024, 13)
+            s = 2.0 ** -10
+            for rep in range(2):
+                fused(3, tp.shard_rows(w_up, rank, world), x, t)                                       # y0 = W_up x          (gathered)
+                fused.rowpar(4, tp.shard_cols(w_dn, t, rank, world), None, t, add_slot=3, add_scale=s)  # y1 = W_dn (s * y0)   (reduced)
+                fused(5, tp.shard_rows(w_up, rank, world), x, t, add_slot=4, add_scale=s, add_parts=world)   # y2 = W_up (x + s * y1)
+                got1, got2 = fused.reduced(4, 1024), fused.gathered(5)
+                y0 = capi.mul_mat_vec_a8(w_up, x, t, n_up)
+                x1 = (s * y0.float()).half()
+                kl = n_up // world
+                parts = [capi.mul_mat_vec_a8(tp.shard_cols(w_dn, t, r, world), x1[:, r * kl:(r + 1) * kl].contiguous().float(), t, 1024)
+                         for r in range(world)]
+                acc = parts[0].clone()
+                for p_ in parts[1:]:
+                    acc += p_
+                y1 = acc.half()
+                y2 = capi.mul_mat_vec_a8(w_up, (x.float() + s * y1.float()).half(), t, n_up)
+                torch.cuda.synchronize()
+                assert capi.last_status() == 0
+                assert torch.equal(got1.view(1, -1), y1), f"{name}: reduced row-parallel GEMV differs (rank {rank})"
+                assert torch.equal(got2, y2), f"{name}: call after the reduction differs (rank {rank})"
+                full = capi.mul_mat_vec_a8(w_dn, x1, t, 1024)
+                assert rel_l2(got1.float().cpu().view(1, -1), full.float().cpu()) <= 1e-3
+                dist.barrier()
+            y_nccl = tp.RowParallelGGUFLinear(w_dn, t, matmul=lambda xx, ww, tt: capi.mul_mat_vec_a8(ww, xx, tt, ww.shape[0]))(
+                x1[:, rank * kl:(rank + 1) * kl].contiguous())
+            assert rel_l2(y_nccl.float().cpu(), full.float().cpu()) <= 2e-3
         # ---- decode through NCCL (the plain collective, for reference) -------------------------
         w = weight(12, 1024, 2048, 5)
         x = act(1, 2048, 6)

@@ -70,7 +70,7 @@ const char* gguf_b200_version(void) { return "gguf_b200 0.1 (sm_100a)"; }
 const char* gguf_b200_error_string(int code) {
   switch (code) {
     case E_OK: return "ok";
-    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q4_1=3, Q5_0=6, Q5_1=7, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14, IQ2_XXS=16, IQ4_NL=20, IQ4_XS=23; dequantize also Q2_K=10, Q3_K=11)";
+    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q4_1=3, Q5_0=6, Q5_1=7, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14, IQ2_XXS=16, IQ4_NL=20, IQ4_XS=23; dequantize also Q2_K=10, Q3_K=11, IQ2_XS=17, IQ3_XXS=18, IQ1_S=19, IQ3_S=21, IQ2_S=22, IQ1_M=29)";
     case E_BAD_DTYPE: return "unsupported dtype (expected f32=0, f16=1, bf16=2)";
     case E_BAD_SHAPE: return "bad shape (negative size, or K not a multiple of the block size)";
     case E_BAD_POINTER: return "null or misaligned pointer (16-byte alignment required)";
@@ -170,15 +170,31 @@ int gguf_b200_mul_mat_vec_a8(const void* W, const void* X, void* Y, void* ws, in
   return launch_gemv(W, ws, Y, type, dtype, M, N, K, st, s);
 }
 
+// the activation quantizer's view of the slot whose contents are added to x (both tensor-parallel decode calls)
+// (the vector in add_slot has `full` elements; the caller needs those from `first` on)
+static int tp_add_setup(Q8Tp& qt, const void* arena_local, const uint32_t* epochs_local, int add_slot, float add_scale, int add_parts,
+                        int64_t slot_packets, int64_t psz, int64_t full, int64_t first, int world) {
+  if (add_slot < 0) return E_OK;
+  if (add_parts != 1 && add_parts != world) return E_BAD_SHAPE;
+  if (add_parts == 1 ? full > slot_packets : (int64_t)add_parts * full * 8 > slot_packets * psz) return E_BAD_SHAPE;
+  qt.add = static_cast<const uint8_t*>(arena_local) + (int64_t)add_slot * slot_packets * psz + first * (add_parts == 1 ? psz : 8);
+  qt.add_epoch = epochs_local + add_slot;
+  qt.add_scale = add_scale;
+  qt.add_parts = add_parts;
+  qt.add_stride = full;
+  return E_OK;
+}
+
 int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* packet_peers, uint32_t* epochs_local, int slot,
-                                int add_slot, float add_scale, int64_t slot_packets, void* ws, int64_t ws_bytes, int type,
-                                int dtype, int64_t N_local, int64_t K, int rank, int world, void* stream) {
+                                int add_slot, float add_scale, int add_parts, int64_t slot_packets, void* ws, int64_t ws_bytes,
+                                int type, int dtype, int64_t N_local, int64_t K, int rank, int world, void* stream) {
   if (!packet_peers || !epochs_local) return E_BAD_POINTER;
   if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0 || slot_packets <= 0) return E_BAD_SHAPE;
   if (!X && add_slot < 0) return E_BAD_POINTER;
   int rc = check_common(W, X ? X : W, packet_peers[rank], type, dtype, 1, N_local, K);
   if (rc || N_local == 0) return rc;
-  if ((int64_t)world * N_local > slot_packets || (add_slot >= 0 && K > slot_packets) || add_slot == slot) return E_BAD_SHAPE;
+  if ((int64_t)world * N_local > slot_packets || add_slot == slot) return E_BAD_SHAPE;
+  if (add_slot >= 0 && add_parts != 1 && add_parts != world) return E_BAD_SHAPE;
   if (!ws || !aligned16(ws)) return E_BAD_POINTER;
   if (ws_bytes < q8_soa_bytes(1, K)) return E_WORKSPACE;
   int* st = status_ptr();
@@ -198,15 +214,65 @@ int gguf_b200_mul_mat_vec_a8_tp(const void* W, const void* X, void* const* packe
   qt.bump = epochs_local + slot;    // this launch's number, read by the GEMV kernel behind the quantizer
   qt.status = st;
   qt.limit_cycles = g_wait_limit_cycles;
-  if (add_slot >= 0) {   // x' = x + add_scale * (vector gathered in add_slot): the quantizer polls its packets
-    qt.add = static_cast<const uint8_t*>(packet_peers[rank]) + (int64_t)add_slot * slot_packets * psz;
-    qt.add_epoch = epochs_local + add_slot;
-    qt.add_scale = add_scale;
-  }
+  // x' = x + add_scale * (vector gathered, or partial vectors reduced, in add_slot): the quantizer polls its packets
+  rc = tp_add_setup(qt, packet_peers[rank], epochs_local, add_slot, add_scale, add_parts, slot_packets, psz, K, 0, world);
+  if (rc) return rc;
   rc = launch_quantize_q8_1(X, dtype, ws, 1, K, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s, 0, &qt);
   if (rc) return rc;
   rc = launch_gemv1(W, ws, nullptr, type, dtype, N_local, K, st, s, &tp);
   return rc == 1 ? E_TOO_LARGE : rc;   // rows too long for the single-vector kernel
+}
+
+int gguf_b200_mul_mat_vec_a8_tp_rowpar(const void* W_local, const void* X_local, void* const* packet_peers, uint32_t* epochs_local,
+                                       int slot, int add_slot, float add_scale, int add_parts, int64_t slot_packets, void* ws,
+                                       int64_t ws_bytes, int type, int dtype, int64_t N, int64_t K_local, int rank, int world,
+                                       void* stream) {
+  if (!packet_peers || !epochs_local) return E_BAD_POINTER;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0 || slot_packets <= 0) return E_BAD_SHAPE;
+  if (!X_local && add_slot < 0) return E_BAD_POINTER;
+  int rc = check_common(W_local, X_local ? X_local : W_local, packet_peers[rank], type, dtype, 1, N, K_local);
+  if (rc || N == 0) return rc;
+  const int64_t psz = dtype == DT_F32 ? 8 : 4;   // bytes per packet unit of the arena (the partials always take 8)
+  if ((int64_t)world * N * 8 > slot_packets * psz || add_slot == slot) return E_BAD_SHAPE;
+  if (add_slot >= 0 && add_parts != 1 && add_parts != world) return E_BAD_SHAPE;
+  if (!ws || !aligned16(ws)) return E_BAD_POINTER;
+  if (ws_bytes < q8_soa_bytes(1, K_local)) return E_WORKSPACE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  GemvTp tp{};
+  tp.world = world;
+  tp.slot = slot;
+  tp.epoch = epochs_local;
+  tp.y_off = (int64_t)rank * N;    // partial vector r sits N fp32 packets after partial vector r - 1
+  for (int r = 0; r < world; ++r) {
+    if (!packet_peers[r] || (reinterpret_cast<uintptr_t>(packet_peers[r]) & 15)) return E_BAD_POINTER;
+    tp.ll_peer[r] = static_cast<uint8_t*>(packet_peers[r]) + (int64_t)slot * slot_packets * psz;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Q8Tp qt{};
+  qt.bump = epochs_local + slot;
+  qt.status = st;
+  qt.limit_cycles = g_wait_limit_cycles;
+  // (this rank's slice of the vector in add_slot: gathered or reduced vectors are indexed from the slice's first element)
+  rc = tp_add_setup(qt, packet_peers[rank], epochs_local, add_slot, add_scale, add_parts, slot_packets, psz, (int64_t)world * K_local,
+                    (int64_t)rank * K_local, world);
+  if (rc) return rc;
+  rc = launch_quantize_q8_1(X_local, dtype, ws, 1, K_local, Q8_MODE_SOA, gemv_sum_mode(type), 0, CORR_NONE, nullptr, 1, 0, s, 0, &qt);
+  if (rc) return rc;
+  rc = launch_gemv1(W_local, ws, nullptr, type, DT_F32, N, K_local, st, s, &tp);   // fp32 partial sums travel as 8-byte packets
+  return rc == 1 ? E_TOO_LARGE : rc;
+}
+
+int gguf_b200_tp_unpack_sum(const void* packets_local, const uint32_t* epochs_local, int slot, int64_t slot_packets, int64_t n,
+                            int parts, void* out, int dtype, void* stream) {
+  if (!packets_local || !epochs_local || !out) return E_BAD_POINTER;
+  if (!dtype_ok(dtype)) return E_BAD_DTYPE;
+  const int64_t psz = dtype == DT_F32 ? 8 : 4;
+  if (slot < 0 || n < 0 || parts < 1 || parts > 8 || (int64_t)parts * n * 8 > slot_packets * psz) return E_BAD_SHAPE;
+  int* st = status_ptr();
+  if (!st) return E_CUDA;
+  return launch_tp_unpack_sum(packets_local, epochs_local, slot, slot_packets * psz, n, parts, out, dtype, g_wait_limit_cycles, st,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int gguf_b200_tp_unpack(const void* packets_local, const uint32_t* epochs_local, int slot0, int nslots, int64_t slot_packets,

@@ -32,6 +32,15 @@ enum : int { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T
 //   Q5_K   176 : half d | half dmin | u8 scales[12] | u8 qh[32] | u8 qs[128]
 //   IQ4_NL  18 : half d | u8 qs[16]                               4-bit indices into the IQ4 level table
 enum : int { T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q2_K = 10, T_Q3_K = 11, T_Q5_K = 13, T_IQ4_NL = 20 };
+// code-book types with a standalone dequantizer only (256 values per block; the matmul callers
+// dequantize and then multiply, as the reference does above its GEMV threshold):
+//   IQ2_XS   74 : half d | u16 qs[32] | u8 scales[8]
+//   IQ2_S    82 : half d | u8 qs[32] | u8 signs[32] | u8 qh[8] | u8 scales[8]
+//   IQ3_XXS  98 : half d | u8 qs[64] | u32 scales_and_signs[8]
+//   IQ3_S   110 : half d | u8 qs[64] | u8 qh[8] | u8 signs[32] | u8 scales[4]
+//   IQ1_S    50 : half d | u8 qs[32] | u16 qh[8]
+//   IQ1_M    56 : u8 qs[32] | u8 qh[16] | u8 scales[8]   (the fp16 scale is spread over the top nibbles of scales)
+enum : int { T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ1_S = 19, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ1_M = 29 };
 enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 
 // error codes returned through the C-ABI (0 = success)
@@ -61,6 +70,12 @@ template <> struct BlockTraits<T_Q2_K>    { static constexpr int QK = 256, TS = 
 template <> struct BlockTraits<T_Q3_K>    { static constexpr int QK = 256, TS = 110; };
 template <> struct BlockTraits<T_Q5_K>    { static constexpr int QK = 256, TS = 176; };
 template <> struct BlockTraits<T_IQ4_NL>  { static constexpr int QK = 32,  TS = 18;  };
+template <> struct BlockTraits<T_IQ2_XS>  { static constexpr int QK = 256, TS = 74;  };
+template <> struct BlockTraits<T_IQ2_S>   { static constexpr int QK = 256, TS = 82;  };
+template <> struct BlockTraits<T_IQ3_XXS> { static constexpr int QK = 256, TS = 98;  };
+template <> struct BlockTraits<T_IQ3_S>   { static constexpr int QK = 256, TS = 110; };
+template <> struct BlockTraits<T_IQ1_S>   { static constexpr int QK = 256, TS = 50;  };
+template <> struct BlockTraits<T_IQ1_M>   { static constexpr int QK = 256, TS = 56;  };
 
 // block geometry of the types the matmul entry points take
 __host__ __device__ inline int type_size(int t) {
@@ -90,6 +105,12 @@ __host__ __device__ inline int dequant_type_size(int t) {
   switch (t) {
     case T_Q2_K: return 84;
     case T_Q3_K: return 110;
+    case T_IQ2_XS: return 74;
+    case T_IQ2_S: return 82;
+    case T_IQ3_XXS: return 98;
+    case T_IQ3_S: return 110;
+    case T_IQ1_S: return 50;
+    case T_IQ1_M: return 56;
   }
   return type_size(t);
 }

@@ -205,6 +205,69 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
       for (int j = 0; j < 8; ++j)
         f[j] = d * (float)((uint32_t)(grid >> (8 * j)) & 0xffu) * ((signs >> j) & 1 ? -1.f : 1.f);
       store_from_float(y + o, f);
+    } else if (TYPE == T_IQ2_XS || TYPE == T_IQ2_S || TYPE == T_IQ3_XXS || TYPE == T_IQ3_S) {
+      // dequantize_block_iq2_xs / iq2_s / iq3_xxs / iq3_s (dequantize.cuh:277-353): eight values =
+      // sub-block scale * code-book magnitudes * signs, all in fp32, one rounding at the store.
+      // The code books are read from global memory (this kernel is bound by its stores).
+      const uint8_t* blk = w + c * TS;
+      const int ib = lane >> 2, il = lane & 3;
+      const float dh = __half2float(__ushort_as_half((unsigned short)ldg_u16(blk)));
+      uint64_t grid;      // eight magnitudes, byte j = value j
+      uint32_t signs;     // bit j set = value j negative
+      float d;
+      if (TYPE == T_IQ2_XS) {
+        const uint32_t q = ldg_u16(blk + 2 + 2 * (4 * ib + il));
+        grid = __ldg(&d_iq2xs_grid[q & 511]);
+        signs = __ldg(&d_ksigns_iq2xs[q >> 9]);
+        d = dh * (0.5f + (float)((__ldg(blk + 66 + ib) >> (4 * (il / 2))) & 0xf)) * 0.25f;
+      } else if (TYPE == T_IQ2_S) {
+        const uint32_t qh = __ldg(blk + 66 + ib);
+        grid = __ldg(&d_iq2s_grid[__ldg(blk + 2 + 4 * ib + il) | ((qh << (8 - 2 * il)) & 0x300)]);
+        signs = __ldg(blk + 2 + 32 + 4 * ib + il);
+        d = dh * (0.5f + (float)((__ldg(blk + 74 + ib) >> (4 * (il / 2))) & 0xf)) * 0.25f;
+      } else if (TYPE == T_IQ3_XXS) {
+        const uint8_t* q3 = blk + 2 + 8 * ib;
+        const uint32_t aux32 = ldg_u16(blk + 2 + 64 + 4 * ib) | (ldg_u16(blk + 2 + 64 + 4 * ib + 2) << 16);
+        grid = (uint64_t)__ldg(&d_iq3xxs_grid[__ldg(q3 + 2 * il)]) | ((uint64_t)__ldg(&d_iq3xxs_grid[__ldg(q3 + 2 * il + 1)]) << 32);
+        signs = __ldg(&d_ksigns_iq2xs[(aux32 >> (7 * il)) & 127]);
+        d = dh * (0.5f + (float)(aux32 >> 28)) * 0.5f;
+      } else {
+        const uint8_t* qs = blk + 2 + 8 * ib;
+        const uint32_t qh = __ldg(blk + 66 + ib);
+        grid = (uint64_t)__ldg(&d_iq3s_grid[__ldg(qs + 2 * il) | ((qh << (8 - 2 * il)) & 256)]) |
+               ((uint64_t)__ldg(&d_iq3s_grid[__ldg(qs + 2 * il + 1) | ((qh << (7 - 2 * il)) & 256)]) << 32);
+        signs = __ldg(blk + 74 + 4 * ib + il);
+        d = dh * (0.5f + (float)((__ldg(blk + 106 + ib / 2) >> (4 * (ib % 2))) & 0xf)) * 0.5f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        f[j] = d * (float)((uint32_t)(grid >> (8 * j)) & 0xffu) * ((signs >> j) & 1 ? -1.f : 1.f);
+      store_from_float(y + o, f);
+    } else if (TYPE == T_IQ1_S || TYPE == T_IQ1_M) {
+      // dequantize_block_iq1_s / iq1_m (dequantize.cuh:355-399): value = d * (q + delta), q in {0,1,2}
+      // from the code book (nibble-packed), delta = -1 -+ 1/8 chosen per group by a bit of qh.
+      const uint8_t* blk = w + c * TS;
+      const int ib = lane >> 2, il = lane & 3;
+      float d, delta;
+      uint32_t g;
+      if (TYPE == T_IQ1_S) {
+        const uint32_t qh = ldg_u16(blk + 34 + 2 * ib);
+        delta = (qh & 0x8000) ? -1.f - 0.125f : -1.f + 0.125f;
+        d = __half2float(__ushort_as_half((unsigned short)ldg_u16(blk))) * (float)(2 * ((qh >> 12) & 7) + 1);
+        g = __ldg(&d_iq1s_grid[__ldg(blk + 2 + 4 * ib + il) | (((qh >> (3 * il)) & 7) << 8)]);
+      } else {
+        const uint32_t sc0 = ldg_u16(blk + 48), sc1 = ldg_u16(blk + 50), sc2 = ldg_u16(blk + 52), sc3 = ldg_u16(blk + 54);
+        const uint32_t s16 = (sc0 >> 12) | ((sc1 >> 8) & 0x00f0) | ((sc2 >> 4) & 0x0f00) | (sc3 & 0xf000);
+        const int ib16 = 2 * ib + il / 2;
+        const uint32_t scw = ldg_u16(blk + 48 + 2 * (ib16 / 4));
+        d = __half2float(__ushort_as_half((unsigned short)s16)) * (float)(2 * ((scw >> (3 * (ib16 % 4))) & 7) + 1);
+        const uint32_t qh = __ldg(blk + 32 + 2 * ib + il / 2);
+        delta = (qh & (0x08u << (4 * (il % 2)))) ? -1.f - 0.125f : -1.f + 0.125f;
+        g = __ldg(&d_iq1s_grid[__ldg(blk + 4 * ib + il) | (((qh >> (4 * (il % 2))) & 7) << 8)]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = d * ((float)((g >> (8 * (j & 3) + 4 * (j >> 2))) & 0xfu) + delta);
+      store_from_float(y + o, f);
     } else if (TYPE == T_Q4_1) {  // dequantize_q4_1: q*d + m
       const uint8_t* blk = w + (c * 8 + (lane >> 2)) * TS;
       const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(blk));
@@ -358,6 +421,12 @@ int launch_dequantize(const void* w, int type, void* out, int out_dtype, int64_t
     case T_Q3_K: return launch_d<T_Q3_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
     case T_Q5_K: return launch_d<T_Q5_K>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
     case T_IQ4_NL: return launch_d<T_IQ4_NL>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ2_XS: return launch_d<T_IQ2_XS>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ2_S: return launch_d<T_IQ2_S>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ3_XXS: return launch_d<T_IQ3_XXS>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ3_S: return launch_d<T_IQ3_S>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ1_S: return launch_d<T_IQ1_S>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
+    case T_IQ1_M: return launch_d<T_IQ1_M>(w, out, out_dtype, n_elems, q4k_contract, stream, rg);
   }
   return E_BAD_TYPE;
 }

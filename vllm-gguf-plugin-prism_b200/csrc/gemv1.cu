@@ -692,7 +692,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
     float2* s_ds = reinterpret_cast<float2*>(s_x + (size_t)MV * kpad);
     const bool vec_ok = (p.k % 8 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
     for (int i0 = threadIdx.x; i0 < MV * per_vec; i0 += G1_WARPS * 32) {   // (a multiple of 64 items: whole warps)
-      const int v = i0 / per_vec, idx = i0 - v * per_vec, k = idx * 8;
+      const int v = MV == 1 ? 0 : i0 / per_vec, idx = i0 - v * per_vec, k = idx * 8;
       const out_t* src = xr + (size_t)v * p.k + k;
       float val[8];
       if (vec_ok && k + 8 <= p.k) {

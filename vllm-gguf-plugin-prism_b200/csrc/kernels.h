@@ -23,6 +23,8 @@ struct Q8Tp {
   const void* add = nullptr;        // packets of the vector to add (element type = the x dtype), or null
   const unsigned* add_epoch = nullptr;
   float add_scale = 0.f;
+  int add_parts = 1;                // > 1: the slot holds that many fp32 partial vectors (a row-parallel call's), add_stride
+  int64_t add_stride = 0;           //      packets apart; their sum, taken in rank order, is the vector that is added
   unsigned* bump = nullptr;
   long long limit_cycles = 0;
   int* status = nullptr;
@@ -82,6 +84,8 @@ int launch_tp_wait(const unsigned* flag, const unsigned* epoch, int slot, int wo
                    cudaStream_t stream);
 int launch_tp_unpack(const void* packets, const unsigned* epoch, int slot0, int nslots, int64_t slot_packets, int64_t n,
                      void* out, int64_t out_stride, int dtype, long long limit_cycles, int* status, cudaStream_t stream);
+int launch_tp_unpack_sum(const void* packets, const unsigned* epoch, int slot, int64_t slot_bytes, int64_t n, int parts, void* out,
+                         int dtype, long long limit_cycles, int* status, cudaStream_t stream);
 // per-(token,expert) GEMV of the small-batch MoE entry point
 int launch_moe_gemv(const void* w, const void* xq_soa, void* y, const int32_t* topk_ids, int type, int out_dtype,
                     int64_t tokens, int64_t top_k, int64_t N, int64_t K, int64_t n_experts, int* status,

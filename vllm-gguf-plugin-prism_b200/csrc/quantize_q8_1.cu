@@ -55,7 +55,17 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
     float xi = (x && have && k < K) ? to_float<in_t>(x[src * K + k]) : 0.0f;
     if (MODE == Q8_MODE_SOA && tp.add && k < K) {   // (one vector: row == 0)
       float a;
-      if (!packet_read<in_t>(tp.add, k, add_tag, tp.limit_cycles, a)) atomicExch(tp.status, E_TIMEOUT);
+      if (tp.add_parts > 1) {   // all-reduce of a row-parallel call: partial vectors in fp32, summed in rank order, rounded once
+        a = 0.f;
+        for (int r = 0; r < tp.add_parts; ++r) {
+          float part;
+          if (!packet_read<float>(tp.add, r * tp.add_stride + k, add_tag, tp.limit_cycles, part)) atomicExch(tp.status, E_TIMEOUT);
+          a += part;
+        }
+        a = to_float<in_t>(from_float<in_t>(a));
+      } else if (!packet_read<in_t>(tp.add, k, add_tag, tp.limit_cycles, a)) {
+        atomicExch(tp.status, E_TIMEOUT);
+      }
       xi = to_float<in_t>(from_float<in_t>(xi + tp.add_scale * a));   // x' is a vector of the activation type
     }
     const Q8Lane r = quantize_lane(xi);

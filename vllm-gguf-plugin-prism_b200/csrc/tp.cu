@@ -60,6 +60,51 @@ __global__ void __launch_bounds__(256) tp_unpack_kernel(const void* packets, con
   if (!ok) atomicExch(status, E_TIMEOUT);
 }
 
+// All-reduce side of a row-parallel call: the slot holds `parts` fp32 partial vectors (one per rank,
+// n packets apart); out[i] = their sum in rank order -- the same order on every rank, so all ranks
+// hold identical bits -- rounded once to T.
+template <typename T>
+__global__ void __launch_bounds__(256) tp_unpack_sum_kernel(const void* packets, const unsigned* epoch, int slot, int64_t slot_bytes,
+                                                            int64_t n, int parts, T* out, long long limit_cycles, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const unsigned want = epoch[slot];
+  const char* base = static_cast<const char*>(packets) + (int64_t)slot * slot_bytes;
+  bool ok = true;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int r = 0; r < parts; ++r) {
+      float v;
+      ok = packet_read<float>(base, (int64_t)r * n + i, want, ok ? limit_cycles : 0, v) && ok;
+      s += v;
+    }
+    out[i] = from_float<T>(s);
+  }
+  if (!ok) atomicExch(status, E_TIMEOUT);
+}
+
+int launch_tp_unpack_sum(const void* packets, const unsigned* epoch, int slot, int64_t slot_bytes, int64_t n, int parts, void* out,
+                         int dtype, long long limit_cycles, int* status, cudaStream_t stream) {
+  if (n <= 0) return E_OK;
+  const int64_t want = (n + 255) / 256;
+  const dim3 grid((unsigned)(want > 148 ? 148 : want));
+  cudaError_t e;
+  switch (dtype) {
+    case DT_F32:
+      e = launch_pdl(tp_unpack_sum_kernel<float>, grid, dim3(256), 0, stream, packets, epoch, slot, slot_bytes, n, parts, static_cast<float*>(out), limit_cycles, status);
+      break;
+    case DT_F16:
+      e = launch_pdl(tp_unpack_sum_kernel<__half>, grid, dim3(256), 0, stream, packets, epoch, slot, slot_bytes, n, parts, static_cast<__half*>(out), limit_cycles, status);
+      break;
+    case DT_BF16:
+      e = launch_pdl(tp_unpack_sum_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, packets, epoch, slot, slot_bytes, n, parts, static_cast<__nv_bfloat16*>(out), limit_cycles, status);
+      break;
+    default:
+      return E_BAD_DTYPE;
+  }
+  return e == cudaSuccess ? E_OK : E_CUDA;
+}
+
 int launch_tp_unpack(const void* packets, const unsigned* epoch, int slot0, int nslots, int64_t slot_packets, int64_t n,
                      void* out, int64_t out_stride, int dtype, long long limit_cycles, int* status, cudaStream_t stream) {
   if (nslots <= 0 || n <= 0) return E_OK;

@@ -41,8 +41,10 @@ SIGNATURES = {
     "gguf_b200_fused_moe": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _L, _L, _L, _L, _L, _P]),
     "gguf_b200_moe_a8_vec": (_I, [_P, _P, _P, _P, _L, _P, _L, _I, _I, _L, _L, _L, _L, _P]),
     "gguf_b200_mul_mat_vec_a8_noalloc": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _P]),
-    "gguf_b200_mul_mat_vec_a8_tp": (_I, [_P, _P, _P, _P, _I, _I, _F, _L, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
+    "gguf_b200_mul_mat_vec_a8_tp": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _L, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
+    "gguf_b200_mul_mat_vec_a8_tp_rowpar": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _L, _P, _L, _I, _I, _L, _L, _I, _I, _P]),
     "gguf_b200_tp_unpack": (_I, [_P, _P, _I, _I, _L, _L, _P, _L, _I, _P]),
+    "gguf_b200_tp_unpack_sum": (_I, [_P, _P, _I, _L, _L, _I, _P, _I, _P]),
     "gguf_b200_matmul_tp": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _L, _I, _I, _L, _L, _L, _I, _I, _P]),
     "gguf_b200_tp_wait": (_I, [_P, _P, _I, _I, _P]),
     "gguf_b200_set_wait_limit_cycles": (None, [_L]),
@@ -213,10 +215,11 @@ def _ptr_array(ptrs):
 
 
 def mul_mat_vec_a8_tp(W_local, X, packet_ptrs, epochs_local, slot, slot_packets, qtype, rank, add_slot=-1,
-                      add_scale=0.0, dtype=None):
+                      add_scale=0.0, dtype=None, add_parts=1):
     """Rank `rank`'s rows of a decode GEMV, sent as tagged packets into every rank's packet arena
     (packet_ptrs: device addresses of the arenas, one per rank, mapped into this process).
-    Activations x' = X + add_scale * gathered[add_slot] (X may be None when add_slot >= 0)."""
+    Activations x' = X + add_scale * v[add_slot] (X may be None when add_slot >= 0); v is a gathered
+    vector (add_parts = 1) or the sum of the partial vectors of a row-parallel call (add_parts = world)."""
     world = len(packet_ptrs)
     n_local = W_local.shape[0]
     K = k_of(W_local, qtype)
@@ -226,8 +229,36 @@ def mul_mat_vec_a8_tp(W_local, X, packet_ptrs, epochs_local, slot, slot_packets,
     keep, pa = _ptr_array(packet_ptrs)
     _check(lib().gguf_b200_mul_mat_vec_a8_tp(W_local.data_ptr(), X.data_ptr() if X is not None else None, pa,
                                              epochs_local.data_ptr(), int(slot), int(add_slot), float(add_scale),
-                                             int(slot_packets), ws.data_ptr(), nbytes, qtype, _DT[dt], n_local, K,
-                                             int(rank), world, _stream(W_local)), "mul_mat_vec_a8_tp")
+                                             int(add_parts), int(slot_packets), ws.data_ptr(), nbytes, qtype, _DT[dt],
+                                             n_local, K, int(rank), world, _stream(W_local)), "mul_mat_vec_a8_tp")
+
+
+def mul_mat_vec_a8_tp_rowpar(W_local, X_local, packet_ptrs, epochs_local, slot, slot_packets, qtype, rank, add_slot=-1,
+                             add_scale=0.0, dtype=None, add_parts=1):
+    """Rank `rank`'s K-shard of a decode GEMV (W_local: every row's K_local columns; X_local: the
+    rank's K_local activations): the fp32 partial sums go to every rank's packet arena; their sum
+    (tp_unpack_sum, or the next call's add path with add_parts = world) is the all-reduced result."""
+    world = len(packet_ptrs)
+    n = W_local.shape[0]
+    k_local = k_of(W_local, qtype)
+    dt = X_local.dtype if X_local is not None else dtype
+    nbytes = lib().gguf_b200_workspace_bytes(OP_GEMV, qtype, 1, n, k_local)
+    ws = _ws(W_local, nbytes)
+    keep, pa = _ptr_array(packet_ptrs)
+    _check(lib().gguf_b200_mul_mat_vec_a8_tp_rowpar(W_local.data_ptr(), X_local.data_ptr() if X_local is not None else None, pa,
+                                                    epochs_local.data_ptr(), int(slot), int(add_slot), float(add_scale),
+                                                    int(add_parts), int(slot_packets), ws.data_ptr(), nbytes, qtype, _DT[dt],
+                                                    n, k_local, int(rank), world, _stream(W_local)), "mul_mat_vec_a8_tp_rowpar")
+
+
+def tp_unpack_sum(packets_local: torch.Tensor, epochs_local: torch.Tensor, slot: int, slot_packets: int, n: int, parts: int,
+                  dtype=torch.float16, out=None) -> torch.Tensor:
+    """The all-reduced vector of a row-parallel call: sum of the `parts` partial vectors of `slot`."""
+    if out is None:
+        out = torch.empty((n,), dtype=dtype, device=packets_local.device)
+    _check(lib().gguf_b200_tp_unpack_sum(packets_local.data_ptr(), epochs_local.data_ptr(), int(slot), int(slot_packets), int(n),
+                                         int(parts), out.data_ptr(), _DT[out.dtype], _stream(packets_local)), "tp_unpack_sum")
+    return out
 
 
 def tp_unpack(packets_local: torch.Tensor, epochs_local: torch.Tensor, slot0: int, nslots: int, slot_packets: int, n: int,

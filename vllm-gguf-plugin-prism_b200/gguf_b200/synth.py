@@ -13,16 +13,20 @@ import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K, IQ2_XXS, IQ4_XS = 2, 8, 12, 14, 16, 23
 Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL = 3, 6, 7, 10, 11, 13, 20
+IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M = 17, 18, 19, 21, 22, 29
 #             type: (values per block, bytes per block)
 QUANT_SIZES = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ2_XXS: (256, 66),
                IQ4_XS: (256, 136),
                Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q2_K: (256, 84), Q3_K: (256, 110), Q5_K: (256, 176),
-               IQ4_NL: (32, 18)}
+               IQ4_NL: (32, 18),
+               IQ2_XS: (256, 74), IQ2_S: (256, 82), IQ3_XXS: (256, 98), IQ3_S: (256, 110), IQ1_S: (256, 50), IQ1_M: (256, 56)}
 NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ2_XXS: "IQ2_XXS", IQ4_XS: "IQ4_XS",
-         Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q2_K: "Q2_K", Q3_K: "Q3_K", Q5_K: "Q5_K", IQ4_NL: "IQ4_NL"}
+         Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q2_K: "Q2_K", Q3_K: "Q3_K", Q5_K: "Q5_K", IQ4_NL: "IQ4_NL",
+         IQ2_XS: "IQ2_XS", IQ2_S: "IQ2_S", IQ3_XXS: "IQ3_XXS", IQ3_S: "IQ3_S", IQ1_S: "IQ1_S", IQ1_M: "IQ1_M"}
 # where the fp16 scale(s) sit inside a block, and the |N(0,1)| multiplier the configs name
 _D_OFFSETS = {Q4_0: (0,), Q8_0: (0,), Q4_K: (0, 2), Q6_K: (208,), IQ2_XXS: (0,), IQ4_XS: (0,),
-              Q4_1: (0, 2), Q5_0: (0,), Q5_1: (0, 2), Q2_K: (80, 82), Q3_K: (108,), Q5_K: (0, 2), IQ4_NL: (0,)}
+              Q4_1: (0, 2), Q5_0: (0,), Q5_1: (0, 2), Q2_K: (80, 82), Q3_K: (108,), Q5_K: (0, 2), IQ4_NL: (0,),
+              IQ2_XS: (0,), IQ2_S: (0,), IQ3_XXS: (0,), IQ3_S: (0,), IQ1_S: (0,), IQ1_M: ()}
 _D_SCALE = {Q4_0: 0.01, Q8_0: 0.002, Q4_K: 0.01, Q6_K: 0.01, IQ2_XXS: 0.01, IQ4_XS: 0.01}
 
 
@@ -42,6 +46,14 @@ def make_weight(qtype: int, n: int, k: int, seed: int = 0, d_scale: float | None
     for off in _D_OFFSETS[qtype]:
         d = (np.abs(rng.standard_normal(nb)) * scale).astype(np.float16)
         blocks[:, off:off + 2] = d.view(np.uint8).reshape(nb, 2)
+    if qtype == IQ1_M:
+        # the fp16 scale has no field of its own: its four nibbles are the top nibbles of the four
+        # 16-bit scale words at byte 48 (bits 0-3 in word 0, .. bits 12-15 in word 3)
+        d = (np.abs(rng.standard_normal(nb)) * scale).astype(np.float16).view(np.uint16)
+        sc = blocks[:, 48:56].copy().view(np.uint16)
+        for i in range(4):
+            sc[:, i] = (sc[:, i] & 0x0FFF) | (((d >> (4 * i)) & 0xF) << 12).astype(np.uint16)
+        blocks[:, 48:56] = sc.view(np.uint8)
     if qtype == Q8_0:
         # int8 quants uniform in [-127, 127]
         blocks[:, 2:] = rng.integers(-127, 128, size=(nb, 32), dtype=np.int8).view(np.uint8)

@@ -34,6 +34,19 @@ def shard_rows(weight: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return weight.narrow(dim, rank * shard, shard).contiguous()
 
 
+def shard_cols(weight: torch.Tensor, qtype: int, rank: int, world: int) -> torch.Tensor:
+    """Rank ``rank``'s K-shard of a packed ``[N, bytes]`` weight: whole blocks of every row, the way
+    the reference narrows dim 1 of a row-parallel layer (quantization/params.py:259-264)."""
+    from . import synth
+
+    block, size = synth.QUANT_SIZES[int(qtype)]
+    blocks = weight.shape[-1] // size
+    if blocks % world != 0:
+        raise ValueError(f"{blocks} blocks per row are not divisible by the tensor-parallel size {world}")
+    b = blocks // world * size
+    return weight.narrow(weight.dim() - 1, rank * b, b).contiguous()
+
+
 def gather_columns(y_local: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather ``[M, N/g]`` slices into ``[M, N]`` (rank order = column order)."""
     world = dist.get_world_size(group)
@@ -74,6 +87,32 @@ class ColumnParallelGGUFLinear:
         return gather_columns(y, self.group) if self.world > 1 else y
 
 
+class RowParallelGGUFLinear:
+    """A packed GGUF weight split by K (whole blocks of every row) over the ranks of ``group``;
+    ``__call__(x_local)`` takes this rank's K/g activations and returns the all-reduced ``[M, N]``
+    product on every rank (plain collective: the baseline of the fused ``FusedGatherGemv.rowpar``)."""
+
+    def __init__(self, weight: torch.Tensor, qtype: int, group=None,
+                 matmul: Callable[[torch.Tensor, torch.Tensor, int], torch.Tensor] | None = None):
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.qtype = int(qtype)
+        self.weight = shard_cols(weight, qtype, self.rank, self.world)
+        if matmul is None:
+            from vllm_gguf_plugin.quantization.linear import _fused_mul_mat_gguf as matmul
+        self.matmul = matmul
+
+    def local(self, x_local: torch.Tensor) -> torch.Tensor:
+        return self.matmul(x_local, self.weight, self.qtype)
+
+    def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
+        y = self.local(x_local)
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
+
 def _group_info(group):
     """(group, rank, world); without an initialised process group: a group of one."""
     if not dist.is_initialized():
@@ -110,24 +149,40 @@ class FusedGatherGemv:
     dependent GEMVs then contains no collective and no wait kernel.  ``gathered(slot)`` returns plain
     vectors for any other consumer.  All ranks must make the same sequence of calls; needs CUDA
     peer access between the ranks' GPUs.
+
+    ``rowpar(slot, w_kshard, x_local, qtype, ...)`` is the row-parallel (K-sharded) form with the
+    all-reduce fused in: this rank's partial sums over its K columns go to every rank as fp32
+    packets, and ``reduced(slot, n)`` -- or a later call with ``add_slot=slot, add_parts=world`` --
+    adds the ``world`` partial vectors in rank order.  ``reduce_n`` (constructor) is the longest
+    vector reduced that way; a slot then has room for ``world`` fp32 partial vectors of that length.
     """
 
-    def __init__(self, n_total: int, slots: int, dtype: torch.dtype, device: torch.device, group=None):
+    def __init__(self, n_total: int, slots: int, dtype: torch.dtype, device: torch.device, group=None, reduce_n: int = 0):
         from . import capi
 
         self.capi = capi
         self.group, self.rank, self.world = _group_info(group)
         self.n_total, self.slots, self.dtype = int(n_total), int(slots), dtype
         self.packet_bytes = 8 if dtype == torch.float32 else 4
-        self.slot_packets = (self.n_total + 63) // 64 * 64
+        units = max(self.n_total, (self.world * int(reduce_n) * 8 + self.packet_bytes - 1) // self.packet_bytes)
+        self.slot_packets = (units + 63) // 64 * 64
         self.arena, self.handle, self.base_ptrs = _symmetric_arena(self.slots * self.slot_packets * self.packet_bytes,
                                                                    device, self.group)
         self.epochs = torch.zeros(self.slots, dtype=torch.int32, device=device)
 
     def __call__(self, slot: int, w_local: torch.Tensor, x: torch.Tensor | None, qtype: int, add_slot: int = -1,
-                 add_scale: float = 0.0) -> None:
+                 add_scale: float = 0.0, add_parts: int = 1) -> None:
         self.capi.mul_mat_vec_a8_tp(w_local, x, self.base_ptrs, self.epochs, slot, self.slot_packets, qtype, self.rank,
-                                    add_slot, add_scale, dtype=self.dtype)
+                                    add_slot, add_scale, dtype=self.dtype, add_parts=add_parts)
+
+    def rowpar(self, slot: int, w_kshard: torch.Tensor, x_local: torch.Tensor | None, qtype: int, add_slot: int = -1,
+               add_scale: float = 0.0, add_parts: int = 1) -> None:
+        self.capi.mul_mat_vec_a8_tp_rowpar(w_kshard, x_local, self.base_ptrs, self.epochs, slot, self.slot_packets, qtype,
+                                           self.rank, add_slot, add_scale, dtype=self.dtype, add_parts=add_parts)
+
+    def reduced(self, slot: int, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The all-reduced ``[n]`` vector of a row-parallel call (waits for all ranks' partial sums)."""
+        return self.capi.tp_unpack_sum(self.arena, self.epochs, slot, self.slot_packets, n, self.world, self.dtype, out=out)
 
     def gathered(self, slot0: int, nslots: int = 1, n: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         """Plain ``[nslots, n]`` tensor of the vectors gathered in slots slot0.. (waits for all ranks' packets)."""
