@@ -6,7 +6,7 @@
  * It restates, in plain C, the arithmetic of the reference plugin's CUDA kernels
  * (vllm_gguf_plugin/csrc/gguf/ of akmorley/vllm-gguf-plugin-prism) for these block types:
  *   Q4_0 (2), Q8_0 (8), Q4_K (12), Q6_K (14), IQ2_XXS (16), IQ4_XS (23), and later additions
- *   (Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL; dequantize only: IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M).
+ *   (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M; dequantize only: Q2_K, Q3_K).
  * Each function names the reference lines it follows.  Half-precision steps are
  * emulated exactly (one IEEE rounding per __hmul/__hsub/__int2half_rn), so the
  * dequantize outputs are bit patterns, not approximations.  Matmul entry points are
@@ -205,7 +205,7 @@ int oracle_type_size(int type) {
     case T_Q3_K: return 110;
     case T_Q5_K: return 176;
     case T_IQ4_NL: return 18;
-    case T_IQ2_XS: return 74;  /* (the code-book types below: dequantize only) */
+    case T_IQ2_XS: return 74;
     case T_IQ2_S: return 82;
     case T_IQ3_XXS: return 98;
     case T_IQ3_S: return 110;
@@ -654,6 +654,53 @@ static void unpack_codes(const uint8_t* blk, int type, int8_t* w) {
           w[64 * il + 32 + l] = (int8_t)((blk[48 + 32 * il + l] >> 4) | (((blk[16 + l] >> (2 * il + 1)) & 1) << 4));
         }
       break;
+    case T_IQ2_XS: case T_IQ2_S: case T_IQ3_XXS: case T_IQ3_S:
+      /* signed code-book magnitudes, group (ib, il) of eight values as in oracle_dequantize */
+      for (int ib = 0; ib < 8; ++ib)
+        for (int il = 0; il < 4; ++il) {
+          uint64_t grid;
+          uint32_t signs;
+          if (type == T_IQ2_XS) {
+            uint32_t q = rd16(blk + 2 + 2 * (4 * ib + il));
+            grid = gguf_b200_iq2xs_grid[q & 511];
+            signs = gguf_b200_ksigns_iq2xs[q >> 9];
+          } else if (type == T_IQ2_S) {
+            grid = gguf_b200_iq2s_grid[blk[2 + 4 * ib + il] | (((uint32_t)blk[66 + ib] << (8 - 2 * il)) & 0x300)];
+            signs = blk[2 + 32 + 4 * ib + il];
+          } else if (type == T_IQ3_XXS) {
+            const uint8_t* q3 = blk + 2 + 8 * ib;
+            const uint8_t* g = blk + 2 + 64 + 4 * ib;
+            uint32_t aux32 = (uint32_t)g[0] | ((uint32_t)g[1] << 8) | ((uint32_t)g[2] << 16) | ((uint32_t)g[3] << 24);
+            grid = (uint64_t)gguf_b200_iq3xxs_grid[q3[2 * il]] | ((uint64_t)gguf_b200_iq3xxs_grid[q3[2 * il + 1]] << 32);
+            signs = gguf_b200_ksigns_iq2xs[(aux32 >> (7 * il)) & 127];
+          } else {
+            const uint8_t* qs = blk + 2 + 8 * ib;
+            uint32_t qh = blk[66 + ib];
+            grid = (uint64_t)gguf_b200_iq3s_grid[qs[2 * il] | ((qh << (8 - 2 * il)) & 256)] |
+                   ((uint64_t)gguf_b200_iq3s_grid[qs[2 * il + 1] | ((qh << (7 - 2 * il)) & 256)] << 32);
+            signs = blk[74 + 4 * ib + il];
+          }
+          for (int j = 0; j < 8; ++j) {
+            int g = (int)((grid >> (8 * j)) & 0xff);
+            w[32 * ib + 8 * il + j] = (int8_t)(((signs >> j) & 1) ? -g : g);
+          }
+        }
+      break;
+    case T_IQ1_S: case T_IQ1_M:
+      /* code-book values q in {0,1,2} (the "- 1 +- 1/8" enters through the activation sums) */
+      for (int ib = 0; ib < 8; ++ib)
+        for (int il = 0; il < 4; ++il) {
+          uint32_t g;
+          if (type == T_IQ1_S) {
+            uint32_t qh = rd16(blk + 34 + 2 * ib);
+            g = gguf_b200_iq1s_grid[blk[2 + 4 * ib + il] | (((qh >> (3 * il)) & 7) << 8)];
+          } else {
+            uint32_t qh = blk[32 + 2 * ib + il / 2];
+            g = gguf_b200_iq1s_grid[blk[4 * ib + il] | (((qh >> (4 * (il % 2))) & 7) << 8)];
+          }
+          for (int j = 0; j < 8; ++j) w[32 * ib + 8 * il + j] = (int8_t)((g >> (8 * (j & 3) + 4 * (j >> 2))) & 0xf);
+        }
+      break;
   }
 }
 
@@ -712,6 +759,54 @@ static double block_dot(const uint8_t* blk, int type, const uint8_t* y, int mmq)
         const uint8_t* yb = y + 36 * g;
         uint32_t s = blk[2 + 8 * g + 7] >> 4;
         acc += d * (0.5 + s) * h2f(rd16(yb)) * 0.25 * idot(w + 32 * g, (const int8_t*)yb + 4, 32);
+      }
+    } break;
+    case T_IQ2_XS: case T_IQ2_S: { /* d*d8*0.25*((0.5+ls1)*sumi1 + (0.5+ls2)*sumi2), vecdotq.cuh:1554-1620 */
+      double d = h2f(rd16(blk));
+      const uint8_t* sc = blk + (type == T_IQ2_XS ? 66 : 74);
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        acc += d * h2f(rd16(yb)) * 0.25 * ((0.5 + (sc[g] & 0xf)) * idot(w + 32 * g, q8, 16) + (0.5 + (sc[g] >> 4)) * idot(w + 32 * g + 16, q8 + 16, 16));
+      }
+    } break;
+    case T_IQ3_XXS: case T_IQ3_S: { /* d*(0.5+s)*d8*0.5*sumi, vecdotq.cuh:1622-1672 */
+      double d = h2f(rd16(blk));
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        uint32_t s = type == T_IQ3_XXS ? (uint32_t)(blk[2 + 64 + 4 * g + 3] >> 4) : (uint32_t)((blk[106 + g / 2] >> (4 * (g % 2))) & 0xf);
+        acc += d * (0.5 + s) * h2f(rd16(yb)) * 0.5 * idot(w + 32 * g, (const int8_t*)yb + 4, 32);
+      }
+    } break;
+    case T_IQ1_S: { /* d*(2s+1) * (d8*sumi + s8*delta), vecdotq.cuh:1674-1704 */
+      double d = h2f(rd16(blk));
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        uint32_t qh = rd16(blk + 34 + 2 * g);
+        double delta = (qh & 0x8000) ? -1.0 - 0.125 : -1.0 + 0.125;
+        acc += d * (double)(2 * ((qh >> 12) & 7) + 1) * (h2f(rd16(yb)) * idot(w + 32 * g, (const int8_t*)yb + 4, 32) + h2f(rd16(yb + 2)) * delta);
+      }
+    } break;
+    case T_IQ1_M: { /* d*d8 * sum over the two halves of (sumi + delta*sum(q8)) * (2s+1), vecdotq.cuh:1706-1750 */
+      uint32_t sc0 = rd16(blk + 48), sc1 = rd16(blk + 50), sc2 = rd16(blk + 52), sc3 = rd16(blk + 54);
+      double d = h2f((uint16_t)((sc0 >> 12) | ((sc1 >> 8) & 0x00f0) | ((sc2 >> 4) & 0x0f00) | (sc3 & 0xf000)));
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        uint32_t tmp = rd16(blk + 48 + 2 * (g / 2)) >> (6 * (g % 2));
+        double part = 0;
+        for (int h = 0; h < 2; ++h) {      /* halves of 16 values, each with its own 3-bit scale */
+          double sumf = 0;
+          for (int l = 0; l < 2; ++l) {    /* groups of 8 values, each with its own delta bit */
+            uint32_t qhl = blk[32 + 2 * g + h] >> (4 * l);
+            double delta = (qhl & 0x08) ? -1.0 - 0.125 : -1.0 + 0.125;
+            int sumy = 0;
+            for (int j = 0; j < 8; ++j) sumy += q8[16 * h + 8 * l + j];
+            sumf += delta * sumy;
+          }
+          part += (idot(w + 32 * g + 16 * h, q8 + 16 * h, 16) + sumf) * (double)(2 * ((tmp >> (3 * h)) & 7) + 1);
+        }
+        acc += d * h2f(rd16(yb)) * part;
       }
     } break;
     case T_IQ4_XS: { /* d*(ls-32)*d8*(sumi1+sumi2), vecdotq.cuh:1791-1812 */

@@ -374,7 +374,12 @@ def test_ops_api_equals_capi_and_dispatcher_end_to_end():
         assert torch.equal(ops.ggml_mul_mat_vec_a8(w, x1, t, 256), capi.mul_mat_vec_a8(w, x1, t, 256))
         assert torch.equal(ops.ggml_dequantize(w, t, 256, 1024, torch.float16), capi.dequantize(w, t, 256, 1024))
         y = linear._fused_mul_mat_gguf(x64, w, t)
-        want = capi.mul_mat_a8(w, x64, t, 256) if name in MMQ_TYPES else capi.dequant_matmul(w, x64, t, 256)
+        if name in MMQ_TYPES:
+            want = capi.mul_mat_a8(w, x64, t, 256)
+        elif t in ops._DEQUANT_MATMUL_TYPES:
+            want = capi.dequant_matmul(w, x64, t, 256)
+        else:   # code-book types with a GEMV only: the reference's two steps (linear.py:50-54)
+            want = x64 @ capi.dequantize(w, t, 256, 1024).T
         assert torch.equal(y, want)
     with pytest.raises(NotImplementedError):
         ops.ggml_mul_mat_vec_a8(w, x1, 10, 256)

@@ -32,8 +32,8 @@ enum : int { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T
 //   Q5_K   176 : half d | half dmin | u8 scales[12] | u8 qh[32] | u8 qs[128]
 //   IQ4_NL  18 : half d | u8 qs[16]                               4-bit indices into the IQ4 level table
 enum : int { T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q2_K = 10, T_Q3_K = 11, T_Q5_K = 13, T_IQ4_NL = 20 };
-// code-book types with a standalone dequantizer only (256 values per block; the matmul callers
-// dequantize and then multiply, as the reference does above its GEMV threshold):
+// code-book types served by the dequantizer and the decode GEMV (256 values per block; for more
+// tokens the callers dequantize and then multiply, as the reference does above its GEMV threshold):
 //   IQ2_XS   74 : half d | u16 qs[32] | u8 scales[8]
 //   IQ2_S    82 : half d | u8 qs[32] | u8 signs[32] | u8 qh[8] | u8 scales[8]
 //   IQ3_XXS  98 : half d | u8 qs[64] | u32 scales_and_signs[8]
@@ -91,6 +91,12 @@ __host__ __device__ inline int type_size(int t) {
     case T_Q5_1: return 24;
     case T_Q5_K: return 176;
     case T_IQ4_NL: return 18;
+    case T_IQ2_XS: return 74;
+    case T_IQ2_S: return 82;
+    case T_IQ3_XXS: return 98;
+    case T_IQ3_S: return 110;
+    case T_IQ1_S: return 50;
+    case T_IQ1_M: return 56;
   }
   return 0;
 }
@@ -105,12 +111,6 @@ __host__ __device__ inline int dequant_type_size(int t) {
   switch (t) {
     case T_Q2_K: return 84;
     case T_Q3_K: return 110;
-    case T_IQ2_XS: return 74;
-    case T_IQ2_S: return 82;
-    case T_IQ3_XXS: return 98;
-    case T_IQ3_S: return 110;
-    case T_IQ1_S: return 50;
-    case T_IQ1_M: return 56;
   }
   return type_size(t);
 }

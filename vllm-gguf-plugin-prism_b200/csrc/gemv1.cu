@@ -292,6 +292,171 @@ template <> struct G1<T_IQ2_XXS> {
   }
 };
 
+// ---- the other code-book types: IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M ---------------------
+// unit ib = 32 values (one q8_1 block).  Their code books (1 to 8 KB each) are read from global
+// memory through the read-only path, as the reference's vec_dot_iq*_q8_1 do (vecdotq.cuh:1554-1750):
+// these formats trade arithmetic for size and are bound by the look-ups, not by the weight stream.
+__device__ __forceinline__ uint32_t pl8(uint32_t a) {
+  uint32_t v;
+  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+// bit j of a nibble -> byte j of a word all ones (the reference's __vcmpeq4 form, vecdotq.cuh:1598-1599)
+__device__ __forceinline__ uint32_t sign_mask4(uint32_t nib) { return __vcmpeq4(((nib & 0xfu) * 0x01010101u) & 0x08040201u, 0x08040201u); }
+// seven sign bits + the eighth that makes the parity even (the ksigns_iq2xs table, computed)
+__device__ __forceinline__ uint32_t signs_from7(uint32_t s7) { return s7 | ((__popc(s7) & 1u) << 7); }
+// dot product of eight signed code-book magnitudes (two words, sign bit j = value j negative) with eight int8 activations
+__device__ __forceinline__ int dot8_signed(uint32_t g0, uint32_t g1, uint32_t signs, uint32_t x0, uint32_t x1, int acc) {
+  const uint32_t m0 = sign_mask4(signs), m1 = sign_mask4(signs >> 4);
+  acc = __dp4a((int)__vsub4(g0 ^ m0, m0), (int)x0, acc);
+  return __dp4a((int)__vsub4(g1 ^ m1, m1), (int)x1, acc);
+}
+
+template <> struct G1<T_IQ2_XS> {   // half d | u16 qs[32] | u8 scales[8]   (vecdotq.cuh:1554-1583)
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = plh(blk);
+    uint32_t q[2];
+    lds_a2<2>(blk + 2 + 8 * ib, q);
+    const uint32_t sc = pl8(blk + 66 + ib);
+    int s1 = 0, s2 = 0;
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t idx = (q[l >> 1] >> (16 * (l & 1))) & 0xFFFFu;
+      const uint64_t g = __ldg(&d_iq2xs_grid[idx & 511]);
+      const int v = dot8_signed((uint32_t)g, (uint32_t)(g >> 32), signs_from7(idx >> 9), x[2 * l], x[2 * l + 1], 0);
+      if (l < 2) s1 += v; else s2 += v;
+    }
+    return d * xd[0] * 0.25f * ((0.5f + (float)(sc & 0xf)) * (float)s1 + (0.5f + (float)(sc >> 4)) * (float)s2);
+  }
+};
+
+template <> struct G1<T_IQ2_S> {   // half d | u8 qs[32] | u8 signs[32] | u8 qh[8] | u8 scales[8]   (vecdotq.cuh:1585-1620)
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = plh(blk);
+    uint32_t q[1], sg[1];
+    lds_a2<1>(blk + 2 + 4 * ib, q);
+    lds_a2<1>(blk + 34 + 4 * ib, sg);
+    const uint32_t qh = pl8(blk + 66 + ib), sc = pl8(blk + 74 + ib);
+    int s1 = 0, s2 = 0;
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint64_t g = __ldg(&d_iq2s_grid[((q[0] >> (8 * l)) & 0xFF) | ((qh << (8 - 2 * l)) & 0x300)]);
+      const int v = dot8_signed((uint32_t)g, (uint32_t)(g >> 32), (sg[0] >> (8 * l)) & 0xFF, x[2 * l], x[2 * l + 1], 0);
+      if (l < 2) s1 += v; else s2 += v;
+    }
+    return d * xd[0] * 0.25f * ((0.5f + (float)(sc & 0xf)) * (float)s1 + (0.5f + (float)(sc >> 4)) * (float)s2);
+  }
+};
+
+template <> struct G1<T_IQ3_XXS> {   // half d | u8 qs[64] | u32 scale_and_signs[8]   (vecdotq.cuh:1622-1647)
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = plh(blk);
+    uint32_t q[2], a[1];
+    lds_a2<2>(blk + 2 + 8 * ib, q);
+    lds_a2<1>(blk + 66 + 4 * ib, a);
+    const uint32_t aux = a[0];
+    int s = 0;
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t w = q[l >> 1] >> (16 * (l & 1));
+      const uint32_t g0 = __ldg(&d_iq3xxs_grid[w & 0xFF]), g1 = __ldg(&d_iq3xxs_grid[(w >> 8) & 0xFF]);
+      s = dot8_signed(g0, g1, signs_from7((aux >> (7 * l)) & 127), x[2 * l], x[2 * l + 1], s);
+    }
+    return d * (0.5f + (float)(aux >> 28)) * xd[0] * 0.5f * (float)s;
+  }
+};
+
+template <> struct G1<T_IQ3_S> {   // half d | u8 qs[64] | u8 qh[8] | u8 signs[32] | u8 scales[4]   (vecdotq.cuh:1649-1672)
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = plh(blk);
+    uint32_t q[2], sg[1];
+    lds_a2<2>(blk + 2 + 8 * ib, q);
+    lds_a2<1>(blk + 74 + 4 * ib, sg);
+    const uint32_t qh = pl8(blk + 66 + ib);
+    const uint32_t sc = (pl8(blk + 106 + (ib >> 1)) >> (4 * (ib & 1))) & 0xf;
+    int s = 0;
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t w = q[l >> 1] >> (16 * (l & 1));
+      const uint32_t g0 = __ldg(&d_iq3s_grid[(w & 0xFF) | ((qh << (8 - 2 * l)) & 256)]);
+      const uint32_t g1 = __ldg(&d_iq3s_grid[((w >> 8) & 0xFF) | ((qh << (7 - 2 * l)) & 256)]);
+      s = dot8_signed(g0, g1, (sg[0] >> (8 * l)) & 0xFF, x[2 * l], x[2 * l + 1], s);
+    }
+    return d * (0.5f + (float)sc) * xd[0] * 0.5f * (float)s;
+  }
+};
+
+template <> struct G1<T_IQ1_S> {   // half d | u8 qs[32] | u16 qh[8]   (vecdotq.cuh:1674-1704); xd[1] = fp16 sum of the 32 inputs
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const float d = plh(blk);
+    uint32_t q[1];
+    lds_a2<1>(blk + 2 + 4 * ib, q);
+    const uint32_t qh = pl16(blk + 34 + 2 * ib);
+    int s = 0;
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t g = __ldg(&d_iq1s_grid[((q[0] >> (8 * l)) & 0xFF) | (((qh >> (3 * l)) & 7) << 8)]);
+      s = __dp4a((int)(g & 0x0F0F0F0Fu), (int)x[2 * l], s);
+      s = __dp4a((int)((g >> 4) & 0x0F0F0F0Fu), (int)x[2 * l + 1], s);
+    }
+    const float delta = (qh & 0x8000u) ? -1.f - 0.125f : -1.f + 0.125f;
+    return d * (float)(2 * ((qh >> 12) & 7) + 1) * (xd[0] * (float)s + xd[1] * delta);
+  }
+};
+
+template <> struct G1<T_IQ1_M> {   // u8 qs[32] | u8 qh[16] | u16 scales[4] (the fp16 scale in their top nibbles)   (vecdotq.cuh:1706-1750)
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int ib, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const uint32_t q = pl32(blk + 4 * ib);                 // 56-byte blocks: 8-byte aligned
+    const uint32_t qh = pl16(blk + 32 + 2 * ib);
+    const uint2 scw = pl64(blk + 48);
+    const uint32_t s16 = ((scw.x >> 12) & 0x000Fu) | ((scw.x >> 24) & 0x00F0u) | ((scw.y >> 4) & 0x0F00u) | ((scw.y >> 16) & 0xF000u);
+    const float d = __half2float(__ushort_as_half((unsigned short)s16));
+    float part[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int si = 0;
+      float sf = 0.f;
+#pragma unroll
+      for (int l2 = 0; l2 < 2; ++l2) {
+        const int l = 2 * h + l2;
+        const uint32_t qhl = qh >> (4 * l);
+        const uint32_t g = __ldg(&d_iq1s_grid[((q >> (8 * l)) & 0xFF) | ((qhl & 7) << 8)]);
+        si = __dp4a((int)(g & 0x0F0F0F0Fu), (int)x[2 * l], si);
+        si = __dp4a((int)((g >> 4) & 0x0F0F0F0Fu), (int)x[2 * l + 1], si);
+        const int sy = __dp4a((int)x[2 * l + 1], 0x01010101, __dp4a((int)x[2 * l], 0x01010101, 0));
+        sf += ((qhl & 8u) ? -1.f - 0.125f : -1.f + 0.125f) * (float)sy;
+      }
+      part[h] = (float)si + sf;
+    }
+    const uint32_t tmp = (((ib & 4) ? scw.y : scw.x) >> (16 * ((ib >> 1) & 1) + 6 * (ib & 1)));   // scales word ib/2, shifted by 6*(ib%2)
+    return d * xd[0] * (part[0] * (float)(2 * (tmp & 7) + 1) + part[1] * (float)(2 * ((tmp >> 3) & 7) + 1));
+  }
+};
+
 // ---- Q4_1: value = q*d + m; the min term uses the fp16 sum of the inputs (vecdotq.cuh:72-96) -----
 // Both products of the reference (d*d8 and m*s8) are formed in half precision (__hmul2) before
 // they are widened; the same is done here.
@@ -1062,6 +1227,12 @@ int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_d
     case T_Q5_1: return launch_g1_out<T_Q5_1>(p, out_dtype, vectors, stream);
     case T_Q5_K: return launch_g1_out<T_Q5_K>(p, out_dtype, vectors, stream);
     case T_IQ4_NL: return launch_g1_out<T_IQ4_NL>(p, out_dtype, vectors, stream);
+    case T_IQ2_XS: return launch_g1_out<T_IQ2_XS>(p, out_dtype, vectors, stream);
+    case T_IQ2_S: return launch_g1_out<T_IQ2_S>(p, out_dtype, vectors, stream);
+    case T_IQ3_XXS: return launch_g1_out<T_IQ3_XXS>(p, out_dtype, vectors, stream);
+    case T_IQ3_S: return launch_g1_out<T_IQ3_S>(p, out_dtype, vectors, stream);
+    case T_IQ1_S: return launch_g1_out<T_IQ1_S>(p, out_dtype, vectors, stream);
+    case T_IQ1_M: return launch_g1_out<T_IQ1_M>(p, out_dtype, vectors, stream);
   }
   return E_BAD_TYPE;
 }

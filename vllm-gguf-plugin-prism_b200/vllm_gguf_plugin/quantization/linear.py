@@ -63,10 +63,9 @@ def _fused_mul_mat_gguf(x: torch.Tensor, weight: torch.Tensor, weight_type: int)
     if weight_type in UNQUANTIZED_TYPES:
         return x @ weight.T
     if int(weight_type) in ops.DEQUANT_ONLY_SIZES:
-        # Q2_K, Q3_K and the code-book types IQ2_XS/S, IQ3_XXS/S, IQ1_S/M have a dequantize kernel here
-        # but no fused matmul: dequantize, then a dense product -- the reference's own route for the IQ
-        # types above its GEMV threshold (linear.py:50-54).  (Below it the reference quantizes the
-        # activations to q8_1, so this differs from it there by that quantization noise, about 5e-3.)
+        # Q2_K / Q3_K have a dequantize kernel here but no fused matmul: dequantize, then a dense
+        # product.  (The reference quantizes the activations to q8_1 on its route for these types, so
+        # this differs from it by that quantization noise, about 5e-3 relative.)
         block_size, type_size = quant_sizes(weight_type)
         shape = (weight.shape[0], weight.shape[1] // type_size * block_size)
         y = x @ ops.ggml_dequantize(weight, weight_type, *shape, x.dtype).T
@@ -75,7 +74,7 @@ def _fused_mul_mat_gguf(x: torch.Tensor, weight: torch.Tensor, weight_type: int)
     elif weight_type in MMQ_QUANT_TYPES:
         y = ops.ggml_mul_mat_a8(weight, x, weight_type, weight.shape[0])
     elif weight_type in DEQUANT_TYPES:
-        if x.dtype in (torch.float16, torch.bfloat16):
+        if x.dtype in (torch.float16, torch.bfloat16) and int(weight_type) in ops._DEQUANT_MATMUL_TYPES:
             y = ops.ggml_dequant_matmul(weight, x, weight_type, weight.shape[0])
         else:  # fp32 activations: the reference's two steps
             block_size, type_size = quant_sizes(weight_type)
