@@ -349,22 +349,54 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
         if (++rs == p.raw_stages) { rs = 0; rph ^= 1u; }
       }
-      // correction columns (Q4_0 / Q4_K): a few stages at the end, straight from global memory
+      // correction columns (Q4_0 / Q4_K ...): a few stages at the end, straight from global memory
       int i0 = nmain;
       while ((i0 % NG) != GI) ++i0;
-      for (int i = i0; i < nk && ok; i += NG) {
-        uint32_t v[32];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
-          if (live) {
-            Decoder<TYPE, ab_t>::corr(row, 2 * (i - nmain) + h, p.K, vh);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) vh[j] = 0;
+      if constexpr (Decoder<TYPE, ab_t>::CORR_OFF >= 0) {
+        // The correction value of a block is one fp16 of the block itself (d or m).  A thread that
+        // collected the 64 values of its own row would issue 64 two-byte loads whose 32 lanes touch
+        // 32 different rows; instead the warp walks its 32 rows and each lane takes one block of the
+        // row, so a load instruction touches five or six lines, and every lane stores its value
+        // straight into the swizzled A slot.
+        constexpr int TS_ = BlockTraits<TYPE>::TS;
+        const int rb = r - lane;   // first tile row of this warp
+        for (int i = i0; i < nk && ok; i += NG) {
+          if (!wait_or_note(&empty_a[s], ph ^ 1u, 2, i)) { ok = false; break; }
+          uint8_t* slotp = sA + (size_t)s * MMQ_A_STAGE;
+          const int64_t g0 = (int64_t)(i - nmain) * 64 + lane;   // this lane's blocks: g0 and g0 + 32
+          const bool h0 = g0 * 32 < p.K, h1 = (g0 + 32) * 32 < p.K;
+#pragma unroll 8
+          for (int rr = 0; rr < 32; ++rr) {
+            const int ri = rb + rr;
+            const bool have = n0 + ri < p.N;
+            const uint8_t* src = wbase + (n0 + (have ? ri : 0)) * p.row_bytes + g0 * TS_ + Decoder<TYPE, ab_t>::CORR_OFF;
+            const unsigned short a = (have && h0) ? __ldg(reinterpret_cast<const unsigned short*>(src)) : (unsigned short)0;
+            const unsigned short b = (have && h1) ? __ldg(reinterpret_cast<const unsigned short*>(src + 32 * TS_)) : (unsigned short)0;
+            uint8_t* drow = slotp + (ri >> 3) * 1024 + (ri & 7) * 128 + (lane & 7) * 2;
+            *reinterpret_cast<unsigned short*>(drow + ((((lane >> 3)) ^ (ri & 7)) << 4)) = a;
+            *reinterpret_cast<unsigned short*>(drow + (((4 + (lane >> 3)) ^ (ri & 7)) << 4)) = b;
           }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_a[s]);
+          s += NG;
+          while (s >= SA) { s -= SA; ph ^= 1u; }
         }
-        ok = publish(v, i);
+      } else {
+        for (int i = i0; i < nk && ok; i += NG) {
+          uint32_t v[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
+            if (live) {
+              Decoder<TYPE, ab_t>::corr(row, 2 * (i - nmain) + h, p.K, vh);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) vh[j] = 0;
+            }
+          }
+          ok = publish(v, i);
+        }
       }
     };
     if (g == 0) run(std::integral_constant<int, 0>{});

@@ -98,8 +98,9 @@ template <int TYPE> struct RawGeom {
   static constexpr int SLOT = (S16 % 2 ? S16 : S16 + 1) * 16;
 };
 
-// ---- Q4_0: value = half((q - 8) * d); unit = one 18-byte block ------------------------------
+// ---- Q4_0: value = half(q * d), q unsigned (see Stage64<T_Q4_0>); unit = one 18-byte block ----
 template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
+  static constexpr int CORR_OFF = 0;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 7;   // 18 bytes at 2-byte alignment: <= 6 words (+1 for the shifts)
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     ldg_cover<RW - 1>(row + (int64_t)u * 18, 18, raw);
@@ -107,7 +108,7 @@ template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
   }
   static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
     const uint32_t sh = shift_of(row + (int64_t)u * 18);
-    const __half2 off = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 off = __floats2half2_rn(1024.f, 1024.f);
     const uint32_t du = word_at(raw, 0, sh) & 0xFFFFu;
     const __half2 d2 = u32_as_h2(du | (du << 16));
 #pragma unroll
@@ -119,7 +120,7 @@ template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
       out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((t >> 4) & 0xF, (t >> 12) & 0xF), off), d2));
     }
   }
-  // correction columns [32c, 32c+32): A'[n, g] = d of block g (pairs with 8*(d8*sum(q8) - s8) on the B side)
+  // correction columns [32c, 32c+32): A'[n, g] = d of block g (pairs with -8 * s8 on the B side)
   static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -133,6 +134,7 @@ template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
 
 // ---- Q8_0: value = half(q * d); unit = one 34-byte block ---------------------------------------
 template <typename ab_t> struct Decoder<T_Q8_0, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 11;  // 34 bytes: <= 10 words (+1)
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     ldg_cover<RW - 1>(row + (int64_t)u * 34, 34, raw);
@@ -171,6 +173,7 @@ __device__ __forceinline__ void q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t
 // ---- Q4_K: A = half(d1 * q) with d1 = half(d * sc); the -dmin*m part is a correction column ----
 // unit u: super-block u>>3, sub-block j = u&7: nibble (j&1) of the 32 bytes qs[32*(j>>1) ..]
 template <typename ab_t> struct Decoder<T_Q4_K, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 12;  // header (16 bytes) + 32 bytes of nibbles, all 16-byte aligned
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 144;
@@ -221,6 +224,7 @@ template <typename ab_t> struct Decoder<T_Q4_K, ab_t> {
 
 // ---- Q4_1: A = half(q * d); the min term m * s8 is a correction column (B side: +s8) -----------------
 template <typename ab_t> struct Decoder<T_Q4_1, ab_t> {
+  static constexpr int CORR_OFF = 2;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 5;   // 20 bytes, 4-byte aligned
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint32_t* b = reinterpret_cast<const uint32_t*>(row + (int64_t)u * 20);
@@ -255,6 +259,7 @@ __device__ __forceinline__ uint32_t q5_code(uint32_t nib, uint32_t qh, int j) { 
 
 // ---- Q5_0: value = half((q - 16) * d), 22-byte blocks (2-byte aligned): d | qh[4] | qs[16] ------------
 template <typename ab_t> struct Decoder<T_Q5_0, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 8;   // 22 bytes at 2-byte alignment: <= 6 words (+ shifts)
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     ldg_cover<7>(row + (int64_t)u * 22, 22, raw);
@@ -279,6 +284,7 @@ template <typename ab_t> struct Decoder<T_Q5_0, ab_t> {
 
 // ---- Q5_1: A = half(q * d), 24-byte blocks (8-byte aligned): d | m | qh[4] | qs[16]; correction column m ----
 template <typename ab_t> struct Decoder<T_Q5_1, ab_t> {
+  static constexpr int CORR_OFF = 2;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 6;
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint2* b = reinterpret_cast<const uint2*>(row + (int64_t)u * 24);
@@ -311,6 +317,7 @@ template <typename ab_t> struct Decoder<T_Q5_1, ab_t> {
 // 176-byte blocks (16-byte aligned): d | dmin | scales[12] | qh[32] | qs[128].  unit u: sub-block j = u&7:
 // nibble (j&1) of qs[32*(j>>1) + l], bit j of qh[l], l = 0..31.
 template <typename ab_t> struct Decoder<T_Q5_K, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 20;  // header (16) + 32 bytes of nibbles + 32 bytes of high bits
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 176;
@@ -369,6 +376,7 @@ template <typename ab_t> struct Decoder<T_Q5_K, ab_t> {
 //   scales sc[8ip + 2q] (l < 16) and sc[8ip + 2q + 1].
 // Raw: [0..9] 32 bytes of ql (+ cover), [10..19] 32 bytes of qh (+ cover), [20..21] scale half-word, [22] d.
 template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 23;
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 210;
@@ -407,6 +415,7 @@ template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
 
 // ---- IQ4_XS: fp32 d*(ls-32)*level rounded once to ab_t; unit = 32-value group ib = u&7 -----------
 template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 6;   // header (8 bytes) + 16 index bytes, 8-byte aligned
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 136;
@@ -434,6 +443,7 @@ template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
 
 // ---- IQ4_NL: fp32 d*level rounded once to ab_t; unit = one 18-byte block (2-byte aligned) ----------
 template <typename ab_t> struct Decoder<T_IQ4_NL, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 7;
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     ldg_cover<RW - 1>(row + (int64_t)u * 18, 18, raw);
@@ -458,6 +468,7 @@ template <typename ab_t> struct Decoder<T_IQ4_NL, ab_t> {
 // (value = +-round(d * magnitude): the product is formed in fp32 and rounded once, as in the
 // reference; multiplying by -1.f afterwards is exact, so flipping the sign bit is the same)
 template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
+  static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 5;   // [0] word holding d, [1..3] the group's 8 bytes (+ cover), [4] pad
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 66;
@@ -554,15 +565,31 @@ template <> struct Stage64<T_Q4_K, __half> {
 template <> struct Stage64<T_Q4_0, __half> {
   static constexpr bool FAST = true;
   static constexpr int PERM = 1;
+  // The operand is half(q * d) with the UNSIGNED code q = 0..15 (the "- 8" of the format rides in the
+  // correction column: -8 * d * s8, which is the reference's own tiled formula d * (sumi * d8 - 8 * s8),
+  // vecdotq.cuh:61-64), so one HFMA2 makes a pair: (1024 + q) * d - 1024 * d is q * d rounded once.
   static __device__ __forceinline__ void block(const uint32_t (&q)[4], __half2 d2, uint32_t* out) {
-    const __half2 o0 = h2const(1032.f), o1 = h2const(72.f);   // 1024 + 8, 64 + 8
+    const float ad = fabsf(__low2float(d2));
+    if (ad < 32.f) {
+      const __half2 c0 = __hmul2_rn(d2, h2const(-1024.f)), c1 = __hmul2_rn(d2, h2const(-64.f));   // exact
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {   // bytes 4j..4j+3: low nibbles = values 4j.., high nibbles = values 16+4j..
-      const uint32_t a = q[j], b = q[j] >> 8;
-      out[2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), o0), d2));
-      out[2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), o0), d2));
-      out[8 + 2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), o1), d2));
-      out[8 + 2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), o1), d2));
+      for (int j = 0; j < 4; ++j) {   // bytes 4j..4j+3: low nibbles = values 4j.., high nibbles = values 16+4j..
+        const uint32_t a = q[j], b = q[j] >> 8;
+        out[2 * j] = h2_as_u32(__hfma2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), d2, c0));
+        out[2 * j + 1] = h2_as_u32(__hfma2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), d2, c0));
+        out[8 + 2 * j] = h2_as_u32(__hfma2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), d2, c1));
+        out[8 + 2 * j + 1] = h2_as_u32(__hfma2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), d2, c1));
+      }
+    } else {   // 1024 * d would overflow fp16: subtract the offset first (exact), then scale
+      const __half2 o0 = h2const(1024.f), o1 = h2const(64.f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t a = q[j], b = q[j] >> 8;
+        out[2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), o0), d2));
+        out[2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), o0), d2));
+        out[8 + 2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), o1), d2));
+        out[8 + 2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), o1), d2));
+      }
     }
   }
   template <int SC> static __device__ __forceinline__ void decode(const uint8_t* chunk, uint32_t (&out)[32]) {

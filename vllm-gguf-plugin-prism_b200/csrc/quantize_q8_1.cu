@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const in_t* __restri
           // contains (offset-free part) . x^; the appended column carries what is left.
           const float s8 = __half2float(hs);
           float c;
-          if (corr_mode == CORR_Q4_0) c = 8.0f * (d8 * (float)qs - s8);  // weights stored as (q-8): add back 8*d*(d8*sum(q) - s8)
+          if (corr_mode == CORR_Q4_0) c = -8.0f * s8;                    // weights decoded as q * d: the format's -8 * d meets the sum here
           else c = corr_mode == CORR_PLUS ? s8 : -s8;                    // CORR_PLUS: + m * s8;  CORR_MIN: minus min * s8
           xb[row * ldb + kpad + kb] = __float2half_rn(c);
         }
@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(256) quantize_f16x8_kernel(const in_t* __restr
       qs += __shfl_xor_sync(0xffffffffu, qs, 1, 32);
       if (inb && t == 0) {
         const float s8 = __half2float(hs);
-        const float c = corr_mode == CORR_Q4_0 ? 8.0f * (d8 * (float)qs - s8) : (corr_mode == CORR_PLUS ? s8 : -s8);   // see quantize_q8_1_kernel
+        const float c = corr_mode == CORR_Q4_0 ? -8.0f * s8 : (corr_mode == CORR_PLUS ? s8 : -s8);   // see quantize_q8_1_kernel
         xb[row * ldb + kpad + kb] = __float2half_rn(c);
       }
       if (inb && kb == 0)
