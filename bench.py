@@ -411,6 +411,14 @@ def run_ncu_case(spec: str):
 
     op, t, n, k, m = spec.split(",")
     t, n, k, m = int(t), int(n), int(k), int(m)
+    if op == "moe":   # the MoE configuration's gate/up GEMM (type, sizes fixed by moe_case)
+        c = moe_case()
+        s_, e_, n_ = c["ours"]
+        for _ in range(4):
+            capi.moe_a8(c["x1"], c["w13"], s_, e_, n_, c["t"], 2 * c["inter"], c["top_k"], c["tokens"])
+        torch.cuda.synchronize()
+        print("ncu case done, device status", capi.last_status())
+        return
     base = synth.make_weight(t, n, k, seed=1)
     ws = [torch.from_numpy(base).to("cuda") for _ in range(6)]
     x = torch.from_numpy(synth.make_activation(m, k, seed=0)).to("cuda")
@@ -789,7 +797,7 @@ def main():
     bytes_per_launch = total_bytes / g / calls_per_step
     achieved = bytes_per_launch / t_k / 1e9
     roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-            "traffic": 33082500 // g,
+            "traffic": 33104128 // g,
             "traffic_source": "constant: dram__bytes_read.sum + dram__bytes_write.sum of one launch on a 33 MB matrix from an ncu "
                               "capture of this kernel (not measured in this run); divided by the number of ranks",
             "peak_source": which_peak, "kernel": "gemv1_kernel<Q4_K> (single-vector GEMV)",
