@@ -10,8 +10,8 @@
  *
  * Types: GGML ids 2 (Q4_0), 3 (Q4_1), 6 (Q5_0), 7 (Q5_1), 8 (Q8_0), 12 (Q4_K), 13 (Q5_K), 14 (Q6_K),
  * 16 (IQ2_XXS), 20 (IQ4_NL), 23 (IQ4_XS); the dequantize and the GEMV entry points (mul_mat_vec_a8,
- * moe_a8_vec and their variants) also take 17 (IQ2_XS), 18 (IQ3_XXS), 19 (IQ1_S), 21 (IQ3_S),
- * 22 (IQ2_S), 29 (IQ1_M); the standalone dequantize also takes 10 (Q2_K), 11 (Q3_K).
+ * moe_a8_vec and their variants) also take 10 (Q2_K), 11 (Q3_K), 17 (IQ2_XS), 18 (IQ3_XXS), 19 (IQ1_S),
+ * 21 (IQ3_S), 22 (IQ2_S), 29 (IQ1_M) -- all nineteen block types of the reference's dispatch.
  * Weights W are raw GGUF blocks, row-major `uint8 [N][K/QK*type_size]`, base 16-byte aligned.
  * Activations X are `[M][K]` contiguous in `dtype`; outputs Y are `[M][N]` in the same dtype.
  */
@@ -60,7 +60,7 @@ int gguf_b200_quantize_q8_1(const void* x, int dtype, void* out, int64_t M, int6
 
 /* Standalone dequantize, bit-exact with the reference.
  * Replaces: ggml_dequantize, gguf_kernel.cu:87-102 (+ dequantize.cuh:527-571 dispatch).
- * Types: all matmul types plus Q2_K and Q3_K (every type of the reference's dispatch).
+ * Types: all nineteen (every type of the reference's dispatch).
  * Writes n_elems = m*n values (a multiple of the block size); every output element is
  * written, so the caller need not zero-fill. */
 int gguf_b200_dequantize(const void* W, int type, void* out, int out_dtype, int64_t n_elems, void* stream);

@@ -201,7 +201,7 @@ int oracle_type_size(int type) {
     case T_Q4_1: return 20;
     case T_Q5_0: return 22;
     case T_Q5_1: return 24;
-    case T_Q2_K: return 84;  /* (Q2_K, Q3_K: dequantize only) */
+    case T_Q2_K: return 84;  /* (Q2_K, Q3_K: dequantize and GEMV; no tiled kernel here) */
     case T_Q3_K: return 110;
     case T_Q5_K: return 176;
     case T_IQ4_NL: return 18;
@@ -654,6 +654,21 @@ static void unpack_codes(const uint8_t* blk, int type, int8_t* w) {
           w[64 * il + 32 + l] = (int8_t)((blk[48 + 32 * il + l] >> 4) | (((blk[16 + l] >> (2 * il + 1)) & 1) << 4));
         }
       break;
+    case T_Q2_K: /* scales[16] | qs[64] | d | dmin: value 128n + 32i + l = (qs[32n + l] >> 2i) & 3  (dequantize.cuh:97-118) */
+      for (int n = 0; n < 2; ++n)
+        for (int i = 0; i < 4; ++i)
+          for (int l = 0; l < 32; ++l) w[128 * n + 32 * i + l] = (int8_t)((blk[16 + 32 * n + l] >> (2 * i)) & 3);
+      break;
+    case T_Q3_K: /* hmask[32] | qs[64] | scales[12] | d: two low bits from qs, minus 4 unless the hmask bit is set
+                    (vecdotq.cuh:1024-1048, :269-300) */
+      for (int n = 0; n < 2; ++n)
+        for (int i = 0; i < 4; ++i)
+          for (int l = 0; l < 32; ++l) {
+            int q2 = (blk[32 + 32 * n + l] >> (2 * i)) & 3;
+            int h = (blk[l] >> (4 * n + i)) & 1;
+            w[128 * n + 32 * i + l] = (int8_t)(q2 - (h ? 0 : 4));
+          }
+      break;
     case T_IQ2_XS: case T_IQ2_S: case T_IQ3_XXS: case T_IQ3_S:
       /* signed code-book magnitudes, group (ib, il) of eight values as in oracle_dequantize */
       for (int ib = 0; ib < 8; ++ib)
@@ -760,6 +775,36 @@ static double block_dot(const uint8_t* blk, int type, const uint8_t* y, int mmq)
         uint32_t s = blk[2 + 8 * g + 7] >> 4;
         acc += d * (0.5 + s) * h2f(rd16(yb)) * 0.25 * idot(w + 32 * g, (const int8_t*)yb + 4, 32);
       }
+    } break;
+    case T_Q2_K: { /* d * sum d8*(dot16*(sc&15)) - dmin * sum d8*((sc>>4)*sum16(q8)), vecdotq.cuh:204-232, 923-944 */
+      double d = h2f(rd16(blk + 80)), dmin = h2f(rd16(blk + 82)), sd = 0, sm = 0;
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        double d8 = h2f(rd16(yb));
+        for (int h = 0; h < 2; ++h) {
+          int sc = blk[2 * g + h], sq = 0;
+          for (int j = 0; j < 16; ++j) sq += q8[16 * h + j];
+          sd += d8 * (double)(idot(w + 32 * g + 16 * h, q8 + 16 * h, 16) * (sc & 0xF));
+          sm += d8 * (double)((sc >> 4) * sq);
+        }
+      }
+      acc = d * sd - dmin * sm;
+    } break;
+    case T_Q3_K: { /* d * sum d8*(dot16*(sc6-32)), vecdotq.cuh:269-300, 1024-1048 */
+      double d = h2f(rd16(blk + 108)), sf = 0;
+      const uint8_t* sc = blk + 96;
+      for (int g = 0; g < nsub; ++g) {
+        const uint8_t* yb = y + 36 * g;
+        const int8_t* q8 = (const int8_t*)yb + 4;
+        double d8 = h2f(rd16(yb));
+        for (int h = 0; h < 2; ++h) {
+          int j = 2 * g + h;
+          int s6 = (((sc[j % 8] >> (4 * (j / 8))) & 0xF) | (((sc[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32;
+          sf += d8 * (double)(idot(w + 32 * g + 16 * h, q8 + 16 * h, 16) * s6);
+        }
+      }
+      acc = d * sf;
     } break;
     case T_IQ2_XS: case T_IQ2_S: { /* d*d8*0.25*((0.5+ls1)*sumi1 + (0.5+ls2)*sumi2), vecdotq.cuh:1554-1620 */
       double d = h2f(rd16(blk));

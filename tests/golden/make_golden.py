@@ -32,9 +32,9 @@ sys.path.insert(0, str(ROOT))
 
 TYPES = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14, "IQ2_XXS": 16, "IQ4_XS": 23,
          "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q5_K": 13, "IQ4_NL": 20,
-         "IQ2_XS": 17, "IQ3_XXS": 18, "IQ1_S": 19, "IQ3_S": 21, "IQ2_S": 22, "IQ1_M": 29}
+         "IQ2_XS": 17, "IQ3_XXS": 18, "IQ1_S": 19, "IQ3_S": 21, "IQ2_S": 22, "IQ1_M": 29, "Q2_K": 10, "Q3_K": 11}
 # dequantize fixtures only (no fused matmul for these in this library)
-DEQUANT_ONLY = {"Q2_K": 10, "Q3_K": 11}
+DEQUANT_ONLY: dict = {}
 
 
 def gguf_py_fixture():

@@ -33,7 +33,7 @@ def test_geometry_and_error_codes(native_libs):
     sizes = {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210), 16: (256, 66), 23: (256, 136)}
     for t, (bs, ts) in sizes.items():
         assert lib.gguf_b200_block_size(t) == bs and lib.gguf_b200_type_size(t) == ts
-    assert lib.gguf_b200_type_size(10) == 84 and lib.gguf_b200_block_size(11) == 256    # dequantize-only types
+    assert lib.gguf_b200_type_size(10) == 84 and lib.gguf_b200_block_size(11) == 256
     assert lib.gguf_b200_type_size(9) == 0 and lib.gguf_b200_block_size(9) == 0
     assert lib.gguf_b200_q8_1_row_bytes(1024) == 1024 // 32 * 36
     assert lib.gguf_b200_q8_1_row_bytes(800) == 1024 // 32 * 36
@@ -44,7 +44,8 @@ def test_geometry_and_error_codes(native_libs):
     # argument validation happens before any CUDA call
     null = ctypes.c_void_p(0)
     p = ctypes.c_void_p(4096)
-    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 11, 1, 1, 8, 256, null) == -1  # type (Q3_K: dequantize only)
+    assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 9, 1, 1, 8, 256, null) == -1   # type (Q8_1 is not a weight type)
+    assert lib.gguf_b200_mul_mat_a8(p, p, p, p, 1 << 20, 11, 1, 1, 8, 256, null) == -1       # Q3_K has no tiled kernel here
     assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 12, 7, 1, 8, 256, null) == -2  # dtype
     assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 12, 1, 1, 8, 100, null) == -3  # K % 256
     assert lib.gguf_b200_mul_mat_vec_a8(null, p, p, p, 1 << 20, 12, 1, 1, 8, 256, null) == -4
@@ -86,13 +87,13 @@ def test_tensor_parallel_entry_points_validate_arguments(native_libs):
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(slot=-1)) == -3
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(sp=100)) == -3          # slot too small for world * N_local
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(add=0)) == -3           # a call cannot consume its own slot
-    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(type=10)) == -1
+    assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(type=9)) == -1
     assert lib.gguf_b200_mul_mat_vec_a8_tp(*args(add=1, parts=3)) == -3  # partial vectors come one per rank, or not at all
     # row-parallel: same arguments, N and K_local in place of N_local and K; a slot holds world * N fp32 partials
     assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(y=null)) == -4
     assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(world=9)) == -3
     assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(sp=200)) == -3   # 2 ranks x 64 rows x 8 bytes > 200 x 4
-    assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(type=11)) == -1
+    assert lib.gguf_b200_mul_mat_vec_a8_tp_rowpar(*args(type=9)) == -1
     assert lib.gguf_b200_tp_unpack_sum(null, p, 0, 1024, 64, 2, p, 1, null) == -4
     assert lib.gguf_b200_tp_unpack_sum(p, p, 0, 1024, 64, 9, p, 1, null) == -3
     assert lib.gguf_b200_tp_unpack_sum(p, p, 0, 1024, 4096, 2, p, 1, null) == -3   # partials beyond the slot

@@ -382,7 +382,7 @@ def test_ops_api_equals_capi_and_dispatcher_end_to_end():
             want = x64 @ capi.dequantize(w, t, 256, 1024).T
         assert torch.equal(y, want)
     with pytest.raises(NotImplementedError):
-        ops.ggml_mul_mat_vec_a8(w, x1, 10, 256)
+        ops.ggml_mul_mat_vec_a8(w, x1, 9, 256)
     with pytest.raises(RuntimeError):
         ops.ggml_mul_mat_vec_a8(w[:, :-1].contiguous(), x1, 23, 256)      # not a whole number of blocks
 

@@ -61,5 +61,5 @@ def test_noalloc_rejects_sizes_beyond_its_array(native_libs):
     null = ctypes.c_void_p(0)
     assert lib.gguf_b200_mul_mat_vec_a8_noalloc(p, p, p, 12, 1, 9, 64, 4096, null) == -7      # M > 8
     assert lib.gguf_b200_mul_mat_vec_a8_noalloc(p, p, p, 12, 1, 1, 64, 65536, null) == -7     # K > 32768
-    assert lib.gguf_b200_mul_mat_vec_a8_noalloc(p, p, p, 10, 1, 1, 64, 4096, null) == -1      # unsupported type
+    assert lib.gguf_b200_mul_mat_vec_a8_noalloc(p, p, p, 9, 1, 1, 64, 4096, null) == -1       # unsupported type (Q8_1 is not a weight type)
     assert b"limit" in lib.gguf_b200_error_string(-7)

@@ -70,7 +70,7 @@ const char* gguf_b200_version(void) { return "gguf_b200 0.1 (sm_100a)"; }
 const char* gguf_b200_error_string(int code) {
   switch (code) {
     case E_OK: return "ok";
-    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q4_1=3, Q5_0=6, Q5_1=7, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14, IQ2_XXS=16, IQ2_XS=17, IQ3_XXS=18, IQ1_S=19, IQ4_NL=20, IQ3_S=21, IQ2_S=22, IQ4_XS=23, IQ1_M=29; dequantize also Q2_K=10, Q3_K=11; the tensor-core entry points take fewer)";
+    case E_BAD_TYPE: return "unsupported GGML block type (supported: Q4_0=2, Q4_1=3, Q5_0=6, Q5_1=7, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14, Q2_K=10, Q3_K=11, IQ2_XXS=16, IQ2_XS=17, IQ3_XXS=18, IQ1_S=19, IQ4_NL=20, IQ3_S=21, IQ2_S=22, IQ4_XS=23, IQ1_M=29; the tensor-core entry points take fewer)";
     case E_BAD_DTYPE: return "unsupported dtype (expected f32=0, f16=1, bf16=2)";
     case E_BAD_SHAPE: return "bad shape (negative size, or K not a multiple of the block size)";
     case E_BAD_POINTER: return "null or misaligned pointer (16-byte alignment required)";

@@ -23,7 +23,7 @@
 namespace gguf_b200 {
 
 enum : int { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_XS = 23 };
-// further block types (Q2_K and Q3_K: standalone dequantize only):
+// further block types (Q2_K, Q3_K: dequantize and GEMV):
 //   Q4_1    20 : half d | half m | u8 qs[16]                      value = q*d + m
 //   Q5_0    22 : half d | u8 qh[4] | u8 qs[16]                    5th bit of value j in bit j (j+16: bit j+16... see dequantize.cu)
 //   Q5_1    24 : half d | half m | u8 qh[4] | u8 qs[16]
@@ -97,6 +97,8 @@ __host__ __device__ inline int type_size(int t) {
     case T_IQ3_S: return 110;
     case T_IQ1_S: return 50;
     case T_IQ1_M: return 56;
+    case T_Q2_K: return 84;
+    case T_Q3_K: return 110;
   }
   return 0;
 }
@@ -106,14 +108,8 @@ __host__ __device__ inline int block_size(int t) {
   }
   return type_size(t) ? 256 : 0;
 }
-// the same for every type the standalone dequantize knows (a superset of the matmul types)
-__host__ __device__ inline int dequant_type_size(int t) {
-  switch (t) {
-    case T_Q2_K: return 84;
-    case T_Q3_K: return 110;
-  }
-  return type_size(t);
-}
+// the same for every type the standalone dequantize knows (today the same set)
+__host__ __device__ inline int dequant_type_size(int t) { return type_size(t); }
 __host__ __device__ inline int dequant_block_size(int t) { return type_size(t) ? block_size(t) : (dequant_type_size(t) ? 256 : 0); }
 __host__ __device__ inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 

@@ -626,7 +626,7 @@ int launch_gemv(const void* w, const void* xq_soa, void* y, int type, int out_dt
     if (rc <= 0) return rc;  // done or failed; 1 = shape outside the register-resident kernel's reach
   }
   if (type == T_Q4_1 || type == T_Q5_0 || type == T_Q5_1 || type == T_Q5_K || type == T_IQ4_NL || type == T_IQ2_XS || type == T_IQ2_S ||
-      type == T_IQ3_XXS || type == T_IQ3_S || type == T_IQ1_S || type == T_IQ1_M) {
+      type == T_IQ3_XXS || type == T_IQ3_S || type == T_IQ1_S || type == T_IQ1_M || type == T_Q2_K || type == T_Q3_K) {
     // these types exist only in the register-resident kernel: larger batches go two vectors at a time
     for (int64_t m0 = 0; m0 < M; m0 += 2) {
       const int rc = launch_gemv1(w, xq_soa, y, type, out_dtype, N, K, status, stream, nullptr, M - m0 >= 2 ? 2 : 1, nullptr, (int)m0, (int)M);

@@ -457,6 +457,67 @@ template <> struct G1<T_IQ1_M> {   // u8 qs[32] | u8 qh[16] | u16 scales[4] (the
   }
 };
 
+// ---- Q2_K: scales[16] | qs[64] | d | dmin; unit g = 32 values = sub-blocks 2g, 2g+1 (vecdotq.cuh:204-232, 923-944) ----
+// value 128n + 32i + l = (qs[32n + l] >> 2i) & 3, so q8_1 block g = 4n + i reads the 32 bytes qs[32n ..] shifted by 2i.
+// The min term needs sum(q8) of each 16-value half: constants of the lane, packed in x[8].
+template <> struct G1<T_Q2_K> {
+  static constexpr int UPB = 8, XW = 9, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int, uint32_t (&x)[XW], float (&xd)[XD]) {
+    const uint4* p = reinterpret_cast<const uint4*>(qs + (size_t)u * 32);
+    const uint4 a = p[0], b = p[1];
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    int s0 = 0, s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s0 = __dp4a(0x01010101, (int)x[i], s0);
+      s1 = __dp4a(0x01010101, (int)x[4 + i], s1);
+    }
+    x[8] = ((uint32_t)s0 & 0xFFFFu) | ((uint32_t)s1 << 16);
+    const float2 d = ds[u];
+    xd[0] = d.x; xd[1] = d.y;
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int g, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    const __half2 dm = u32_as_half2(pl32(blk + 80));       // 84-byte blocks: 4-byte aligned
+    const uint32_t sc = pl16(blk + 2 * g);
+    const uint32_t qb = blk + 16 + 32 * (g >> 2), sh = 2 * (g & 3);
+    int a0 = 0, a1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a0 = __dp4a((int)((pl32(qb + 4 * i) >> sh) & 0x03030303u), (int)x[i], a0);
+      a1 = __dp4a((int)((pl32(qb + 16 + 4 * i) >> sh) & 0x03030303u), (int)x[4 + i], a1);
+    }
+    const int s0 = (int)(short)(x[8] & 0xFFFFu), s1 = (int)(short)(x[8] >> 16);
+    const float sd = (float)(a0 * (int)(sc & 0xF) + a1 * (int)((sc >> 8) & 0xF));
+    const float sm = (float)(s0 * (int)((sc >> 4) & 0xF) + s1 * (int)(sc >> 12));
+    return xd[0] * (__low2float(dm) * sd - __high2float(dm) * sm);
+  }
+};
+
+// ---- Q3_K: hmask[32] | qs[64] | scales[12] | d; unit g = 32 values (vecdotq.cuh:269-300, 1024-1048) ----
+// value 128n + 32i + l = ((qs[32n + l] >> 2i) & 3) - (bit 4n+i of hmask[l] ? 0 : 4); 6-bit scales minus 32.
+template <> struct G1<T_Q3_K> {
+  static constexpr int UPB = 8, XW = 8, XD = 2, UMAX = 4;
+  static __device__ __forceinline__ void load_x(const uint8_t* qs, const float2* ds, int u, int b, uint32_t (&x)[XW], float (&xd)[XD]) {
+    G1<T_Q8_0>::load_x(qs, ds, u, b, x, xd);
+  }
+  static __device__ __forceinline__ float unit(uint32_t blk, int g, const uint32_t (&x)[XW], const float (&xd)[XD], const Tab1&) {
+    uint32_t hm[8], q[8];
+    lds_a2<8>(blk, hm);                                     // 110-byte blocks: 2-byte aligned
+    lds_a2<8>(blk + 32 + 32 * (g >> 2), q);
+    const uint32_t lo = pl16(blk + 96 + ((2 * g) & 7)) >> (4 * (g >> 2)), hi = pl16(blk + 104 + ((2 * g) & 3)) >> (2 * (g >> 1));
+    const int sc0 = (int)((lo & 0xF) | ((hi & 3) << 4)) - 32, sc1 = (int)(((lo >> 8) & 0xF) | (((hi >> 8) & 3) << 4)) - 32;
+    const uint32_t sh = 2 * (g & 3);
+    int a0 = 0, a1 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t v = __vsub4((q[i] >> sh) & 0x03030303u, ((~hm[i] >> g) << 2) & 0x04040404u);
+      if (i < 4) a0 = __dp4a((int)v, (int)x[i], a0);
+      else a1 = __dp4a((int)v, (int)x[i], a1);
+    }
+    return plh(blk + 108) * xd[0] * (float)(a0 * sc0 + a1 * sc1);
+  }
+};
+
 // ---- Q4_1: value = q*d + m; the min term uses the fp16 sum of the inputs (vecdotq.cuh:72-96) -----
 // Both products of the reference (d*d8 and m*s8) are formed in half precision (__hmul2) before
 // they are widened; the same is done here.
@@ -1227,6 +1288,8 @@ int launch_gemv1(const void* w, const void* xq_soa, void* y, int type, int out_d
     case T_Q5_1: return launch_g1_out<T_Q5_1>(p, out_dtype, vectors, stream);
     case T_Q5_K: return launch_g1_out<T_Q5_K>(p, out_dtype, vectors, stream);
     case T_IQ4_NL: return launch_g1_out<T_IQ4_NL>(p, out_dtype, vectors, stream);
+    case T_Q2_K: return launch_g1_out<T_Q2_K>(p, out_dtype, vectors, stream);
+    case T_Q3_K: return launch_g1_out<T_Q3_K>(p, out_dtype, vectors, stream);
     case T_IQ2_XS: return launch_g1_out<T_IQ2_XS>(p, out_dtype, vectors, stream);
     case T_IQ2_S: return launch_g1_out<T_IQ2_S>(p, out_dtype, vectors, stream);
     case T_IQ3_XXS: return launch_g1_out<T_IQ3_XXS>(p, out_dtype, vectors, stream);

@@ -62,18 +62,14 @@ def _fused_mul_mat_gguf(x: torch.Tensor, weight: torch.Tensor, weight_type: int)
         return torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
     if weight_type in UNQUANTIZED_TYPES:
         return x @ weight.T
-    if int(weight_type) in ops.DEQUANT_ONLY_SIZES:
-        # Q2_K / Q3_K have a dequantize kernel here but no fused matmul: dequantize, then a dense
-        # product.  (The reference quantizes the activations to q8_1 on its route for these types, so
-        # this differs from it by that quantization noise, about 5e-3 relative.)
-        block_size, type_size = quant_sizes(weight_type)
-        shape = (weight.shape[0], weight.shape[1] // type_size * block_size)
-        y = x @ ops.ggml_dequantize(weight, weight_type, *shape, x.dtype).T
-    elif x.shape[0] <= mmvq_safe and weight_type in MMVQ_QUANT_TYPES:
+    if x.shape[0] <= mmvq_safe and weight_type in MMVQ_QUANT_TYPES:
         y = ops.ggml_mul_mat_vec_a8(weight, x, weight_type, weight.shape[0])
-    elif weight_type in MMQ_QUANT_TYPES:
+    elif weight_type in MMQ_QUANT_TYPES and int(weight_type) in ops._CUDA_GEMM_QUANT_TYPES:
         y = ops.ggml_mul_mat_a8(weight, x, weight_type, weight.shape[0])
     elif weight_type in DEQUANT_TYPES:
+        # (also Q2_K / Q3_K above the GEMV threshold: they have no tiled kernel here, so they take the
+        #  reference's route for IQ types -- dequantize, then a dense product -- which differs from the
+        #  reference's tiled kernel by its q8_1 activation-quantization noise, about 5e-3 relative)
         if x.dtype in (torch.float16, torch.bfloat16) and int(weight_type) in ops._DEQUANT_MATMUL_TYPES:
             y = ops.ggml_dequant_matmul(weight, x, weight_type, weight.shape[0])
         else:  # fp32 activations: the reference's two steps

@@ -27,7 +27,7 @@ SUPPORTED_QUANT_SIZES = {Q4_0: (32, 18), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (
                          IQ2_XXS: (256, 66), IQ4_NL: (32, 18), IQ4_XS: (256, 136),
                          IQ2_XS: (256, 74), IQ2_S: (256, 82), IQ3_XXS: (256, 98), IQ3_S: (256, 110), IQ1_S: (256, 50),
                          IQ1_M: (256, 56),   # (decode GEMV; more tokens: dequantize + matmul, as in the reference)
-                         Q2_K: (256, 84), Q3_K: (256, 110)}   # (dequantize route only)
+                         Q2_K: (256, 84), Q3_K: (256, 110)}   # (decode GEMV; more tokens: dequantize + matmul)
 
 
 def quant_sizes(weight_type: int) -> tuple[int, int]:
