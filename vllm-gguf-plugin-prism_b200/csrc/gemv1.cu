@@ -1066,17 +1066,43 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) gemv1_kernel(const G1Params 
         case 3: rows(std::integral_constant<int, 3>{}); break;
         default: rows(std::integral_constant<int, 4>{}); break;
       }
+      // Warp reduction of the cnt row sums together.  The butterfly of ONE value adds lane l^16,
+      // then l^8, l^4, l^2, l^1.  With two or four values the first one or two levels are done
+      // "transposed": a lane keeps the value of the row its bit 4 (and bit 3) selects and gives the
+      // other one away, so that after them every lane holds a partial sum of ONE row and the
+      // remaining levels serve all rows at once -- 5 or 6 shuffles instead of 10 to 20.  Every
+      // addition has the same two operands as in the one-value butterfly, so the bits of a row's
+      // sum do not depend on how many rows shared the item.
 #pragma unroll
-      for (int rr = 0; rr < G1_R; ++rr) {
-        if (rr < cnt) {
-#pragma unroll
-          for (int m = 0; m < MV; ++m) {
-            const float v = warp_sum(acc[m][rr]);
-            if (lane == 0) {
-              if (!staged) store_result<out_t>(p, c_row + rr, v, m, 0u);
-              else partial[(((rl_i * G1_BATCH + (i % G1_BATCH)) * G1_R + rr) * MV + m) * p.ks + ks_i] = v;
-            }
+      for (int m = 0; m < MV; ++m) {
+        float v;
+        int my_rr;
+        if (cnt == 1) {
+          v = acc[m][0];
+          v += __shfl_xor_sync(0xffffffffu, v, 16);
+          v += __shfl_xor_sync(0xffffffffu, v, 8);
+          my_rr = 0;
+        } else {
+          const bool up = (lane & 16) != 0;
+          float a = up ? acc[m][1] : acc[m][0];
+          a += __shfl_xor_sync(0xffffffffu, up ? acc[m][0] : acc[m][1], 16);
+          if (cnt == 2) {
+            v = a + __shfl_xor_sync(0xffffffffu, a, 8);
+            my_rr = up ? 1 : 0;
+          } else {
+            float b = up ? acc[m][3] : acc[m][2];
+            b += __shfl_xor_sync(0xffffffffu, up ? acc[m][2] : acc[m][3], 16);
+            const bool hi = (lane & 8) != 0;
+            v = (hi ? b : a) + __shfl_xor_sync(0xffffffffu, hi ? a : b, 8);
+            my_rr = (up ? 1 : 0) + (hi ? 2 : 0);
           }
+        }
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((lane & 7) == 0 && my_rr < cnt && (cnt > 2 || (lane & 8) == 0) && (cnt > 1 || lane == 0)) {   // one writer lane per row
+          if (!staged) store_result<out_t>(p, c_row + my_rr, v, m, 0u);
+          else partial[(((rl_i * G1_BATCH + (i % G1_BATCH)) * G1_R + my_rr) * MV + m) * p.ks + ks_i] = v;
         }
       }
       __syncwarp();   // every lane is done with the stage: the next pass may refill it
