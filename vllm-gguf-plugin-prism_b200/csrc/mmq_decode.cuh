@@ -35,15 +35,17 @@ __device__ __forceinline__ __half2 ints_plus_1024(uint32_t a, uint32_t b) { retu
 __device__ __forceinline__ __half2 hmul2_rn(__half2 a, __half2 b) { return __hmul2_rn(a, b); }
 __device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
 
-// N aligned words covering `len` bytes from the (2-byte aligned) address p; words that hold no
-// needed byte are not loaded (no read past the end of the buffer).  Plain loads: the pointer may
-// be global memory or the shared-memory staging area of the raw weight bytes.
+// N aligned words covering `len` bytes from the (2-byte aligned) address p in the shared-memory
+// staging area of the raw weight bytes; words that hold no needed byte are not loaded.  The loads
+// are explicit shared-window loads: rounding the address down through an integer made the
+// compiler forget the address space, and generic loads of shared memory travel the global-memory
+// pipeline (ncu: `lg_throttle` and `long_scoreboard` stalls in the decode warps).
 template <int N> __device__ __forceinline__ void ldg_cover(const uint8_t* p, int len, uint32_t* r) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const uint32_t* al = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
-  const int need = (len + (int)(a & 3) + 3) >> 2;
+  const uint32_t a = smem_u32(p);
+  const uint32_t al = a & ~3u;
+  const int need = (len + (int)(a & 3u) + 3) >> 2;
 #pragma unroll
-  for (int i = 0; i < N; ++i) r[i] = i < need ? al[i] : 0u;
+  for (int i = 0; i < N; ++i) r[i] = i < need ? lds32(al + 4u * i) : 0u;
 }
 // word i of the byte stream that starts `sh` bits into r[0]
 __device__ __forceinline__ uint32_t word_at(const uint32_t* r, int i, uint32_t sh) { return __funnelshift_r(r[i], r[i + 1], sh); }
