@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
     const int64_t n = n0 + r;
     const bool live = n < p.N;
     const uint8_t* row = wbase + (live ? n : 0) * p.row_bytes;
-    DecodeCtx cx{s_sel, s_sgn, s_kv};
+    DecodeCtx cx{smem_u32(s_sel), smem_u32(s_sgn), smem_u32(s_kv)};
     const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
     const int nunits = (int)((p.K + 31) / 32);   // 32-value units of a row that exist
     int s = g;                 // A slot of this group's next stage and its phase

@@ -51,10 +51,29 @@ template <int N> __device__ __forceinline__ void ldg_cover(const uint8_t* p, int
 __device__ __forceinline__ uint32_t word_at(const uint32_t* r, int i, uint32_t sh) { return __funnelshift_r(r[i], r[i + 1], sh); }
 __device__ __forceinline__ uint32_t shift_of(const uint8_t* p) { return (uint32_t)(reinterpret_cast<uintptr_t>(p) & 3) * 8u; }
 
+// Tables in shared memory, held as 32-bit shared-window addresses so that every look-up is an
+// ld.shared (through a generic pointer the look-ups travel the global-memory pipeline).  The
+// look-ups are plain (non-volatile) asm: their index comes from weight bytes that are read long
+// after the barrier that published the tables.
 struct DecodeCtx {
-  const uint2* sel;       // IQ2_XXS: per grid entry, the byte-permute selectors of its four value pairs (see Decoder<T_IQ2_XXS>)
-  const uint4* sgn;       // IQ2_XXS: per 7-bit sign index, the sign-bit masks of the four value pairs
-  const int8_t* kv;       // IQ4_XS levels in shared memory
+  uint32_t sel;       // IQ2_XXS: per grid entry (8 bytes), the byte-permute selectors of its four value pairs (see Decoder<T_IQ2_XXS>)
+  uint32_t sgn;       // IQ2_XXS: per 7-bit sign index (16 bytes), the sign-bit masks of the four value pairs
+  uint32_t kv;        // IQ4_NL / IQ4_XS: the 16 levels, one signed byte each
+  __device__ __forceinline__ uint2 sel_at(uint32_t i) const {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(sel + 8u * i));
+    return v;
+  }
+  __device__ __forceinline__ uint4 sgn_at(uint32_t i) const {
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sgn + 16u * i));
+    return v;
+  }
+  __device__ __forceinline__ float level(uint32_t i) const {
+    int v;
+    asm("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(kv + i));
+    return (float)v;
+  }
 };
 // Shared-memory tables of the IQ2_XXS decoder, built once per CTA from the format's grid and
 // sign tables.  A grid entry holds eight magnitudes, each one of {8, 25, 43}; with the three
@@ -179,9 +198,8 @@ template <typename ab_t> struct Decoder<T_Q4_K, ab_t> {
   static constexpr int RW = 12;  // header (16 bytes) + 32 bytes of nibbles, all 16-byte aligned
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 144;
-    const uint4 h = *reinterpret_cast<const uint4*>(blk);
-    const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + 32 * ((u >> 1) & 3));
-    const uint4 a = qp[0], b = qp[1];
+    const uint32_t sb = smem_u32(blk), sq = sb + 16 + 32 * ((u >> 1) & 3);
+    const uint4 h = lds128s(sb), a = lds128s(sq), b = lds128s(sq + 16);
     raw[0] = h.x; raw[1] = h.y; raw[2] = h.z; raw[3] = h.w;
     raw[4] = a.x; raw[5] = a.y; raw[6] = a.z; raw[7] = a.w; raw[8] = b.x; raw[9] = b.y; raw[10] = b.z; raw[11] = b.w;
   }
@@ -229,9 +247,9 @@ template <typename ab_t> struct Decoder<T_Q4_1, ab_t> {
   static constexpr int CORR_OFF = 2;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 5;   // 20 bytes, 4-byte aligned
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
-    const uint32_t* b = reinterpret_cast<const uint32_t*>(row + (int64_t)u * 20);
+    const uint32_t sb = smem_u32(row + (int64_t)u * 20);
 #pragma unroll
-    for (int i = 0; i < 5; ++i) raw[i] = b[i];
+    for (int i = 0; i < 5; ++i) raw[i] = lds32(sb + 4u * i);
   }
   static __device__ __forceinline__ void decode(const uint8_t*, int, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
     const uint32_t du = raw[0] & 0xFFFFu;
@@ -289,8 +307,8 @@ template <typename ab_t> struct Decoder<T_Q5_1, ab_t> {
   static constexpr int CORR_OFF = 2;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
   static constexpr int RW = 6;
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
-    const uint2* b = reinterpret_cast<const uint2*>(row + (int64_t)u * 24);
-    const uint2 a0 = b[0], a1 = b[1], a2 = b[2];
+    const uint32_t sb = smem_u32(row + (int64_t)u * 24);
+    const uint2 a0 = lds64(sb), a1 = lds64(sb + 8), a2 = lds64(sb + 16);
     raw[0] = a0.x; raw[1] = a0.y; raw[2] = a1.x; raw[3] = a1.y; raw[4] = a2.x; raw[5] = a2.y;
   }
   static __device__ __forceinline__ void decode(const uint8_t*, int, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
@@ -323,10 +341,8 @@ template <typename ab_t> struct Decoder<T_Q5_K, ab_t> {
   static constexpr int RW = 20;  // header (16) + 32 bytes of nibbles + 32 bytes of high bits
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 176;
-    const uint4 h = *reinterpret_cast<const uint4*>(blk);
-    const uint4* qp = reinterpret_cast<const uint4*>(blk + 48 + 32 * ((u >> 1) & 3));
-    const uint4* hp = reinterpret_cast<const uint4*>(blk + 16);
-    const uint4 a = qp[0], b = qp[1], c = hp[0], e = hp[1];
+    const uint32_t sb = smem_u32(blk), sq = sb + 48 + 32 * ((u >> 1) & 3);
+    const uint4 h = lds128s(sb), a = lds128s(sq), b = lds128s(sq + 16), c = lds128s(sb + 16), e = lds128s(sb + 32);
     raw[0] = h.x; raw[1] = h.y; raw[2] = h.z; raw[3] = h.w;
     raw[4] = a.x; raw[5] = a.y; raw[6] = a.z; raw[7] = a.w; raw[8] = b.x; raw[9] = b.y; raw[10] = b.z; raw[11] = b.w;
     raw[12] = c.x; raw[13] = c.y; raw[14] = c.z; raw[15] = c.w; raw[16] = e.x; raw[17] = e.y; raw[18] = e.z; raw[19] = e.w;
@@ -421,9 +437,8 @@ template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
   static constexpr int RW = 6;   // header (8 bytes) + 16 index bytes, 8-byte aligned
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 136;
-    const uint2 h = *reinterpret_cast<const uint2*>(blk);
-    const uint2* qp = reinterpret_cast<const uint2*>(blk + 8 + 16 * (u & 7));
-    const uint2 a = qp[0], b = qp[1];
+    const uint32_t sb = smem_u32(blk);
+    const uint2 h = lds64(sb), a = lds64(sb + 8 + 16 * (u & 7)), b = lds64(sb + 16 + 16 * (u & 7));
     raw[0] = h.x; raw[1] = h.y; raw[2] = a.x; raw[3] = a.y; raw[4] = b.x; raw[5] = b.y;
   }
   static __device__ __forceinline__ void decode(const uint8_t*, int u, const uint32_t (&raw)[RW], const DecodeCtx& cx, uint32_t (&out)[16]) {
@@ -434,10 +449,10 @@ template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // bytes 4i..4i+3: values 4i.. (low nibbles) and 16+4i.. (high)
       const uint32_t w = raw[2 + i];
-      out[2 * i] = pack2<ab_t>(dl * (float)cx.kv[w & 0xF], dl * (float)cx.kv[(w >> 8) & 0xF]);
-      out[2 * i + 1] = pack2<ab_t>(dl * (float)cx.kv[(w >> 16) & 0xF], dl * (float)cx.kv[(w >> 24) & 0xF]);
-      out[8 + 2 * i] = pack2<ab_t>(dl * (float)cx.kv[(w >> 4) & 0xF], dl * (float)cx.kv[(w >> 12) & 0xF]);
-      out[8 + 2 * i + 1] = pack2<ab_t>(dl * (float)cx.kv[(w >> 20) & 0xF], dl * (float)cx.kv[(w >> 28) & 0xF]);
+      out[2 * i] = pack2<ab_t>(dl * cx.level(w & 0xF), dl * cx.level((w >> 8) & 0xF));
+      out[2 * i + 1] = pack2<ab_t>(dl * cx.level((w >> 16) & 0xF), dl * cx.level((w >> 24) & 0xF));
+      out[8 + 2 * i] = pack2<ab_t>(dl * cx.level((w >> 4) & 0xF), dl * cx.level((w >> 12) & 0xF));
+      out[8 + 2 * i + 1] = pack2<ab_t>(dl * cx.level((w >> 20) & 0xF), dl * cx.level((w >> 28) & 0xF));
     }
   }
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
@@ -459,8 +474,8 @@ template <typename ab_t> struct Decoder<T_IQ4_NL, ab_t> {
       const int h = 1 + i;
       const uint32_t wv = word_at(raw, h >> 1, sh);
       const uint32_t t = (h & 1) ? (wv >> 16) : (wv & 0xFFFFu);
-      out[i] = pack2<ab_t>(d * (float)cx.kv[t & 0xF], d * (float)cx.kv[(t >> 8) & 0xF]);
-      out[8 + i] = pack2<ab_t>(d * (float)cx.kv[(t >> 4) & 0xF], d * (float)cx.kv[(t >> 12) & 0xF]);
+      out[i] = pack2<ab_t>(d * cx.level(t & 0xF), d * cx.level((t >> 8) & 0xF));
+      out[8 + i] = pack2<ab_t>(d * cx.level((t >> 4) & 0xF), d * cx.level((t >> 12) & 0xF));
     }
   }
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
@@ -488,8 +503,8 @@ template <typename ab_t> struct Decoder<T_IQ2_XXS, ab_t> {
     const uint32_t r0 = pack2<ab_t>(d * 8.f, d * 25.f), r1 = pack2<ab_t>(d * 43.f, 0.f);
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
-      const uint2 sel = cx.sel[(idx >> (8 * il)) & 0xFF];
-      const uint4 sg = cx.sgn[(aux >> (7 * il)) & 127];
+      const uint2 sel = cx.sel_at((idx >> (8 * il)) & 0xFF);
+      const uint4 sg = cx.sgn_at((aux >> (7 * il)) & 127);
       out[4 * il + 0] = __byte_perm(r0, r1, sel.x) ^ sg.x;
       out[4 * il + 1] = __byte_perm(r0, r1, sel.x >> 16) ^ sg.y;
       out[4 * il + 2] = __byte_perm(r0, r1, sel.y) ^ sg.z;
@@ -520,7 +535,7 @@ template <int TYPE, typename ab_t> struct Stage64 {
   static constexpr int PERM = 0;
 };
 
-__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return lds128s(smem_u32(p)); }
 __device__ __forceinline__ __half2 h2const(float v) { return __floats2half2_rn(v, v); }
 
 // ---- Q4_K: chunk = one 144-byte super-block; stage SC = sub-blocks 2SC (low nibbles) and 2SC+1 ----
