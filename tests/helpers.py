@@ -12,7 +12,7 @@ TYPES = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14, "IQ2_XXS": 16, "IQ4_XS": 
          "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q5_K": 13, "IQ4_NL": 20,
          "IQ2_XS": 17, "IQ3_XXS": 18, "IQ1_S": 19, "IQ3_S": 21, "IQ2_S": 22, "IQ1_M": 29, "Q2_K": 10, "Q3_K": 11}
 # ... of which the q8_1 tensor-core GEMM serves these (the others take the dequantize-matmul route)
-MMQ_TYPES = {k: TYPES[k] for k in ("Q4_0", "Q8_0", "Q4_K", "Q6_K", "Q4_1", "Q5_0", "Q5_1", "Q5_K")}
+MMQ_TYPES = {k: TYPES[k] for k in ("Q4_0", "Q8_0", "Q4_K", "Q6_K", "Q4_1", "Q5_0", "Q5_1", "Q5_K", "Q2_K", "Q3_K")}
 # types served by the standalone dequantize only
 DEQUANT_ONLY_TYPES: dict = {}   # (none left: every type of the reference's dispatch has a GEMV here)
 # the tolerance the task states for matmul outputs against the reference's own kernels

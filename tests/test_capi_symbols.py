@@ -37,7 +37,7 @@ def test_geometry_and_error_codes(native_libs):
     assert lib.gguf_b200_type_size(9) == 0 and lib.gguf_b200_block_size(9) == 0
     assert lib.gguf_b200_q8_1_row_bytes(1024) == 1024 // 32 * 36
     assert lib.gguf_b200_q8_1_row_bytes(800) == 1024 // 32 * 36
-    assert lib.gguf_b200_moe_block_size(2) == 64 and lib.gguf_b200_moe_block_size(16) == 0
+    assert lib.gguf_b200_moe_block_size(2) == 64 and lib.gguf_b200_moe_block_size(11) == 64 and lib.gguf_b200_moe_block_size(16) == 0
     assert lib.gguf_b200_workspace_bytes(capi.OP_GEMV, 12, 2, 0, 4096) == 2 * 4096 + 2 * 128 * 8
     assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 8, 4, 0, 1024) == 4 * 1024 * 2
     assert lib.gguf_b200_workspace_bytes(capi.OP_MMQ, 12, 4, 0, 1024) == 4 * (1024 + 64) * 2
@@ -45,7 +45,7 @@ def test_geometry_and_error_codes(native_libs):
     null = ctypes.c_void_p(0)
     p = ctypes.c_void_p(4096)
     assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 9, 1, 1, 8, 256, null) == -1   # type (Q8_1 is not a weight type)
-    assert lib.gguf_b200_mul_mat_a8(p, p, p, p, 1 << 20, 11, 1, 1, 8, 256, null) == -1       # Q3_K has no tiled kernel here
+    assert lib.gguf_b200_mul_mat_a8(p, p, p, p, 1 << 20, 21, 1, 1, 8, 256, null) == -1       # IQ3_S has no tiled kernel
     assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 12, 7, 1, 8, 256, null) == -2  # dtype
     assert lib.gguf_b200_mul_mat_vec_a8(p, p, p, p, 1 << 20, 12, 1, 1, 8, 100, null) == -3  # K % 256
     assert lib.gguf_b200_mul_mat_vec_a8(null, p, p, p, 1 << 20, 12, 1, 1, 8, 256, null) == -4

@@ -310,7 +310,7 @@ def moe_case(t, E, N, K, T, top_k, seed):
     return w, x, tw, ids
 
 
-@pytest.mark.parametrize("name", ["Q4_0", "Q4_K", "Q8_0"])
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_K", "Q8_0", "Q2_K", "Q3_K"])
 def test_moe_a8_parity(ref, name):
     t = TYPES[name]
     E, N, K, T, top_k = 8, 192, 1024, 70, 2

@@ -46,7 +46,8 @@ int64_t mmq_ldb(int type, int64_t K) {
 }
 
 static bool is_mmq_type(int t) {
-  return t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K || t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1 || t == T_Q5_K;
+  return t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K || t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1 || t == T_Q5_K || t == T_Q2_K ||
+         t == T_Q3_K;
 }
 static bool dtype_ok(int d) { return d == DT_F32 || d == DT_F16 || d == DT_BF16; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -919,6 +919,8 @@ int launch_mmq(const MmqArgs& a, cudaStream_t stream) {
     case T_Q5_0: return bf ? E_BAD_DTYPE : launch_out<T_Q5_0, __half>(a, p, stream);
     case T_Q5_1: return bf ? E_BAD_DTYPE : launch_out<T_Q5_1, __half>(a, p, stream);
     case T_Q5_K: return bf ? E_BAD_DTYPE : launch_out<T_Q5_K, __half>(a, p, stream);
+    case T_Q2_K: return bf ? E_BAD_DTYPE : launch_out<T_Q2_K, __half>(a, p, stream);
+    case T_Q3_K: return bf ? E_BAD_DTYPE : launch_out<T_Q3_K, __half>(a, p, stream);
     // the dequantize-then-matmul route computes and returns in the activations' own 16-bit type
     case T_IQ2_XXS:
       if (a.out_dtype != a.b_dtype) return E_BAD_DTYPE;

@@ -431,6 +431,95 @@ template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
 };
 
+// ---- Q2_K: value = fp32 (d*sc)*q - dmin*m rounded once (the dequantized weight itself: the 16-value
+// sub-blocks are finer than the 32-value sums of q8_1, so the min term cannot ride in a correction
+// column); unit = 32-value group g = u&7 = 4n + j: bytes qs[32n..32n+31] >> 2j, scales 2g, 2g+1.
+// A sub-block has only four possible values; they are rounded once each, parked in two registers
+// as four halves, and every pair of weights is one byte-permute whose selector is the pair's two
+// 2-bit codes times 0x22 plus 0x1010 (code c picks bytes 2c, 2c+1).
+template <typename ab_t> struct Decoder<T_Q2_K, ab_t> {
+  static constexpr int CORR_OFF = -1;
+  static constexpr int RW = 10;   // 32 code bytes, the word holding the two scale bytes, (d, dmin): all 4-byte aligned
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint32_t sb = smem_u32(row + (int64_t)(u >> 3) * 84);
+    const int g = u & 7;
+    const uint32_t sq = sb + 16 + 32 * (g >> 2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) raw[i] = lds32(sq + 4u * i);
+    raw[8] = lds32(sb + ((2 * g) & ~3));
+    raw[9] = lds32(sb + 80);
+  }
+  static __device__ __forceinline__ void decode(const uint8_t*, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    const int g = u & 7, sh = 2 * (g & 3);
+    const float d = __half2float(__ushort_as_half((unsigned short)(raw[9] & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(raw[9] >> 16)));
+    const uint32_t sc2 = raw[8] >> (16 * (g & 1));
+#pragma unroll
+    for (int hb = 0; hb < 2; ++hb) {   // the two 16-value sub-blocks of the unit
+      const uint32_t sc = (sc2 >> (8 * hb)) & 0xFFu;
+      const float dl = d * (float)(sc & 0xFu), ml = dmin * (float)(sc >> 4);
+      const uint32_t r0 = pack2<ab_t>(-ml, dl - ml), r1 = pack2<ab_t>(fmaf(2.f, dl, -ml), fmaf(3.f, dl, -ml));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {    // word 4hb + i: values 16hb + 4i .. + 3
+        const uint32_t x = (raw[4 * hb + i] >> sh) & 0x03030303u;
+        out[8 * hb + 2 * i] = __byte_perm(r0, r1, x * 0x22u + 0x1010u);
+        out[8 * hb + 2 * i + 1] = __byte_perm(r0, r1, (x >> 16) * 0x22u + 0x1010u);
+      }
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
+// ---- Q3_K: value = d * ((sc6 - 32) * (c - 4)), c = 2 low bits | hmask bit << 2; unit = 32-value group
+// g = u&7 = 4n + j: bytes qs[32n..32n+31] >> 2j, bit g of hmask[0..31], scales 2g, 2g+1.  Blocks are
+// 110 bytes, so everything is read as covering words and realigned.  The code lands at bits 3-5 of
+// a byte (two rotates, two masks per four weights), one byte-permute per pair turns it into the
+// half 128 + c (0x5800 | c << 3), one HFMA2 gives (c - 4) * sc exactly (|.| <= 128; the addend
+// -132 * sc has 11 significant bits) and the multiplication by d rounds once.
+template <typename ab_t> struct Decoder<T_Q3_K, ab_t> {
+  static constexpr int CORR_OFF = -1;
+  static constexpr int RW = 26;   // [0..9] code words, [10..19] hmask words, [20..24] the 12 scale bytes, [25] d
+  static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 110;
+    const int g = u & 7;
+    ldg_cover<9>(blk + 32 + 32 * (g >> 2), 32, raw);
+    raw[9] = 0;
+    ldg_cover<9>(blk, 32, raw + 10);
+    raw[19] = 0;
+    ldg_cover<4>(blk + 96, 12, raw + 20);
+    raw[24] = 0;
+    ldg_cover<1>(blk + 108, 2, raw + 25);
+  }
+  static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
+    static_assert(sizeof(ab_t) == 2 && std::is_same<ab_t, __half>::value, "Q3_K is decoded with fp16 arithmetic");
+    const uint8_t* blk = row + (int64_t)(u >> 3) * 110;
+    const int g = u & 7, k = g >> 1;
+    const uint32_t sh_q = shift_of(blk + 32 + 32 * (g >> 2)), sh_h = shift_of(blk), sh_s = shift_of(blk + 96);
+    // 6-bit scales 2g, 2g+1: low nibbles from byte 2g (mod 8) of the first eight scale bytes, shifted by
+    // four for g >= 4; the two high bits from byte 2g mod 4 of the last four, bit pair g / 2
+    const uint32_t a01 = word_at(raw + 20, k & 1, sh_s), tmp = word_at(raw + 20, 2, sh_s);
+    const uint32_t us4 = ((a01 >> (4 * (k >> 1))) & 0x0F0F0F0Fu) | (((tmp >> (2 * k)) & 0x03030303u) << 4);
+    const uint32_t us2 = us4 >> (16 * (g & 1));
+    const uint32_t du = (raw[25] >> shift_of(blk + 108)) & 0xFFFFu;
+    const __half2 d2 = u32_as_h2(du | (du << 16));
+    const uint32_t rot_q = (uint32_t)(2 * (g & 3) - 3) & 31u, rot_h = (uint32_t)(g - 5) & 31u;
+#pragma unroll
+    for (int hb = 0; hb < 2; ++hb) {
+      const __half s = __int2half_rn((int)((us2 >> (8 * hb)) & 0xFFu) - 32);
+      const __half2 s2 = __half2half2(s), c2 = __half2half2(__hmul(s, __float2half_rn(-132.f)));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t wq = word_at(raw, 4 * hb + i, sh_q), wh = word_at(raw + 10, 4 * hb + i, sh_h);
+        const uint32_t c = (__funnelshift_r(wq, wq, rot_q) & 0x18181818u) | (__funnelshift_r(wh, wh, rot_h) & 0x20202020u);
+        const __half2 p0 = u32_as_h2(__byte_perm(c, 0x58585858u, 0x4140)), p1 = u32_as_h2(__byte_perm(c, 0x58585858u, 0x4342));
+        out[8 * hb + 2 * i] = h2_as_u32(hmul2_rn(__hfma2(p0, s2, c2), d2));
+        out[8 * hb + 2 * i + 1] = h2_as_u32(hmul2_rn(__hfma2(p1, s2, c2), d2));
+      }
+    }
+  }
+  static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
+};
+
 // ---- IQ4_XS: fp32 d*(ls-32)*level rounded once to ab_t; unit = 32-value group ib = u&7 -----------
 template <typename ab_t> struct Decoder<T_IQ4_XS, ab_t> {
   static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)

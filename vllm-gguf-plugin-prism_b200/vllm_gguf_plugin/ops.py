@@ -8,10 +8,10 @@ same names, argument order and meaning -- on top of the ``_C_gguf`` torch librar
 Differences from the reference, all deliberate:
 * no Triton backend and no CPU fallback: if the extension is missing, import fails loudly;
   ``VLLM_GGUF_USE_CUDA`` is accepted for compatibility but selects nothing;
-* supported block types are Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ2_XXS, IQ4_NL, IQ4_XS
-  and, for ggml_dequantize, ggml_mul_mat_vec_a8 and ggml_moe_a8_vec, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M
-  and Q2_K, Q3_K -- with them every type of the reference's dequantize dispatch (dequantize.cuh:527-571) and of its
-  GEMV dispatch is covered; the tensor-core entry points take fewer types (see each); any other type raises
+* supported block types are Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K (every type of the reference's
+  tiled kernels, ggml_mul_mat_a8 / ggml_moe_a8), IQ2_XXS, IQ4_NL, IQ4_XS and, for ggml_dequantize, ggml_mul_mat_vec_a8
+  and ggml_moe_a8_vec, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M -- with them every type of the reference's
+  dequantize dispatch (dequantize.cuh:527-571) and of its GEMV dispatch is covered; any other type raises
   ``NotImplementedError`` (the reference silently returns zeros for an unknown type in its
   matmul switch, gguf_kernel.cu:236-289);
 * ``ggml_moe_get_block_size`` returns this library's token-block size (64, tensor-core tile)
@@ -83,15 +83,15 @@ QUANT_SIZES = {
     21: (256, 110),   # IQ3_S
     19: (256, 50),    # IQ1_S
     29: (256, 56),    # IQ1_M
-    GGML_TYPE_Q2_K: (256, 84),    # (decode GEMV here; the reference's tiled kernel for these two is replaced by
-    GGML_TYPE_Q3_K: (256, 110),   #  dequantize + matmul, see quantization/linear.py)
+    GGML_TYPE_Q2_K: (256, 84),
+    GGML_TYPE_Q3_K: (256, 110),
 }
 _CUDA_GEMV_QUANT_TYPES = frozenset(QUANT_SIZES)
 # types that only ggml_dequantize serves (none at present: every type of the reference's dispatch has a GEMV too)
 DEQUANT_ONLY_SIZES: dict = {}
 _CUDA_DEQUANT_TYPES = _CUDA_GEMV_QUANT_TYPES | frozenset(DEQUANT_ONLY_SIZES)
 _CUDA_GEMM_QUANT_TYPES = frozenset({GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q5_0, GGML_TYPE_Q5_1, GGML_TYPE_Q8_0,
-                                    GGML_TYPE_Q4_K, GGML_TYPE_Q5_K, GGML_TYPE_Q6_K})
+                                    GGML_TYPE_Q2_K, GGML_TYPE_Q3_K, GGML_TYPE_Q4_K, GGML_TYPE_Q5_K, GGML_TYPE_Q6_K})
 _DEQUANT_MATMUL_TYPES = frozenset({GGML_TYPE_IQ2_XXS, GGML_TYPE_IQ4_NL, GGML_TYPE_IQ4_XS})
 
 

@@ -67,9 +67,7 @@ def _fused_mul_mat_gguf(x: torch.Tensor, weight: torch.Tensor, weight_type: int)
     elif weight_type in MMQ_QUANT_TYPES and int(weight_type) in ops._CUDA_GEMM_QUANT_TYPES:
         y = ops.ggml_mul_mat_a8(weight, x, weight_type, weight.shape[0])
     elif weight_type in DEQUANT_TYPES:
-        # (also Q2_K / Q3_K above the GEMV threshold: they have no tiled kernel here, so they take the
-        #  reference's route for IQ types -- dequantize, then a dense product -- which differs from the
-        #  reference's tiled kernel by its q8_1 activation-quantization noise, about 5e-3 relative)
+        # the reference's route for the code-book types: dequantize, then a dense product (fused for three of them)
         if x.dtype in (torch.float16, torch.bfloat16) and int(weight_type) in ops._DEQUANT_MATMUL_TYPES:
             y = ops.ggml_dequant_matmul(weight, x, weight_type, weight.shape[0])
         else:  # fp32 activations: the reference's two steps

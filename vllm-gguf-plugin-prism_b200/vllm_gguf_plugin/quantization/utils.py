@@ -23,11 +23,10 @@ MMQ_QUANT_TYPES = STANDARD_QUANT_TYPES | KQUANT_TYPES
 
 # block geometry of the types this build has kernels for: type -> (values, bytes) per block
 SUPPORTED_QUANT_SIZES = {Q4_0: (32, 18), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q8_0: (32, 34),
-                         Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210),
+                         Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210),
                          IQ2_XXS: (256, 66), IQ4_NL: (32, 18), IQ4_XS: (256, 136),
                          IQ2_XS: (256, 74), IQ2_S: (256, 82), IQ3_XXS: (256, 98), IQ3_S: (256, 110), IQ1_S: (256, 50),
-                         IQ1_M: (256, 56),   # (decode GEMV; more tokens: dequantize + matmul, as in the reference)
-                         Q2_K: (256, 84), Q3_K: (256, 110)}   # (decode GEMV; more tokens: dequantize + matmul)
+                         IQ1_M: (256, 56)}   # (these six: decode GEMV; more tokens: dequantize + matmul, as in the reference)
 
 
 def quant_sizes(weight_type: int) -> tuple[int, int]:
