@@ -61,7 +61,7 @@ __host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two) { r
 // only has to cover the TMA latency.  With 256-token tiles the two-group kernels keep a 3-deep
 // A ring so that two padded raw chunks of the widest rows (34 KB each) still fit; the
 // two-CTA-per-SM kernels have half the shared memory each and run 3-deep rings as well.
-__host__ __device__ constexpr int mmq_b_stages(bool two, int tn) { return (tn > 128 || two) ? 3 : 4; }
+__host__ __device__ constexpr int mmq_b_stages(bool fast, bool two, int tn) { return (tn > 128 || two) ? 3 : 4; }
 __host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) {
   return (two || (mmq_groups(type, fast, two) <= 3 && tn > 128)) ? 3 : 4;
 }
@@ -152,7 +152,9 @@ struct MmqParams {
   int* status;
   int n_experts;          // MoE: expert ids outside [0, n_experts) are skipped
   const float* row_scale; // MoE: routing weight of every output row (null: none)
-  int raw_tma;            // 1: raw weight chunks arrive as 2-D TMA boxes (wmap), 0: as one 1-D bulk copy per row and chunk
+  int raw_tma;            // 1: raw weight chunks arrive as dense 2-D TMA boxes (wmap); 2: as one padded box per alignment class
+                          // of rows (see the loader); 0: as one 1-D bulk copy per row and chunk
+  int raw_class_log2;     // raw_tma == 2: log2 of the number of alignment classes
   int raw_stages;         // depth of the raw ring
   int64_t w_row0;         // first row of this matrix in wmap (MoE: added to expert * N)
   int y_tma;              // 1: the output tile leaves through shared memory and one TMA store (ymap)
@@ -194,12 +196,12 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
-  constexpr int SA = mmq_a_stages(TYPE, FAST, TWO, TN), SB = mmq_b_stages(TWO, TN);
+  constexpr int SA = mmq_a_stages(TYPE, FAST, TWO, TN), SB = mmq_b_stages(FAST, TWO, TN);
   constexpr int NG = mmq_groups(TYPE, FAST, TWO);
   static_assert(NG <= SA, "a producer group may not lap the A ring");
   constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
   // raw ring geometry: dense TMA boxes, or padded slots that each take one row's bulk copy
-  const bool tma = FAST || p.raw_tma;
+  const bool tma = FAST || p.raw_tma == 1;
   const int kc = tma ? TmaGeom<TYPE>::KC_T : RawGeom<TYPE>::KC;
   const int rbc = kc / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;
   const int slot = tma ? rbc : RawGeom<TYPE>::SLOT;
@@ -304,6 +306,9 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
     };
     int rs = 0;                // raw ring slot and phase (TMA staging)
     uint32_t rph = 0;
+    // slot of this thread's row inside a raw stage: the row itself, or (class boxes) class r mod P, then r / P
+    const int cl2 = p.raw_tma == 2 ? p.raw_class_log2 : 0;
+    const int rslot = ((r & ((1 << cl2) - 1)) << (7 - cl2)) | (r >> cl2);
     auto run = [&](auto G) {
       constexpr int GI = decltype(G)::value;
       for (int c = 0; c < nchunks; ++c) {
@@ -324,7 +329,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
         } else {
           // row pointer such that (pointer + byte offset in the row) lands in this thread's slot of chunk c
           const int64_t beg = n * p.row_bytes + (int64_t)(c + c_begin) * rbc;
-          const uint8_t* srow = sRaw + (size_t)rs * RAW_STAGE + (size_t)r * slot + (tma ? 0 : (beg & 15)) - (int64_t)(c + c_begin) * rbc;
+          const uint8_t* srow = sRaw + (size_t)rs * RAW_STAGE + (size_t)rslot * slot + (tma ? 0 : (beg & 15)) - (int64_t)(c + c_begin) * rbc;
           for (int i = c * SPC + GI; i < (c + 1) * SPC && i < nmain && ok; i += NG) {
             uint32_t v[32];
 #pragma unroll
@@ -514,6 +519,32 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq
           if (!wait_or_note(&raw_empty[st], sph ^ 1u, 5, c)) { ok = false; break; }
           mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
           tma_load_2d(sRaw + (size_t)st * RAW_STAGE, &wmap, (c + c_begin) * (rbc / 4), (int)wrow, &raw_full[st]);
+          if (++st == p.raw_stages) { st = 0; sph ^= 1u; }
+        }
+      }
+    } else if (p.raw_tma == 2) {
+      // Rows or chunk starts that are not 16-byte aligned, P = 16 / gcd(16, row bytes) alignment classes:
+      // the tensor map views the matrix as rows of P weight rows each (P * row bytes IS a multiple of 16),
+      // so weight row P*j + k is the piece at byte k * row_bytes of map row j, and rows of one class k
+      // share the remainder of their chunk starts modulo 16.  One box per class and chunk -- 128 / P map
+      // rows x one padded slot, from the chunk start rounded down to 16 bytes -- replaces 128 / P bulk
+      // copies (the bulk copies cost about 90 clocks each on the SM's copy engine, which bounded every
+      // kernel that used them); the decoders index from the remainder, exactly as below.  Bytes beyond the
+      // end of a map row are zero-filled by the copy engine and never fetched.
+      if (lane == 0) {
+        int64_t wrow = p.w_row0 + n0;
+        if (MOE) wrow += (int64_t)p.expert_ids[blockIdx.y] * p.N;
+        const int cl2 = p.raw_class_log2, rows_per = MMQ_ROWS >> cl2;
+        int st = 0;
+        uint32_t sph = 0;
+        for (int c = 0; c < nchunks; ++c) {
+          if (!wait_or_note(&raw_empty[st], sph ^ 1u, 5, c)) { ok = false; break; }
+          mbar_expect_tx(&raw_full[st], (uint32_t)RAW_STAGE);
+          for (int k = 0; k < (1 << cl2); ++k) {
+            const int64_t off = (int64_t)k * p.row_bytes + (int64_t)(c + c_begin) * rbc;
+            tma_load_2d(sRaw + (size_t)st * RAW_STAGE + (size_t)k * rows_per * slot, &wmap, (int)((off & ~int64_t(15)) >> 2), (int)(wrow >> cl2),
+                        &raw_full[st]);
+          }
           if (++st == p.raw_stages) { st = 0; sph ^= 1u; }
         }
       }
@@ -746,13 +777,34 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return E_CUDA;
   }
-  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TWO, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(TWO, TN) * TN * MMQ_BK * 2 + mmq_aux_bytes(TYPE);
+  // alignment-class boxes for everything the dense boxes cannot take (see the loader)
+  int class_log2 = -1;
+  if (!raw_tma) {
+    static const char* no_cls = getenv("GGUF_B200_MMQ_NO_CLASS_TMA");
+    int cl = 0;
+    while (((pp.row_bytes << cl) & 15) != 0 && cl < 4) ++cl;
+    const int64_t map_rows = MOE ? a.N * pp.n_experts : a.N;
+    const bool ok = !(no_cls && no_cls[0] == '1') && cl <= 3 && a.N % (1 << cl) == 0 && RawGeom<TYPE>::SLOT <= 1024 &&
+                    (!MOE || (a.expert_stride_bytes == a.N * pp.row_bytes && a.N % MMQ_ROWS == 0));
+    if (ok) {
+      const cuuint32_t estr[2] = {1, 1};
+      const cuuint64_t wd[2] = {(cuuint64_t)((pp.row_bytes << cl) / 4), (cuuint64_t)(map_rows >> cl)};
+      const cuuint64_t ws[1] = {(cuuint64_t)(pp.row_bytes << cl)};
+      const cuuint32_t wb[2] = {(cuuint32_t)(RawGeom<TYPE>::SLOT / 4), (cuuint32_t)(MMQ_ROWS >> cl)};
+      if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.w), wd, ws, wb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return E_CUDA;
+      class_log2 = cl;
+    }
+  }
+  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TWO, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(FAST, TWO, TN) * TN * MMQ_BK * 2 + mmq_aux_bytes(TYPE);
   const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
   const size_t budget = (TWO ? 113 : 226) * 1024;   // two CTAs share the SM's 228 KB (1 KB each is reserved)
   int rs = (int)((budget - ab_bytes) / raw_stage);
   if (rs > MMQ_MAX_RAW) rs = MMQ_MAX_RAW;
   if (rs < 2) rs = 2;
-  pp.raw_tma = raw_tma ? 1 : 0;
+  pp.raw_tma = raw_tma ? 1 : (class_log2 >= 0 ? 2 : 0);
+  pp.raw_class_log2 = class_log2 >= 0 ? class_log2 : 0;
   pp.raw_stages = rs;
   pp.w_row0 = 0;
   const size_t smem = ab_bytes + (size_t)rs * raw_stage;
