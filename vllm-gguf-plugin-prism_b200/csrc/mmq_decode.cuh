@@ -417,15 +417,18 @@ template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
     const __half2 off = __floats2half2_rn(1056.f, 1056.f);  // 1024 + 32
     const __half2 s_lo = __half2half2(__int2half_rn((int)(int8_t)(sc2 & 0xFF)));
     const __half2 s_hi = __half2half2(__int2half_rn((int)(int8_t)(sc2 >> 8)));
+    // the 6-bit code of each of a word's four values as one byte: low nibble from ql, bits 4-5 from qh
+    // rotated into place; one byte-permute per pair then builds the halves 1024 + code (0x6400 | code)
+    const uint32_t sl = 4 * (q >> 1), rot_h = (uint32_t)(2 * q - 4) & 31u;
 #pragma unroll
     for (int wi = 0; wi < 8; ++wi) {             // word wi: values 4wi..4wi+3 of the unit
-      const uint32_t l = word_at(raw, wi, sh_l) >> (4 * (q >> 1));
-      const uint32_t h = word_at(raw + 10, wi, sh_h) >> (2 * q);
+      const uint32_t l = word_at(raw, wi, sh_l) >> sl;
+      const uint32_t h = word_at(raw + 10, wi, sh_h);
+      const uint32_t c = (l & 0x0F0F0F0Fu) | (__funnelshift_r(h, h, rot_h) & 0x30303030u);
       const __half2 s2 = wi < 4 ? s_lo : s_hi;
-      const uint32_t c0 = (l & 0xF) | ((h & 3) << 4), c1 = ((l >> 8) & 0xF) | (((h >> 8) & 3) << 4);
-      const uint32_t c2 = ((l >> 16) & 0xF) | (((h >> 16) & 3) << 4), c3 = ((l >> 24) & 0xF) | (((h >> 24) & 3) << 4);
-      out[2 * wi] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(ints_plus_1024(c0, c1), off))));
-      out[2 * wi + 1] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(ints_plus_1024(c2, c3), off))));
+      const __half2 p0 = u32_as_h2(__byte_perm(c, 0x64646464u, 0x4140)), p1 = u32_as_h2(__byte_perm(c, 0x64646464u, 0x4342));
+      out[2 * wi] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(p0, off))));
+      out[2 * wi + 1] = h2_as_u32(hmul2_rn(d2, hmul2_rn(s2, __hsub2(p1, off))));
     }
   }
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
