@@ -53,8 +53,12 @@ constexpr int MMQ_BK = 64;
 // limit, so two independent pipelines per SM raise the rate -- when the grid has enough CTAs to
 // put two on every SM (MoE, many row tiles); with fewer CTAs than SMs the one-CTA form keeps
 // all 16 decode warps on the tile (`two` is chosen per launch).
-__host__ __device__ constexpr int mmq_groups(int type, bool fast, bool two) { return two ? 2 : ((fast || type == T_IQ2_XXS) ? 4 : 2); }
-__host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two) { return (4 * mmq_groups(type, fast, two) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
+// (Q8_0 with 256-token tiles: its 34 KB raw chunks fit beside three 32 KB activation stages only with a 3-deep A
+// ring, hence two groups there.)
+__host__ __device__ constexpr int mmq_groups(int type, bool fast, bool two, int tn) {
+  return two ? 2 : (fast ? ((type == T_Q8_0 && tn > 128) ? 2 : 4) : (type == T_IQ2_XXS ? 4 : 2));
+}
+__host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two, int tn) { return (4 * mmq_groups(type, fast, two, tn) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
 // Ring depths.  The A ring (16 KB slots) is never shallower than the number of producer groups:
 // a group that runs ahead may be at most one use of a slot ahead of the MMA warp, or the
 // one-bit phase parity of the slot's barrier would alias.  The B ring (TN * 128 bytes per slot)
@@ -63,7 +67,7 @@ __host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two) { r
 // two-CTA-per-SM kernels have half the shared memory each and run 3-deep rings as well.
 __host__ __device__ constexpr int mmq_b_stages(bool fast, bool two, int tn) { return (tn > 128 || two) ? 3 : 4; }
 __host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) {
-  return (two || (mmq_groups(type, fast, two) <= 3 && tn > 128)) ? 3 : 4;
+  return (two || (mmq_groups(type, fast, two, tn) <= 3 && tn > 128)) ? 3 : 4;
 }
 constexpr int MMQ_MAX_RAW = 6;
 // shared memory between the operand rings and the raw ring: barriers, then the decoder's tables
@@ -191,13 +195,13 @@ __device__ __forceinline__ void tp_finish(unsigned* epoch, unsigned* const* flag
 }
 
 template <int TYPE, typename ab_t, typename out_t, int TN, bool MOE, bool FAST, bool TWO>
-__global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO), TWO ? 2 : 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
+__global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1) mmq_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap ymap, const MmqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
   constexpr int SA = mmq_a_stages(TYPE, FAST, TWO, TN), SB = mmq_b_stages(FAST, TWO, TN);
-  constexpr int NG = mmq_groups(TYPE, FAST, TWO);
+  constexpr int NG = mmq_groups(TYPE, FAST, TWO, TN);
   static_assert(NG <= SA, "a producer group may not lap the A ring");
   constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
   // raw ring geometry: dense TMA boxes, or padded slots that each take one row's bulk copy
@@ -857,7 +861,7 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
     configured[dev & 63] = smem;
   }
   dim3 grid((unsigned)((a.N + MMQ_ROWS - 1) / MMQ_ROWS), (unsigned)((b_rows + TN - 1) / TN), (unsigned)pp.ksplit);
-  kern<<<grid, mmq_threads(TYPE, FAST, TWO), smem, stream>>>(map, wmap, ymap, pp);
+  kern<<<grid, mmq_threads(TYPE, FAST, TWO, TN), smem, stream>>>(map, wmap, ymap, pp);
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   if (pp.ksplit > 1 && a.tp) {
     const int64_t n8 = a.M * a.N / 8;
