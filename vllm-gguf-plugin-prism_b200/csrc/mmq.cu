@@ -53,26 +53,32 @@ constexpr int MMQ_BK = 64;
 // limit, so two independent pipelines per SM raise the rate -- when the grid has enough CTAs to
 // put two on every SM (MoE, many row tiles); with fewer CTAs than SMs the one-CTA form keeps
 // all 16 decode warps on the tile (`two` is chosen per launch).
-// (Q8_0 with 256-token tiles: its 34 KB raw chunks fit beside three 32 KB activation stages only with a 3-deep A
-// ring, hence two groups there.)
 __host__ __device__ constexpr int mmq_groups(int type, bool fast, bool two, int tn) {
-  return two ? 2 : (fast ? ((type == T_Q8_0 && tn > 128) ? 2 : 4) : (type == T_IQ2_XXS ? 4 : 2));
+  return two ? 2 : ((fast || type == T_IQ2_XXS) ? 4 : 2);
 }
 __host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two, int tn) { return (4 * mmq_groups(type, fast, two, tn) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
-// Ring depths.  The A ring (16 KB slots) is never shallower than the number of producer groups:
-// a group that runs ahead may be at most one use of a slot ahead of the MMA warp, or the
-// one-bit phase parity of the slot's barrier would alias.  The B ring (TN * 128 bytes per slot)
-// only has to cover the TMA latency.  With 256-token tiles the two-group kernels keep a 3-deep
-// A ring so that two padded raw chunks of the widest rows (34 KB each) still fit; the
-// two-CTA-per-SM kernels have half the shared memory each and run 3-deep rings as well.
-__host__ __device__ constexpr int mmq_b_stages(bool fast, bool two, int tn) { return (tn > 128 || two) ? 3 : 4; }
-__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) {
-  return (two || (mmq_groups(type, fast, two, tn) <= 3 && tn > 128)) ? 3 : 4;
+// Ring depths.  The decoded weights (operand A) never touch shared memory: a producer thread writes
+// the 64 values of its row for one stage -- 32 registers of two fp16 each -- into 32 columns of its own
+// lane of tensor memory (tcgen05.st), and the MMA reads its A operand from there.  The A ring is four
+// such 32-column slots next to the accumulator's TN columns; it is never shallower than the number
+// of producer groups (a group that runs ahead may be at most one use of a slot ahead of the MMA warp,
+// or the one-bit phase parity of the slot's barrier would alias).  Shared memory then carries only
+// the activations (the B ring, TN * 128 bytes per slot, four slots: the finished tile is staged in
+// them, up to TN * 128 fp32 values) and the raw weight bytes.
+__host__ __device__ constexpr int mmq_b_stages(int type, bool fast, bool two, int tn) { return 4; }
+__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) { return 4; }
+constexpr int MMQ_A_COLS = 32;   // tensor-memory columns of one A slot: 64 fp16 values per lane
+__host__ __device__ constexpr uint32_t mmq_tmem_cols(int tn) {
+  return (tn < 32 ? 32 : tn) + 4 * MMQ_A_COLS <= 256 ? 256u : 512u;
+}
+// per-warp transposition scratch of the types whose correction value is one fp16 of the block (see the producers)
+constexpr int MMQ_CORR_ROW = 80;    // bytes per row: 32 fp16 + 16 (an odd number of 16-byte units: conflict-free row reads)
+template <int TYPE> __host__ __device__ constexpr int mmq_scratch_bytes(int groups) {
+  return Decoder<TYPE, __half>::CORR_OFF >= 0 ? groups * 4 * 32 * MMQ_CORR_ROW : 0;
 }
 constexpr int MMQ_MAX_RAW = 6;
 // shared memory between the operand rings and the raw ring: barriers, then the decoder's tables
 __host__ __device__ constexpr int mmq_aux_bytes(int type) { return type == T_IQ2_XXS ? 8192 : 4096; }
-constexpr int MMQ_A_STAGE = MMQ_ROWS * MMQ_BK * 2;  // 16 KB
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot_smem, uint32_t ncols) {
@@ -107,6 +113,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
+      : "memory");
+}
+// 32 registers -> 32 consecutive columns of this thread's lane (warp w owns lanes 32 * (w % 4) ...)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 8 columns (16 fp16 values per row, two per column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -200,7 +227,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
   // carve: the swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int B_STAGE = TN * MMQ_BK * 2;
-  constexpr int SA = mmq_a_stages(TYPE, FAST, TWO, TN), SB = mmq_b_stages(FAST, TWO, TN);
+  constexpr int SA = mmq_a_stages(TYPE, FAST, TWO, TN), SB = mmq_b_stages(TYPE, FAST, TWO, TN);
   constexpr int NG = mmq_groups(TYPE, FAST, TWO, TN);
   static_assert(NG <= SA, "a producer group may not lap the A ring");
   constexpr int MMQ_PRODUCER_WARPS = 4 * NG;
@@ -220,12 +247,12 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
   const int ncorr = (int)blockIdx.z == p.ksplit - 1 ? p.ncorr : 0;
   const int c_begin = i_begin / SPC;
   const int nchunks = (nmain + SPC - 1) / SPC;
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + SA * MMQ_A_STAGE;
+  uint8_t* sB = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB + SB * B_STAGE);
-  uint8_t* sRaw = sB + SB * B_STAGE + mmq_aux_bytes(TYPE);   // barriers and decoder tables sit in between
-  // One "full" and one "empty" barrier per A slot serve both operands of a stage, so the MMA
-  // thread polls and commits once per stage: full[i % SA] collects the warps of the group that
+  uint8_t* sScr = sB + SB * B_STAGE + mmq_aux_bytes(TYPE);   // barriers and decoder tables sit in between
+  uint8_t* sRaw = sScr + mmq_scratch_bytes<TYPE>(NG);
+  // One "full" and one "empty" barrier per A slot (tensor memory) serve both operands of a stage, so the
+  // MMA thread polls and commits once per stage: full[i % SA] collects the warps of the group that
   // decoded stage i plus the B loader's expect-tx arrival and bytes; empty[i % SA] is the
   // tcgen05.commit after stage i, which frees A slot i % SA and B slot i % SB alike.
   uint64_t* full_a = bars;                    // [8]
@@ -233,6 +260,11 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
   uint64_t* accum = bars + 32;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 33);
   volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);   // set by any thread whose wait ran out
+  // A B ring deeper than the A ring gets "full" barriers of its own (a B box for stage i may be under way
+  // while A slot i % SA still serves stage i - SA, so it cannot count on that slot's barrier).
+  constexpr bool SPLIT_B = SB > SA;
+  uint64_t* full_b = bars + 50;               // [6], used when SPLIT_B
+  static_assert(SB <= 6, "room for the B barriers");
   uint64_t* raw_full = bars + 34;             // [MMQ_MAX_RAW]
   uint64_t* raw_empty = bars + 34 + MMQ_MAX_RAW;
   int8_t* s_kv = reinterpret_cast<int8_t*>(bars + 48);                 // 16 bytes
@@ -249,14 +281,17 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     if (t0 >= (int64_t)p.n_post_pad[0]) return;      // nothing routed to this block
     wbase += (int64_t)e * p.expert_stride_bytes;
   }
-  constexpr uint32_t TMEM_COLS = TN < 32 ? 32 : TN;
+  constexpr uint32_t TMEM_COLS = mmq_tmem_cols(TN);
+  constexpr uint32_t A_COL0 = TN < 32 ? 32 : TN;   // first column of the A ring, right of the accumulator
   const int nk = nmain + ncorr;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SA; ++s) {
-      mbar_init(&full_a[s], MMQ_PRODUCER_WARPS / NG + 1);   // the warps of the one group that fills the stage + the B loader
+      mbar_init(&full_a[s], MMQ_PRODUCER_WARPS / NG + (SPLIT_B ? 0 : 1));   // the warps of the one group that fills the stage (+ the B loader)
       mbar_init(&empty_a[s], 1);
     }
+    if constexpr (SPLIT_B)
+      for (int s = 0; s < SB; ++s) mbar_init(&full_b[s], 1);
     mbar_init(accum, 1);
     *gave_up = 0;
     for (int s = 0; s < MMQ_MAX_RAW; ++s) {
@@ -290,18 +325,19 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     const bool live = n < p.N;
     const uint8_t* row = wbase + (live ? n : 0) * p.row_bytes;
     DecodeCtx cx{smem_u32(s_sel), smem_u32(s_sgn), smem_u32(s_kv)};
-    const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
     const int nunits = (int)((p.K + 31) / 32);   // 32-value units of a row that exist
     int s = g;                 // A slot of this group's next stage and its phase
     uint32_t ph = 0;
     while (s >= SA) { s -= SA; ph ^= 1u; }
+    // this thread's lane of tensor memory (warp w reaches lanes 32 * (w % 4) ...: lane = tile row r), column of A slot 0
+    const uint32_t a_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + A_COL0;
     auto publish = [&](const uint32_t (&v)[32], int i) -> bool {   // wait for the slot, store the row, signal the MMA warp
-      if (!wait_or_note(&empty_a[s], ph ^ 1u, 2, i)) return false;
-      uint8_t* dst = sA + (size_t)s * MMQ_A_STAGE + row_off;
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc)
-        *reinterpret_cast<uint4*>(dst + ((cc ^ (r & 7)) << 4)) = make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
-      fence_proxy_async();
+      const bool got = wait_or_note(&empty_a[s], ph ^ 1u, 2, i);
+      if (!__all_sync(0xffffffffu, got)) return false;    // (the tensor-memory store below is warp-wide)
+      tc_fence_after();
+      tmem_st32(a_lane + (uint32_t)(s * MMQ_A_COLS), v);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
       s += NG;
@@ -365,31 +401,35 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
         // The correction value of a block is one fp16 of the block itself (d or m).  A thread that
         // collected the 64 values of its own row would issue 64 two-byte loads whose 32 lanes touch
         // 32 different rows; instead the warp walks its 32 rows and each lane takes one block of the
-        // row, so a load instruction touches five or six lines, and every lane stores its value
-        // straight into the swizzled A slot.
+        // row, so a load instruction touches five or six lines.  The values cross to the row's own
+        // thread through this warp's scratch in shared memory ([row][32 values], rows 80 bytes apart), half a
+        // stage at a time.
         constexpr int TS_ = BlockTraits<TYPE>::TS;
         const int rb = r - lane;   // first tile row of this warp
+        uint8_t* scr = sScr + (size_t)warp * (32 * MMQ_CORR_ROW);
         for (int i = i0; i < nk && ok; i += NG) {
-          if (!wait_or_note(&empty_a[s], ph ^ 1u, 2, i)) { ok = false; break; }
-          uint8_t* slotp = sA + (size_t)s * MMQ_A_STAGE;
-          const int64_t g0 = (int64_t)(i - nmain) * 64 + lane;   // this lane's blocks: g0 and g0 + 32
-          const bool h0 = g0 * 32 < p.K, h1 = (g0 + 32) * 32 < p.K;
+          uint32_t v[32];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int64_t g0 = (int64_t)(i - nmain) * 64 + 32 * hh + lane;   // this lane's block
+            const bool h0 = g0 * 32 < p.K;
+            __syncwarp();   // the row reads of the previous half are done
 #pragma unroll 8
-          for (int rr = 0; rr < 32; ++rr) {
-            const int ri = rb + rr;
-            const bool have = n0 + ri < p.N;
-            const uint8_t* src = wbase + (n0 + (have ? ri : 0)) * p.row_bytes + g0 * TS_ + Decoder<TYPE, ab_t>::CORR_OFF;
-            const unsigned short a = (have && h0) ? __ldg(reinterpret_cast<const unsigned short*>(src)) : (unsigned short)0;
-            const unsigned short b = (have && h1) ? __ldg(reinterpret_cast<const unsigned short*>(src + 32 * TS_)) : (unsigned short)0;
-            uint8_t* drow = slotp + (ri >> 3) * 1024 + (ri & 7) * 128 + (lane & 7) * 2;
-            *reinterpret_cast<unsigned short*>(drow + ((((lane >> 3)) ^ (ri & 7)) << 4)) = a;
-            *reinterpret_cast<unsigned short*>(drow + (((4 + (lane >> 3)) ^ (ri & 7)) << 4)) = b;
+            for (int rr = 0; rr < 32; ++rr) {
+              const int ri = rb + rr;
+              const bool have = n0 + ri < p.N;
+              const uint8_t* src = wbase + (n0 + (have ? ri : 0)) * p.row_bytes + g0 * TS_ + Decoder<TYPE, ab_t>::CORR_OFF;
+              const unsigned short a = (have && h0) ? __ldg(reinterpret_cast<const unsigned short*>(src)) : (unsigned short)0;
+              *reinterpret_cast<unsigned short*>(scr + rr * MMQ_CORR_ROW + 2 * lane) = a;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              const uint4 q = lds128s(smem_u32(scr + lane * MMQ_CORR_ROW + 16 * cc));
+              v[16 * hh + 4 * cc] = q.x; v[16 * hh + 4 * cc + 1] = q.y; v[16 * hh + 4 * cc + 2] = q.z; v[16 * hh + 4 * cc + 3] = q.w;
+            }
           }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_a[s]);
-          s += NG;
-          while (s >= SA) { s -= SA; ph ^= 1u; }
+          ok = publish(v, i);
         }
       } else {
         for (int i = i0; i < nk && ok; i += NG) {
@@ -504,8 +544,9 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
           if (++se == SA) { se = 0; phe ^= 1u; }
         }
         const int64_t col = i < nmain ? (int64_t)(i + i_begin) * MMQ_BK : p.kpad + (int64_t)(i - nmain) * MMQ_BK;
-        mbar_expect_tx(&full_a[sa], (uint32_t)B_STAGE);
-        tma_load_2d(sB + (size_t)sb * B_STAGE, &bmap, (int)col, (int)t0, &full_a[sa]);
+        uint64_t* fb = SPLIT_B ? &full_b[sb] : &full_a[sa];
+        mbar_expect_tx(fb, (uint32_t)B_STAGE);
+        tma_load_2d(sB + (size_t)sb * B_STAGE, &bmap, (int)col, (int)t0, fb);
         if (++sa == SA) sa = 0;
         if (++sb == SB) sb = 0;
       }
@@ -606,22 +647,25 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     {
       const uint32_t idesc = umma_idesc(MMQ_ROWS, TN, sizeof(ab_t) == 2 && std::is_same<ab_t, __nv_bfloat16>::value ? 1 : 0);
       int sa = 0, sb = 0;
-      uint32_t pha = 0;
-      const uint64_t ad0 = umma_desc_sw128(smem_u32(sA)), bd0 = umma_desc_sw128(smem_u32(sB));
+      uint32_t pha = 0, phb = 0;
+      const uint64_t bd0 = umma_desc_sw128(smem_u32(sB));
+      const uint32_t a_ring = tmem_base + A_COL0;
       for (int i = 0; i < nk; ++i) {
-        const bool got = wait_or_note(&full_a[sa], pha, 6, i);
+        bool got = wait_or_note(&full_a[sa], pha, 6, i);
+        if constexpr (SPLIT_B) got = got && wait_or_note(&full_b[sb], phb, 7, i);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t ad = ad0 + (uint64_t)(sa * (MMQ_A_STAGE >> 4)), bd = bd0 + (uint64_t)(sb * (B_STAGE >> 4));
+        const uint64_t bd = bd0 + (uint64_t)(sb * (B_STAGE >> 4));
+        const uint32_t at = a_ring + (uint32_t)(sa * MMQ_A_COLS);
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < MMQ_BK / 16; ++kk)  // 16 values = 32 bytes = +2 in the descriptor's 16-byte units
-            umma_f16(tmem_base, ad + 2 * kk, bd + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < MMQ_BK / 16; ++kk)  // 16 values = 8 columns of A, 32 bytes of B = +2 in the descriptor's 16-byte units
+            umma_f16_ts(tmem_base, at + 8 * kk, bd + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&empty_a[sa]);
         }
         __syncwarp();
         if (++sa == SA) { sa = 0; pha ^= 1u; }
-        if (++sb == SB) sb = 0;
+        if (++sb == SB) { sb = 0; phb ^= 1u; }
       }
       // committed in every case: `accum` then completes once every tcgen05.mma this warp issued
       // has finished, which is what the exit path below waits for after a time-out
@@ -801,7 +845,8 @@ static int launch_kernel(const MmqArgs& a, const MmqParams& p, const CUtensorMap
       class_log2 = cl;
     }
   }
-  const size_t ab_bytes = 1024 + (size_t)mmq_a_stages(TYPE, FAST, TWO, TN) * MMQ_A_STAGE + (size_t)mmq_b_stages(FAST, TWO, TN) * TN * MMQ_BK * 2 + mmq_aux_bytes(TYPE);
+  const size_t ab_bytes = 1024 + (size_t)mmq_b_stages(TYPE, FAST, TWO, TN) * TN * MMQ_BK * 2 + mmq_aux_bytes(TYPE) +
+                          mmq_scratch_bytes<TYPE>(mmq_groups(TYPE, FAST, TWO, TN));
   const size_t raw_stage = (size_t)MMQ_ROWS * (raw_tma ? TmaGeom<TYPE>::RBC_T : RawGeom<TYPE>::SLOT);
   const size_t budget = (TWO ? 113 : 226) * 1024;   // two CTAs share the SM's 228 KB (1 KB each is reserved)
   int rs = (int)((budget - ab_bytes) / raw_stage);
