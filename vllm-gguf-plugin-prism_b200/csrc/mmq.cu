@@ -16,9 +16,13 @@
 // "sum" terms the reference's tiled kernels use (Q4_0: -8*d*s8, Q4_K: -dmin*m*s8, with s8 the
 // fp16 sum of the *unquantized* activations) ride along as K/32 extra contraction columns.
 //
-// Tile: 128 weight rows (UMMA M) x TN tokens (UMMA N, 32..256) x 64 values per stage, both
-// operands K-major in shared memory with the 128-byte swizzle.  Weight rows sit on the M axis
-// so that small token counts (MoE blocks) do not waste the 128-row instruction.
+// Tile: 128 weight rows (UMMA M) x TN tokens (UMMA N, 32..256) x 64 values per stage.  Operand A
+// (the decoded weights) lives in tensor memory: a producer thread owns one weight row = one lane,
+// and stores the 64 fp16 values of a stage -- 32 registers -- into 32 columns of that lane with
+// tcgen05.st; the MMA takes A from there ([a_tmem] operand form).  Operand B (activations) is
+// K-major in shared memory with the 128-byte swizzle, one TMA box per stage.  Weight rows sit on
+// the M axis so that small token counts (MoE blocks) do not waste the 128-row instruction.
+// Tensor memory: columns [0, TN) the fp32 accumulator, then four A slots of 32 columns.
 // Warp roles (P = 4 * groups producer warps, groups = 2 or 4):
 //   warps 0..P-1  producers: group g = 128 threads, one per weight row, decodes all 64 values of
 //                 its row for the stages i = g, g + groups, ... from the raw-byte ring into the A
@@ -27,10 +31,18 @@
 //                 written by one TMA store, or stored directly for MoE)
 //   warp P        B loader: one TMA box of activations per stage; owns the TMEM allocation
 //   warp P+1      MMA issuer: warp-uniform loop, an elected lane issues 4 tcgen05.mma + 1 commit per stage
-//   warp P+2      raw-weight loader: one 2-D TMA box (256-value chunk x 128 rows) per chunk
+//   warp P+2      raw-weight loader: one 2-D TMA box (256-value chunk x 128 rows) per chunk, or one
+//                 padded box per alignment class of rows when rows are not multiples of 16 bytes
 // One full/empty mbarrier pair per A slot serves both operands.  K may be split over grid.z
 // (fp32 partial tiles, added by add_partials_kernel).  Every wait is bounded in time and
 // reports through the status word.
+//
+// What bounds it (B200, measured): with 256-token tiles every CTA pulls 32 KB of activations per
+// stage through L2; at M = 512, 2048 and with 128-token tiles alike the kernel moves 8.1-8.4 TB/s
+// from L2 to the SMs in aggregate (about 1000 clocks per stage against 512 of tensor work), whatever
+// the number of producer groups, the depth of either ring, the decode cost of the type or the
+// place operand A is kept.  The next step is tcgen05 cta_group::2 (a CTA pair sharing one
+// activation tile, each loading half), not built here.
 #include <cuda.h>
 
 #include <type_traits>
@@ -47,14 +59,15 @@ constexpr int MMQ_BK = 64;
 // Producer groups of 128 threads (one thread per weight row) that take the K stages in turn.
 // The whole-stage decoders are short enough for four groups (16 warps) to fit the register
 // file; the generic 32-value decoders need more registers per thread and measured faster with
-// two groups (IQ2_XXS, the longest decode, still gains from four).  Token tiles of 64 or less
+// two groups (IQ2_XXS, the longest decode, and Q2_K, the shortest, gain from four; with four Q6_K
+// went 77 -> 92 us, IQ4_XS 80 -> 112 us, Q3_K 88 -> 93 us).  Token tiles of 64 or less
 // with a whole-stage decoder run TWO CTAs of two groups per SM instead of one CTA of four: the
 // tensor work per stage is small there and the per-stage cost of one MMA-issuing warp is the
 // limit, so two independent pipelines per SM raise the rate -- when the grid has enough CTAs to
 // put two on every SM (MoE, many row tiles); with fewer CTAs than SMs the one-CTA form keeps
 // all 16 decode warps on the tile (`two` is chosen per launch).
 __host__ __device__ constexpr int mmq_groups(int type, bool fast, bool two, int tn) {
-  return two ? 2 : ((fast || type == T_IQ2_XXS) ? 4 : 2);
+  return two ? 2 : ((fast || type == T_IQ2_XXS || type == T_Q2_K) ? 4 : 2);
 }
 __host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two, int tn) { return (4 * mmq_groups(type, fast, two, tn) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
 // Ring depths.  The decoded weights (operand A) never touch shared memory: a producer thread writes
@@ -460,8 +473,10 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     out_t* y = static_cast<out_t*>(p.y);
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const int64_t npp = MOE ? (int64_t)p.n_post_pad[0] : 0;
-    constexpr int CH = TN / NG;          // columns per thread of the NG threads that share a row (a multiple of 16)
-    const int cbeg = g * CH, cend = cbeg + CH;
+    // columns per thread of the NG threads that share a row: a multiple of 16 (one tcgen05.ld), so with a
+    // 32-token tile and four groups only the first two groups take part
+    constexpr int CH = TN / NG < 16 ? 16 : TN / NG;
+    const int cbeg = g * CH, cend = cbeg + CH < TN ? cbeg + CH : TN;
     if (!MOE && p.y_tma) {
       // Stage the tile as [token][128 rows] in the (now idle) operand stages and let one TMA
       // store write it: full lines to global memory, edges clipped by the tensor map.
