@@ -8,10 +8,10 @@
  * never allocates, never synchronises.  Work is enqueued on `stream` (a cudaStream_t passed
  * as void*).  Scratch memory is provided by the caller (gguf_b200_workspace_bytes).
  *
- * Types: GGML ids 2 (Q4_0), 3 (Q4_1), 6 (Q5_0), 7 (Q5_1), 8 (Q8_0), 12 (Q4_K), 13 (Q5_K), 14 (Q6_K),
- * 16 (IQ2_XXS), 20 (IQ4_NL), 23 (IQ4_XS); the dequantize and the GEMV entry points (mul_mat_vec_a8,
- * moe_a8_vec and their variants) also take 10 (Q2_K), 11 (Q3_K), 17 (IQ2_XS), 18 (IQ3_XXS), 19 (IQ1_S),
- * 21 (IQ3_S), 22 (IQ2_S), 29 (IQ1_M) -- all nineteen block types of the reference's dispatch.
+ * Types: GGML ids 2 (Q4_0), 3 (Q4_1), 6 (Q5_0), 7 (Q5_1), 8 (Q8_0), 10 (Q2_K), 11 (Q3_K), 12 (Q4_K), 13 (Q5_K),
+ * 14 (Q6_K) -- every type of the reference's tiled kernels -- and 16 (IQ2_XXS), 20 (IQ4_NL), 23 (IQ4_XS); the
+ * dequantize and the GEMV entry points (mul_mat_vec_a8, moe_a8_vec and their variants) also take 17 (IQ2_XS),
+ * 18 (IQ3_XXS), 19 (IQ1_S), 21 (IQ3_S), 22 (IQ2_S), 29 (IQ1_M) -- all nineteen block types of the reference's dispatch.
  * Weights W are raw GGUF blocks, row-major `uint8 [N][K/QK*type_size]`, base 16-byte aligned.
  * Activations X are `[M][K]` contiguous in `dtype`; outputs Y are `[M][N]` in the same dtype.
  */
@@ -97,7 +97,7 @@ int gguf_b200_gemv_prepared(const void* W, const void* workspace, void* Y, int t
                             int64_t M, int64_t N, int64_t K, void* stream);
 
 /* Prefill GEMM on tensor cores (same q8_1-quantized activations).
- * Replaces: ggml_mul_mat_a8, gguf_kernel.cu:220-290 (+ mmq.cuh).  Types 2, 3, 6, 7, 8, 12, 13, 14. */
+ * Replaces: ggml_mul_mat_a8, gguf_kernel.cu:220-290 (+ mmq.cuh).  Types 2, 3, 6, 7, 8, 10, 11, 12, 13, 14. */
 int gguf_b200_mul_mat_a8(const void* W, const void* X, void* Y, void* workspace, int64_t workspace_bytes,
                          int type, int dtype, int64_t M, int64_t N, int64_t K, void* stream);
 
