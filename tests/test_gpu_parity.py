@@ -266,6 +266,29 @@ def test_mmq_block_multiple_of_32_but_not_64():
         assert rel_l2(y.float().cpu().numpy(), y64) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("N", [264, 260])
+@pytest.mark.parametrize("name", ["Q6_K", "Q3_K", "Q2_K", "Q5_0", "IQ2_XXS"])
+def test_mmq_rows_of_every_alignment(ref, name, N):
+    """K = 768: rows of 630 / 330 / 252 / 528 / 198 bytes, i.e. eight (or four, or one) alignment classes of rows.
+    N = 264 is a multiple of eight (one TMA box per class), N = 260 is not (one bulk copy per row)."""
+    t = TYPES[name]
+    K, M = 768, 40
+    wn, w = dev_w(t, N, K, seed=N)
+    x = dev_x(M, K, seed=3)
+    if name == "IQ2_XXS":
+        y = capi.dequant_matmul(w, x, t, N)
+        want = (x @ capi.dequantize(w, t, N, K, torch.float16).T).float().cpu().numpy()
+    else:
+        y = capi.mul_mat_a8(w, x, t, N)
+        want, _ = cpu.matmul_a8(wn, t, x.cpu().numpy(), "float16", mmq=True)
+        if ref.available:
+            r = ref.ops.ggml_mul_mat_a8(w, x, t, N)
+            assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    assert rel_l2(y.float().cpu().numpy(), want) <= REL_L2_TOL
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_mmq_other_dtypes(dtype):
     t = 12
@@ -328,6 +351,23 @@ def test_moe_a8_parity(ref, name):
         r = ref.ops.ggml_moe_a8(x, w, torch.from_numpy(s4).to(DEV), torch.from_numpy(e4).to(DEV),
                                 torch.from_numpy(n4).to(DEV), t, N, top_k, T)
         assert rel_l2(y.float().cpu(), r.float().cpu()) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("name", ["Q6_K", "Q3_K"])
+def test_moe_a8_whole_row_tiles_of_unaligned_rows(name):
+    """N a multiple of 128 with rows that are not a multiple of 16 bytes: the experts' raw weights arrive as
+    alignment-class TMA boxes over the stacked [E * N] rows."""
+    t = TYPES[name]
+    E, N, K, T, top_k = 6, 256, 1024, 50, 2
+    wn, xn, _, ids = moe_case(t, E, N, K, T, top_k, seed=17)
+    w, x = torch.from_numpy(wn).to(DEV), torch.from_numpy(xn).to(DEV)
+    blk = capi.lib().gguf_b200_moe_block_size(t)
+    s, e, n = synth.moe_align_block_size(ids, blk, E)
+    y = capi.moe_a8(x, w, torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV), t, N, top_k, T)
+    torch.cuda.synchronize()
+    assert capi.last_status() == 0
+    y64, _ = cpu.moe_a8(wn, t, xn, s, e, int(n[0]), blk, top_k, T)
+    assert rel_l2(y.float().cpu().numpy(), y64) <= REL_L2_TOL
 
 
 def test_moe_a8_padding_rows_are_zero_and_bad_experts_skipped():
