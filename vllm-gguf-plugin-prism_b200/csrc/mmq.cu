@@ -37,12 +37,16 @@
 // (fp32 partial tiles, added by add_partials_kernel).  Every wait is bounded in time and
 // reports through the status word.
 //
-// What bounds it (B200, measured): with 256-token tiles every CTA pulls 32 KB of activations per
-// stage through L2; at M = 512, 2048 and with 128-token tiles alike the kernel moves 8.1-8.4 TB/s
-// from L2 to the SMs in aggregate (about 1000 clocks per stage against 512 of tensor work), whatever
-// the number of producer groups, the depth of either ring, the decode cost of the type or the
-// place operand A is kept.  The next step is tcgen05 cta_group::2 (a CTA pair sharing one
-// activation tile, each loading half), not built here.
+// What bounds it (B200, measured on Q4_K 14336 x 4096, 256-token tiles, about 940 clocks per stage
+// against 512 of tensor work): no single resource.  Leaving out, one at a time, in builds made for
+// the measurement only: the activation loads (every stage reuses the first boxes) -8 %; the decode
+// arithmetic (constant operand) -7 %; the tcgen05.mma instructions -23 % (730 clocks per stage
+// remain); polling instead of parked barrier waits +2 %.  Neither the number of producer groups
+// (2, 4), the depth of the A ring (3, 4) or of the B ring (3, 4), nor the type's decode cost
+// (Q8_0 = Q4_K = Q4_0) moves it.  Three stages of 500-730 clocks each -- decode and hand-over
+// (about 600 per stage where the other two are small, 64-token tiles), activation boxes (730 with
+// the MMAs off, 32 KB per stage and CTA through L2) and the MMAs (512) -- are coupled through the
+// shared full / empty barriers of a stage and overlap imperfectly.
 #include <cuda.h>
 
 #include <type_traits>
