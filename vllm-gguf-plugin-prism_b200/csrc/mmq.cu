@@ -95,7 +95,7 @@ template <int TYPE> __host__ __device__ constexpr int mmq_scratch_bytes(int grou
 }
 constexpr int MMQ_MAX_RAW = 6;
 // shared memory between the operand rings and the raw ring: barriers, then the decoder's tables
-__host__ __device__ constexpr int mmq_aux_bytes(int type) { return type == T_IQ2_XXS ? 8192 : 4096; }
+__host__ __device__ constexpr int mmq_aux_bytes(int type) { return type == T_IQ2_XXS ? 50176 : 4096; }   // IQ2_XXS: 512 + 16 KB + 32 KB of tables
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot_smem, uint32_t ncols) {
@@ -277,8 +277,8 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
   uint64_t* raw_full = bars + 34;             // [MMQ_MAX_RAW]
   uint64_t* raw_empty = bars + 34 + MMQ_MAX_RAW;
   int8_t* s_kv = reinterpret_cast<int8_t*>(bars + 48);                 // 16 bytes
-  uint4* s_sgn = reinterpret_cast<uint4*>(bars + 64);                   // IQ2_XXS: 128 x 16 bytes at offset 512
-  uint2* s_sel = reinterpret_cast<uint2*>(s_sgn + 128);                 // IQ2_XXS: 256 x 8 bytes
+  uint4* s_sgn = reinterpret_cast<uint4*>(bars + 64);                   // IQ2_XXS: 8 copies x 128 x 16 bytes at offset 512
+  uint2* s_sel = reinterpret_cast<uint2*>(s_sgn + 8 * 128);             // IQ2_XXS: 16 copies x 256 x 8 bytes
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n0 = (int64_t)blockIdx.x * MMQ_ROWS;
@@ -310,8 +310,8 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     fence_barrier_init();
   }
   if (TYPE == T_IQ2_XXS) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_sel[i] = iq2xxs_pair_selectors(d_iq2xxs_grid[i]);
-    for (int i = threadIdx.x; i < 128; i += blockDim.x) s_sgn[i] = iq2xxs_pair_signs(d_ksigns_iq2xs[i]);
+    for (int i = threadIdx.x; i < 16 * 256; i += blockDim.x) s_sel[i] = iq2xxs_pair_selectors(d_iq2xxs_grid[i >> 4]);
+    for (int i = threadIdx.x; i < 8 * 128; i += blockDim.x) s_sgn[i] = iq2xxs_pair_signs(d_ksigns_iq2xs[i >> 3]);
   }
   if ((TYPE == T_IQ4_XS || TYPE == T_IQ4_NL) && threadIdx.x < 16) s_kv[threadIdx.x] = d_kvalues_iq4nl[threadIdx.x];
   if (warp == MMQ_PRODUCER_WARPS) {
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     const int64_t n = n0 + r;
     const bool live = n < p.N;
     const uint8_t* row = wbase + (live ? n : 0) * p.row_bytes;
-    DecodeCtx cx{smem_u32(s_sel), smem_u32(s_sgn), smem_u32(s_kv)};
+    DecodeCtx cx{smem_u32(s_sel) + 8u * (lane & 15), smem_u32(s_sgn) + 16u * (lane & 7), smem_u32(s_kv)};
     const int nunits = (int)((p.K + 31) / 32);   // 32-value units of a row that exist
     int s = g;                 // A slot of this group's next stage and its phase
     uint32_t ph = 0;

@@ -56,17 +56,22 @@ __device__ __forceinline__ uint32_t shift_of(const uint8_t* p) { return (uint32_
 // look-ups are plain (non-volatile) asm: their index comes from weight bytes that are read long
 // after the barrier that published the tables.
 struct DecodeCtx {
+  // The two IQ2_XXS tables are replicated, entry i of copy c at index COPIES * i + c -- the sign table
+  // (16-byte entries) eight times, the selector table (8-byte entries) sixteen times -- and a thread
+  // reads copy (lane mod COPIES): the lanes that share a 128-byte access phase then sit in different
+  // columns of the 128 bytes whatever entries they look up (random look-ups into a single copy averaged
+  // 2.5 to 3 bank conflicts per access).  `sel` and `sgn` already point at this thread's copy.
   uint32_t sel;       // IQ2_XXS: per grid entry (8 bytes), the byte-permute selectors of its four value pairs (see Decoder<T_IQ2_XXS>)
   uint32_t sgn;       // IQ2_XXS: per 7-bit sign index (16 bytes), the sign-bit masks of the four value pairs
   uint32_t kv;        // IQ4_NL / IQ4_XS: the 16 levels, one signed byte each
   __device__ __forceinline__ uint2 sel_at(uint32_t i) const {
     uint2 v;
-    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(sel + 8u * i));
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(sel + 128u * i));
     return v;
   }
   __device__ __forceinline__ uint4 sgn_at(uint32_t i) const {
     uint4 v;
-    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sgn + 16u * i));
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sgn + 128u * i));
     return v;
   }
   __device__ __forceinline__ float level(uint32_t i) const {
