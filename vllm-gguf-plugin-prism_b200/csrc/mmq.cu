@@ -381,18 +381,34 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
           const uint8_t* srow = sRaw + (size_t)rs * RAW_STAGE + (size_t)rslot * slot + (tma ? 0 : (beg & 15)) - (int64_t)(c + c_begin) * rbc;
           for (int i = c * SPC + GI; i < (c + 1) * SPC && i < nmain && ok; i += NG) {
             uint32_t v[32];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int u = 2 * (i + i_begin) + h;
-              uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
-              if (live && u < nunits) {
-                constexpr int RW = Decoder<TYPE, ab_t>::RW;
+            constexpr int RW = Decoder<TYPE, ab_t>::RW;
+            if constexpr (decoder_pair_load<TYPE>()) {
+              // the two 32-value units of a stage read the same words of the block: one load serves both
+              const int u = 2 * (i + i_begin);
+              uint32_t (&v0)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[0]);
+              uint32_t (&v1)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16]);
+              if (live && u + 1 < nunits) {
                 uint32_t raw[RW];
                 Decoder<TYPE, ab_t>::load(srow, u, raw);
-                Decoder<TYPE, ab_t>::decode(srow, u, raw, cx, vh);
+                Decoder<TYPE, ab_t>::decode(srow, u, raw, cx, v0);
+                Decoder<TYPE, ab_t>::decode(srow, u + 1, raw, cx, v1);
               } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) vh[j] = 0;
+                for (int j = 0; j < 32; ++j) v[j] = 0;
+              }
+            } else {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int u = 2 * (i + i_begin) + h;
+                uint32_t (&vh)[16] = *reinterpret_cast<uint32_t (*)[16]>(&v[16 * h]);
+                if (live && u < nunits) {
+                  uint32_t raw[RW];
+                  Decoder<TYPE, ab_t>::load(srow, u, raw);
+                  Decoder<TYPE, ab_t>::decode(srow, u, raw, cx, vh);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) vh[j] = 0;
+                }
               }
             }
             ok = publish(v, i);

@@ -124,6 +124,10 @@ template <int TYPE> struct RawGeom {
   static constexpr int SLOT = (S16 % 2 ? S16 : S16 + 1) * 16;
 };
 
+// Types whose two 32-value units of a 64-value stage (units 2j and 2j + 1 of a 256-value super-block, always
+// whole) are cut from the same words of the block: load() depends on the unit only through u >> 1.
+template <int TYPE> __host__ __device__ constexpr bool decoder_pair_load() { return TYPE == T_Q2_K || TYPE == T_Q3_K || TYPE == T_Q5_K; }
+
 // ---- Q4_0: value = half(q * d), q unsigned (see Stage64<T_Q4_0>); unit = one 18-byte block ----
 template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
   static constexpr int CORR_OFF = 0;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
