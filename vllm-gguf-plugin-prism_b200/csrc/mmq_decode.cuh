@@ -126,7 +126,7 @@ template <int TYPE> struct RawGeom {
 
 // Types whose two 32-value units of a 64-value stage (units 2j and 2j + 1 of a 256-value super-block, always
 // whole) are cut from the same words of the block: load() depends on the unit only through u >> 1.
-template <int TYPE> __host__ __device__ constexpr bool decoder_pair_load() { return TYPE == T_Q2_K || TYPE == T_Q3_K || TYPE == T_Q5_K; }
+template <int TYPE> __host__ __device__ constexpr bool decoder_pair_load() { return TYPE == T_Q2_K || TYPE == T_Q3_K || TYPE == T_Q5_K || TYPE == T_Q6_K; }
 
 // ---- Q4_0: value = half(q * d), q unsigned (see Stage64<T_Q4_0>); unit = one 18-byte block ----
 template <typename ab_t> struct Decoder<T_Q4_0, ab_t> {
@@ -401,27 +401,29 @@ template <typename ab_t> struct Decoder<T_Q5_K, ab_t> {
 // unit u: super-block u>>3, group g = u&7: ip = g>>2 (128-value half), q = g&3:
 //   low 4 bits = nibble (q>>1) of ql[64ip + 32(q&1) + l], high 2 bits = bits 2q.. of qh[32ip + l], l = 0..31,
 //   scales sc[8ip + 2q] (l < 16) and sc[8ip + 2q + 1].
-// Raw: [0..9] 32 bytes of ql (+ cover), [10..19] 32 bytes of qh (+ cover), [20..21] scale half-word, [22] d.
+// The units 2j and 2j + 1 of a stage differ in q & 1 only, so one load serves both (decoder_pair_load):
+// Raw: [0..17] the 64 bytes of ql of the half (+ cover), [18..27] 32 bytes of qh (+ cover), [28..30] the four
+// scale bytes of the pair (+ cover), [31] d.
 template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
   static constexpr int CORR_OFF = -1;   // byte offset in a block of the fp16 that is the block's correction value (-1: none / computed)
-  static constexpr int RW = 23;
+  static constexpr int RW = 32;
   static __device__ __forceinline__ void load(const uint8_t* row, int u, uint32_t (&raw)[RW]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 210;
-    const int g = u & 7, ip = g >> 2, q = g & 3;
-    ldg_cover<9>(blk + 64 * ip + 32 * (q & 1), 32, raw);
-    raw[9] = 0;
-    ldg_cover<9>(blk + 128 + 32 * ip, 32, raw + 10);
-    raw[19] = 0;
-    ldg_cover<1>(blk + 192 + 8 * ip + 2 * q, 2, raw + 20);
-    raw[21] = 0;
-    ldg_cover<1>(blk + 208, 2, raw + 22);
+    const int g = u & 7, ip = g >> 2, q = g & 2;
+    ldg_cover<17>(blk + 64 * ip, 64, raw);
+    raw[17] = 0;
+    ldg_cover<9>(blk + 128 + 32 * ip, 32, raw + 18);
+    raw[27] = 0;
+    ldg_cover<2>(blk + 192 + 8 * ip + 2 * q, 4, raw + 28);
+    raw[30] = 0;
+    ldg_cover<1>(blk + 208, 2, raw + 31);
   }
   static __device__ __forceinline__ void decode(const uint8_t* row, int u, const uint32_t (&raw)[RW], const DecodeCtx&, uint32_t (&out)[16]) {
     const uint8_t* blk = row + (int64_t)(u >> 3) * 210;
     const int g = u & 7, ip = g >> 2, q = g & 3;
-    const uint32_t sh_l = shift_of(blk + 64 * ip + 32 * (q & 1)), sh_h = shift_of(blk + 128 + 32 * ip);
-    const uint32_t sc2 = (raw[20] >> shift_of(blk + 192 + 8 * ip + 2 * q)) & 0xFFFFu;   // two int8 scales
-    const uint32_t du = (raw[22] >> shift_of(blk + 208)) & 0xFFFFu;
+    const uint32_t sh_l = shift_of(blk + 64 * ip), sh_h = shift_of(blk + 128 + 32 * ip);
+    const uint32_t sc2 = (word_at(raw + 28, 0, shift_of(blk + 192 + 8 * ip + 2 * (q & 2))) >> (16 * (q & 1))) & 0xFFFFu;   // two int8 scales
+    const uint32_t du = (raw[31] >> shift_of(blk + 208)) & 0xFFFFu;
     const __half2 d2 = u32_as_h2(du | (du << 16));
     const __half2 off = __floats2half2_rn(1056.f, 1056.f);  // 1024 + 32
     const __half2 s_lo = __half2half2(__int2half_rn((int)(int8_t)(sc2 & 0xFF)));
@@ -431,8 +433,8 @@ template <typename ab_t> struct Decoder<T_Q6_K, ab_t> {
     const uint32_t sl = 4 * (q >> 1), rot_h = (uint32_t)(2 * q - 4) & 31u;
 #pragma unroll
     for (int wi = 0; wi < 8; ++wi) {             // word wi: values 4wi..4wi+3 of the unit
-      const uint32_t l = word_at(raw, wi, sh_l) >> sl;
-      const uint32_t h = word_at(raw + 10, wi, sh_h);
+      const uint32_t l = word_at(raw, wi + 8 * (q & 1), sh_l) >> sl;
+      const uint32_t h = word_at(raw + 18, wi, sh_h);
       const uint32_t c = (l & 0x0F0F0F0Fu) | (__funnelshift_r(h, h, rot_h) & 0x30303030u);
       const __half2 s2 = wi < 4 ? s_lo : s_hi;
       const __half2 p0 = u32_as_h2(__byte_perm(c, 0x64646464u, 0x4140)), p1 = u32_as_h2(__byte_perm(c, 0x64646464u, 0x4342));
