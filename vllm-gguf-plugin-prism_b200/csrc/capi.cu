@@ -135,7 +135,10 @@ int gguf_b200_dequantize_rows(const void* W, int type, const int64_t* row_ids, i
 // Measured cross-over on 14336x4096: the types with whole-stage tensor-core decoders win from 5
 // tokens on (Q4_K, 8 tokens: 26.9 us against 37.3 us through the GEMV); the others keep the GEMV
 // up to 16.
-static int64_t mmq_gemv_max_tokens(int type) { return (type == T_Q4_K || type == T_Q4_0 || type == T_Q8_0) ? 4 : 16; }
+// Largest batch that ggml_mul_mat_a8 serves with the GEMV kernels (tiled formulas) instead of the tensor cores.  Types
+// that exist only in the two-vector register-resident GEMV would need a pass per pair of tokens: beyond two passes the
+// tiled kernel (about 25 us on a 14336x4096 matrix whatever the batch) is faster.  Q6_K has the multi-vector kernel.
+static int64_t mmq_gemv_max_tokens(int type) { return type == T_Q6_K ? 16 : 4; }
 
 // activation matrix of the tensor-core kernels, rounded so that what follows it stays aligned
 static int64_t mmq_b_bytes(int type, int64_t M, int64_t K) { return round_up(M * mmq_ldb(type, K) * 2, 256); }

@@ -754,7 +754,7 @@ static int pick_tn(int64_t M) {
 static bool raw_tma_ok(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_bytes) {
   static const char* no_tma = getenv("GGUF_B200_MMQ_NO_RAW_TMA");
   if (no_tma && no_tma[0] == '1') return false;
-  if (!(type == T_Q4_0 || type == T_Q8_0 || type == T_Q4_K || type == T_IQ4_XS)) return false;
+  if (!(type == T_Q4_0 || type == T_Q8_0 || type == T_Q4_K || type == T_Q5_K || type == T_IQ4_XS)) return false;
   const int64_t row_bytes = K / block_size(type) * type_size(type);
   if (K % 32 != 0 || row_bytes % 16 != 0) return false;
   if (moe && (expert_stride_bytes != N * row_bytes || N % MMQ_ROWS != 0)) return false;
@@ -765,6 +765,7 @@ int mmq_perm(int type, int64_t N, int64_t K, bool moe, int64_t expert_stride_byt
   switch (type) {
     case T_Q4_0: return Stage64<T_Q4_0, __half>::PERM;
     case T_Q4_K: return Stage64<T_Q4_K, __half>::PERM;
+    case T_Q5_K: return Stage64<T_Q5_K, __half>::PERM;
     case T_Q8_0: return Stage64<T_Q8_0, __half>::PERM;
   }
   return 0;

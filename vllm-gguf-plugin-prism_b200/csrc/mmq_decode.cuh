@@ -111,11 +111,11 @@ template <int TYPE, typename ab_t> struct Decoder;
 // the 128 rows of a tile spread over all shared-memory banks.
 // TMA variant of the staging (row bytes a multiple of 16 and chunk starts 16-byte aligned): a
 // chunk of KC_T values per row is one 2-D box of RBC_T bytes x 128 rows, stored densely.  RBC_T
-// is 16 mod 128 for every supported type, so dense rows are bank-conflict free as well.
+// is an odd multiple of 16 for every supported type, so dense rows are bank-conflict free as well.
 template <int TYPE> struct TmaGeom {
-  static constexpr bool OK = TYPE == T_Q4_0 || TYPE == T_Q8_0 || TYPE == T_Q4_K || TYPE == T_IQ4_XS;
+  static constexpr bool OK = TYPE == T_Q4_0 || TYPE == T_Q8_0 || TYPE == T_Q4_K || TYPE == T_Q5_K || TYPE == T_IQ4_XS;
   static constexpr int KC_T = TYPE == T_IQ4_XS ? 512 : 256;
-  static constexpr int RBC_T = KC_T / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;   // 144 or 272
+  static constexpr int RBC_T = KC_T / BlockTraits<TYPE>::QK * BlockTraits<TYPE>::TS;   // 144, 176 or 272
 };
 template <int TYPE> struct RawGeom {
   static constexpr int KC = TYPE == T_IQ2_XXS ? 512 : 256;   // multiples of 256: every producer group meets every chunk
@@ -676,6 +676,53 @@ template <> struct Stage64<T_Q4_K, __half> {
         out[2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), o0), s0));
         out[16 + 2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x00F000F0u) | 0x54005400u), o1), s1));
         out[16 + 2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x00F000F0u) | 0x54005400u), o1), s1));
+      }
+    }
+  }
+};
+
+// ---- Q5_K: chunk = one 176-byte super-block (d, dmin, 12 scale bytes, 32 bytes of fifth bits, 128 bytes of
+// nibbles); stage SC = sub-blocks 2SC (low nibbles of qs[32SC..], bit 2SC of qh[l]) and 2SC+1 (high nibbles,
+// bit 2SC+1).  As Q4_K with one more AND/OR per pair: the fifth bit lands at mantissa bit 4 of 1024 + n
+// (low nibbles) or at mantissa bit 8 of 64 + n / 16 (high nibbles, n sits four bits up).
+template <> struct Stage64<T_Q5_K, __half> {
+  static constexpr bool FAST = true;
+  static constexpr int PERM = 1;
+  template <int SC> static __device__ __forceinline__ void decode(const uint8_t* blk, uint32_t (&out)[32]) {
+    const uint4 h = lds128(blk);
+    const uint4 ha = lds128(blk + 16), hb = lds128(blk + 32);
+    const uint4 qa = lds128(blk + 48 + 32 * SC), qb = lds128(blk + 64 + 32 * SC);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+    const __half dall = __ushort_as_half((unsigned short)(h.x & 0xffff));
+    int sc0, sc1, m;
+    q4k_scale_min(h.y, h.z, h.w, 2 * SC, sc0, m);
+    q4k_scale_min(h.y, h.z, h.w, 2 * SC + 1, sc1, m);
+    const __half d0 = __hmul_rn(dall, __int2half_rn(sc0)), d1 = __hmul_rn(dall, __int2half_rn(sc1));
+    const __half2 s0 = __half2half2(d0), s1 = __half2half2(d1);
+    const float big = fmaxf(fabsf(__half2float(d0)), fabsf(__half2float(d1)));
+    if (big < 32.f) {
+      // (1024 + n) * s - 1024 * s: the product term is exact, so this is n * s rounded once
+      const __half2 c0 = __hmul2_rn(s0, h2const(-1024.f)), c1 = __hmul2_rn(s1, h2const(-64.f));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t a = w[j], b = w[j] >> 8;
+        const uint32_t x = hw[j] >> (2 * SC), y = hw[j] >> (2 * SC + 8);   // fifth bits of values (4j, 4j+2) / (4j+1, 4j+3) at bits 0 and 16
+        out[2 * j] = h2_as_u32(__hfma2(u32_as_h2((a & 0x000F000Fu) | ((x << 4) & 0x00100010u) | 0x64006400u), s0, c0));
+        out[2 * j + 1] = h2_as_u32(__hfma2(u32_as_h2((b & 0x000F000Fu) | ((y << 4) & 0x00100010u) | 0x64006400u), s0, c0));
+        out[16 + 2 * j] = h2_as_u32(__hfma2(u32_as_h2((a & 0x00F000F0u) | ((x << 7) & 0x01000100u) | 0x54005400u), s1, c1));
+        out[16 + 2 * j + 1] = h2_as_u32(__hfma2(u32_as_h2((b & 0x00F000F0u) | ((y << 7) & 0x01000100u) | 0x54005400u), s1, c1));
+      }
+    } else {  // 1024 * s would overflow fp16: subtract the offset first (exact), then scale
+      const __half2 o0 = h2const(1024.f), o1 = h2const(64.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t a = w[j], b = w[j] >> 8;
+        const uint32_t x = hw[j] >> (2 * SC), y = hw[j] >> (2 * SC + 8);
+        out[2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x000F000Fu) | ((x << 4) & 0x00100010u) | 0x64006400u), o0), s0));
+        out[2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x000F000Fu) | ((y << 4) & 0x00100010u) | 0x64006400u), o0), s0));
+        out[16 + 2 * j] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((a & 0x00F000F0u) | ((x << 7) & 0x01000100u) | 0x54005400u), o1), s1));
+        out[16 + 2 * j + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2((b & 0x00F000F0u) | ((y << 7) & 0x01000100u) | 0x54005400u), o1), s1));
       }
     }
   }
