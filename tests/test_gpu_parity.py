@@ -306,7 +306,7 @@ def test_mmq_other_dtypes(dtype):
 def test_dequant_matmul_parity(ref, name, dtype):
     """IQ types above the GEMV threshold: the reference dequantizes and calls a dense matmul."""
     t = TYPES[name]
-    for (N, K, M) in [(256, 1024, 16), (1000, 2048, 40), (384, 4096, 128)]:
+    for (N, K, M) in [(256, 1024, 16), (1000, 2048, 40), (384, 4096, 128), (264, 2048, 300)]:   # the last: 256-token tiles
         wn, w = dev_w(t, N, K, seed=N)
         x = dev_x(M, K, seed=M, dtype=dtype)
         y = capi.dequant_matmul(w, x, t, N)
