@@ -22,7 +22,7 @@
 // tcgen05.st; the MMA takes A from there ([a_tmem] operand form).  Operand B (activations) is
 // K-major in shared memory with the 128-byte swizzle, one TMA box per stage.  Weight rows sit on
 // the M axis so that small token counts (MoE blocks) do not waste the 128-row instruction.
-// Tensor memory: columns [0, TN) the fp32 accumulator, then four A slots of 32 columns.
+// Tensor memory: columns [0, TN) the fp32 accumulator, then four or eight A slots of 32 columns.
 // Warp roles (P = 4 * groups producer warps, groups = 2 or 4):
 //   warps 0..P-1  producers: group g = 128 threads, one per weight row, decodes all 64 values of
 //                 its row for the stages i = g, g + groups, ... from the raw-byte ring into the A
@@ -76,17 +76,21 @@ __host__ __device__ constexpr int mmq_groups(int type, bool fast, bool two, int 
 __host__ __device__ constexpr int mmq_threads(int type, bool fast, bool two, int tn) { return (4 * mmq_groups(type, fast, two, tn) + 3) * 32; }   // + B loader, MMA issuer, raw-weight loader
 // Ring depths.  The decoded weights (operand A) never touch shared memory: a producer thread writes
 // the 64 values of its row for one stage -- 32 registers of two fp16 each -- into 32 columns of its own
-// lane of tensor memory (tcgen05.st), and the MMA reads its A operand from there.  The A ring is four
-// such 32-column slots next to the accumulator's TN columns; it is never shallower than the number
+// lane of tensor memory (tcgen05.st), and the MMA reads its A operand from there.  The A ring is four or
+// eight such 32-column slots next to the accumulator's TN columns; it is never shallower than the number
 // of producer groups (a group that runs ahead may be at most one use of a slot ahead of the MMA warp,
-// or the one-bit phase parity of the slot's barrier would alias).  Shared memory then carries only
+// or the one-bit phase parity of the slot's barrier would alias).  Eight slots let a group publish its
+// next stage while the MMA of its previous one is still queued (Q4_K M = 2048 214 -> 208 us, M = 512
+// 62.6 -> 60.1, Q4_0 64.4 -> 61.8); the types that run four groups of 32-value decoders measured slower
+// with eight (IQ2_XXS 103 -> 109 us, Q2_K 60 -> 66) and keep four, as do the two-CTA-per-SM kernels, whose
+// two allocations must fit the SM's 512 columns.  Shared memory then carries only
 // the activations (the B ring, TN * 128 bytes per slot, four slots: the finished tile is staged in
 // them, up to TN * 128 fp32 values) and the raw weight bytes.
 __host__ __device__ constexpr int mmq_b_stages(int type, bool fast, bool two, int tn) { return 4; }
-__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) { return 4; }
+__host__ __device__ constexpr int mmq_a_stages(int type, bool fast, bool two, int tn) { return (two || type == T_IQ2_XXS || type == T_Q2_K) ? 4 : 8; }
 constexpr int MMQ_A_COLS = 32;   // tensor-memory columns of one A slot: 64 fp16 values per lane
-__host__ __device__ constexpr uint32_t mmq_tmem_cols(int tn) {
-  return (tn < 32 ? 32 : tn) + 4 * MMQ_A_COLS <= 256 ? 256u : 512u;
+__host__ __device__ constexpr uint32_t mmq_tmem_cols(int tn, int a_stages) {
+  return (tn < 32 ? 32 : tn) + a_stages * MMQ_A_COLS <= 256 ? 256u : 512u;
 }
 // per-warp transposition scratch of the types whose correction value is one fp16 of the block (see the producers)
 constexpr int MMQ_CORR_ROW = 80;    // bytes per row: 32 fp16 + 16 (an odd number of 16-byte units: conflict-free row reads)
@@ -290,7 +294,7 @@ __global__ void __launch_bounds__(mmq_threads(TYPE, FAST, TWO, TN), TWO ? 2 : 1)
     if (t0 >= (int64_t)p.n_post_pad[0]) return;      // nothing routed to this block
     wbase += (int64_t)e * p.expert_stride_bytes;
   }
-  constexpr uint32_t TMEM_COLS = mmq_tmem_cols(TN);
+  constexpr uint32_t TMEM_COLS = mmq_tmem_cols(TN, SA);
   constexpr uint32_t A_COL0 = TN < 32 ? 32 : TN;   // first column of the A ring, right of the accumulator
   const int nk = nmain + ncorr;
 
