@@ -241,7 +241,8 @@ GEMM_CASES = [("mmq", Q4_K, 14336, 4096, 2048), ("mmq", Q4_K, 14336, 4096, 512),
               ("mmq", Q4_K, 14336, 4096, 4), ("mmq", Q4_K, 14336, 4096, 16),
               ("mmq", Q6_K, 37888, 3584, 256), ("mmq", Q6_K, 3584, 18944, 256), ("mmq", Q8_0, 14336, 4096, 512), ("mmq", Q4_0, 14336, 4096, 512),
               ("dqmm", IQ2_XXS, 28672, 8192, 128), ("dqmm", IQ2_XXS, 8192, 28672, 128), ("dqmm", IQ4_XS, 37888, 3584, 256),
-              ("dqmm", IQ4_XS, 3584, 18944, 256), ("mmq", 10, 14336, 4096, 512), ("mmq", 11, 14336, 4096, 512), ("mmq", 13, 14336, 4096, 512)]   # 10, 11, 13 = Q2_K, Q3_K, Q5_K
+              ("dqmm", IQ4_XS, 3584, 18944, 256), ("mmq", 10, 14336, 4096, 512), ("mmq", 11, 14336, 4096, 512), ("mmq", 13, 14336, 4096, 512),
+              ("mmq", 3, 14336, 4096, 512), ("mmq", 6, 14336, 4096, 512), ("mmq", 7, 14336, 4096, 512)]   # 10, 11, 13 = Q2_K, Q3_K, Q5_K; 3, 6, 7 = Q4_1, Q5_0, Q5_1
 
 
 def sweep_gemv(ref):

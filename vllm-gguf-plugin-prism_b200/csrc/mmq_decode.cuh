@@ -284,7 +284,19 @@ template <typename ab_t> struct Decoder<T_Q4_1, ab_t> {
 };
 
 // fifth bits: bit j of qh belongs to value j
-__device__ __forceinline__ uint32_t q5_code(uint32_t nib, uint32_t qh, int j) { return nib | (((qh >> j) & 1u) << 4); }
+// Word k of a 5-bit legacy block (qs[4k..4k+3]) -> the four pairs it holds: values 4k, 4k+1 | 4k+2, 4k+3 (low nibbles,
+// fifth bits 4k.. of qh) and 16+4k.. (high nibbles, fifth bits 16+4k..).  Four consecutive bits of qh are spread to bit 4
+// of four bytes with one multiplication (t * 0x02040810 puts bit j of t at bit 8j + 4, no carries for t < 16), the code
+// bytes become halves 1024 + code by byte-permute, the offset is subtracted exactly and d multiplies once.
+__device__ __forceinline__ void q5_word(uint32_t q, uint32_t qh, int k, __half2 off, __half2 d2, uint32_t& lo01, uint32_t& lo23,
+                                        uint32_t& hi01, uint32_t& hi23) {
+  const uint32_t cl = (q & 0x0F0F0F0Fu) | ((((qh >> (4 * k)) & 0xFu) * 0x02040810u) & 0x10101010u);
+  const uint32_t ch = ((q >> 4) & 0x0F0F0F0Fu) | ((((qh >> (16 + 4 * k)) & 0xFu) * 0x02040810u) & 0x10101010u);
+  lo01 = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(cl, 0x64646464u, 0x4140)), off), d2));
+  lo23 = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(cl, 0x64646464u, 0x4342)), off), d2));
+  hi01 = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(ch, 0x64646464u, 0x4140)), off), d2));
+  hi23 = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(ch, 0x64646464u, 0x4342)), off), d2));
+}
 
 // ---- Q5_0: value = half((q - 16) * d), 22-byte blocks (2-byte aligned): d | qh[4] | qs[16] ------------
 template <typename ab_t> struct Decoder<T_Q5_0, ab_t> {
@@ -300,12 +312,9 @@ template <typename ab_t> struct Decoder<T_Q5_0, ab_t> {
     const uint32_t du = w0 & 0xFFFFu, qh = (w0 >> 16) | (w1 << 16);
     const __half2 d2 = u32_as_h2(du | (du << 16)), off = __floats2half2_rn(1040.f, 1040.f);   // 1024 + 16
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // half-word 3+i of the block holds qs[2i], qs[2i+1]
-      const int h = 3 + i;
-      const uint32_t wv = word_at(raw, h >> 1, sh);
-      const uint32_t t = (h & 1) ? (wv >> 16) : (wv & 0xFFFFu);
-      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code(t & 0xF, qh, 2 * i), q5_code((t >> 8) & 0xF, qh, 2 * i + 1)), off), d2));
-      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code((t >> 4) & 0xF, qh, 16 + 2 * i), q5_code((t >> 12) & 0xF, qh, 17 + 2 * i)), off), d2));
+    for (int k = 0; k < 4; ++k) {  // bytes 6 + 4k .. of the block = qs[4k..4k+3]: values 4k.. (low nibbles) and 16 + 4k.. (high)
+      const uint32_t q = __funnelshift_r(word_at(raw, 1 + k, sh), word_at(raw, 2 + k, sh), 16);
+      q5_word(q, qh, k, off, d2, out[2 * k], out[2 * k + 1], out[8 + 2 * k], out[8 + 2 * k + 1]);
     }
   }
   static __device__ __forceinline__ void corr(const uint8_t*, int, int64_t, uint32_t (&)[16]) {}
@@ -324,12 +333,7 @@ template <typename ab_t> struct Decoder<T_Q5_1, ab_t> {
     const uint32_t du = raw[0] & 0xFFFFu, qh = raw[1];
     const __half2 d2 = u32_as_h2(du | (du << 16)), off = __floats2half2_rn(1024.f, 1024.f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t wv = raw[2 + (i >> 1)];
-      const uint32_t t = (i & 1) ? (wv >> 16) : (wv & 0xFFFFu);
-      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code(t & 0xF, qh, 2 * i), q5_code((t >> 8) & 0xF, qh, 2 * i + 1)), off), d2));
-      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(q5_code((t >> 4) & 0xF, qh, 16 + 2 * i), q5_code((t >> 12) & 0xF, qh, 17 + 2 * i)), off), d2));
-    }
+    for (int k = 0; k < 4; ++k) q5_word(raw[2 + k], qh, k, off, d2, out[2 * k], out[2 * k + 1], out[8 + 2 * k], out[8 + 2 * k + 1]);
   }
   static __device__ __forceinline__ void corr(const uint8_t* row, int c, int64_t K, uint32_t (&out)[16]) {
 #pragma unroll
