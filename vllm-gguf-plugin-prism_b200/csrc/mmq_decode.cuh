@@ -264,11 +264,12 @@ template <typename ab_t> struct Decoder<T_Q4_1, ab_t> {
     const uint32_t du = raw[0] & 0xFFFFu;
     const __half2 d2 = u32_as_h2(du | (du << 16)), off = __floats2half2_rn(1024.f, 1024.f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // half-word i of the nibble bytes holds qs[2i], qs[2i+1]
-      const uint32_t wv = raw[1 + (i >> 1)];
-      const uint32_t t = (i & 1) ? (wv >> 16) : (wv & 0xFFFFu);
-      out[i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024(t & 0xF, (t >> 8) & 0xF), off), d2));
-      out[8 + i] = h2_as_u32(hmul2_rn(__hsub2(ints_plus_1024((t >> 4) & 0xF, (t >> 12) & 0xF), off), d2));
+    for (int k = 0; k < 4; ++k) {  // word k = qs[4k..4k+3]: values 4k.. (low nibbles) and 16 + 4k.. (high); halves 1024 + code by byte-permute
+      const uint32_t cl = raw[1 + k] & 0x0F0F0F0Fu, ch = (raw[1 + k] >> 4) & 0x0F0F0F0Fu;
+      out[2 * k] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(cl, 0x64646464u, 0x4140)), off), d2));
+      out[2 * k + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(cl, 0x64646464u, 0x4342)), off), d2));
+      out[8 + 2 * k] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(ch, 0x64646464u, 0x4140)), off), d2));
+      out[8 + 2 * k + 1] = h2_as_u32(hmul2_rn(__hsub2(u32_as_h2(__byte_perm(ch, 0x64646464u, 0x4342)), off), d2));
     }
   }
   // correction columns [32c, 32c+32): A'[n, g] = m of block g
