@@ -6,7 +6,7 @@
  * It restates, in plain C, the arithmetic of the reference plugin's CUDA kernels
  * (vllm_gguf_plugin/csrc/gguf/ of akmorley/vllm-gguf-plugin-prism) for these block types:
  *   Q4_0 (2), Q8_0 (8), Q4_K (12), Q6_K (14), IQ2_XXS (16), IQ4_XS (23), and later additions
- *   (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M; dequantize only: Q2_K, Q3_K).
+ *   (Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M).
  * Each function names the reference lines it follows.  Half-precision steps are
  * emulated exactly (one IEEE rounding per __hmul/__hsub/__int2half_rn), so the
  * dequantize outputs are bit patterns, not approximations.  Matmul entry points are
@@ -201,7 +201,7 @@ int oracle_type_size(int type) {
     case T_Q4_1: return 20;
     case T_Q5_0: return 22;
     case T_Q5_1: return 24;
-    case T_Q2_K: return 84;  /* (Q2_K, Q3_K: dequantize and GEMV; no tiled kernel here) */
+    case T_Q2_K: return 84;
     case T_Q3_K: return 110;
     case T_Q5_K: return 176;
     case T_IQ4_NL: return 18;
